@@ -1,0 +1,259 @@
+"""TEST INFRASTRUCTURE ONLY -- ctypes doors to the two CPU checkers.
+
+* ``port()``: ``liboracle_port.so`` built from ``oracle/port.c`` (a plain-C
+  restatement of the reference's x86 arithmetic; builds anywhere).
+* ``ref()``:  ``oracle/_ref/libnntr_ref.so`` = the reference's own sources
+  compiled unmodified together with ``ref_shim.cpp`` (only where a reference
+  checkout was available at build time; the file then travels with the tree).
+
+Only ``tests/``, the smoke check and the CPU-baseline leg of ``bench.py`` may
+import this module. Nothing under ``nntrainer_b200/`` does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from functools import lru_cache
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+Q4_K_BLOCK = 144
+Q4_KX8_BLOCK = 1152
+Q4_0_BLOCK = 18
+Q4_0X8_BLOCK = 144
+Q6_K_BLOCK = 210
+Q8_K_BLOCK = 292
+Q8_KX4_BLOCK = 1168
+Q8_0_BLOCK = 34
+Q8_0X4_BLOCK = 136
+
+_fp = C.POINTER(C.c_float)
+_vp = C.c_void_p
+_GEMM_SIG = [C.c_uint, C.c_uint, C.c_uint, _vp, C.c_uint, _vp, C.c_uint, _vp, C.c_uint]
+
+
+def build(ref: bool = True) -> None:
+    """Compile the checkers (make -C oracle). The reference build is skipped by
+    the Makefile when no checkout is present."""
+    subprocess.run(["make", "-C", HERE, "port"] + (["ref"] if ref else []),
+                   check=True, stdout=subprocess.DEVNULL)
+
+
+def _cpu_flags() -> set:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    return set(line.split(":", 1)[1].split())
+    except OSError:
+        pass
+    return set()
+
+
+def _ptr(a) -> int:
+    if a is None:
+        return 0
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data
+
+
+class _Lib:
+    """Thin typed wrapper; ``prefix`` is ``ref_`` or ``port_``."""
+
+    def __init__(self, path: str, prefix: str):
+        self.path = path
+        self.prefix = prefix
+        self.lib = C.CDLL(path)
+        if prefix == "ref_":
+            self.lib.ref_init()
+        for q in ("q4_0", "q4_K", "q6_K"):
+            f = getattr(self.lib, f"{prefix}gemm_{q}")
+            f.argtypes = _GEMM_SIG
+            f.restype = None if prefix == "ref_" else C.c_int
+        f = getattr(self.lib, f"{prefix}vec_dot_q6_K_q8_K")
+        f.argtypes = [C.c_uint, _vp, _vp]
+        f.restype = C.c_float
+
+    # -- activation quantizers ------------------------------------------------
+    def _quant(self, name: str, x: np.ndarray, out_bytes: int) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.zeros(out_bytes, dtype=np.uint8)
+        f = getattr(self.lib, self.prefix + name)
+        f.argtypes = [_vp, _vp, C.c_int64]
+        f.restype = None
+        f(_ptr(x), _ptr(out), x.shape[-1])
+        return out
+
+    def quantize_row_q8_K(self, x):
+        return self._quant("quantize_row_q8_K", x, x.size // 256 * Q8_K_BLOCK)
+
+    def quantize_row_q8_0(self, x):
+        return self._quant("quantize_row_q8_0", x, x.size // 32 * Q8_0_BLOCK)
+
+    def quantize_mat_q8_K_4x8(self, x4):
+        assert x4.shape[0] == 4
+        return self._quant("quantize_mat_q8_K_4x8", x4, x4.shape[1] // 256 * Q8_KX4_BLOCK)
+
+    def quantize_mat_q8_0_4x8(self, x4):
+        assert x4.shape[0] == 4
+        return self._quant("quantize_mat_q8_0_4x8", x4, x4.shape[1] // 32 * Q8_0X4_BLOCK)
+
+    # -- dequantizers (plain rows) ---------------------------------------------
+    def dequantize_row(self, qtype: str, blocks: np.ndarray, k: int) -> np.ndarray:
+        out = np.empty(k, dtype=np.float32)
+        f = getattr(self.lib, f"{self.prefix}dequantize_row_{qtype}")
+        f.argtypes = [_vp, _vp, C.c_int64]
+        f.restype = None
+        f(_ptr(np.ascontiguousarray(blocks)), _ptr(out), k)
+        return out
+
+    # -- GEMV / GEMM drivers ---------------------------------------------------
+    def gemm(self, qtype: str, A: np.ndarray, B: np.ndarray, N: int, ldc: int | None = None):
+        A = np.ascontiguousarray(A, dtype=np.float32)
+        if A.ndim == 1:
+            A = A[None, :]
+        M, K = A.shape
+        ldc = N if ldc is None else ldc
+        Cm = np.zeros((M, ldc), dtype=np.float32)
+        getattr(self.lib, f"{self.prefix}gemm_{qtype}")(M, N, K, _ptr(A), K, _ptr(B), N, _ptr(Cm), ldc)
+        return Cm
+
+    def vec_dot_q6_K_q8_K(self, K, w, a) -> float:
+        return float(getattr(self.lib, f"{self.prefix}vec_dot_q6_K_q8_K")(K, _ptr(w), _ptr(a)))
+
+
+class Ref(_Lib):
+    """The reference's own code. Adds the offline weight quantizers and repack."""
+
+    def quantize_weight(self, qtype: str, W: np.ndarray) -> np.ndarray:
+        """W is [nrow, k] fp32 (the transposed weight, one row per output column).
+        Returns PLAIN (not interleaved) blocks."""
+        W = np.ascontiguousarray(W, dtype=np.float32)
+        nrow, k = W.shape
+        per = {"q4_0": (32, Q4_0_BLOCK), "q4_K": (256, Q4_K_BLOCK), "q6_K": (256, Q6_K_BLOCK)}[qtype]
+        out = np.zeros(nrow * k // per[0] * per[1], dtype=np.uint8)
+        f = getattr(self.lib, f"ref_quantize_{qtype}")
+        f.argtypes = [_vp, _vp, C.c_int64, C.c_int64]
+        f.restype = C.c_size_t
+        n = f(_ptr(W), _ptr(out), nrow, k)
+        assert n == out.size, (n, out.size)
+        return out
+
+    def repack(self, qtype: str, plain: np.ndarray, nrow: int, k: int) -> np.ndarray:
+        out = np.zeros_like(plain)
+        f = getattr(self.lib, {"q4_0": "ref_repack_q4_0_to_q4_0_8", "q4_K": "ref_repack_q4_K_to_q4_K_8"}[qtype])
+        f.argtypes = [_vp, _vp, C.c_size_t, C.c_uint, C.c_uint]
+        f.restype = None
+        f(_ptr(out), _ptr(np.ascontiguousarray(plain)), plain.size, nrow, k)
+        return out
+
+    def micro(self, name: str, n: int, bs: int, vx, vy, nr: int, nc: int) -> np.ndarray:
+        """Single-thread microkernel ``nntr_{name}`` (gemv_/gemm_ q4_K/q4_0 8x8)."""
+        out = np.zeros((nr, bs), dtype=np.float32)
+        f = getattr(self.lib, "ref_" + name)
+        f.argtypes = [C.c_int, _vp, C.c_size_t, _vp, _vp, C.c_int, C.c_int]
+        f.restype = None
+        f(n, _ptr(out), bs, _ptr(vx), _ptr(vy), nr, nc)
+        return out
+
+
+class Port(_Lib):
+    def quantize_row_q8_K_rule(self, x, rule: int):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.zeros(x.size // 256 * Q8_K_BLOCK, dtype=np.uint8)
+        f = self.lib.port_quantize_row_q8_K_rule
+        f.argtypes = [_vp, _vp, C.c_int64, C.c_int]
+        f.restype = None
+        f(_ptr(x), _ptr(out), x.size, rule)
+        return out
+
+    def repack(self, qtype: str, plain: np.ndarray, nrow: int, k: int) -> np.ndarray:
+        out = np.zeros_like(plain)
+        f = getattr(self.lib, {"q4_0": "port_repack_q4_0_to_q4_0_8", "q4_K": "port_repack_q4_K_to_q4_K_8"}[qtype])
+        f.argtypes = [_vp, _vp, C.c_int64, C.c_int64]
+        f.restype = C.c_int
+        assert f(_ptr(out), _ptr(np.ascontiguousarray(plain)), nrow, k) == 0
+        return out
+
+    def unpack(self, qtype: str, packed: np.ndarray, nrow: int, k: int) -> np.ndarray:
+        out = np.zeros_like(packed)
+        f = getattr(self.lib, {"q4_0": "port_unpack_q4_0_8_to_q4_0", "q4_K": "port_unpack_q4_K_8_to_q4_K"}[qtype])
+        f.argtypes = [_vp, _vp, C.c_int64, C.c_int64]
+        f.restype = C.c_int
+        assert f(_ptr(out), _ptr(np.ascontiguousarray(packed)), nrow, k) == 0
+        return out
+
+    def fp16_to_fp32(self, h: int) -> float:
+        f = self.lib.port_fp16_to_fp32
+        f.argtypes = [C.c_uint16]
+        f.restype = C.c_float
+        return float(f(h))
+
+    def fp32_to_fp16(self, x: float) -> int:
+        f = self.lib.port_fp32_to_fp16
+        f.argtypes = [C.c_float]
+        f.restype = C.c_uint16
+        return int(f(x))
+
+
+@lru_cache(maxsize=None)
+def port() -> Port:
+    path = os.path.join(HERE, "liboracle_port.so")
+    if not os.path.exists(path):
+        build(ref=False)
+    return Port(path, "port_")
+
+
+def ref_available() -> bool:
+    return os.path.exists(os.path.join(HERE, "_ref", "libnntr_ref.so"))
+
+
+@lru_cache(maxsize=None)
+def ref(fast: bool = False) -> Ref:
+    """``fast=True`` picks the AVX-512 build when this host can run it (timing
+    only; identical bits on the inference path), else the pinned AVX2 build."""
+    name = "libnntr_ref.so"
+    if fast:
+        need = {"avx512f", "avx512bw", "avx512vl", "avx512dq", "avx512_vnni"}
+        if need <= _cpu_flags() and os.path.exists(os.path.join(HERE, "_ref", "libnntr_ref_avx512.so")):
+            name = "libnntr_ref_avx512.so"
+    path = os.path.join(HERE, "_ref", name)
+    if not os.path.exists(path):
+        raise FileNotFoundError(f"{path}: build it with `make -C oracle ref` where the reference checkout exists")
+    return Ref(path, "ref_")
+
+
+# ---------------------------------------------------------------------------
+# Synthetic weights that need no reference quantizer: any byte pattern with
+# finite fp16 scales is a valid block, and random bytes exercise every nibble,
+# 6-bit scale and sign combination.
+# ---------------------------------------------------------------------------
+def _rand_f16(rng, n, lo, hi):
+    return rng.uniform(lo, hi, size=n).astype(np.float16).view(np.uint16)
+
+
+def random_q4_Kx8(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
+    nblk = (N // 8) * (K // 256)
+    b = rng.integers(0, 256, size=(nblk, Q4_KX8_BLOCK), dtype=np.uint8)
+    b[:, 0:16] = _rand_f16(rng, nblk * 8, 1e-4, 3e-3).view(np.uint8).reshape(nblk, 16)
+    b[:, 16:32] = _rand_f16(rng, nblk * 8, 1e-4, 3e-3).view(np.uint8).reshape(nblk, 16)
+    return b.reshape(-1)
+
+
+def random_q4_0x8(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
+    nblk = (N // 8) * (K // 32)
+    b = rng.integers(0, 256, size=(nblk, Q4_0X8_BLOCK), dtype=np.uint8)
+    d = _rand_f16(rng, nblk * 8, 1e-3, 1e-2)
+    d ^= (rng.integers(0, 2, size=d.size, dtype=np.uint16) << 15)  # random sign
+    b[:, 0:16] = d.view(np.uint8).reshape(nblk, 16)
+    return b.reshape(-1)
+
+
+def random_q6_K(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
+    nblk = N * (K // 256)
+    b = rng.integers(0, 256, size=(nblk, Q6_K_BLOCK), dtype=np.uint8)
+    b[:, 208:210] = _rand_f16(rng, nblk, 1e-5, 2e-4).view(np.uint8).reshape(nblk, 2)
+    return b.reshape(-1)
