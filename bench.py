@@ -1,0 +1,350 @@
+#!/usr/bin/env python
+"""bench.py -- the decode GEMV of NNTrainer's block-quantized matmul path on B200.
+
+Workload (N = 1 GPU): BASELINE config "Single Q4_K x Q8_K decode GEMV": M=1,
+K=4096, N=4096, weights N(0, 0.02^2) seed 0 quantized by the reference's Q4_K
+quantizer and 8-row interleaved, activation N(0,1) quantized per call inside the
+kernel. One "step" = one pass over a ring of RING distinct weight matrices
+(RING x 9.4 MB > the 126 MB L2, so every launch streams its weights from HBM),
+chained like decoder layers (each output is the next input) and launched with
+programmatic dependent launch from one CUDA graph.
+
+With --gpus P > 1 the projection is N-split: the global weight is
+[4096*P, 4096], every rank holds a 4096-row shard (the same per-GPU work: weak
+scaling) and the output slices are all-gathered over NCCL after every GEMV.
+
+Prints ONE JSON line (rank 0). `value` = algorithmic GB/s of the whole job with
+inputs resident in HBM; `e2e` = the same metric through the host-pointer C ABI
+(nntr_cuda_gemm_q4_K: host activation in, host output back, weights cached in
+HBM); `roofline` = the GEMV kernel against the measured HBM peak;
+`cpu_baseline` = the reference's own CPU code on this box's host cores.
+`--impl reference` times only that CPU code, same config and metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_ROWS = 4096
+K_COLS = 4096
+RING = 48
+WEIGHT_BYTES = N_ROWS * K_COLS // 256 * 144          # 9 437 184
+ALG_BYTES = WEIGHT_BYTES + 4 * K_COLS + 4 * N_ROWS   # 9 469 952 per GEMV
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# --------------------------------------------------------------------------
+# inputs
+# --------------------------------------------------------------------------
+def make_base_weight():
+    """cfg1 weight bytes (block_q4_Kx8) and how they were made."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(0)
+    if O.ref_available():
+        R = O.ref()
+        W = (rng.standard_normal((N_ROWS, K_COLS)) * 0.02).astype(np.float32)
+        plain = R.quantize_weight("q4_K", W)
+        return R.repack("q4_K", plain, N_ROWS, K_COLS), "N(0,0.02^2) seed 0, reference Q4_K quantizer + 8-row interleave"
+    return O.random_q4_Kx8(rng, N_ROWS, K_COLS), "random block bytes (reference quantizer not built)"
+
+
+def ring_host(base: np.ndarray) -> list[np.ndarray]:
+    """RING distinct matrices with the statistics of the base one: row groups rotated."""
+    g = base.reshape(N_ROWS // 8, -1)
+    return [np.ascontiguousarray(np.roll(g, 11 * i, axis=0)).reshape(-1) for i in range(RING)]
+
+
+# --------------------------------------------------------------------------
+# clocks sampler
+# --------------------------------------------------------------------------
+class Clocks:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), [t.strip() for t in line.split(",")]))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for (t, r) in self.samples if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 9] or \
+               [r for (_, r) in self.samples if len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(r[1]) for r in rows)
+        reasons = set()
+        for r in rows:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
+                "samples": len(rows)}
+
+
+# --------------------------------------------------------------------------
+# the reference's CPU path on the host cores
+# --------------------------------------------------------------------------
+def cpu_reference_gbps(ring: list[np.ndarray], budget_s: float, min_passes: int = 1):
+    """Times ref_gemm_q4_K (M=1: quantize_row_q8_K + 4-thread GEMV, exactly the
+    reference's driver) over the ring; returns (GB/s, description dict)."""
+    from oracle import oracle as O
+    os.environ.setdefault("OMP_WAIT_POLICY", "active")
+    kind = "reference" if O.ref_available() else "port"
+    lib = O.ref(fast=True) if kind == "reference" else O.port()
+    x = np.random.default_rng(1).standard_normal((1, K_COLS)).astype(np.float32)
+    for W in ring[:4]:
+        lib.gemm("q4_K", x, W, N_ROWS)
+    calls, t0 = 0, time.perf_counter()
+    while True:
+        for W in ring:
+            lib.gemm("q4_K", x, W, N_ROWS)
+        calls += len(ring)
+        dt = time.perf_counter() - t0
+        if dt >= budget_s and calls >= min_passes * len(ring):
+            break
+    gbps = calls * ALG_BYTES / dt / 1e9
+    desc = {"value": round(gbps, 3), "unit": "GB/s", "cores": 4, "kind": kind,
+            "sample": f"{calls} GEMV calls (M=1,N=K=4096) over a ring of {len(ring)} matrices in {dt:.1f} s; "
+                      f"{os.path.basename(lib.path)}; host has {os.cpu_count()} logical cores, the reference's GEMV driver "
+                      f"uses 4 OpenMP threads (ggml_interface_omp.cpp:406)"}
+    return gbps, desc, dt / calls
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base, how = make_base_weight()
+    ring = ring_host(base)
+    per_step_budget = 2.0
+    for _ in range(args.warmup):
+        cpu_reference_gbps(ring[:8], 0.2)
+    vals, ms = [], []
+    for _ in range(args.steps):
+        g, desc, per_call = cpu_reference_gbps(ring, per_step_budget)
+        vals.append(g)
+        ms.append(per_call * len(ring) * 1e3)
+    value = float(np.mean(vals))
+    desc["value"] = round(value, 3)
+    out = {"impl": "reference", "metric": "Q4_K GEMV HBM GB/s", "value": round(value, 3), "unit": "GB/s",
+           "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(float(np.mean(ms)), 3),
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u4xs8->s32, f32 scales",
+           "data": "synthetic: " + how,
+           "config": {"workload": "cfg1 Q4_K x Q8_K decode GEMV M=1 K=4096 N=4096, ring of %d matrices" % RING,
+                      "l2": "ring of %d MB exceeds host LLC" % (RING * WEIGHT_BYTES // 2**20)},
+           "cpu_baseline": desc,
+           "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(out))
+
+
+# --------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from nntrainer_b200 import backend as be
+    from nntrainer_b200 import build as nb_build
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    nb_build.build()
+    be.init(local)
+    dev = torch.device("cuda", local)
+
+    base, how = make_base_weight()
+    host_ring = ring_host(base)
+    ring = [torch.from_numpy(w).to(dev) for w in host_ring]
+    x0 = torch.from_numpy(np.random.default_rng(1).standard_normal(K_COLS).astype(np.float32)).to(dev)
+    # every step restarts from the same input, then ping-pongs between two buffers
+    # (with P ranks a buffer is the gathered [P*4096] vector and a rank reads its own slice)
+    gathered = [torch.zeros(world * N_ROWS, device=dev) for _ in range(2)]
+    pdl = not args.no_pdl
+    lo, hi = rank * N_ROWS, (rank + 1) * N_ROWS
+
+    def step_body():
+        src = x0
+        for i, W in enumerate(ring):
+            dst = gathered[i % 2]
+            if world == 1:
+                be.gemv("q4_K", N_ROWS, K_COLS, src, W, dst, pdl=pdl)
+            else:
+                be.gemv("q4_K", N_ROWS, K_COLS, src, W, dst[lo:hi], pdl=False)
+                dist.all_gather_into_tensor(dst, dst[lo:hi])
+            src = dst[lo:hi]
+
+    def renorm():
+        pass
+
+    # one CUDA graph per step (single GPU): the launch loop is otherwise bound by the host
+    graph = None
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        step_body()
+        stream.synchronize()
+        renorm()
+        if world == 1 and not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step_body()
+
+        def step():
+            if graph is not None:
+                graph.replay()
+            else:
+                step_body()
+
+        for _ in range(max(args.warmup, 3)):
+            step()
+            renorm()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        clocks = Clocks(local)
+        if rank == 0:
+            clocks.start()
+            time.sleep(0.3)
+        torch.cuda.synchronize()
+        launches0 = be.launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        ev0.record(stream)
+        for _ in range(args.steps):
+            step()
+        ev1.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        t1 = time.time()
+        if world > 1:
+            dist.barrier()
+        ms = ev0.elapsed_time(ev1)
+        launches = (be.launch_count() - launches0) if graph is None else RING * args.steps
+        clk = clocks.stop(t0, t1) if rank == 0 else None
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        finite = bool(torch.isfinite(gathered[0]).all() and torch.isfinite(gathered[1]).all())
+
+    # ---- end to end through the host-pointer C ABI: host x in, host y out, per GEMV
+    e2e = None
+    if world == 1 and rank == 0 and not args.no_e2e:
+        xh = torch.empty((1, K_COLS), dtype=torch.float32).pin_memory()
+        yh = torch.empty((1, N_ROWS), dtype=torch.float32).pin_memory()
+        xh.copy_(x0.cpu()[None])
+        xn, yn = xh.numpy(), yh.numpy()
+        for W in host_ring:
+            be.register_weight("q4_K", W, N_ROWS, K_COLS)
+        e2e_steps = max(1, min(args.steps, 20))
+        for _ in range(2):
+            for W in host_ring:
+                be.gemm_q4_K(1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS)
+        torch.cuda.synchronize()
+        tt0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            for W in host_ring:
+                be.gemm_q4_K(1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS)
+                xn[0, :] = yn[0, :] / max(float(np.abs(yn).max()), 1e-20)  # chain on the host
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - tt0
+        e2e = {"value": round(e2e_steps * RING * ALG_BYTES / dt / 1e9, 2), "unit": "GB/s",
+               "h2d_bytes_per_step": RING * 4 * K_COLS, "d2h_bytes_per_step": RING * 4 * N_ROWS,
+               "us_per_call": round(dt / (e2e_steps * RING) * 1e6, 2),
+               "api": "nntr_cuda_gemm_q4_K (host pointers, weights cached in HBM)"}
+        for W in host_ring:
+            be.unregister_weight(W)
+
+    if rank == 0:
+        peak, which = measured_peak()
+        total_bytes = world * args.steps * RING * ALG_BYTES
+        value = total_bytes / (ms * 1e-3) / 1e9
+        per_launch_us = ms * 1e3 / (args.steps * RING)
+        achieved = ALG_BYTES / (per_launch_us * 1e-6) / 1e9
+        cpu_desc = None
+        if world == 1 and not args.no_cpu:
+            _, cpu_desc, _ = cpu_reference_gbps(host_ring, args.cpu_seconds)
+        out = {"metric": "Q4_K GEMV HBM GB/s", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+               "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 5),
+               "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+               "dtype": "u4xs8->s32, f32 scales", "data": "synthetic: " + how,
+               "config": {"workload": "cfg1 Q4_K x Q8_K decode GEMV M=1 K=4096 N=4096 per GPU, ring of %d matrices "
+                                      "chained like decoder layers" % RING,
+                          "l2": "inputs larger than L2: %d MB of distinct weights per step" % (RING * WEIGHT_BYTES // 2**20),
+                          "launch": ("CUDA graph, " if graph is not None else "eager, ") +
+                                    ("programmatic dependent launch" if (pdl and world == 1) else "plain launches"),
+                          "parallelism": "single GPU" if world == 1 else f"N-split x{world} + NCCL all-gather per GEMV",
+                          "outputs_finite": finite},
+               "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                            "frac": round(achieved / peak, 4), "peak_source": which + " (copy bandwidth)",
+                            "us_per_launch": round(per_launch_us, 4), "traffic": args.traffic,
+                            "kernel": "gemv_q4_K_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
+               "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk}
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer end-to-end leg (profiling runs)")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="DRAM bytes per launch of the GEMV kernel from an ncu capture (reported as roofline.traffic)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

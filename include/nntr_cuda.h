@@ -1,0 +1,149 @@
+/* SPDX-License-Identifier: Apache-2.0 */
+/**
+ * @file  nntr_cuda.h
+ * @brief C ABI of libnntr_cuda.so: NNTrainer's block-quantized weight matmul
+ *        path (Q4_0 / Q4_K / Q6_K weights x activations quantized on the fly to
+ *        Q8_0 / Q8_K) as hand-written CUDA kernels for sm_100a.
+ *
+ * Plain C: pointers and sizes only, no C++ or framework types. Every function
+ * returns NNTR_CUDA_OK (0) or a negative code; nntr_cuda_last_error() gives the
+ * text for the calling thread. Nothing here falls back to the CPU: without a
+ * usable CUDA device every compute entry point fails with NNTR_CUDA_ERR_CUDA.
+ *
+ * Citations name the interface of the reference project that each entry point
+ * stands in for (paths relative to the reference root; cpu_backend.h =
+ * nntrainer/tensor/cpu_backend/cpu_backend.h, GI = nntrainer/tensor/
+ * cpu_backend/ggml_interface).
+ *
+ * Layouts are the reference's own, unchanged: block_q4_0x8 (144 B), block_q4_Kx8
+ * (1152 B), block_q6_K (210 B), block_q8_0 (34 B), block_q8_K (292 B)
+ * (GI/nntr_ggml_impl/nntr_ggml_impl_common.h:72-150). A weight operand "B" is
+ * exactly the byte string a Q4_0 / Q4_K / Q6_K tensor holds in memory and in
+ * the .bin file: N rows of K weights (the transposed matrix), 8-row interleaved
+ * for Q4_0 and Q4_K, plain rows for Q6_K.
+ *
+ * Streams: "stream" is a cudaStream_t passed as void* (NULL = the legacy
+ * default stream). *_dev entry points take device pointers and only enqueue
+ * work. The host-pointer entry points (same names as cpu_backend.h) are
+ * synchronous, re-entrant, and may be called from many threads at once.
+ */
+#ifndef NNTR_CUDA_H_
+#define NNTR_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NNTR_CUDA_OK 0
+#define NNTR_CUDA_ERR_INVALID (-1)     /* bad shape / pointer: the CPU path throws std::invalid_argument */
+#define NNTR_CUDA_ERR_CUDA (-2)        /* CUDA runtime failure, or no device: std::runtime_error */
+#define NNTR_CUDA_ERR_UNSUPPORTED (-3) /* nntrainer::exception::not_supported */
+#define NNTR_CUDA_ERR_NOMEM (-4)       /* std::bad_alloc */
+#define NNTR_CUDA_ERR_TIMEOUT (-5)     /* a bounded device-side wait ran out */
+
+/** Weight / activation block formats; values follow the reference's ggml_type
+ *  numbering (GI/nntr_ggml_impl/nntr_ggml_impl_common.h:169-179). */
+typedef enum {
+  NNTR_Q4_0 = 2,
+  NNTR_Q8_0 = 8,
+  NNTR_Q4_K = 12,
+  NNTR_Q6_K = 14,
+  NNTR_Q8_K = 15
+} nntr_qtype;
+
+/* ------------------------------------------------------------------ set-up */
+
+/** Bind the calling process to a CUDA device (cudaSetDevice + kernel attribute
+ *  set-up). Stands in for init_backend() -> __ggml_init()
+ *  (cpu_backend.h:533 / GI/ggml_interface.cpp:24). Idempotent. */
+int nntr_cuda_init(int device);
+/** Number of visible CUDA devices, or a negative error code. */
+int nntr_cuda_device_count(void);
+/** Text of the last error on the calling thread ("" if none). */
+const char *nntr_cuda_last_error(void);
+/** Number of streaming multiprocessors of the bound device (grid sizing). */
+int nntr_cuda_sm_count(void);
+/** How many kernels of this library have been launched by this process. */
+uint64_t nntr_cuda_launch_count(void);
+
+/* ---------------------------------------------- device-pointer entry points */
+
+/** fp32 rows -> block_q8_K rows. rule 0: nntr_quantize_row_q8_K
+ *  (GI/nntr_ggml_impl/nntr_ggml_impl_quant.cpp:1334-1459); rule 1: the sign rule
+ *  of the 4-row quantizer nntr_quantize_mat_q8_K_4x8
+ *  (GI/nntr_ggml_impl/nntr_ggml_impl.cpp:7496-7737), stored as plain rows.
+ *  x: [rows][k] fp32 (row stride ldx elements), y: [rows][k/256] blocks. */
+int nntr_cuda_quantize_q8_K_dev(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, int rule, void *stream);
+/** fp32 rows -> block_q8_0 rows: nntr_quantize_row_q8_0 as the x86 build runs it
+ *  (GI/nntr_ggml_impl/nntr_ggml_impl_quant.cpp:532-701). */
+int nntr_cuda_quantize_q8_0_dev(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, void *stream);
+
+/** Plain-row dequantizers: cpu_backend.h:1047-1075,1165 dequantize_row_q4_K / q4_0 /
+ *  q6_K / q8_K / q8_0. qtype
+ *  picks the format; x holds k/blocksize plain blocks; y gets k floats. */
+int nntr_cuda_dequantize_row_dev(int qtype, const void *x, float *y, int64_t k, void *stream);
+/** Whole weight tensor -> fp32 [N][K], from the layout the tensor actually
+ *  holds (8-row interleaved for Q4_0 / Q4_K, plain rows for Q6_K). Element
+ *  values equal dequantize_row_* applied to the un-interleaved rows. */
+int nntr_cuda_dequantize_weight_dev(int qtype, const void *w, float *y, int64_t N, int64_t K, void *stream);
+
+/** Bytes of scratch a *_dev GEMM call needs for its quantized activations. */
+size_t nntr_cuda_gemm_workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K);
+
+/** C[M][N] = A[M][K] x W^T with W a quantized [N][K] weight (device pointers).
+ *  Same argument meaning as cpu_backend.h:937-977 gemm_q4_0 / gemm_q4_K /
+ *  gemm_q6_K -> GI/ggml_interface_omp.cpp:303,404,506: lda and ldb are ignored,
+ *  ldc is the row stride of C. M == 1 runs the decode GEMV (activation
+ *  quantized inside the kernel, no workspace needed); M > 1 quantizes A into
+ *  `workspace` first. K % 256 == 0 (Q4_K, Q6_K) or K % 32 == 0 (Q4_0);
+ *  N % 8 == 0 (Q4_0, Q4_K). */
+int nntr_cuda_gemm_q4_K_dev(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B,
+                            unsigned ldb, float *C, unsigned ldc, void *workspace, size_t workspace_bytes,
+                            void *stream);
+int nntr_cuda_gemm_q4_0_dev(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B,
+                            unsigned ldb, float *C, unsigned ldc, void *workspace, size_t workspace_bytes,
+                            void *stream);
+int nntr_cuda_gemm_q6_K_dev(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B,
+                            unsigned ldb, float *C, unsigned ldc, void *workspace, size_t workspace_bytes,
+                            void *stream);
+
+/** Launch flags for the GEMV kernels (bitwise or). */
+#define NNTR_CUDA_GEMV_PDL 1u /* programmatic dependent launch: the kernel's weight prefetch may \
+                                 overlap the tail of the previous kernel in the stream */
+/** Decode GEMV with explicit launch flags; otherwise as nntr_cuda_gemm_*_dev with M == 1. */
+int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
+                       void *stream);
+
+/* ------------------------------------------------ host-pointer entry points */
+
+/** Upload a weight tensor's bytes to device memory once, keyed by its host
+ *  address (weights sit at fixed addresses in the reference's memory pool for a
+ *  model's lifetime: nntrainer/tensor/memory_pool.cpp:170-188). Later
+ *  host-pointer GEMM calls whose B equals host_ptr, or lies inside a registered
+ *  range (a row-slice of a tensor), use the device copy. */
+int nntr_cuda_register_weight(const void *host_ptr, size_t bytes, int qtype, unsigned N, unsigned K);
+int nntr_cuda_unregister_weight(const void *host_ptr);
+/** Device address of a registered weight (NULL if unknown). */
+const void *nntr_cuda_weight_device_ptr(const void *host_ptr);
+
+/** Drop-ins for cpu_backend.h:937-977: A, C host fp32; B the host address of the
+ *  weight blocks (uploaded on first use if not registered). Synchronous. */
+int nntr_cuda_gemm_q4_0(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B, unsigned ldb,
+                        float *C, unsigned ldc);
+int nntr_cuda_gemm_q4_K(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B, unsigned ldb,
+                        float *C, unsigned ldc);
+int nntr_cuda_gemm_q6_K(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B, unsigned ldb,
+                        float *C, unsigned ldc);
+/** cpu_backend.h:1093 quantize_row_q8_K, :1140 quantize_row_q8_0 (host pointers). */
+int nntr_cuda_quantize_row_q8_K(const float *src, void *dst, int64_t k);
+int nntr_cuda_quantize_row_q8_0(const float *src, void *dst, int64_t k);
+/** cpu_backend.h:1047-1075,1165 dequantize_row_* (host pointers, plain rows). */
+int nntr_cuda_dequantize_row(int qtype, const void *x, float *y, int64_t k);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNTR_CUDA_H_ */

@@ -1,0 +1,162 @@
+"""Python face of the C ABI, named after the reference's cpu_backend functions
+for this path (nntrainer/tensor/cpu_backend/cpu_backend.h:937-1165).
+
+Two kinds of operand are accepted and never mixed:
+
+* numpy arrays -> the host-pointer entry points (``nntr_cuda_gemm_q4_K`` ...):
+  exactly the call a ``FloatTensor::dotQnK`` would make, host buffers in and out.
+* torch CUDA tensors -> the ``*_dev`` entry points on torch's current stream.
+
+PyTorch is used for device memory and streams only; all arithmetic happens in
+libnntr_cuda.so. A missing library or device raises -- there is no CPU path.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import capi
+from .capi import QTYPE, check, lib
+
+_BLOCK = {"q4_0": (32, 18), "q8_0": (32, 34), "q4_K": (256, 144), "q6_K": (256, 210), "q8_K": (256, 292)}
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def init(device: int = 0) -> None:
+    check(lib().nntr_cuda_init(device))
+
+
+def launch_count() -> int:
+    return int(lib().nntr_cuda_launch_count())
+
+
+def _stream() -> int:
+    return int(_torch().cuda.current_stream().cuda_stream)
+
+
+def _np_ptr(a: np.ndarray) -> int:
+    if not a.flags["C_CONTIGUOUS"]:
+        raise ValueError("array must be C-contiguous")
+    return a.ctypes.data
+
+
+def weight_nbytes(qtype: str, N: int, K: int) -> int:
+    bs, bb = _BLOCK[qtype]
+    return N * (K // bs) * bb
+
+
+# ----------------------------------------------------------------- weights
+def register_weight(qtype: str, B: np.ndarray, N: int, K: int) -> None:
+    """Upload a weight tensor's bytes to HBM once; later host-pointer GEMMs
+    that pass this array (or a row-slice of it) use the resident copy."""
+    check(lib().nntr_cuda_register_weight(_np_ptr(B), B.nbytes, QTYPE[qtype], N, K))
+
+
+def unregister_weight(B: np.ndarray) -> None:
+    check(lib().nntr_cuda_unregister_weight(_np_ptr(B)))
+
+
+# --------------------------------------------------------------- GEMV / GEMM
+def _gemm(qtype: str, M: int, N: int, K: int, A, lda: int, B, ldb: int, C, ldc: int, workspace=None):
+    L = lib()
+    if isinstance(A, np.ndarray):
+        fn = getattr(L, f"nntr_cuda_gemm_{qtype}")
+        check(fn(M, N, K, _np_ptr(A), lda, _np_ptr(B), ldb, _np_ptr(C), ldc))
+        return C
+    torch = _torch()
+    if not (A.is_cuda and B.is_cuda and C.is_cuda):
+        raise ValueError("device path needs CUDA tensors for A, B and C")
+    need = int(L.nntr_cuda_gemm_workspace_bytes(QTYPE[qtype], M, N, K))
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=A.device)
+    ws_ptr = workspace.data_ptr() if workspace is not None else 0
+    ws_len = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    fn = getattr(L, f"nntr_cuda_gemm_{qtype}_dev")
+    check(fn(M, N, K, A.data_ptr(), lda, B.data_ptr(), ldb, C.data_ptr(), ldc, ws_ptr, ws_len, _stream()))
+    return C
+
+
+def gemm_q4_0(M, N, K, A, lda, B, ldb, C, ldc, workspace=None):
+    """cpu_backend.h:937 -- C[M,N] = A[M,K] x W^T, W = Q4_0 (8-row interleaved)."""
+    return _gemm("q4_0", M, N, K, A, lda, B, ldb, C, ldc, workspace)
+
+
+def gemm_q4_K(M, N, K, A, lda, B, ldb, C, ldc, workspace=None):
+    """cpu_backend.h:955 -- W = Q4_K (8-row interleaved)."""
+    return _gemm("q4_K", M, N, K, A, lda, B, ldb, C, ldc, workspace)
+
+
+def gemm_q6_K(M, N, K, A, lda, B, ldb, C, ldc, workspace=None):
+    """cpu_backend.h:974 -- W = Q6_K (plain rows)."""
+    return _gemm("q6_K", M, N, K, A, lda, B, ldb, C, ldc, workspace)
+
+
+def gemv(qtype: str, N: int, K: int, x, B, y, pdl: bool = False):
+    """Decode GEMV on device tensors with explicit launch flags."""
+    check(lib().nntr_cuda_gemv_dev(QTYPE[qtype], N, K, x.data_ptr(), B.data_ptr(), y.data_ptr(),
+                                   capi.GEMV_PDL if pdl else 0, _stream()))
+    return y
+
+
+# ---------------------------------------------------------------- quantizers
+def quantize_row_q8_K(src, dst=None, k: int | None = None):
+    """cpu_backend.h:1093. numpy in -> numpy uint8 blocks out (host entry point)."""
+    src = np.ascontiguousarray(src, dtype=np.float32)
+    k = src.size if k is None else k
+    dst = np.zeros(k // 256 * 292, dtype=np.uint8) if dst is None else dst
+    check(lib().nntr_cuda_quantize_row_q8_K(_np_ptr(src), _np_ptr(dst), k))
+    return dst
+
+
+def quantize_row_q8_0(src, dst=None, k: int | None = None):
+    """cpu_backend.h:1140."""
+    src = np.ascontiguousarray(src, dtype=np.float32)
+    k = src.size if k is None else k
+    dst = np.zeros(k // 32 * 34, dtype=np.uint8) if dst is None else dst
+    check(lib().nntr_cuda_quantize_row_q8_0(_np_ptr(src), _np_ptr(dst), k))
+    return dst
+
+
+def quantize_q8_K_dev(x, rule: int = 0):
+    """Device rows [rows, k] fp32 -> uint8 tensor of block_q8_K rows."""
+    torch = _torch()
+    rows, k = x.shape
+    y = torch.zeros(rows * (k // 256) * 292, dtype=torch.uint8, device=x.device)
+    check(lib().nntr_cuda_quantize_q8_K_dev(x.data_ptr(), x.stride(0), y.data_ptr(), rows, k, rule, _stream()))
+    return y
+
+
+def quantize_q8_0_dev(x):
+    torch = _torch()
+    rows, k = x.shape
+    y = torch.zeros(rows * (k // 32) * 34, dtype=torch.uint8, device=x.device)
+    check(lib().nntr_cuda_quantize_q8_0_dev(x.data_ptr(), x.stride(0), y.data_ptr(), rows, k, _stream()))
+    return y
+
+
+# -------------------------------------------------------------- dequantizers
+def dequantize_row(qtype: str, x, y=None, k: int | None = None):
+    """cpu_backend.h:1047-1075,1165 dequantize_row_q4_K / q4_0 / q6_K / q8_K / q8_0
+    on plain (un-interleaved) blocks. numpy -> host entry point; CUDA tensor -> device."""
+    bs, bb = _BLOCK[qtype]
+    if isinstance(x, np.ndarray):
+        k = x.size // bb * bs if k is None else k
+        y = np.empty(k, dtype=np.float32) if y is None else y
+        check(lib().nntr_cuda_dequantize_row(QTYPE[qtype], _np_ptr(x), _np_ptr(y), k))
+        return y
+    torch = _torch()
+    k = x.numel() // bb * bs if k is None else k
+    y = torch.empty(k, dtype=torch.float32, device=x.device) if y is None else y
+    check(lib().nntr_cuda_dequantize_row_dev(QTYPE[qtype], x.data_ptr(), y.data_ptr(), k, _stream()))
+    return y
+
+
+def dequantize_weight(qtype: str, w, N: int, K: int):
+    """Whole device weight tensor (in the layout the tensor holds) -> fp32 [N, K]."""
+    torch = _torch()
+    y = torch.empty((N, K), dtype=torch.float32, device=w.device)
+    check(lib().nntr_cuda_dequantize_weight_dev(QTYPE[qtype], w.data_ptr(), y.data_ptr(), N, K, _stream()))
+    return y

@@ -1,0 +1,82 @@
+"""ctypes binding of libnntr_cuda.so (the C ABI declared in include/nntr_cuda.h).
+
+There is no fallback: if the shared library is missing or a call fails, an
+exception is raised. Error codes map to the exception types the reference's
+CPU path throws (std::invalid_argument -> ValueError, std::runtime_error ->
+RuntimeError, nntrainer::exception::not_supported -> NotImplementedError,
+std::bad_alloc -> MemoryError).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+from functools import lru_cache
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libnntr_cuda.so")
+HEADER = os.path.join(HERE, "..", "include", "nntr_cuda.h")
+
+Q4_0, Q8_0, Q4_K, Q6_K, Q8_K = 2, 8, 12, 14, 15
+QTYPE = {"q4_0": Q4_0, "q8_0": Q8_0, "q4_K": Q4_K, "q6_K": Q6_K, "q8_K": Q8_K}
+GEMV_PDL = 1
+
+OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOMEM, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5
+_EXC = {ERR_INVALID: ValueError, ERR_CUDA: RuntimeError, ERR_UNSUPPORTED: NotImplementedError,
+        ERR_NOMEM: MemoryError, ERR_TIMEOUT: TimeoutError}
+
+_vp, _u, _i64, _sz, _i = C.c_void_p, C.c_uint, C.c_int64, C.c_size_t, C.c_int
+_GEMM_DEV = [_u, _u, _u, _vp, _u, _vp, _u, _vp, _u, _vp, _sz, _vp]
+_GEMM_HOST = [_u, _u, _u, _vp, _u, _vp, _u, _vp, _u]
+
+SIGNATURES = {
+    "nntr_cuda_init": (_i, [_i]),
+    "nntr_cuda_device_count": (_i, []),
+    "nntr_cuda_last_error": (C.c_char_p, []),
+    "nntr_cuda_sm_count": (_i, []),
+    "nntr_cuda_launch_count": (C.c_uint64, []),
+    "nntr_cuda_quantize_q8_K_dev": (_i, [_vp, _i64, _vp, _i64, _i64, _i, _vp]),
+    "nntr_cuda_quantize_q8_0_dev": (_i, [_vp, _i64, _vp, _i64, _i64, _vp]),
+    "nntr_cuda_dequantize_row_dev": (_i, [_i, _vp, _vp, _i64, _vp]),
+    "nntr_cuda_dequantize_weight_dev": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
+    "nntr_cuda_gemm_workspace_bytes": (_sz, [_i, _u, _u, _u]),
+    "nntr_cuda_gemm_q4_K_dev": (_i, _GEMM_DEV),
+    "nntr_cuda_gemm_q4_0_dev": (_i, _GEMM_DEV),
+    "nntr_cuda_gemm_q6_K_dev": (_i, _GEMM_DEV),
+    "nntr_cuda_gemv_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _u, _vp]),
+    "nntr_cuda_register_weight": (_i, [_vp, _sz, _i, _u, _u]),
+    "nntr_cuda_unregister_weight": (_i, [_vp]),
+    "nntr_cuda_weight_device_ptr": (_vp, [_vp]),
+    "nntr_cuda_gemm_q4_0": (_i, _GEMM_HOST),
+    "nntr_cuda_gemm_q4_K": (_i, _GEMM_HOST),
+    "nntr_cuda_gemm_q6_K": (_i, _GEMM_HOST),
+    "nntr_cuda_quantize_row_q8_K": (_i, [_vp, _vp, _i64]),
+    "nntr_cuda_quantize_row_q8_0": (_i, [_vp, _vp, _i64]),
+    "nntr_cuda_dequantize_row": (_i, [_i, _vp, _vp, _i64]),
+}
+
+
+def declared_symbols() -> list[str]:
+    """Every function name include/nntr_cuda.h declares."""
+    with open(HEADER) as f:
+        text = f.read()
+    return sorted(set(re.findall(r"\b(nntr_cuda_[A-Za-z0-9_]+)\s*\(", text)))
+
+
+@lru_cache(maxsize=None)
+def lib() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m nntrainer_b200.build` (there is no CPU fallback)")
+    L = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    return L
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        msg = lib().nntr_cuda_last_error().decode(errors="replace")
+        raise _EXC.get(rc, RuntimeError)(f"nntr_cuda error {rc}: {msg}")

@@ -1,0 +1,494 @@
+// SPDX-License-Identifier: Apache-2.0
+/**
+ * @file  capi.cu
+ * @brief The extern "C" surface of libnntr_cuda.so (declared in
+ *        include/nntr_cuda.h): argument checks, error text, the weight cache
+ *        keyed by host address, and the host-pointer drop-ins that mirror
+ *        nntrainer/tensor/cpu_backend/cpu_backend.h.
+ *
+ * Threading: the reference calls Tensor::dot from inside OpenMP regions (MoE
+ * experts) and loads weights from one thread per layer, so every host-pointer
+ * entry point is re-entrant: each calling thread owns a stream and a pair of
+ * staging buffers (created on first use, grown on demand), and the weight
+ * cache is guarded by a mutex.
+ */
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <atomic>
+#include <map>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace nntr {
+
+static thread_local char tl_error[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+static std::atomic<int> g_sms{0};
+
+int set_error(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error, sizeof tl_error, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_cuda(cudaError_t e, const char *what) {
+  if (e == cudaSuccess)
+    return NNTR_CUDA_OK;
+  const int code = (e == cudaErrorMemoryAllocation) ? NNTR_CUDA_ERR_NOMEM : NNTR_CUDA_ERR_CUDA;
+  return set_error(code, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int sm_count() {
+  int v = g_sms.load(std::memory_order_relaxed);
+  if (v > 0)
+    return v;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess)
+    return 148;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+    return 148;
+  g_sms.store(v, std::memory_order_relaxed);
+  return v;
+}
+
+/* ---------------------------------------------------------------- weights */
+struct WeightEntry {
+  void *dev;
+  size_t bytes;
+  int qtype;
+  unsigned N, K;
+};
+static std::mutex g_wmutex;
+static std::map<uintptr_t, WeightEntry> g_weights; // key: host address of the first byte
+
+/* device address for a host address inside a registered range, or nullptr */
+static const void *lookup_weight(const void *host) {
+  const uintptr_t h = reinterpret_cast<uintptr_t>(host);
+  std::lock_guard<std::mutex> lk(g_wmutex);
+  auto it = g_weights.upper_bound(h);
+  if (it == g_weights.begin())
+    return nullptr;
+  --it;
+  if (h >= it->first && h < it->first + it->second.bytes)
+    return static_cast<const uint8_t *>(it->second.dev) + (h - it->first);
+  return nullptr;
+}
+
+static size_t weight_bytes(int qtype, unsigned N, unsigned K) {
+  switch (qtype) {
+  case NNTR_Q4_0:
+    return (size_t)N * (K / 32) * sizeof(BlockQ40);
+  case NNTR_Q4_K:
+    return (size_t)N * (K / 256) * sizeof(BlockQ4K);
+  case NNTR_Q6_K:
+    return (size_t)N * (K / 256) * sizeof(BlockQ6K);
+  default:
+    return 0;
+  }
+}
+
+static int check_weight_shape(int qtype, unsigned N, unsigned K) {
+  switch (qtype) {
+  case NNTR_Q4_0:
+    if (K == 0 || K % 32 || N % 8)
+      return set_error(NNTR_CUDA_ERR_INVALID, "q4_0 weight: need K %% 32 == 0 and N %% 8 == 0 (N=%u K=%u)", N, K);
+    return NNTR_CUDA_OK;
+  case NNTR_Q4_K:
+    if (K == 0 || K % 256 || N % 8)
+      return set_error(NNTR_CUDA_ERR_INVALID, "q4_K weight: need K %% 256 == 0 and N %% 8 == 0 (N=%u K=%u)", N, K);
+    return NNTR_CUDA_OK;
+  case NNTR_Q6_K:
+    if (K == 0 || K % 256)
+      return set_error(NNTR_CUDA_ERR_INVALID, "q6_K weight: need K %% 256 == 0 (K=%u)", K);
+    return NNTR_CUDA_OK;
+  default:
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "qtype %d is not a weight format", qtype);
+  }
+}
+
+/* ------------------------------------------------- per-thread host staging */
+struct ThreadCtx {
+  cudaStream_t stream = nullptr;
+  void *dA = nullptr, *dC = nullptr, *dQ = nullptr; // device staging: activations, outputs, quantized rows
+  size_t capA = 0, capC = 0, capQ = 0;
+  int device = -1;
+  ~ThreadCtx() {
+    // best effort; the context may already be gone at thread exit
+    if (dA)
+      cudaFree(dA);
+    if (dC)
+      cudaFree(dC);
+    if (dQ)
+      cudaFree(dQ);
+    if (stream)
+      cudaStreamDestroy(stream);
+  }
+};
+static thread_local ThreadCtx tl_ctx;
+
+static int ensure_ctx(ThreadCtx *&out) {
+  ThreadCtx &c = tl_ctx;
+  if (!c.stream) {
+    NNTR_CHECK_CUDA(cudaGetDevice(&c.device));
+    NNTR_CHECK_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+  }
+  out = &c;
+  return NNTR_CUDA_OK;
+}
+
+static int grow(void *&p, size_t &cap, size_t need) {
+  if (need <= cap)
+    return NNTR_CUDA_OK;
+  if (p) {
+    NNTR_CHECK_CUDA(cudaFree(p));
+    p = nullptr;
+    cap = 0;
+  }
+  size_t want = need < 4096 ? 4096 : need + need / 4;
+  NNTR_CHECK_CUDA(cudaMalloc(&p, want));
+  cap = want;
+  return NNTR_CUDA_OK;
+}
+
+/* --------------------------------------------------------- GEMM dispatch */
+static size_t workspace_bytes(int qtype, unsigned M, unsigned K) {
+  if (M <= 1)
+    return 0;
+  if (qtype == NNTR_Q4_0)
+    return (size_t)M * (K / 32) * sizeof(BlockQ80);
+  return (size_t)M * (K / 256) * sizeof(BlockQ8K);
+}
+
+static int gemm_dev(int qtype, unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C,
+                    unsigned ldc, void *ws, size_t ws_bytes, cudaStream_t st) {
+  int rc = check_weight_shape(qtype, N, K);
+  if (rc)
+    return rc;
+  if (M == 0 || N == 0)
+    return NNTR_CUDA_OK;
+  if (!A || !B || !C)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm: null pointer");
+  if (M == 1) {
+    switch (qtype) {
+    case NNTR_Q4_K:
+      return launch_gemv_q4_K(N, K, A, B, C, 0, st);
+    case NNTR_Q4_0:
+      return launch_gemv_q4_0(N, K, A, B, C, 0, st);
+    default:
+      return launch_gemv_q6_K(N, K, A, B, C, 0, st);
+    }
+  }
+  if (ldc < N)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm: ldc (%u) < N (%u)", ldc, N);
+  const size_t need = workspace_bytes(qtype, M, K);
+  if (!ws || ws_bytes < need)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm: workspace of %zu bytes needed, %zu given", need, ws_bytes);
+  if (reinterpret_cast<uintptr_t>(ws) & 15)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm: workspace must be 16-byte aligned");
+  /* Rows below 4*floor(M/4) are quantized the way the reference's 4-row
+   * quantizer does it, the last M%4 rows the way its row quantizer does
+   * (ggml_interface_omp.cpp:433-461). */
+  const unsigned M4 = (M / 4) * 4;
+  if (qtype == NNTR_Q4_0) {
+    rc = launch_quantize_q8_0(A, K, ws, M, K, st);
+  } else if (qtype == NNTR_Q6_K) {
+    rc = launch_quantize_q8_K(A, K, ws, M, K, 0, st); // ggml_interface_omp.cpp:545-551: row quantizer for all rows
+  } else {
+    rc = M4 ? launch_quantize_q8_K(A, K, ws, M4, K, 1, st) : NNTR_CUDA_OK;
+    if (!rc && M4 < M)
+      rc = launch_quantize_q8_K(A + (size_t)M4 * K, K, static_cast<uint8_t *>(ws) + (size_t)M4 * (K / 256) * sizeof(BlockQ8K),
+                                M - M4, K, 0, st);
+  }
+  if (rc)
+    return rc;
+  switch (qtype) {
+  case NNTR_Q4_K:
+    return launch_gemm_q4_K(M, N, K, ws, B, C, ldc, st);
+  case NNTR_Q4_0:
+    return launch_gemm_q4_0(M, N, K, ws, B, C, ldc, st);
+  default:
+    return launch_gemm_q6_K(M, N, K, ws, B, C, ldc, st);
+  }
+}
+
+static int gemm_host(int qtype, unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C,
+                     unsigned ldc) {
+  int rc = check_weight_shape(qtype, N, K);
+  if (rc)
+    return rc;
+  if (M == 0 || N == 0)
+    return NNTR_CUDA_OK;
+  if (!A || !B || !C)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm: null pointer");
+  if (M > 1 && ldc < N)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm: ldc (%u) < N (%u)", ldc, N);
+  const void *dB = lookup_weight(B);
+  if (!dB) {
+    rc = nntr_cuda_register_weight(B, weight_bytes(qtype, N, K), qtype, N, K);
+    if (rc)
+      return rc;
+    dB = lookup_weight(B);
+  }
+  ThreadCtx *c;
+  rc = ensure_ctx(c);
+  if (rc)
+    return rc;
+  /* The reference writes GEMM rows with stride ldc and the leftover M%4 rows
+   * (and the GEMV) with stride N (ggml_interface_omp.cpp:463-491). The device
+   * result is dense [M][N]; the copy back reproduces those strides. */
+  const size_t bytesA = (size_t)M * K * sizeof(float), bytesC = (size_t)M * N * sizeof(float);
+  if ((rc = grow(c->dA, c->capA, bytesA)) || (rc = grow(c->dC, c->capC, bytesC)) ||
+      (rc = grow(c->dQ, c->capQ, workspace_bytes(qtype, M, K))))
+    return rc;
+  NNTR_CHECK_CUDA(cudaMemcpyAsync(c->dA, A, bytesA, cudaMemcpyHostToDevice, c->stream));
+  rc = gemm_dev(qtype, M, N, K, static_cast<const float *>(c->dA), dB, static_cast<float *>(c->dC), N, c->dQ,
+                c->capQ, c->stream);
+  if (rc)
+    return rc;
+  const unsigned M4 = (M == 1 || qtype == NNTR_Q6_K) ? M : (M / 4) * 4; // rows written with stride ldc
+  if (M == 1) {
+    NNTR_CHECK_CUDA(cudaMemcpyAsync(C, c->dC, bytesC, cudaMemcpyDeviceToHost, c->stream));
+  } else {
+    if (M4)
+      NNTR_CHECK_CUDA(cudaMemcpy2DAsync(C, (size_t)ldc * sizeof(float), c->dC, (size_t)N * sizeof(float),
+                                        (size_t)N * sizeof(float), M4, cudaMemcpyDeviceToHost, c->stream));
+    if (M4 < M)
+      NNTR_CHECK_CUDA(cudaMemcpyAsync(C + (size_t)M4 * N, static_cast<float *>(c->dC) + (size_t)M4 * N,
+                                      (size_t)(M - M4) * N * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  }
+  NNTR_CHECK_CUDA(cudaStreamSynchronize(c->stream));
+  return NNTR_CUDA_OK;
+}
+
+} // namespace nntr
+
+using namespace nntr;
+
+extern "C" {
+
+int nntr_cuda_init(int device) {
+  int n = 0;
+  NNTR_CHECK_CUDA(cudaGetDeviceCount(&n));
+  if (device < 0 || device >= n)
+    return set_error(NNTR_CUDA_ERR_INVALID, "init: device %d of %d", device, n);
+  NNTR_CHECK_CUDA(cudaSetDevice(device));
+  int major = 0;
+  NNTR_CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  if (major != 10)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "init: kernels are built for sm_100a only (device is sm_%d*)", major);
+  NNTR_CHECK_CUDA(cudaFree(nullptr)); // force context creation
+  g_sms.store(0);
+  (void)sm_count();
+  return NNTR_CUDA_OK;
+}
+
+int nntr_cuda_device_count(void) {
+  int n = 0;
+  int rc = check_cuda(cudaGetDeviceCount(&n), "cudaGetDeviceCount");
+  return rc ? rc : n;
+}
+
+const char *nntr_cuda_last_error(void) { return tl_error; }
+int nntr_cuda_sm_count(void) { return sm_count(); }
+uint64_t nntr_cuda_launch_count(void) { return g_launches.load(); }
+
+int nntr_cuda_quantize_q8_K_dev(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, int rule, void *stream) {
+  return launch_quantize_q8_K(x, ldx, y, rows, k, rule, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_quantize_q8_0_dev(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, void *stream) {
+  return launch_quantize_q8_0(x, ldx, y, rows, k, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_dequantize_row_dev(int qtype, const void *x, float *y, int64_t k, void *stream) {
+  return launch_dequantize_row(qtype, x, y, k, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_dequantize_weight_dev(int qtype, const void *w, float *y, int64_t N, int64_t K, void *stream) {
+  return launch_dequantize_weight(qtype, w, y, N, K, static_cast<cudaStream_t>(stream));
+}
+
+size_t nntr_cuda_gemm_workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K) {
+  (void)N;
+  return workspace_bytes(qtype, M, K);
+}
+
+int nntr_cuda_gemm_q4_K_dev(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B,
+                            unsigned ldb, float *C, unsigned ldc, void *ws, size_t ws_bytes, void *stream) {
+  (void)lda;
+  (void)ldb;
+  return gemm_dev(NNTR_Q4_K, M, N, K, A, B, C, ldc, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_gemm_q4_0_dev(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B,
+                            unsigned ldb, float *C, unsigned ldc, void *ws, size_t ws_bytes, void *stream) {
+  (void)lda;
+  (void)ldb;
+  return gemm_dev(NNTR_Q4_0, M, N, K, A, B, C, ldc, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_gemm_q6_K_dev(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B,
+                            unsigned ldb, float *C, unsigned ldc, void *ws, size_t ws_bytes, void *stream) {
+  (void)lda;
+  (void)ldb;
+  return gemm_dev(NNTR_Q6_K, M, N, K, A, B, C, ldc, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
+                       void *stream) {
+  int rc = check_weight_shape(qtype, N, K);
+  if (rc)
+    return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (qtype) {
+  case NNTR_Q4_K:
+    return launch_gemv_q4_K(N, K, x, B, y, flags, st);
+  case NNTR_Q4_0:
+    return launch_gemv_q4_0(N, K, x, B, y, flags, st);
+  default:
+    return launch_gemv_q6_K(N, K, x, B, y, flags, st);
+  }
+}
+
+int nntr_cuda_register_weight(const void *host_ptr, size_t bytes, int qtype, unsigned N, unsigned K) {
+  int rc = check_weight_shape(qtype, N, K);
+  if (rc)
+    return rc;
+  if (!host_ptr)
+    return set_error(NNTR_CUDA_ERR_INVALID, "register_weight: null pointer");
+  if (bytes != weight_bytes(qtype, N, K))
+    return set_error(NNTR_CUDA_ERR_INVALID, "register_weight: %zu bytes given, N=%u K=%u needs %zu", bytes, N, K,
+                     weight_bytes(qtype, N, K));
+  const uintptr_t h = reinterpret_cast<uintptr_t>(host_ptr);
+  {
+    std::lock_guard<std::mutex> lk(g_wmutex);
+    auto it = g_weights.find(h);
+    if (it != g_weights.end()) {
+      if (it->second.bytes == bytes && it->second.qtype == qtype)
+        return NNTR_CUDA_OK; // already resident
+      return set_error(NNTR_CUDA_ERR_INVALID, "register_weight: address already registered with another shape");
+    }
+  }
+  void *dev = nullptr;
+  NNTR_CHECK_CUDA(cudaMalloc(&dev, bytes ? bytes : 16));
+  cudaError_t e = cudaMemcpy(dev, host_ptr, bytes, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    cudaFree(dev);
+    return check_cuda(e, "register_weight upload");
+  }
+  std::lock_guard<std::mutex> lk(g_wmutex);
+  auto ins = g_weights.emplace(h, WeightEntry{dev, bytes, qtype, N, K});
+  if (!ins.second) // another thread won the race
+    cudaFree(dev);
+  return NNTR_CUDA_OK;
+}
+
+int nntr_cuda_unregister_weight(const void *host_ptr) {
+  void *dev = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_wmutex);
+    auto it = g_weights.find(reinterpret_cast<uintptr_t>(host_ptr));
+    if (it == g_weights.end())
+      return set_error(NNTR_CUDA_ERR_INVALID, "unregister_weight: address not registered");
+    dev = it->second.dev;
+    g_weights.erase(it);
+  }
+  NNTR_CHECK_CUDA(cudaDeviceSynchronize());
+  NNTR_CHECK_CUDA(cudaFree(dev));
+  return NNTR_CUDA_OK;
+}
+
+const void *nntr_cuda_weight_device_ptr(const void *host_ptr) { return lookup_weight(host_ptr); }
+
+int nntr_cuda_gemm_q4_0(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B, unsigned ldb,
+                        float *C, unsigned ldc) {
+  (void)lda;
+  (void)ldb;
+  return gemm_host(NNTR_Q4_0, M, N, K, A, B, C, ldc);
+}
+int nntr_cuda_gemm_q4_K(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B, unsigned ldb,
+                        float *C, unsigned ldc) {
+  (void)lda;
+  (void)ldb;
+  return gemm_host(NNTR_Q4_K, M, N, K, A, B, C, ldc);
+}
+int nntr_cuda_gemm_q6_K(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B, unsigned ldb,
+                        float *C, unsigned ldc) {
+  (void)lda;
+  (void)ldb;
+  return gemm_host(NNTR_Q6_K, M, N, K, A, B, C, ldc);
+}
+
+static int quantize_row_host(int qtype, const float *src, void *dst, int64_t k) {
+  const int bs = qtype == NNTR_Q8_0 ? 32 : 256;
+  if (!src || !dst || k < 0 || k % bs)
+    return set_error(NNTR_CUDA_ERR_INVALID, "quantize_row: k must be a multiple of %d", bs);
+  if (k == 0)
+    return NNTR_CUDA_OK;
+  ThreadCtx *c;
+  int rc = ensure_ctx(c);
+  if (rc)
+    return rc;
+  const size_t out_bytes = (size_t)(k / bs) * (qtype == NNTR_Q8_0 ? sizeof(BlockQ80) : sizeof(BlockQ8K));
+  if ((rc = grow(c->dA, c->capA, (size_t)k * sizeof(float))) || (rc = grow(c->dQ, c->capQ, out_bytes)))
+    return rc;
+  NNTR_CHECK_CUDA(cudaMemcpyAsync(c->dA, src, (size_t)k * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  rc = (qtype == NNTR_Q8_0) ? launch_quantize_q8_0(static_cast<float *>(c->dA), k, c->dQ, 1, k, c->stream)
+                            : launch_quantize_q8_K(static_cast<float *>(c->dA), k, c->dQ, 1, k, 0, c->stream);
+  if (rc)
+    return rc;
+  NNTR_CHECK_CUDA(cudaMemcpyAsync(dst, c->dQ, out_bytes, cudaMemcpyDeviceToHost, c->stream));
+  NNTR_CHECK_CUDA(cudaStreamSynchronize(c->stream));
+  return NNTR_CUDA_OK;
+}
+
+int nntr_cuda_quantize_row_q8_K(const float *src, void *dst, int64_t k) {
+  return quantize_row_host(NNTR_Q8_K, src, dst, k);
+}
+int nntr_cuda_quantize_row_q8_0(const float *src, void *dst, int64_t k) {
+  return quantize_row_host(NNTR_Q8_0, src, dst, k);
+}
+
+int nntr_cuda_dequantize_row(int qtype, const void *x, float *y, int64_t k) {
+  size_t bs, bb;
+  switch (qtype) {
+  case NNTR_Q4_0:
+    bs = 32, bb = sizeof(BlockQ40);
+    break;
+  case NNTR_Q8_0:
+    bs = 32, bb = sizeof(BlockQ80);
+    break;
+  case NNTR_Q4_K:
+    bs = 256, bb = sizeof(BlockQ4K);
+    break;
+  case NNTR_Q6_K:
+    bs = 256, bb = sizeof(BlockQ6K);
+    break;
+  case NNTR_Q8_K:
+    bs = 256, bb = sizeof(BlockQ8K);
+    break;
+  default:
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "dequantize_row: unknown qtype %d", qtype);
+  }
+  if (!x || !y || k < 0 || (size_t)k % bs)
+    return set_error(NNTR_CUDA_ERR_INVALID, "dequantize_row: k must be a multiple of %zu", bs);
+  if (k == 0)
+    return NNTR_CUDA_OK;
+  ThreadCtx *c;
+  int rc = ensure_ctx(c);
+  if (rc)
+    return rc;
+  const size_t in_bytes = (size_t)k / bs * bb;
+  if ((rc = grow(c->dQ, c->capQ, in_bytes)) || (rc = grow(c->dC, c->capC, (size_t)k * sizeof(float))))
+    return rc;
+  NNTR_CHECK_CUDA(cudaMemcpyAsync(c->dQ, x, in_bytes, cudaMemcpyHostToDevice, c->stream));
+  rc = launch_dequantize_row(qtype, c->dQ, static_cast<float *>(c->dC), k, c->stream);
+  if (rc)
+    return rc;
+  NNTR_CHECK_CUDA(cudaMemcpyAsync(y, c->dC, (size_t)k * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  NNTR_CHECK_CUDA(cudaStreamSynchronize(c->stream));
+  return NNTR_CUDA_OK;
+}
+
+} // extern "C"

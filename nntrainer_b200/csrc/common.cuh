@@ -1,0 +1,233 @@
+// SPDX-License-Identifier: Apache-2.0
+/**
+ * @file  common.cuh
+ * @brief Block layouts, error plumbing and small device helpers shared by the
+ *        kernels of libnntr_cuda.so.
+ *
+ * The block structs restate the layouts of the reference project's
+ * nntrainer/tensor/cpu_backend/ggml_interface/nntr_ggml_impl/
+ * nntr_ggml_impl_common.h:72-150 byte for byte (checked by static_asserts);
+ * device memory holds exactly the bytes a host tensor holds.
+ */
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/nntr_cuda.h"
+
+namespace nntr {
+
+constexpr int QK_K = 256;
+constexpr unsigned FULL = 0xffffffffu;
+
+struct __align__(2) BlockQ4K { // 144 B: one row, 256 weights
+  uint16_t d, dmin;
+  uint8_t scales[12];
+  uint8_t qs[128];
+};
+struct __align__(16) BlockQ4Kx8 { // 1152 B: 8 rows x 256 weights
+  uint16_t d[8];
+  uint16_t dmin[8];
+  uint8_t scales[96];
+  uint8_t qs[1024];
+};
+struct __align__(2) BlockQ40 { // 18 B: one row, 32 weights
+  uint16_t d;
+  uint8_t qs[16];
+};
+struct __align__(16) BlockQ40x8 { // 144 B: 8 rows x 32 weights, nibbles XOR 8
+  uint16_t d[8];
+  uint8_t qs[128];
+};
+struct __align__(2) BlockQ6K { // 210 B: one row, 256 weights
+  uint8_t ql[128];
+  uint8_t qh[64];
+  int8_t scales[16];
+  uint16_t d;
+};
+struct __align__(4) BlockQ8K { // 292 B
+  float d;
+  int8_t qs[256];
+  int16_t bsums[16];
+};
+struct __align__(2) BlockQ80 { // 34 B
+  uint16_t d;
+  int8_t qs[32];
+};
+static_assert(sizeof(BlockQ4K) == 144 && sizeof(BlockQ4Kx8) == 1152, "q4_K layout");
+static_assert(sizeof(BlockQ40) == 18 && sizeof(BlockQ40x8) == 144, "q4_0 layout");
+static_assert(sizeof(BlockQ6K) == 210, "q6_K layout");
+static_assert(sizeof(BlockQ8K) == 292 && sizeof(BlockQ80) == 34, "q8 layout");
+
+/* ---- host-side error plumbing (defined in capi.cu) ---- */
+int set_error(int code, const char *fmt, ...);
+int check_cuda(cudaError_t e, const char *what);
+void count_launch(unsigned n = 1);
+int sm_count();
+
+#define NNTR_CHECK_CUDA(expr)                                                                                          \
+  do {                                                                                                                 \
+    int _rc = ::nntr::check_cuda((expr), #expr);                                                                       \
+    if (_rc != NNTR_CUDA_OK)                                                                                           \
+      return _rc;                                                                                                      \
+  } while (0)
+
+/* ---- device helpers ---- */
+__device__ __forceinline__ float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ uint16_t float_to_half_bits_rn(float f) { return __half_as_ushort(__float2half_rn(f)); }
+
+/** 6-bit scale / min of entry j in a 12-byte packed group
+ *  (get_scale_min_k4, nntr_ggml_impl_quant.cpp:368-378). In block_q4_K j is the
+ *  sub-block; in block_q4_Kx8 group sb, j is the row. */
+__device__ __forceinline__ void scale_min_k4(int j, const uint8_t *q, int &sc, int &m) {
+  if (j < 4) {
+    sc = q[j] & 63;
+    m = q[j + 4] & 63;
+  } else {
+    sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
+    m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+  }
+}
+
+/** Programmatic dependent launch: wait until the kernels this one depends on
+ *  have finished and their writes are visible (no-op without the attribute). */
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+/** Allow the next kernel in the stream to start its independent prologue. */
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+/** streaming 8-/16-byte loads that do not allocate in L1 */
+__device__ __forceinline__ uint2 ldg_stream_u2(const void *p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ldg_stream_u4(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
+/* ------------------------------------------------------------------------
+ * Warp-level Q8_K quantization of one 256-element block. Lane l owns elements
+ * 8l..8l+7. Follows quantize_row_q8_K_ref (nntr_ggml_impl_quant.cpp:1334-1374):
+ * max = the FIRST element with the strictly greatest |x|; iscale = -127/max;
+ * q = min(127, round-to-nearest-even(iscale*x)) with the product rounded to
+ * fp32 first (no fused multiply-add); d = 1/iscale. rule 1 replaces the sign
+ * choice by that of the 4-row quantizer (nntr_ggml_impl.cpp:7504-7600): the
+ * scale is negative iff +amax occurs anywhere in the block.
+ * ---------------------------------------------------------------------- */
+struct Q8KLane {
+  uint32_t w0, w1; // the lane's 8 quantized values, little-endian bytes
+  int sum8;        // their sum
+  float d;         // block scale (same in every lane)
+};
+
+__device__ __forceinline__ Q8KLane q8K_quantize_warp(const float4 a, const float4 b, int lane, int rule) {
+  const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  float amax = 0.f, maxv = 0.f;
+  bool plus = false;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float ax = fabsf(v[j]);
+    if (ax > amax) {
+      amax = ax;
+      maxv = v[j];
+    }
+  }
+  const float gmax = __uint_as_float(__reduce_max_sync(FULL, __float_as_uint(amax)));
+  Q8KLane out;
+  if (gmax == 0.f) {
+    out.w0 = out.w1 = 0u;
+    out.sum8 = 0;
+    out.d = 0.f;
+    return out;
+  }
+  const unsigned holders = __ballot_sync(FULL, amax == gmax);
+  float mx = __shfl_sync(FULL, maxv, __ffs(holders) - 1);
+  if (rule == 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      plus |= (v[j] == gmax);
+    mx = __any_sync(FULL, plus) ? gmax : -gmax;
+  }
+  const float iscale = __fdiv_rn(-127.f, mx);
+  int q[8];
+  int s = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    int t = __float2int_rn(__fmul_rn(iscale, v[j]));
+    t = t < 127 ? t : 127;
+    q[j] = t;
+    s += t;
+  }
+  out.w0 = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+  out.w1 = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+  out.sum8 = s;
+  out.d = __fdiv_rn(1.f, iscale);
+  (void)lane;
+  return out;
+}
+
+/* ------------------------------------------------------------------------
+ * Warp-level Q8_0 quantization of 8 consecutive 32-element blocks (256
+ * elements; lane l owns 8l..8l+7, so a 32-block is 4 adjacent lanes). Follows
+ * the x86 SIMD branch of nntr_quantize_row_q8_0 (nntr_ggml_impl_quant.cpp:
+ * 613-701): d = amax/127 (stored as fp16, RNE), multiplier 127/amax, RNE.
+ * ---------------------------------------------------------------------- */
+struct Q80Lane {
+  uint32_t w0, w1; // 8 quantized values
+  int sum8;
+  uint16_t d_bits; // fp16 scale of the lane's 32-block
+};
+
+__device__ __forceinline__ Q80Lane q80_quantize_warp(const float4 a, const float4 b) {
+  const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    amax = fmaxf(amax, fabsf(v[j]));
+  amax = fmaxf(amax, __shfl_xor_sync(FULL, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(FULL, amax, 2));
+  const float d = __fdiv_rn(amax, 127.f);
+  const float id = (amax != 0.f) ? __fdiv_rn(127.f, amax) : 0.f;
+  int q[8];
+  int s = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    q[j] = __float2int_rn(__fmul_rn(v[j], id));
+    s += q[j];
+  }
+  Q80Lane out;
+  out.w0 = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+  out.w1 = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+  out.sum8 = s;
+  out.d_bits = float_to_half_bits_rn(d);
+  return out;
+}
+
+/* launchers implemented in the .cu files (host side, return NNTR_CUDA_* codes) */
+int launch_quantize_q8_K(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, int rule, cudaStream_t st);
+int launch_quantize_q8_0(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, cudaStream_t st);
+int launch_dequantize_row(int qtype, const void *x, float *y, int64_t k, cudaStream_t st);
+int launch_dequantize_weight(int qtype, const void *w, float *y, int64_t N, int64_t K, cudaStream_t st);
+int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
+int launch_gemv_q4_0(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
+int launch_gemv_q6_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
+/* M > 1 with activations already quantized to plain Q8 rows in `qa` */
+int launch_gemm_q4_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
+                     cudaStream_t st);
+int launch_gemm_q4_0(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
+                     cudaStream_t st);
+int launch_gemm_q6_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
+                     cudaStream_t st);
+
+} // namespace nntr

@@ -1,0 +1,265 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU checker.
+
+Bars: quantized activations and dequantized weights bit-exact; GEMV / GEMM
+within max-rel 2e-3 of the checker's fp32 result (the stated tolerance) -- and,
+because the kernels reproduce the reference's per-output float chain, the tests
+additionally require bit equality and say so.
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from oracle import oracle as O  # noqa: E402
+
+REL_TOL = 2e-3  # the path's stated tolerance (max |gpu-ref| / max |ref|)
+
+
+@pytest.fixture(scope="module")
+def be():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from nntrainer_b200 import backend, build
+    build.build()
+    backend.init(0)
+    return backend
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def max_rel(got, want):
+    return float(np.max(np.abs(got - want)) / max(np.max(np.abs(want)), 1e-30))
+
+
+def acts(rng, M, K):
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    if M > 1:
+        A[1, :256] = 0.0                                   # all-zero block
+    if M > 2:
+        A[2, :256] = np.round(A[2, :256] * 2) / 2          # rounding ties
+    if M > 3:
+        A[3, :256] = np.where(np.arange(256) % 2 == 0, -2.5, 2.5)  # -amax first, +amax later
+    return A
+
+
+# ------------------------------------------------------------- quantizers
+@pytest.mark.parametrize("K", [256, 768, 4096])
+def test_quantize_q8_K_bit_exact(be, port, K):
+    rng = np.random.default_rng(K)
+    A = acts(rng, 9, K)
+    for rule in (0, 1):
+        got = be.quantize_q8_K_dev(dev(A), rule).cpu().numpy().reshape(9, -1)
+        for m in range(9):
+            assert np.array_equal(got[m], port.quantize_row_q8_K_rule(A[m], rule)), (rule, m)
+    # host entry point
+    assert np.array_equal(be.quantize_row_q8_K(A[0]), port.quantize_row_q8_K(A[0]))
+
+
+@pytest.mark.parametrize("K", [32, 96, 256, 2880, 4096])
+def test_quantize_q8_0_bit_exact(be, port, K):
+    rng = np.random.default_rng(K + 1)
+    A = rng.standard_normal((5, K)).astype(np.float32)
+    A[1, :32] = 0.0
+    A[2] = np.round(A[2] * 2) / 2
+    Ad = torch.zeros((5, (K + 3) // 4 * 4), dtype=torch.float32, device="cuda")
+    Ad[:, :K] = dev(A)
+    got = be.quantize_q8_0_dev(Ad[:, :K] if K % 4 == 0 else Ad).cpu().numpy().reshape(5, -1)
+    for m in range(5):
+        assert np.array_equal(got[m], port.quantize_row_q8_0(A[m])), m
+    assert np.array_equal(be.quantize_row_q8_0(A[0]), port.quantize_row_q8_0(A[0]))
+
+
+def test_golden_quantizers(be, golden):
+    A = golden["A"]
+    got = be.quantize_q8_K_dev(dev(A), 0).cpu().numpy().reshape(A.shape[0], -1)
+    assert np.array_equal(got, golden["q8_K_rows"])
+    got0 = be.quantize_q8_0_dev(dev(A)).cpu().numpy().reshape(A.shape[0], -1)
+    assert np.array_equal(got0, golden["q8_0_rows"])
+
+
+# ------------------------------------------------------------ dequantizers
+@pytest.mark.parametrize("q", ["q4_0", "q4_K", "q6_K"])
+def test_golden_dequantize_rows_bit_exact(be, golden, q):
+    K, N = 512, 16
+    plain = golden[f"{q}_plain"]
+    rb = plain.size // N
+    for r in (0, 5, 15):
+        row = plain[r * rb:(r + 1) * rb]
+        assert np.array_equal(bits(be.dequantize_row(q, dev(row)).cpu().numpy()), bits(golden[f"{q}_dequant"][r]))
+        assert np.array_equal(bits(be.dequantize_row(q, row.copy())), bits(golden[f"{q}_dequant"][r]))
+    tensor_bytes = golden[f"{q}_x8"] if q != "q6_K" else plain
+    full = be.dequantize_weight(q, dev(tensor_bytes), N, K).cpu().numpy()
+    assert np.array_equal(bits(full), bits(golden[f"{q}_dequant"]))
+
+
+def test_golden_dequantize_q8(be, golden):
+    assert np.array_equal(bits(be.dequantize_row("q8_K", dev(golden["q8_K_rows"][0])).cpu().numpy()),
+                          bits(golden["q8_K_dequant"]))
+    assert np.array_equal(bits(be.dequantize_row("q8_0", dev(golden["q8_0_rows"][0])).cpu().numpy()),
+                          bits(golden["q8_0_dequant"]))
+
+
+@pytest.mark.parametrize("q,gen", [("q4_K", O.random_q4_Kx8), ("q4_0", O.random_q4_0x8), ("q6_K", O.random_q6_K)])
+def test_dequantize_weight_random_bytes_bit_exact(be, port, q, gen):
+    rng = np.random.default_rng(11)
+    N, K = 24, 768
+    B = gen(rng, N, K)
+    plain = port.unpack(q, B, N, K) if q != "q6_K" else B
+    rb = plain.size // N
+    want = np.stack([port.dequantize_row(q, plain[r * rb:(r + 1) * rb], K) for r in range(N)])
+    got = be.dequantize_weight(q, dev(B), N, K).cpu().numpy()
+    assert np.array_equal(bits(got), bits(want))
+
+
+# ------------------------------------------------------------------- GEMV
+GEMV_SHAPES = [(8, 256), (16, 512), (72, 1024), (768, 2048), (2048, 768), (4096, 4096), (1024, 12288)]
+
+
+@pytest.mark.parametrize("q,gen", [("q4_K", O.random_q4_Kx8), ("q4_0", O.random_q4_0x8), ("q6_K", O.random_q6_K)])
+@pytest.mark.parametrize("N,K", GEMV_SHAPES)
+def test_gemv_matches_checker(be, port, q, gen, N, K):
+    rng = np.random.default_rng(N * 7 + K)
+    B = gen(rng, N, K)
+    x = acts(rng, 1, K)
+    want = port.gemm(q, x, B, N)[0]
+    y = torch.full((N,), float("nan"), device="cuda")
+    getattr(be, f"gemm_{q}")(1, N, K, dev(x), K, dev(B), N, y, N)
+    got = y.cpu().numpy()
+    assert max_rel(got, want) <= REL_TOL
+    assert np.array_equal(bits(got), bits(want)), "GEMV is expected to reproduce the reference bit for bit"
+
+
+@pytest.mark.parametrize("q", ["q4_K", "q4_0", "q6_K"])
+def test_gemv_golden(be, golden, q):
+    B = golden[f"{q}_x8"] if q != "q6_K" else golden[f"{q}_plain"]
+    y = torch.zeros(16, device="cuda")
+    getattr(be, f"gemm_{q}")(1, 16, 512, dev(golden["A"][:1]), 512, dev(B), 16, y, 16)
+    assert np.array_equal(bits(y.cpu().numpy()), bits(golden[f"{q}_gemv"][0]))
+
+
+@pytest.mark.parametrize("slices", [1, 2, 4, 8])
+def test_gemv_q4_K_every_k_split_gives_same_bits(be, port, slices, monkeypatch):
+    monkeypatch.setenv("NNTR_CUDA_GEMV_SLICES", str(slices))
+    rng = np.random.default_rng(slices)
+    N, K = 264, 2560  # 33 row groups, 10 super-blocks: ragged against 8 warps and against the slices
+    B = O.random_q4_Kx8(rng, N, K)
+    x = acts(rng, 1, K)
+    y = torch.zeros(N, device="cuda")
+    be.gemv("q4_K", N, K, dev(x), dev(B), y)
+    assert np.array_equal(bits(y.cpu().numpy()), bits(port.gemm("q4_K", x, B, N)[0]))
+
+
+def test_gemv_pdl_chain(be, port):
+    """A dependent chain y1 = W1 x, y2 = W2 y1, ... launched with programmatic
+    dependent launch gives the same bits as the checker's chain."""
+    rng = np.random.default_rng(5)
+    n = 1024
+    Ws = [O.random_q4_Kx8(rng, n, n) for _ in range(4)]
+    x = acts(rng, 1, n)
+    want = x
+    for W in Ws:
+        want = port.gemm("q4_K", want, W, n)
+    dW = [dev(W) for W in Ws]
+    bufs = [dev(x[0]), torch.zeros(n, device="cuda")]
+    for i, W in enumerate(dW):
+        be.gemv("q4_K", n, n, bufs[i % 2], W, bufs[(i + 1) % 2], pdl=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(bufs[len(dW) % 2].cpu().numpy()), bits(want[0]))
+
+
+# --------------------------------------------------------- host entry points
+@pytest.mark.parametrize("q,gen", [("q4_K", O.random_q4_Kx8), ("q4_0", O.random_q4_0x8), ("q6_K", O.random_q6_K)])
+def test_host_pointer_gemv_and_weight_cache(be, port, q, gen):
+    rng = np.random.default_rng(21)
+    N, K = 128, 1024
+    B = gen(rng, N, K)
+    x = acts(rng, 1, K)
+    want = port.gemm(q, x, B, N)
+    C1 = np.zeros((1, N), dtype=np.float32)
+    getattr(be, f"gemm_{q}")(1, N, K, x, K, B, N, C1, N)      # uploads B on first use
+    assert np.array_equal(bits(C1), bits(want))
+    # a row-slice of the same tensor (what an N-split shard or a thread's column range passes)
+    rb = B.size // N
+    C2 = np.zeros((1, N - 64), dtype=np.float32)
+    getattr(be, f"gemm_{q}")(1, N - 64, K, x, K, B[64 * rb:], N, C2, N - 64)
+    assert np.array_equal(bits(C2[0]), bits(want[0, 64:]))
+    be.unregister_weight(B)
+
+
+# ------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("q,gen", [("q4_K", O.random_q4_Kx8), ("q4_0", O.random_q4_0x8), ("q6_K", O.random_q6_K)])
+@pytest.mark.parametrize("M", [2, 3, 4, 5, 8, 13, 64, 67])
+def test_gemm_matches_checker(be, port, q, gen, M):
+    rng = np.random.default_rng(100 + M)
+    N, K = 136, 1024
+    B = gen(rng, N, K)
+    A = acts(rng, M, K)
+    want = port.gemm(q, A, B, N)
+    C = torch.full((M, N), float("nan"), device="cuda")
+    getattr(be, f"gemm_{q}")(M, N, K, dev(A), K, dev(B), N, C, N)
+    got = C.cpu().numpy()
+    assert max_rel(got, want) <= REL_TOL
+    assert np.array_equal(bits(got), bits(want)), "dp4a GEMM is expected to reproduce the reference bit for bit"
+
+
+@pytest.mark.parametrize("q", ["q4_K", "q4_0", "q6_K"])
+def test_gemm_golden(be, golden, q):
+    B = golden[f"{q}_x8"] if q != "q6_K" else golden[f"{q}_plain"]
+    A = golden["A"]
+    C = torch.zeros((6, 16), device="cuda")
+    getattr(be, f"gemm_{q}")(6, 16, 512, dev(A), 512, dev(B), 16, C, 16)
+    assert np.array_equal(bits(C.cpu().numpy()), bits(golden[f"{q}_gemm"]))
+
+
+def test_host_pointer_gemm_ldc_quirk(be, port):
+    """Host drop-in keeps the reference's strides: GEMM rows with ldc, the
+    leftover M%4 rows with stride N (ggml_interface_omp.cpp:463-491)."""
+    rng = np.random.default_rng(8)
+    M, N, K, ldc = 6, 16, 512, 24
+    B = O.random_q4_Kx8(rng, N, K)
+    A = acts(rng, M, K)
+    want = port.gemm("q4_K", A, B, N, ldc=ldc)
+    C = np.zeros((M, ldc), dtype=np.float32)
+    be.gemm_q4_K(M, N, K, A, K, B, N, C, ldc)
+    assert np.array_equal(bits(C), bits(want))
+    be.unregister_weight(B)
+
+
+# ------------------------------------------------- full-size property checks
+def test_full_size_gemv_linearity_in_weights_scale(be):
+    """cfg-sized GEMV (N=K=4096): doubling every fp16 block scale doubles the
+    output exactly (power-of-two scaling commutes with every rounding step)."""
+    rng = np.random.default_rng(0)
+    N = K = 4096
+    B = O.random_q4_Kx8(rng, N, K).reshape(-1, 1152)
+    B2 = B.copy()
+    h = B2[:, :32].view(np.float16)
+    h *= 2
+    x = dev(rng.standard_normal(K).astype(np.float32))
+    y1 = torch.zeros(N, device="cuda")
+    y2 = torch.zeros(N, device="cuda")
+    be.gemv("q4_K", N, K, x, dev(B.reshape(-1)), y1)
+    be.gemv("q4_K", N, K, x, dev(B2.reshape(-1)), y2)
+    assert torch.equal(y2, 2 * y1)
+    assert torch.isfinite(y1).all() and float(y1.abs().max()) > 0
+
+
+def test_full_size_gemv_row_permutation(be):
+    """Permuting row GROUPS of the weight permutes the outputs the same way."""
+    rng = np.random.default_rng(1)
+    N = K = 4096
+    B = O.random_q4_Kx8(rng, N, K).reshape(N // 8, -1)
+    perm = rng.permutation(N // 8)
+    x = dev(rng.standard_normal(K).astype(np.float32))
+    y1 = torch.zeros(N, device="cuda")
+    y2 = torch.zeros(N, device="cuda")
+    be.gemv("q4_K", N, K, x, dev(B.reshape(-1)), y1)
+    be.gemv("q4_K", N, K, x, dev(B[perm].reshape(-1)), y2)
+    assert torch.equal(y2.view(N // 8, 8), y1.view(N // 8, 8)[torch.from_numpy(perm).cuda()])
