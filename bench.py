@@ -337,9 +337,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer end-to-end leg (profiling runs)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--ring", type=int, default=RING, help="distinct weight matrices per step (default keeps every launch out of L2)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the GEMV kernel from an ncu capture (reported as roofline.traffic)")
     args = ap.parse_args()
+    globals()["RING"] = args.ring
     if args.impl == "reference":
         run_reference(args)
     else:

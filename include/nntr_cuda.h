@@ -68,6 +68,11 @@ const char *nntr_cuda_last_error(void);
 int nntr_cuda_sm_count(void);
 /** How many kernels of this library have been launched by this process. */
 uint64_t nntr_cuda_launch_count(void);
+/** Synchronizes the device, then reports whether any kernel of this library
+ *  gave up on one of its bounded waits (every device-side wait has an iteration
+ *  limit; on expiry the kernel raises a status word and returns instead of
+ *  hanging): NNTR_CUDA_OK, or NNTR_CUDA_ERR_TIMEOUT. */
+int nntr_cuda_device_status(void);
 
 /* ---------------------------------------------- device-pointer entry points */
 

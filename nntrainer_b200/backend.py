@@ -29,6 +29,11 @@ def init(device: int = 0) -> None:
     check(lib().nntr_cuda_init(device))
 
 
+def device_status() -> None:
+    """Synchronize, then raise TimeoutError if a kernel gave up on a bounded wait."""
+    check(lib().nntr_cuda_device_status())
+
+
 def launch_count() -> int:
     return int(lib().nntr_cuda_launch_count())
 

@@ -35,6 +35,7 @@ SIGNATURES = {
     "nntr_cuda_last_error": (C.c_char_p, []),
     "nntr_cuda_sm_count": (_i, []),
     "nntr_cuda_launch_count": (C.c_uint64, []),
+    "nntr_cuda_device_status": (_i, []),
     "nntr_cuda_quantize_q8_K_dev": (_i, [_vp, _i64, _vp, _i64, _i64, _i, _vp]),
     "nntr_cuda_quantize_q8_0_dev": (_i, [_vp, _i64, _vp, _i64, _i64, _vp]),
     "nntr_cuda_dequantize_row_dev": (_i, [_i, _vp, _vp, _i64, _vp]),

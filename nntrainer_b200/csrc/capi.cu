@@ -298,6 +298,17 @@ const char *nntr_cuda_last_error(void) { return tl_error; }
 int nntr_cuda_sm_count(void) { return sm_count(); }
 uint64_t nntr_cuda_launch_count(void) { return g_launches.load(); }
 
+int nntr_cuda_device_status(void) {
+  NNTR_CHECK_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  int rc = read_device_status(&v);
+  if (rc)
+    return rc;
+  if (v)
+    return set_error(v, "a device kernel gave up on a bounded wait (status %d)", v);
+  return NNTR_CUDA_OK;
+}
+
 int nntr_cuda_quantize_q8_K_dev(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, int rule, void *stream) {
   return launch_quantize_q8_K(x, ldx, y, rows, k, rule, static_cast<cudaStream_t>(stream));
 }

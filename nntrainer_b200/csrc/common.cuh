@@ -66,6 +66,8 @@ int set_error(int code, const char *fmt, ...);
 int check_cuda(cudaError_t e, const char *what);
 void count_launch(unsigned n = 1);
 int sm_count();
+/** reads (and leaves) the status word device kernels raise when a bounded wait expires */
+int read_device_status(int *out);
 
 #define NNTR_CHECK_CUDA(expr)                                                                                          \
   do {                                                                                                                 \

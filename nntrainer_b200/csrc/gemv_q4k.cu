@@ -15,198 +15,350 @@
  *
  * Roofline: HBM. Algorithmic bytes = N*K*4.5/8 (weights, read once) + 4K + 4N.
  * Data layout in HBM is the tensor's own: for each group of 8 output rows,
- * K/256 consecutive block_q4_Kx8 of 1152 B.
+ * K/256 consecutive block_q4_Kx8 of 1152 B, so a CTA's share (a run of whole
+ * row groups) is one contiguous byte range.
  *
- * Work split: a warp owns (row group g, slice s of the K range); a CTA of 8
- * warps owns 8/slices groups per pass. A lane owns one output row r = lane%8
- * and one sub-block pair c = lane/8 of every super-block: four coalesced 8-byte
- * loads per lane per block, straight to registers, issued one block ahead. The
- * first block's loads are issued before the activation is touched, so under
- * programmatic dependent launch they overlap the previous kernel's tail.
+ * Structure (persistent CTAs of 18 warps, one or two per SM):
+ *   - warp 16: streams the CTA's byte range into a ring of 8 stages of 8 blocks
+ *     with bulk async copies (cp.async.bulk, one per block so that blocks sit
+ *     1216 B apart in shared memory and adjacent ones use opposite bank halves;
+ *     completion on an mbarrier per stage). It starts before the activation is
+ *     touched, so under programmatic dependent launch the weight stream overlaps
+ *     the previous kernel; with <= 64 blocks per CTA the whole share is in flight
+ *     at once.
+ *   - warps 0-15: quantize x into shared memory (every CTA redundantly), then
+ *     each warp takes four consecutive blocks per step: lane = (block lane/8,
+ *     row lane%8) owns one whole row of one block -- 256 weights, 64 dp4a, the
+ *     row's eight 6-bit scales and mins -- so no cross-lane reduction is needed.
+ *   - warp 17: when all K/256 blocks of a row group are done (mbarrier), runs
+ *     the ordered float chain for its 8 outputs and stores them; its four
+ *     8-lane groups serve four row groups at a time.
+ * Every wait is bounded: on expiry the kernel raises a status word and leaves.
  */
 #include "common.cuh"
 
 namespace nntr {
 
-constexpr int GEMV_WARPS = 8;
-constexpr int AQ_STRIDE = 288; // 256 quantized activations + 32 B of padding (bank spreading)
-
-/* position of sub-block pair c inside a padded activation block */
-__device__ __forceinline__ int aq_off(int c) { return 64 * c + 16 * (c >> 1); }
-
-/* bytes of the activation part of shared memory, rounded up to 16 */
-__host__ __device__ inline size_t act_smem_bytes(int nb) { return (((size_t)nb * (AQ_STRIDE + 32 + 4)) + 15) & ~(size_t)15; }
-
-struct WBlock { // one lane's share of a block_q4_Kx8
-  uint2 q[4];   // nibble chunks 4c..4c+3 of row r
-  uint32_t hw;  // header word `lane`: 0-3 d[8], 4-7 dmin[8], 8-31 scales[96]
-};
-
-__device__ __forceinline__ WBlock load_wblock(const BlockQ4Kx8 *blk, int lane) {
-  WBlock w;
-  const uint8_t *base = reinterpret_cast<const uint8_t *>(blk);
-  const int r = lane & 7, c = lane >> 3;
-  w.hw = ldg_stream_u32(base + 4 * lane);
-#pragma unroll
-  for (int k = 0; k < 4; ++k)
-    w.q[k] = ldg_stream_u2(base + 128 + ((4 * c + k) * 8 + r) * 8);
-  return w;
-}
-
-/** Integer sums of one super-block for the lane's row, reduced over the four
- *  lanes that share the row. Also returns d_w and dmin_w of the row. */
-__device__ __forceinline__ void block_sums(const WBlock &w, const uint8_t *aq_blk, const int *bs2_blk, int lane, int &I,
-                                           int &J, float &dw, float &dminw) {
-  const int r = lane & 7, c = lane >> 3;
-  // ---- unpack the 6-bit scales: lane t rebuilds word (t&3) of sub-block t>>2
-  const int usb = lane >> 2, which = lane & 3;
-  const uint32_t w0 = __shfl_sync(FULL, w.hw, 8 + 3 * usb);
-  const uint32_t w1 = __shfl_sync(FULL, w.hw, 9 + 3 * usb);
-  const uint32_t w2 = __shfl_sync(FULL, w.hw, 10 + 3 * usb);
-  uint32_t u;
-  if (which == 0)
-    u = w0 & 0x3f3f3f3fu; // scales, rows 0-3
-  else if (which == 1)
-    u = (w2 & 0x0f0f0f0fu) | (((w0 >> 6) & 0x03030303u) << 4); // scales, rows 4-7
-  else if (which == 2)
-    u = w1 & 0x3f3f3f3fu; // mins, rows 0-3
-  else
-    u = ((w2 >> 4) & 0x0f0f0f0fu) | (((w1 >> 6) & 0x03030303u) << 4); // mins, rows 4-7
-  const int src = 8 * c + (r >> 2), sh = 8 * (r & 3);
-  const int sc_lo = (__shfl_sync(FULL, u, src) >> sh) & 0xff;     // sub-block 2c
-  const int sc_hi = (__shfl_sync(FULL, u, src + 4) >> sh) & 0xff; // sub-block 2c+1
-  const int m_lo = (__shfl_sync(FULL, u, src + 2) >> sh) & 0xff;
-  const int m_hi = (__shfl_sync(FULL, u, src + 6) >> sh) & 0xff;
-  const uint32_t dword = __shfl_sync(FULL, w.hw, r >> 1);
-  const uint32_t mword = __shfl_sync(FULL, w.hw, 4 + (r >> 1));
-  dw = half_bits_to_float((uint16_t)((r & 1) ? (dword >> 16) : (dword & 0xffff)));
-  dminw = half_bits_to_float((uint16_t)((r & 1) ? (mword >> 16) : (mword & 0xffff)));
-
-  // ---- 4-bit x 8-bit dot products of the lane's 64 weights
-  const uint4 *a = reinterpret_cast<const uint4 *>(aq_blk + aq_off(c));
-  const uint4 L0 = a[0], L1 = a[1], H0 = a[2], H1 = a[3];
-  const uint32_t lo[8] = {L0.x, L0.y, L0.z, L0.w, L1.x, L1.y, L1.z, L1.w};
-  const uint32_t hi[8] = {H0.x, H0.y, H0.z, H0.w, H1.x, H1.y, H1.z, H1.w};
-  int dlo = 0, dhi = 0;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    dlo = __dp4a((int)(w.q[k].x & 0x0f0f0f0fu), (int)lo[2 * k], dlo);
-    dlo = __dp4a((int)(w.q[k].y & 0x0f0f0f0fu), (int)lo[2 * k + 1], dlo);
-    dhi = __dp4a((int)((w.q[k].x >> 4) & 0x0f0f0f0fu), (int)hi[2 * k], dhi);
-    dhi = __dp4a((int)((w.q[k].y >> 4) & 0x0f0f0f0fu), (int)hi[2 * k + 1], dhi);
+#ifdef NNTR_TRACE
+/* development aid: per-CTA time stamps of the kernel's phases (off in the library build) */
+__device__ unsigned long long *g_trace = nullptr;
+__device__ __forceinline__ void trace_stamp(int slot) {
+  if (g_trace && (threadIdx.x & 31) == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_trace[blockIdx.x * 8 + slot] = t;
   }
-  const int2 bs = *reinterpret_cast<const int2 *>(bs2_blk + 2 * c);
-  const unsigned peers = 0x01010101u << r;
-  I = __reduce_add_sync(peers, sc_lo * dlo + sc_hi * dhi);
-  J = __reduce_add_sync(peers, m_lo * bs.x + m_hi * bs.y);
+}
+/* fine-grained: clock64 stamps of warp 0 of CTA 0 */
+__device__ long long g_fine[64];
+__device__ __forceinline__ void fine_stamp(int i) {
+  if (blockIdx.x == 0 && threadIdx.x == 0 && i < 64)
+    g_fine[i] = clock64();
+}
+#else
+__device__ __forceinline__ void trace_stamp(int) {}
+__device__ __forceinline__ void fine_stamp(int) {}
+#endif
+
+/** raised (non-zero) by a kernel whose bounded wait expired */
+__device__ int g_device_status = 0;
+
+constexpr int CONSUMER_WARPS = 16;
+constexpr int PRODUCER_WARP = 16;
+constexpr int EPILOGUE_WARP = 17;
+constexpr int GEMV_THREADS = 18 * 32;
+constexpr int NSTAGE = 8;       // ring depth
+constexpr int STAGE_BLOCKS = 8; // blocks per stage = two consumer warps
+constexpr int BLK_BYTES = (int)sizeof(BlockQ4Kx8);
+constexpr int BLK_STRIDE = BLK_BYTES + 64; // 304 words = 16 mod 32 banks: adjacent blocks use opposite bank halves
+constexpr int STAGE_BYTES = STAGE_BLOCKS * BLK_STRIDE;
+constexpr int STEP_BLOCKS = 4 * CONSUMER_WARPS; // blocks the CTA consumes per step (= the whole ring)
+constexpr int ACT_STRIDE = 288; // per 256 activations: 256 B q8 | 8 x int16 sums of 32 | fp32 d | pad
+static_assert(NSTAGE * STAGE_BLOCKS == STEP_BLOCKS, "a consumer warp always reads the same ring slot");
+constexpr uint32_t WAIT_POLLS = 1u << 22;
+
+struct SmemLayout {
+  uint32_t ring, act, part, bars, abort_flag, total;
+};
+/* ngslot: row groups whose partial results may be pending at once (power of two) */
+__host__ __device__ inline SmemLayout smem_layout(int nb, int ngslot) {
+  SmemLayout L;
+  uint32_t o = 0;
+  L.ring = o;
+  o += NSTAGE * STAGE_BYTES;
+  L.act = o;
+  o += nb * ACT_STRIDE;
+  L.part = o;
+  o += ngslot * nb * 8 * 16;
+  L.bars = o; // full[NSTAGE], empty[NSTAGE], done[ngslot], free[ngslot]
+  o += (2 * NSTAGE + 2 * ngslot) * 8;
+  L.abort_flag = o;
+  o += 16;
+  L.total = o;
+  return L;
+}
+__host__ __device__ inline int pick_ngslot(int nb) {
+  int want = STEP_BLOCKS / nb + 3, n = 4;
+  while (n < want && n < 128)
+    n *= 2;
+  return n;
 }
 
-/**
- * Shared memory (dynamic):
- *   aq   [nb][288]  quantized activation, padded
- *   bs2  [nb][8]    sums of 32 quantized activations (bsums[2s]+bsums[2s+1])
- *   ad   [nb]       fp32 block scales
- *   part [2][gpc*nb*8] float4 {I, d_w*d_a, J, dmin_w*d_a}   (slices > 1 only)
- */
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+/* ---- mbarrier / bulk-copy primitives (shared::cta addresses as 32-bit) ---- */
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+/** Bounded wait. Returns false (and raises the CTA's abort flag and the device
+ *  status word) if the phase did not complete within WAIT_POLLS polls. */
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  for (uint32_t it = 0; it < WAIT_POLLS; ++it) {
+    if (mbar_try_wait(bar, parity))
+      return true;
+    if (it > 1024) {
+      if (*abort_flag)
+        return false;
+      __nanosleep(32);
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(&g_device_status, NNTR_CUDA_ERR_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void consumer_bar_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+}
+
+/** 4-way dot product of unsigned bytes (a) with signed bytes (b), accumulated in c */
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+/** Integer sums of one super-block (in shared memory at blk) for output row r:
+ *      I = sum_sb sc*dot32,  J = sum_sb m*bsum32.
+ *  act points at the 256 quantized activations of the same super-block, followed
+ *  by their eight sums of 32 as int16. The 12-byte scale groups pack 8 scales +
+ *  8 mins in 6 bits with the ROW in the role get_scale_min_k4
+ *  (nntr_ggml_impl_quant.cpp:368-378) gives the sub-block: rows 0-3 are plain
+ *  6-bit fields, rows 4-7 are split 4 + 2 bits over two bytes. */
+__device__ __forceinline__ void row_block_sums(const uint8_t *blk, const uint8_t *act, int r, int &I, int &J) {
+  const bool hi_row = r >= 4;
+  const uint32_t rb = r & 3;
+  const uint32_t sel = rb | ((4u + rb) << 4) | 0x3200u; // byte rb of each operand into bytes 0 and 1
+  const uint32_t ma = hi_row ? 0x0f0fu : 0x3f3fu, mb = hi_row ? 0x3030u : 0u;
+  const uint4 bsv = *reinterpret_cast<const uint4 *>(act + 256); // 8 x int16: sums of 32 activations
+  const uint32_t bs2[4] = {bsv.x, bsv.y, bsv.z, bsv.w};
+  int i_acc = 0, j_acc = 0;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) { // sub-blocks 2p (low nibbles) and 2p+1 (high nibbles) of 64 weights
+    const uint2 s0 = *reinterpret_cast<const uint2 *>(blk + 32 + 24 * p);
+    const uint2 s1 = *reinterpret_cast<const uint2 *>(blk + 32 + 24 * p + 8);
+    const uint2 s2 = *reinterpret_cast<const uint2 *>(blk + 32 + 24 * p + 16);
+    // group 2p = words (s0.x, s0.y, s1.x), group 2p+1 = (s1.y, s2.x, s2.y)
+    const uint32_t U = __byte_perm(s0.x, s1.y, sel), V = __byte_perm(s0.y, s2.x, sel), Wd = __byte_perm(s1.x, s2.y, sel);
+    const uint32_t S = hi_row ? Wd : U, T = hi_row ? (Wd >> 4) : V;
+    const uint32_t sc2 = (S & ma) | ((U >> 2) & mb); // byte 0: scale of 2p, byte 1: scale of 2p+1
+    const uint32_t m2 = (T & ma) | ((V >> 2) & mb);  // same for the mins
+    const uint4 *a = reinterpret_cast<const uint4 *>(act + 64 * p);
+    const uint4 L0 = a[0], L1 = a[1], H0 = a[2], H1 = a[3];
+    const uint32_t lo[8] = {L0.x, L0.y, L0.z, L0.w, L1.x, L1.y, L1.z, L1.w};
+    const uint32_t hi[8] = {H0.x, H0.y, H0.z, H0.w, H1.x, H1.y, H1.z, H1.w};
+    int dlo = 0;
+    int dhi16 = 0; // 16 x the high-nibble dot product (u8 x s8 with the nibble left in place)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint2 q = *reinterpret_cast<const uint2 *>(blk + 128 + (4 * p + k) * 64 + 8 * r);
+      dlo = __dp4a((int)(q.x & 0x0f0f0f0fu), (int)lo[2 * k], dlo);
+      dlo = __dp4a((int)(q.y & 0x0f0f0f0fu), (int)lo[2 * k + 1], dlo);
+      dhi16 = dp4a_us(q.x & 0xf0f0f0f0u, hi[2 * k], dhi16);
+      dhi16 = dp4a_us(q.y & 0xf0f0f0f0u, hi[2 * k + 1], dhi16);
+    }
+    i_acc += (int)(sc2 & 0xff) * dlo + (int)(sc2 >> 8) * (dhi16 >> 4);
+    j_acc = __dp2a_lo((int)bs2[p], (int)m2, j_acc);
+  }
+  I = i_acc;
+  J = j_acc;
+}
+
+__global__ void __launch_bounds__(GEMV_THREADS, 2)
 gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, float *__restrict__ y, int n_groups,
-                 int nb, int slices, int bps) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  uint8_t *aq = smem;
-  int *bs2 = reinterpret_cast<int *>(smem + (size_t)nb * AQ_STRIDE);
-  float *ad = reinterpret_cast<float *>(bs2 + (size_t)nb * 8);
-  float4 *part = reinterpret_cast<float4 *>(smem + act_smem_bytes(nb));
+                 int nb, int ngslot) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const SmemLayout L = smem_layout(nb, ngslot);
+  uint8_t *ring = smem + L.ring;
+  uint8_t *act = smem + L.act;
+  float4 *part = reinterpret_cast<float4 *>(smem + L.part);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
+  const uint32_t bars = smem_u32(smem + L.bars);
+  const uint32_t full0 = bars, empty0 = bars + 8 * NSTAGE, done0 = bars + 16 * NSTAGE,
+                 free0 = bars + 16 * NSTAGE + 8 * ngslot;
+  const int slot_mask = ngslot - 1;
+  const int slot_shift = 31 - __clz(ngslot);
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int gpc = GEMV_WARPS / slices; // groups per CTA pass
-  const int gl = warp / slices, s = warp - gl * slices;
-  const int b0 = min(s * bps, nb), b1 = min(b0 + bps, nb);
-  const int nbw = b1 - b0;
-  const int passes = (n_groups + gpc * (int)gridDim.x - 1) / (gpc * (int)gridDim.x);
+  // the CTA's share: a contiguous run of whole row groups
+  const int g_first = (int)(((long long)blockIdx.x * n_groups) / gridDim.x);
+  const int g_end = (int)(((long long)(blockIdx.x + 1) * n_groups) / gridDim.x);
+  const int ng = g_end - g_first;
+  const int total_blocks = ng * nb;
+  const int total_stages = (total_blocks + STAGE_BLOCKS - 1) / STAGE_BLOCKS;
+  const uint8_t *src = reinterpret_cast<const uint8_t *>(W + (size_t)g_first * nb);
 
-  // ---- issue the first weight block before anything that depends on x
-  int g = (int)blockIdx.x * gpc + gl;
-  WBlock cur;
-  const bool have0 = nbw > 0 && g < n_groups;
-  if (have0)
-    cur = load_wblock(W + (size_t)g * nb + b0, lane);
-  pdl_launch_dependents();
-  pdl_wait();
-
-  // ---- quantize the activation into shared memory (every CTA does all of it)
-  for (int b = warp; b < nb; b += GEMV_WARPS) {
-    const float *src = x + (size_t)b * QK_K + lane * 8;
-    const float4 v0 = *reinterpret_cast<const float4 *>(src);
-    const float4 v1 = *reinterpret_cast<const float4 *>(src + 4);
-    const Q8KLane q = q8K_quantize_warp(v0, v1, lane, 0);
-    // lane owns elements 8*lane..+7 -> sub-block pair (lane>>3), byte 8*(lane&7) inside it
-    uint2 *dst = reinterpret_cast<uint2 *>(aq + (size_t)b * AQ_STRIDE + aq_off(lane >> 3) + 8 * (lane & 7));
-    *dst = make_uint2(q.w0, q.w1);
-    int s32 = q.sum8 + __shfl_xor_sync(FULL, q.sum8, 1);
-    s32 += __shfl_xor_sync(FULL, s32, 2);
-    if ((lane & 3) == 0)
-      bs2[b * 8 + (lane >> 2)] = s32;
-    if (lane == 0)
-      ad[b] = q.d;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < NSTAGE; ++i) {
+      mbar_init(full0 + 8 * i, 1);
+      mbar_init(empty0 + 8 * i, 2); // the two warps that read a stage
+    }
+    for (int i = 0; i < ngslot; ++i) {
+      mbar_init(done0 + 8 * i, nb); // one arrival per block of the row group
+      mbar_init(free0 + 8 * i, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  trace_stamp(0);
+  pdl_launch_dependents();
 
-  int buf = 0;
-  for (int pass = 0; pass < passes; ++pass) {
-    g = ((int)blockIdx.x + pass * (int)gridDim.x) * gpc + gl;
-    const int g_next = g + (int)gridDim.x * gpc;
-    float acc = 0.f, accm = 0.f;
-    if (g < n_groups) {
-      for (int j = 0; j < nbw; ++j) {
-        // prefetch the next block of this slice, or the first block of the next pass
-        WBlock nxt;
-        const bool more = (j + 1 < nbw);
-        const bool wrap = !more && (pass + 1 < passes) && (g_next < n_groups);
-        if (more)
-          nxt = load_wblock(W + (size_t)g * nb + b0 + j + 1, lane);
-        else if (wrap)
-          nxt = load_wblock(W + (size_t)g_next * nb + b0, lane);
-        const int b = b0 + j;
-        int I, J;
-        float dw, dminw;
-        block_sums(cur, aq + (size_t)b * AQ_STRIDE, bs2 + b * 8, lane, I, J, dw, dminw);
-        if (lane < 8) {
-          const float da = ad[b];
-          const float sd = __fmul_rn(dw, da), sm = __fmul_rn(dminw, da);
-          if (slices == 1) {
-            acc = __fmaf_rn((float)I, sd, acc);
-            accm = __fmaf_rn((float)J, sm, accm);
-          } else {
-            part[(size_t)buf * gpc * nb * 8 + ((size_t)gl * nb + b) * 8 + lane] =
-              make_float4((float)I, sd, (float)J, sm);
-          }
-        }
-        if (more || wrap)
-          cur = nxt;
+  if (warp == PRODUCER_WARP) {
+    // ------------------------------------------------------------ producer
+    // one bulk copy per block, so that blocks land BLK_STRIDE apart
+    int q = 0;
+    bool ok = true;
+    for (; q < total_stages; ++q) {
+      const int st = q % NSTAGE;
+      if (q >= NSTAGE) {
+        if (lane == 0)
+          ok = mbar_wait(empty0 + 8 * st, ((q / NSTAGE) - 1) & 1, abort_flag);
+        ok = __shfl_sync(FULL, ok, 0);
+        if (!ok)
+          break;
       }
-      if (slices == 1 && lane < 8)
-        y[(size_t)g * 8 + lane] = __fsub_rn(acc, accm);
+      const int nblk = min(STAGE_BLOCKS, total_blocks - q * STAGE_BLOCKS);
+      if (lane == 0)
+        mbar_expect_tx(full0 + 8 * st, nblk * BLK_BYTES);
+      __syncwarp();
+      if (lane < nblk)
+        bulk_g2s(smem_u32(ring + st * STAGE_BYTES + lane * BLK_STRIDE),
+                 src + ((size_t)q * STAGE_BLOCKS + lane) * BLK_BYTES, BLK_BYTES, full0 + 8 * st);
     }
-    if (slices > 1) {
-      __syncthreads();
-      // ordered float chain: one thread per output of this pass
-      const int t = threadIdx.x;
-      if (t < gpc * 8) {
-        const int cg = ((int)blockIdx.x + pass * (int)gridDim.x) * gpc + (t >> 3);
-        if (cg < n_groups) {
-          const float4 *p = part + (size_t)buf * gpc * nb * 8 + (size_t)(t >> 3) * nb * 8 + (t & 7);
+    if (!ok && lane == 0) {
+      // leave only after the copies already issued have landed (bounded)
+      for (int i = max(0, q - NSTAGE); i < q; ++i)
+        mbar_wait(full0 + 8 * (i % NSTAGE), (i / NSTAGE) & 1, abort_flag);
+    }
+  } else if (warp == EPILOGUE_WARP) {
+    // ------------------------------------------------------------ epilogue
+    pdl_wait(); // y may still be read by the previous kernel until it has finished
+    const int j = lane >> 3, r = lane & 7;
+    for (int gl0 = 0; gl0 < ng; gl0 += 4) {
+      const int gl = gl0 + j;
+      if (gl < ng) {
+        const int slot = gl & slot_mask;
+        if (mbar_wait(done0 + 8 * slot, (gl >> slot_shift) & 1, abort_flag)) {
+          const float4 *p = part + (size_t)slot * nb * 8 + r;
           float a0 = 0.f, a1 = 0.f;
-#pragma unroll 4
+#pragma unroll 8
           for (int b = 0; b < nb; ++b) {
-            const float4 v = p[(size_t)b * 8];
+            const float4 v = p[b * 8];
             a0 = __fmaf_rn(v.x, v.y, a0);
             a1 = __fmaf_rn(v.z, v.w, a1);
           }
-          y[(size_t)cg * 8 + (t & 7)] = __fsub_rn(a0, a1);
+          y[(size_t)(g_first + gl) * 8 + r] = __fsub_rn(a0, a1);
         }
       }
-      buf ^= 1;
+      __syncwarp();
+      if (r == 0 && gl < ng)
+        mbar_arrive(free0 + 8 * (gl & slot_mask));
+      if (*abort_flag)
+        break;
     }
+    trace_stamp(5);
+  } else {
+    // ----------------------------------------------------------- consumers
+    pdl_wait();
+    trace_stamp(2);
+    for (int b = warp; b < nb; b += CONSUMER_WARPS) {
+      const float *xs = x + b * QK_K + lane * 8;
+      const float4 v0 = *reinterpret_cast<const float4 *>(xs);
+      const float4 v1 = *reinterpret_cast<const float4 *>(xs + 4);
+      const Q8KLane qv = q8K_quantize_warp(v0, v1, lane, 0);
+      uint8_t *dst = act + b * ACT_STRIDE;
+      *reinterpret_cast<uint2 *>(dst + 8 * lane) = make_uint2(qv.w0, qv.w1);
+      int s32 = qv.sum8 + __shfl_xor_sync(FULL, qv.sum8, 1);
+      s32 += __shfl_xor_sync(FULL, s32, 2);
+      if ((lane & 3) == 0)
+        *reinterpret_cast<int16_t *>(dst + 256 + 2 * (lane >> 2)) = (int16_t)s32;
+      if (lane == 0)
+        *reinterpret_cast<float *>(dst + 272) = qv.d;
+    }
+    consumer_bar_sync();
+    trace_stamp(3);
+
+    const int j = lane >> 3, r = lane & 7;
+    const int st = warp >> 1;                // this warp's ring slot, every step
+    const int in_stage = (warp & 1) * 4 + j; // the lane's block inside the stage
+    int t = warp * 4 + j;                    // flat block index inside the CTA's share
+    int gl = t / nb, b = t - gl * nb;
+    const int q64 = STEP_BLOCKS / nb, r64 = STEP_BLOCKS - q64 * nb;
+    for (int step = 0; step * NSTAGE + st < total_stages; ++step) {
+      if (!mbar_wait(full0 + 8 * st, step & 1, abort_flag))
+        break;
+      bool ok = true;
+      if (t < total_blocks) {
+        const int slot = gl & slot_mask;
+        if (gl >= ngslot)
+          ok = mbar_wait(free0 + 8 * slot, ((gl >> slot_shift) - 1) & 1, abort_flag);
+        if (ok) {
+          const uint8_t *blk = ring + st * STAGE_BYTES + in_stage * BLK_STRIDE;
+          const uint8_t *a = act + b * ACT_STRIDE;
+          int I, J;
+          row_block_sums(blk, a, r, I, J);
+          const float da = *reinterpret_cast<const float *>(a + 272);
+          const float dw = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk + 2 * r));
+          const float dmw = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk + 16 + 2 * r));
+          part[((size_t)slot * nb + b) * 8 + r] = make_float4((float)I, __fmul_rn(dw, da), (float)J, __fmul_rn(dmw, da));
+        }
+      }
+      __syncwarp();
+      if (r == 0 && t < total_blocks && ok)
+        mbar_arrive(done0 + 8 * (gl & slot_mask));
+      if (lane == 0)
+        mbar_arrive(empty0 + 8 * st);
+      if (!__all_sync(FULL, ok))
+        break;
+      t += STEP_BLOCKS;
+      b += r64;
+      gl += q64;
+      if (b >= nb) {
+        b -= nb;
+        ++gl;
+      }
+    }
+    trace_stamp(4);
   }
 }
 
@@ -225,35 +377,30 @@ int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, floa
   if (N == 0)
     return NNTR_CUDA_OK;
   const int n_groups = (int)(N / 8), nb = (int)(K / QK_K), sms = sm_count();
-  // K slices per row group: enough warp tasks to fill the machine
-  int slices = 1;
-  while (slices < GEMV_WARPS && (long)n_groups * slices < 16L * sms && nb / (slices * 2) >= 1)
-    slices *= 2;
-  const int forced = env_int("NNTR_CUDA_GEMV_SLICES", 0);
-  if (forced == 1 || forced == 2 || forced == 4 || forced == 8)
-    slices = forced;
-  const int bps = (nb + slices - 1) / slices;
-  const int gpc = GEMV_WARPS / slices;
-  size_t smem = act_smem_bytes(nb);
-  if (slices > 1)
-    smem += 2ull * gpc * nb * 8 * sizeof(float4);
-  if (smem > 200 * 1024)
-    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_q4_K: K=%u needs %zu B of shared memory", K, smem);
-  static bool attr_done[64] = {false};
+  const int ngslot = pick_ngslot(nb);
+  const SmemLayout L = smem_layout(nb, ngslot);
+  if (L.total > 200 * 1024)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_q4_K: K=%u needs %u B of shared memory", K, L.total);
+  static bool attr_done[64] = {};
   int dev = 0;
   NNTR_CHECK_CUDA(cudaGetDevice(&dev));
-  if (smem > 48 * 1024 && !attr_done[dev & 63]) {
+  if (!attr_done[dev & 63]) {
     NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_done[dev & 63] = true;
   }
-  const int ctas_needed = (n_groups + gpc - 1) / gpc;
-  const int max_ctas = sms * env_int("NNTR_CUDA_GEMV_CTAS_PER_SM", 4);
-  const unsigned grid = (unsigned)(ctas_needed < max_ctas ? ctas_needed : max_ctas);
+  // A share that fits the ring (one step per warp) runs one CTA per SM and leaves
+  // room for the next kernel's CTAs under programmatic dependent launch; longer
+  // streams run two CTAs per SM: 32 consumer warps and 16 stages in flight per SM.
+  const long blocks_per_sm = ((long)n_groups * nb + sms - 1) / sms;
+  const bool two_fit = 2u * L.total <= 220u * 1024u;
+  const int per_sm = env_int("NNTR_CUDA_GEMV_CTAS_PER_SM", (blocks_per_sm > STEP_BLOCKS && two_fit) ? 2 : 1);
+  const int max_ctas = sms * per_sm;
+  const unsigned grid = (unsigned)(n_groups < max_ctas ? n_groups : max_ctas);
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(GEMV_WARPS * 32);
-  cfg.dynamicSmemBytes = smem;
+  cfg.blockDim = dim3(GEMV_THREADS);
+  cfg.dynamicSmemBytes = L.total;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -261,9 +408,16 @@ int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, floa
   cfg.attrs = attr;
   cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
   const BlockQ4Kx8 *Wp = static_cast<const BlockQ4Kx8 *>(B);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel, x, Wp, y, n_groups, nb, slices, bps);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel, x, Wp, y, n_groups, nb, ngslot);
   count_launch();
   return check_cuda(e, "gemv_q4_K launch");
+}
+
+int read_device_status(int *out) {
+  int v = 0;
+  NNTR_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
+  *out = v;
+  return NNTR_CUDA_OK;
 }
 
 } // namespace nntr
