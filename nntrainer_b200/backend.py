@@ -130,7 +130,8 @@ def quantize_q8_K_dev(x, rule: int = 0):
     torch = _torch()
     rows, k = x.shape
     y = torch.zeros(rows * (k // 256) * 292, dtype=torch.uint8, device=x.device)
-    check(lib().nntr_cuda_quantize_q8_K_dev(x.data_ptr(), x.stride(0), y.data_ptr(), rows, k, rule, _stream()))
+    check(lib().nntr_cuda_quantize_q8_K_dev(x.data_ptr(), x.stride(0) if rows > 1 else k, y.data_ptr(), rows, k, rule,
+                                            _stream()))
     return y
 
 
@@ -138,7 +139,7 @@ def quantize_q8_0_dev(x):
     torch = _torch()
     rows, k = x.shape
     y = torch.zeros(rows * (k // 32) * 34, dtype=torch.uint8, device=x.device)
-    check(lib().nntr_cuda_quantize_q8_0_dev(x.data_ptr(), x.stride(0), y.data_ptr(), rows, k, _stream()))
+    check(lib().nntr_cuda_quantize_q8_0_dev(x.data_ptr(), x.stride(0) if rows > 1 else k, y.data_ptr(), rows, k, _stream()))
     return y
 
 

@@ -547,15 +547,19 @@ int port_gemm_q4_K(unsigned M, unsigned N, unsigned K, const float *A, unsigned 
   const unsigned M4 = (M == 1) ? 0 : (M / 4) * 4;
   for (unsigned m = 0; m < M; ++m)
     port_quantize_row_q8_K_rule(A + (size_t)m * K, qa + (size_t)m * nb, K, m < M4 ? 1 : 0);
+  /* the reference finishes all GEMM rows before it writes the leftover rows
+   * (which may overlap them when ldc > N), so keep that order */
 #pragma omp parallel for schedule(static)
   for (int64_t n = 0; n < (int64_t)N; ++n) {
     const blk_q4_Kx8 *wg = w + (n / 8) * nb;
-    for (unsigned m = 0; m < M; ++m) {
-      if (m < M4)
-        C[(size_t)m * ldc + n] = q4K_gemm_chain(wg, nb, (int)(n % 8), qa + (size_t)m * nb);
-      else
-        C[(size_t)m * N + n] = q4K_gemv_chain(wg, nb, (int)(n % 8), qa + (size_t)m * nb);
-    }
+    for (unsigned m = 0; m < M4; ++m)
+      C[(size_t)m * ldc + n] = q4K_gemm_chain(wg, nb, (int)(n % 8), qa + (size_t)m * nb);
+  }
+#pragma omp parallel for schedule(static)
+  for (int64_t n = 0; n < (int64_t)N; ++n) {
+    const blk_q4_Kx8 *wg = w + (n / 8) * nb;
+    for (unsigned m = M4; m < M; ++m)
+      C[(size_t)m * N + n] = q4K_gemv_chain(wg, nb, (int)(n % 8), qa + (size_t)m * nb);
   }
   free(qa);
   return 0;
@@ -576,11 +580,12 @@ int port_gemm_q4_0(unsigned M, unsigned N, unsigned K, const float *A, unsigned 
   const unsigned M4 = (M == 1) ? 0 : (M / 4) * 4;
   for (unsigned m = 0; m < M; ++m)
     port_quantize_row_q8_0(A + (size_t)m * K, qa + (size_t)m * nb, K);
+  for (int pass = 0; pass < 2; ++pass) /* GEMM rows first, then the leftover rows (they may overlap when ldc > N) */
 #pragma omp parallel for schedule(static)
   for (int64_t n = 0; n < (int64_t)N; ++n) {
     const blk_q4_0x8 *wg = w + (n / 8) * nb;
     const int j = (int)(n % 8);
-    for (unsigned m = 0; m < M; ++m) {
+    for (unsigned m = (pass ? M4 : 0); m < (pass ? M : M4); ++m) {
       const blk_q8_0 *a = qa + (size_t)m * nb;
       float acc = 0.f;
       for (int64_t b = 0; b < nb; ++b) {

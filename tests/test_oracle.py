@@ -116,8 +116,12 @@ def test_port_ldc_semantics_match_reference(ref, port):
     (ggml_interface_omp.cpp:471-491) -- a quirk callers see, so the checker keeps it."""
     rng = np.random.default_rng(5)
     B = O.random_q4_Kx8(rng, 16, 512)
-    A = rng.standard_normal((8, 512)).astype(np.float32)
-    assert np.array_equal(bits(ref.gemm("q4_K", A, B, 16, ldc=24)), bits(port.gemm("q4_K", A, B, 16, ldc=24)))
+    for M in (8, 6, 7):  # 6 and 7: leftover rows land inside the ldc-strided rows and overwrite them
+        A = rng.standard_normal((M, 512)).astype(np.float32)
+        assert np.array_equal(bits(ref.gemm("q4_K", A, B, 16, ldc=24)), bits(port.gemm("q4_K", A, B, 16, ldc=24)))
+    B0 = O.random_q4_0x8(rng, 16, 512)
+    A = rng.standard_normal((6, 512)).astype(np.float32)
+    assert np.array_equal(bits(ref.gemm("q4_0", A, B0, 16, ldc=24)), bits(port.gemm("q4_0", A, B0, 16, ldc=24)))
 
 
 def test_avx512_build_gives_same_bits(ref):
