@@ -115,6 +115,24 @@ int nntr_cuda_gemm_q6_K_dev(unsigned M, unsigned N, unsigned K, const float *A, 
                             unsigned ldb, float *C, unsigned ldc, void *workspace, size_t workspace_bytes,
                             void *stream);
 
+/** Size of the scratch array built into the library for the entry point below. */
+#define NNTR_CUDA_NOALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
+/** Q4_K GEMM (device pointers, any M >= 1) for callers that cannot allocate
+ *  device memory: a model whose memory was planned and handed out before
+ *  inference began, a fixed device budget, or a hot path that cannot afford the
+ *  device-wide stall of a cudaMalloc. Same arguments and result as
+ *  nntr_cuda_gemm_q4_K_dev with M > 1, minus the workspace: the quantized
+ *  activations go to an array compiled into the library
+ *  (NNTR_CUDA_NOALLOC_SCRATCH_BYTES per GPU, held from load to exit).
+ *  Rejects M * (K/256) * 292 > NNTR_CUDA_NOALLOC_SCRATCH_BYTES with
+ *  NNTR_CUDA_ERR_INVALID. The first call on a device looks up the array's
+ *  address; make that call before any stream capture. All calls on a device
+ *  share the array: calls whose kernels may overlap on the GPU must be ordered
+ *  by the caller. Allocates nothing, frees nothing.
+ *  This entry point has no counterpart in the reference. */
+int nntr_cuda_gemm_q4_K_noalloc_dev(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B,
+                                    unsigned ldb, float *C, unsigned ldc, void *stream);
+
 /** Launch flags for the GEMV kernels (bitwise or). */
 #define NNTR_CUDA_GEMV_PDL 1u /* programmatic dependent launch: the kernel's weight prefetch may \
                                  overlap the tail of the previous kernel in the stream */

@@ -44,6 +44,7 @@ SIGNATURES = {
     "nntr_cuda_gemm_q4_K_dev": (_i, _GEMM_DEV),
     "nntr_cuda_gemm_q4_0_dev": (_i, _GEMM_DEV),
     "nntr_cuda_gemm_q6_K_dev": (_i, _GEMM_DEV),
+    "nntr_cuda_gemm_q4_K_noalloc_dev": (_i, [_u, _u, _u, _vp, _u, _vp, _u, _vp, _u, _vp]),
     "nntr_cuda_gemv_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _u, _vp]),
     "nntr_cuda_register_weight": (_i, [_vp, _sz, _i, _u, _u]),
     "nntr_cuda_unregister_weight": (_i, [_vp]),
