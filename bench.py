@@ -41,6 +41,9 @@ RING = 48
 WEIGHT_BYTES = N_ROWS * K_COLS // 256 * 144          # 9 437 184
 ALG_BYTES = WEIGHT_BYTES + 4 * K_COLS + 4 * N_ROWS   # 9 469 952 per GEMV
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q4_K_kernel launch on this workload, from the ncu
+# capture summarised in profiles/gemv_q4_K_cfg1_4096x4096.md
+NCU_TRAFFIC_BYTES = 9_489_152
 
 
 def measured_peak():
@@ -318,7 +321,8 @@ def run_ours(args):
                           "outputs_finite": finite},
                "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                             "frac": round(achieved / peak, 4), "peak_source": which + " (copy bandwidth)",
-                            "us_per_launch": round(per_launch_us, 4), "traffic": args.traffic,
+                            "us_per_launch": round(per_launch_us, 4),
+                            "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_BYTES,
                             "kernel": "gemv_q4_K_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
                "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk}
         print(json.dumps(out))
@@ -329,7 +333,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
