@@ -195,6 +195,59 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------
+# other decode GEMV shapes of the path (reported beside the headline, same method)
+# --------------------------------------------------------------------------
+OTHER_SHAPES = [  # (label, qtype, N, K)
+    ("Qwen3-4B gate+up", "q4_K", 19456, 2560),
+    ("Qwen3-4B down", "q4_K", 2560, 9728),
+    ("Qwen3-4B lm_head", "q6_K", 151936, 2560),
+    ("Q4_0 FFN 24576x4096", "q4_0", 24576, 4096),
+]
+
+
+def other_shapes(be, torch, dev, peak, steps=20):
+    """Each shape: random block bytes (throughput does not depend on the values), enough distinct matrices to exceed L2,
+    launches back to back from one CUDA graph with programmatic dependent launch; CUDA events on the launching stream."""
+    from oracle import oracle as O
+    gens = {"q4_K": O.random_q4_Kx8, "q4_0": O.random_q4_0x8, "q6_K": O.random_q6_K}
+    per_w = {"q4_K": 144 / 256, "q4_0": 18 / 32, "q6_K": 210 / 256}
+    out = []
+    rng = np.random.default_rng(7)
+    for label, q, N, K in OTHER_SHAPES:
+        wbytes = int(N * K * per_w[q])
+        alg = wbytes + 4 * K + 4 * N
+        n_mat = max(2, min(48, int(300e6 // wbytes) + 1))
+        base = torch.from_numpy(gens[q](rng, N, K)).to(dev)
+        mats = [base] + [torch.roll(base, 4099 * 16 * (i + 1)) for i in range(n_mat - 1)]  # distinct memory, same statistics
+        x = torch.randn(K, device=dev)
+        y = torch.zeros(N, device=dev)
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            for W in mats:
+                be.gemv(q, N, K, x, W, y, pdl=True)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for W in mats:
+                    be.gemv(q, N, K, x, W, y, pdl=True)
+            for _ in range(3):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (steps * n_mat)
+        gbs = alg / (us * 1e-6) / 1e9
+        out.append({"shape": label, "qtype": q, "N": N, "K": K, "us_per_launch": round(us, 3), "GB/s": round(gbs, 1),
+                    "frac_of_hbm_peak": round(gbs / peak, 4), "algorithmic_bytes": alg, "distinct_matrices": n_mat})
+        del mats, base
+        torch.cuda.empty_cache()
+    return out
+
+
+# --------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------
 def run_ours(args):
@@ -323,6 +376,7 @@ def run_ours(args):
         value = total_bytes / (ms * 1e-3) / 1e9
         per_launch_us = ms * 1e3 / (args.steps * RING)
         achieved = ALG_BYTES / (per_launch_us * 1e-6) / 1e9
+        others = other_shapes(be, torch, dev, peak) if (world == 1 and not args.no_extra) else None
         cpu_desc = None
         if world == 1 and not args.no_cpu:
             _, cpu_desc, _ = cpu_reference_gbps(host_ring, args.cpu_seconds)
@@ -342,7 +396,8 @@ def run_ours(args):
                             "us_per_launch": round(per_launch_us, 4),
                             "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_BYTES,
                             "kernel": "gemv_q4_K_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
-               "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk}
+               "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
+               "other_decode_gemv_shapes": others}
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
@@ -357,6 +412,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other decode GEMV shapes")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer end-to-end leg (profiling runs)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--ring", type=int, default=RING, help="distinct weight matrices per step (default keeps every launch out of L2)")

@@ -140,6 +140,44 @@ int nntr_cuda_gemm_q4_K_noalloc_dev(unsigned M, unsigned N, unsigned K, const fl
 int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
                        void *stream);
 
+/* ------------------------------------------------------ mixture of experts */
+
+/** One MoE layer's parameters, all device pointers. Stands in for the weights
+ *  MoELayer / GptOssMoELayer request in finalize()
+ *  (Applications/CausalLM/layers/qwen_moe_layer.cpp:93-141,
+ *  gpt_oss_moe_layer.cpp:136-169). */
+typedef struct {
+  int kind;                  /* 0: Qwen (swish(gate) * up); 1: GPT-OSS (biases, (up+1) * gate * sigmoid(alpha*gate)) */
+  int qtype;                 /* format of the expert weights (NNTR_Q4_K) */
+  unsigned hidden;           /* H */
+  unsigned inter;            /* expert intermediate size I */
+  unsigned n_experts;        /* E (<= 256) */
+  unsigned top_k;            /* experts per token */
+  const float *router_w;     /* fp32 [H][E], as the reference stores the gate weight */
+  const float *router_bias;  /* fp32 [E] or NULL */
+  const void *const *gate_w; /* E pointers: gate projection, quantized [I][H] */
+  const void *const *up_w;   /* E pointers: up projection, quantized [I][H] */
+  const void *const *down_w; /* E pointers: down projection, quantized [H][I] */
+  const float *const *gate_b; /* E pointers to fp32 [I], or NULL (kind 0) */
+  const float *const *up_b;   /* E pointers to fp32 [I], or NULL */
+  const float *const *down_b; /* E pointers to fp32 [H], or NULL */
+  float alpha;               /* GPT-OSS activation slope */
+} nntr_moe_desc;
+
+/** Scratch bytes nntr_cuda_moe_forward_dev needs for `tokens` tokens. */
+size_t nntr_cuda_moe_workspace_bytes(const nntr_moe_desc *d, unsigned tokens);
+/** y[tokens][H] = MoE(x[tokens][H]): MoELayer::incremental_forwarding
+ *  (qwen_moe_layer.cpp:394-503) / GptOssMoELayer (gpt_oss_moe_layer.cpp:457-572)
+ *  for one batch element: router, softmax, top-k, renormalise, per-(token,
+ *  expert) gate/up/down GEMVs with M == 1 as the reference runs them, combine
+ *  in ascending expert order. Device pointers; workspace 256-byte aligned. */
+int nntr_cuda_moe_forward_dev(const nntr_moe_desc *d, unsigned tokens, const float *x, float *y, void *workspace,
+                              size_t workspace_bytes, void *stream);
+/** Routing step alone (qwen_moe_layer.cpp:439-446): expert indices [tokens][top_k]
+ *  and renormalised weights [tokens][top_k], in top-k order. */
+int nntr_cuda_moe_route_dev(const nntr_moe_desc *d, unsigned tokens, const float *x, int *idx_out, float *w_out,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------ host-pointer entry points */
 
 /** Upload a weight tensor's bytes to device memory once, keyed by its host

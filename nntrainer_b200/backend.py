@@ -166,3 +166,61 @@ def dequantize_weight(qtype: str, w, N: int, K: int):
     y = torch.empty((N, K), dtype=torch.float32, device=w.device)
     check(lib().nntr_cuda_dequantize_weight_dev(QTYPE[qtype], w.data_ptr(), y.data_ptr(), N, K, _stream()))
     return y
+
+
+# ------------------------------------------------------------------- MoE
+class MoeLayer:
+    """Device-resident parameters of one MoE layer (the weights MoELayer / GptOssMoELayer hold,
+    Applications/CausalLM/layers/qwen_moe_layer.cpp:93-141). Expert weights are lists of CUDA uint8 tensors in the
+    tensor's own quantized layout; forward() is MoELayer::incremental_forwarding for one batch element."""
+
+    def __init__(self, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=0, router_bias=None, gate_b=None,
+                 up_b=None, down_b=None, alpha=1.0):
+        import ctypes as C
+        torch = _torch()
+        self.H, self.E = router_w.shape
+        self.I = gate_w[0].numel() * _BLOCK[qtype][0] // _BLOCK[qtype][1] // self.H
+        self.top_k = top_k
+        self._keep = [router_w, gate_w, up_w, down_w, router_bias, gate_b, up_b, down_b]
+        dev = router_w.device
+
+        def table(ts):
+            if ts is None:
+                return None
+            t = torch.tensor([x.data_ptr() for x in ts], dtype=torch.int64, device=dev)
+            self._keep.append(t)
+            return t
+
+        self._tabs = [table(gate_w), table(up_w), table(down_w), table(gate_b), table(up_b), table(down_b)]
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        self.desc = capi.MoeDesc(kind, QTYPE[qtype], self.H, self.I, self.E, top_k, router_w.data_ptr(), ptr(router_bias),
+                                 ptr(self._tabs[0]), ptr(self._tabs[1]), ptr(self._tabs[2]), ptr(self._tabs[3]),
+                                 ptr(self._tabs[4]), ptr(self._tabs[5]), alpha)
+        self._ws = None
+        self._C = C
+
+    def _workspace(self, tokens):
+        torch = _torch()
+        need = int(lib().nntr_cuda_moe_workspace_bytes(self._C.byref(self.desc), tokens))
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self._keep[0].device)
+        return self._ws
+
+    def forward(self, x):
+        torch = _torch()
+        T = x.shape[0]
+        y = torch.empty((T, self.H), dtype=torch.float32, device=x.device)
+        ws = self._workspace(T)
+        check(lib().nntr_cuda_moe_forward_dev(self._C.byref(self.desc), T, x.data_ptr(), y.data_ptr(), ws.data_ptr(),
+                                              ws.numel(), _stream()))
+        return y
+
+    def route(self, x):
+        torch = _torch()
+        T = x.shape[0]
+        idx = torch.empty((T, self.top_k), dtype=torch.int32, device=x.device)
+        w = torch.empty((T, self.top_k), dtype=torch.float32, device=x.device)
+        ws = self._workspace(T)
+        check(lib().nntr_cuda_moe_route_dev(self._C.byref(self.desc), T, x.data_ptr(), idx.data_ptr(), w.data_ptr(),
+                                            ws.data_ptr(), ws.numel(), _stream()))
+        return idx, w

@@ -46,6 +46,9 @@ SIGNATURES = {
     "nntr_cuda_gemm_q6_K_dev": (_i, _GEMM_DEV),
     "nntr_cuda_gemm_q4_K_noalloc_dev": (_i, [_u, _u, _u, _vp, _u, _vp, _u, _vp, _u, _vp]),
     "nntr_cuda_gemv_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _u, _vp]),
+    "nntr_cuda_moe_workspace_bytes": (_sz, [_vp, _u]),
+    "nntr_cuda_moe_forward_dev": (_i, [_vp, _u, _vp, _vp, _vp, _sz, _vp]),
+    "nntr_cuda_moe_route_dev": (_i, [_vp, _u, _vp, _vp, _vp, _vp, _sz, _vp]),
     "nntr_cuda_register_weight": (_i, [_vp, _sz, _i, _u, _u]),
     "nntr_cuda_unregister_weight": (_i, [_vp]),
     "nntr_cuda_weight_device_ptr": (_vp, [_vp]),
@@ -56,6 +59,14 @@ SIGNATURES = {
     "nntr_cuda_quantize_row_q8_0": (_i, [_vp, _vp, _i64]),
     "nntr_cuda_dequantize_row": (_i, [_i, _vp, _vp, _i64]),
 }
+
+
+class MoeDesc(C.Structure):
+    """nntr_moe_desc of include/nntr_cuda.h."""
+    _fields_ = [("kind", C.c_int), ("qtype", C.c_int), ("hidden", C.c_uint), ("inter", C.c_uint),
+                ("n_experts", C.c_uint), ("top_k", C.c_uint), ("router_w", C.c_void_p), ("router_bias", C.c_void_p),
+                ("gate_w", C.c_void_p), ("up_w", C.c_void_p), ("down_w", C.c_void_p), ("gate_b", C.c_void_p),
+                ("up_b", C.c_void_p), ("down_b", C.c_void_p), ("alpha", C.c_float)]
 
 
 def declared_symbols() -> list[str]:

@@ -216,12 +216,24 @@ __device__ __forceinline__ Q80Lane q80_quantize_warp(const float4 a, const float
   return out;
 }
 
+/** Batched GEMV launch: problem p (blockIdx.y) multiplies the weight w_table[p] with activation row p / x_div and
+ *  writes output row p. All-zero = a single problem. w_table lives in device memory and may be written by the kernel
+ *  launched just before (expert selection of a MoE router). */
+struct GemvBatch {
+  const void *const *w_table;
+  long long x_stride; // elements between consecutive activation rows
+  int x_div;
+  long long y_stride; // elements between the outputs of consecutive problems
+};
+
 /* launchers implemented in the .cu files (host side, return NNTR_CUDA_* codes) */
 int launch_quantize_q8_K(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, int rule, cudaStream_t st);
 int launch_quantize_q8_0(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, cudaStream_t st);
 int launch_dequantize_row(int qtype, const void *x, float *y, int64_t k, cudaStream_t st);
 int launch_dequantize_weight(int qtype, const void *w, float *y, int64_t N, int64_t K, cudaStream_t st);
 int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
+int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
+                             unsigned n_problems, GemvBatch batch, cudaStream_t st);
 int launch_gemv_q4_0(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
 int launch_gemv_q6_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
 /* M > 1 with activations already quantized to plain Q8 rows in `qa` */

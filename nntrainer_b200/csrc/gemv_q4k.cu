@@ -205,8 +205,13 @@ __device__ __forceinline__ void row_block_sums(const uint8_t *blk, const uint8_t
 
 __global__ void __launch_bounds__(GEMV_THREADS, 2)
 gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, float *__restrict__ y, int n_groups,
-                 int nb, int ngslot) {
+                 int nb, int ngslot, GemvBatch batch) {
   extern __shared__ __align__(128) uint8_t smem[];
+  if (batch.w_table) { // batched launch: blockIdx.y picks the problem
+    const int p = blockIdx.y;
+    x += (long long)(p / batch.x_div) * batch.x_stride;
+    y += (long long)p * batch.y_stride;
+  }
   const SmemLayout L = smem_layout(nb, ngslot);
   uint8_t *ring = smem + L.ring;
   uint8_t *act = smem + L.act;
@@ -225,7 +230,6 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
   const int ng = g_end - g_first;
   const int total_blocks = ng * nb;
   const int total_stages = (total_blocks + STAGE_BLOCKS - 1) / STAGE_BLOCKS;
-  const uint8_t *src = reinterpret_cast<const uint8_t *>(W + (size_t)g_first * nb);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -245,6 +249,11 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
 
   if (warp == PRODUCER_WARP) {
     // ------------------------------------------------------------ producer
+    if (batch.w_table) {
+      pdl_wait(); // the weight table is written by the kernel before this one
+      W = static_cast<const BlockQ4Kx8 *>(batch.w_table[blockIdx.y]);
+    }
+    const uint8_t *src = reinterpret_cast<const uint8_t *>(W + (size_t)g_first * nb);
     // one bulk copy per block, so that blocks land BLK_STRIDE apart
     int q = 0;
     bool ok = true;
@@ -368,8 +377,19 @@ static int env_int(const char *name, int dflt) {
 }
 
 int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st) {
-  if (!x || !B || !y)
+  GemvBatch none = {};
+  return launch_gemv_q4_K_batched(N, K, x, B, y, flags, 1, none, st);
+}
+
+/* n_problems > 1: `batch.w_table` (device memory) holds one weight pointer per problem, B is ignored. */
+int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
+                             unsigned n_problems, GemvBatch batch, cudaStream_t st) {
+  if (!x || !y || (!B && !batch.w_table))
     return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: null pointer");
+  if (batch.w_table && (batch.x_div <= 0 || (batch.x_stride % 4) != 0))
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: bad batch description");
+  if (n_problems == 0)
+    return NNTR_CUDA_OK;
   if (K == 0 || K % QK_K || N % 8)
     return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: need K %% 256 == 0 and N %% 8 == 0 (N=%u K=%u)", N, K);
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
@@ -391,14 +411,16 @@ int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, floa
   // A share that fits the ring (one step per warp) runs one CTA per SM and leaves
   // room for the next kernel's CTAs under programmatic dependent launch; longer
   // streams run two CTAs per SM: 32 consumer warps and 16 stages in flight per SM.
-  const long blocks_per_sm = ((long)n_groups * nb + sms - 1) / sms;
+  const long blocks_per_sm = ((long)n_groups * nb * n_problems + sms - 1) / sms;
   const bool two_fit = 2u * L.total <= 220u * 1024u;
   const int per_sm = env_int("NNTR_CUDA_GEMV_CTAS_PER_SM", (blocks_per_sm > STEP_BLOCKS && two_fit) ? 2 : 1);
-  const int max_ctas = sms * per_sm;
+  int max_ctas = (sms * per_sm + (int)n_problems - 1) / (int)n_problems; // CTAs per problem
+  if (max_ctas < 1)
+    max_ctas = 1;
   const unsigned grid = (unsigned)(n_groups < max_ctas ? n_groups : max_ctas);
 
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = dim3(grid, n_problems);
   cfg.blockDim = dim3(GEMV_THREADS);
   cfg.dynamicSmemBytes = L.total;
   cfg.stream = st;
@@ -408,7 +430,7 @@ int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, floa
   cfg.attrs = attr;
   cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
   const BlockQ4Kx8 *Wp = static_cast<const BlockQ4Kx8 *>(B);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel, x, Wp, y, n_groups, nb, ngslot);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel, x, Wp, y, n_groups, nb, ngslot, batch);
   count_launch();
   return check_cuda(e, "gemv_q4_K launch");
 }

@@ -1,0 +1,312 @@
+// SPDX-License-Identifier: Apache-2.0
+/**
+ * @file  moe.cu
+ * @brief Mixture-of-experts forward pass of the CausalLM layers on device:
+ *        router + softmax + top-k + renormalise, expert FFNs as batched
+ *        quantized GEMVs, weighted combine in the reference's summation order.
+ *
+ * Follows Applications/CausalLM/layers/qwen_moe_layer.cpp:394-503 (and :332-392
+ * for one expert) and gpt_oss_moe_layer.cpp:374-456, 495-572:
+ *   logits = x . Wr (+ bias);  p = softmax(logits);  (v, e) = topK(p, k);  w = v / sum(v)
+ *   for every (token, expert) pair: g = x.Wg[e], u = x.Wu[e]   (quantized GEMV, M = 1, exactly as the reference)
+ *        Qwen:    a = (sigmoid(g) * g) * u
+ *        GPT-OSS: g += bg[e]; u = (u + bu[e]) + 1; a = (g / (exp(-alpha g) + 1)) * u
+ *        d = a.Wd[e] (+ bd[e])
+ *   y[token] = sum over the token's experts in ASCENDING expert index of d * w
+ *
+ * Five launches per layer: router (one CTA per token), batched gate+up GEMV
+ * (2 * pairs problems in one grid; the expert picked per problem through a
+ * device-side pointer table the router writes), activation, batched down GEMV,
+ * combine. The reference runs every expert GEMV with M = 1 even in prefill, so
+ * the batched GEMV reproduces its numerics; top-k ties (measure zero) resolve
+ * to the lower expert index here, unspecified in the reference (heap order of
+ * std::partial_sort). Parity: expert selection exact, outputs within the path's
+ * tolerance (the reference's router product and row sums go through BLAS and
+ * its exp through libm / a polynomial, none of which is reproduced bit for bit).
+ */
+#include "common.cuh"
+
+namespace nntr {
+
+constexpr int ROUTER_WARPS = 8;
+constexpr int MAX_E_PER_LANE = 8; // up to 256 experts
+
+/* one CTA per token */
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, const float *__restrict__ bias, int H, int E,
+                  int topk, const void *const *__restrict__ gate_w, const void *const *__restrict__ up_w,
+                  const void *const *__restrict__ down_w, int *__restrict__ idx_out, float *__restrict__ w_out,
+                  const void **__restrict__ gu_table, const void **__restrict__ dn_table) {
+  extern __shared__ float rsm[]; // [ROUTER_WARPS][E]
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float *xt = x + (size_t)t * H;
+  const int per = (E + 31) / 32;
+  float acc[MAX_E_PER_LANE];
+#pragma unroll
+  for (int i = 0; i < MAX_E_PER_LANE; ++i)
+    acc[i] = 0.f;
+  const int h0 = (int)(((long long)warp * H) / ROUTER_WARPS), h1 = (int)(((long long)(warp + 1) * H) / ROUTER_WARPS);
+  for (int h = h0; h < h1; ++h) {
+    const float xv = xt[h];
+    const float *row = wr + (size_t)h * E;
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; ++i)
+      if (i < per && lane + 32 * i < E)
+        acc[i] = fmaf(xv, row[lane + 32 * i], acc[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < MAX_E_PER_LANE; ++i)
+    if (i < per && lane + 32 * i < E)
+      rsm[warp * E + lane + 32 * i] = acc[i];
+  __syncthreads();
+  if (warp != 0)
+    return;
+  // ---- warp 0: logits, softmax, top-k
+  float p[MAX_E_PER_LANE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAX_E_PER_LANE; ++i) {
+    p[i] = -INFINITY;
+    const int e = lane + 32 * i;
+    if (i < per && e < E) {
+      float s = 0.f;
+      for (int w = 0; w < ROUTER_WARPS; ++w)
+        s += rsm[w * E + e];
+      p[i] = s + (bias ? bias[e] : 0.f);
+      mx = fmaxf(mx, p[i]);
+    }
+  }
+  for (int o = 16; o; o >>= 1)
+    mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_E_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    if (i < per && e < E) {
+      p[i] = expf(p[i] - mx);
+      sum += p[i];
+    } else {
+      p[i] = -1.f; // never selected: probabilities are >= 0
+    }
+  }
+  for (int o = 16; o; o >>= 1)
+    sum += __shfl_xor_sync(FULL, sum, o);
+#pragma unroll
+  for (int i = 0; i < MAX_E_PER_LANE; ++i)
+    if (p[i] >= 0.f)
+      p[i] = __fdiv_rn(p[i], sum);
+  // k rounds of arg-max, ties to the lower expert index
+  float vsel = 0.f; // lane j keeps the j-th selected value / index
+  int esel = 0;
+  float ksum = 0.f;
+  for (int k = 0; k < topk; ++k) {
+    float bv = -1.f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (p[i] > bv) { // ascending e within the lane: the first maximum wins
+        bv = p[i];
+        be = e;
+      }
+    }
+    for (int o = 16; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(FULL, bv, o);
+      const int oe = __shfl_xor_sync(FULL, be, o);
+      if (ov > bv || (ov == bv && oe < be)) {
+        bv = ov;
+        be = oe;
+      }
+    }
+    if ((be & 31) == lane) { // the owner retires the winner
+#pragma unroll
+      for (int i = 0; i < MAX_E_PER_LANE; ++i)
+        if (i == (be >> 5))
+          p[i] = -1.f;
+    }
+    if (lane == k) {
+      vsel = bv;
+      esel = be;
+    }
+    ksum += bv; // same sequential sum in every lane
+  }
+  if (lane < topk) {
+    const int pr = t * topk + lane;
+    idx_out[pr] = esel;
+    w_out[pr] = __fdiv_rn(vsel, ksum);
+    gu_table[2 * pr] = gate_w[esel];
+    gu_table[2 * pr + 1] = up_w[esel];
+    dn_table[pr] = down_w[esel];
+  }
+}
+
+/* a[p][i] from the gate / up GEMV outputs gu[2p][i], gu[2p+1][i] */
+__global__ void moe_act_kernel(const float *__restrict__ gu, float *__restrict__ a, const int *__restrict__ idx,
+                               const float *const *__restrict__ gate_b, const float *const *__restrict__ up_b, int kind,
+                               float alpha, int I, long total) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total)
+    return;
+  const long p = i / I;
+  const int c = (int)(i - p * I);
+  float g = gu[(2 * p) * I + c], u = gu[(2 * p + 1) * I + c];
+  float r;
+  if (kind == 0) {
+    const float sig = (float)(1.0 / (1.0 + (double)expf(-g)));
+    r = __fmul_rn(__fmul_rn(sig, g), u);
+  } else {
+    const int e = idx[p];
+    g = __fadd_rn(g, gate_b[e][c]);
+    u = __fadd_rn(__fadd_rn(u, up_b[e][c]), 1.f);
+    r = __fmul_rn(__fdiv_rn(g, __fadd_rn(expf(-__fmul_rn(alpha, g)), 1.f)), u);
+  }
+  a[i] = r;
+}
+
+/* y[t][h] = sum over the token's experts, ascending expert index, of (d (+ bias)) * w */
+__global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__restrict__ idx, const float *__restrict__ w,
+                                   const float *const *__restrict__ down_b, float *__restrict__ y, int H, int topk,
+                                   long total) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total)
+    return;
+  const long t = i / H;
+  const int h = (int)(i - t * H);
+  float acc = 0.f;
+  int last = -1;
+  for (int k = 0; k < topk; ++k) { // selection sort over at most a handful of experts
+    int best = 0x7fffffff, bj = -1;
+    for (int j = 0; j < topk; ++j) {
+      const int e = idx[t * topk + j];
+      if (e > last && e < best) {
+        best = e;
+        bj = j;
+      }
+    }
+    if (bj < 0)
+      break;
+    last = best;
+    float v = dn[(t * topk + bj) * H + h];
+    if (down_b)
+      v = __fadd_rn(v, down_b[best][h]);
+    acc = __fadd_rn(acc, __fmul_rn(v, w[t * topk + bj]));
+  }
+  y[i] = acc;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct MoeWs {
+  size_t idx, w, gu_tab, dn_tab, gu, act, dn, total;
+};
+static MoeWs moe_ws(unsigned T, unsigned H, unsigned I, unsigned topk) {
+  MoeWs s;
+  const size_t P = (size_t)T * topk;
+  size_t o = 0;
+  s.idx = o;
+  o = align_up(o + P * 4, 256);
+  s.w = o;
+  o = align_up(o + P * 4, 256);
+  s.gu_tab = o;
+  o = align_up(o + 2 * P * 8, 256);
+  s.dn_tab = o;
+  o = align_up(o + P * 8, 256);
+  s.gu = o;
+  o = align_up(o + 2 * P * I * 4, 256);
+  s.act = o;
+  o = align_up(o + P * I * 4, 256);
+  s.dn = o;
+  o = align_up(o + P * H * 4, 256);
+  s.total = o;
+  return s;
+}
+
+} // namespace nntr
+
+using namespace nntr;
+
+extern "C" size_t nntr_cuda_moe_workspace_bytes(const nntr_moe_desc *d, unsigned tokens) {
+  if (!d)
+    return 0;
+  return moe_ws(tokens, d->hidden, d->inter, d->top_k).total;
+}
+
+extern "C" int nntr_cuda_moe_forward_dev(const nntr_moe_desc *d, unsigned tokens, const float *x, float *y,
+                                         void *workspace, size_t workspace_bytes, void *stream) {
+  if (!d || !x || !y)
+    return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: null pointer");
+  if (d->qtype != NNTR_Q4_K)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "moe_forward: expert weights must be Q4_K (got qtype %d)", d->qtype);
+  if (d->kind != 0 && d->kind != 1)
+    return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: kind must be 0 (Qwen) or 1 (GPT-OSS)");
+  if (d->kind == 1 && (!d->gate_b || !d->up_b || !d->down_b))
+    return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: kind 1 needs the three expert bias tables");
+  const unsigned H = d->hidden, I = d->inter, E = d->n_experts, K = d->top_k;
+  if (H == 0 || H % 256 || I == 0 || I % 256 || E == 0 || E > 32 * MAX_E_PER_LANE || K == 0 || K > E || K > 32)
+    return set_error(NNTR_CUDA_ERR_INVALID,
+                     "moe_forward: need hidden %% 256 == 0, inter %% 256 == 0, experts <= 256, top_k <= min(experts, 32)");
+  if (!d->router_w || !d->gate_w || !d->up_w || !d->down_w)
+    return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: null weight table");
+  if (tokens == 0)
+    return NNTR_CUDA_OK;
+  const MoeWs s = moe_ws(tokens, H, I, K);
+  if (!workspace || workspace_bytes < s.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: workspace of %zu bytes (256-byte aligned) needed", s.total);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t *ws = static_cast<uint8_t *>(workspace);
+  int *idx = reinterpret_cast<int *>(ws + s.idx);
+  float *w = reinterpret_cast<float *>(ws + s.w);
+  const void **gu_tab = reinterpret_cast<const void **>(ws + s.gu_tab);
+  const void **dn_tab = reinterpret_cast<const void **>(ws + s.dn_tab);
+  float *gu = reinterpret_cast<float *>(ws + s.gu);
+  float *act = reinterpret_cast<float *>(ws + s.act);
+  float *dn = reinterpret_cast<float *>(ws + s.dn);
+  const unsigned P = tokens * K;
+
+  moe_router_kernel<<<tokens, ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float), st>>>(
+    x, d->router_w, d->router_bias, (int)H, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx, w, gu_tab, dn_tab);
+  count_launch();
+  NNTR_CHECK_CUDA(cudaGetLastError());
+
+  GemvBatch b1 = {gu_tab, (long long)H, (int)(2 * K), (long long)I};
+  int rc = launch_gemv_q4_K_batched(I, H, x, nullptr, gu, 0, 2 * P, b1, st);
+  if (rc)
+    return rc;
+
+  const long n_act = (long)P * I;
+  moe_act_kernel<<<(unsigned)((n_act + 255) / 256), 256, 0, st>>>(gu, act, idx, d->gate_b, d->up_b, d->kind, d->alpha,
+                                                                  (int)I, n_act);
+  count_launch();
+  NNTR_CHECK_CUDA(cudaGetLastError());
+
+  GemvBatch b2 = {dn_tab, (long long)I, 1, (long long)H};
+  rc = launch_gemv_q4_K_batched(H, I, act, nullptr, dn, 0, P, b2, st);
+  if (rc)
+    return rc;
+
+  const long n_out = (long)tokens * H;
+  moe_combine_kernel<<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dn, idx, w, d->kind == 1 ? d->down_b : nullptr, y,
+                                                                      (int)H, (int)K, n_out);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "moe_combine launch");
+}
+
+extern "C" int nntr_cuda_moe_route_dev(const nntr_moe_desc *d, unsigned tokens, const float *x, int *idx_out,
+                                       float *w_out, void *workspace, size_t workspace_bytes, void *stream) {
+  if (!d || !x || !idx_out || !w_out || !d->router_w || !d->gate_w || !d->up_w || !d->down_w)
+    return set_error(NNTR_CUDA_ERR_INVALID, "moe_route: null pointer");
+  const unsigned E = d->n_experts, K = d->top_k;
+  if (E == 0 || E > 32 * MAX_E_PER_LANE || K == 0 || K > E || K > 32)
+    return set_error(NNTR_CUDA_ERR_INVALID, "moe_route: experts <= 256, top_k <= min(experts, 32)");
+  if (tokens == 0)
+    return NNTR_CUDA_OK;
+  const MoeWs s = moe_ws(tokens, d->hidden, d->inter, K);
+  if (!workspace || workspace_bytes < s.gu || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return set_error(NNTR_CUDA_ERR_INVALID, "moe_route: workspace too small");
+  uint8_t *ws = static_cast<uint8_t *>(workspace);
+  moe_router_kernel<<<tokens, ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+    x, d->router_w, d->router_bias, (int)d->hidden, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx_out, w_out,
+    reinterpret_cast<const void **>(ws + s.gu_tab), reinterpret_cast<const void **>(ws + s.dn_tab));
+  count_launch();
+  return check_cuda(cudaGetLastError(), "moe_router launch");
+}

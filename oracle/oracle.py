@@ -186,6 +186,41 @@ class Port(_Lib):
         assert f(_ptr(out), _ptr(np.ascontiguousarray(packed)), nrow, k) == 0
         return out
 
+    def moe_route(self, x, router_w, top_k, router_bias=None):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        T, H = x.shape
+        E = router_w.shape[1]
+        idx = np.zeros((T, top_k), dtype=np.uint32)
+        w = np.zeros((T, top_k), dtype=np.float32)
+        f = self.lib.port_moe_route
+        f.argtypes = [C.c_uint] * 4 + [_vp] * 5
+        f.restype = None
+        f(T, H, E, top_k, _ptr(x), _ptr(router_w), _ptr(router_bias), _ptr(idx), _ptr(w))
+        return idx, w
+
+    def moe_forward(self, x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=0, router_bias=None,
+                    gate_b=None, up_b=None, down_b=None, alpha=1.0):
+        """gate_w/up_w/down_w: lists of E uint8 arrays (quantized [I][H], [I][H], [H][I])."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        T, H = x.shape
+        E = router_w.shape[1]
+        per = {"q4_K": (256, 144), "q4_0": (32, 18)}[qtype]
+        I = gate_w[0].size * per[0] // per[1] // H
+
+        def table(arrs):
+            if arrs is None:
+                return None
+            return (C.c_void_p * E)(*[a.ctypes.data for a in arrs])
+
+        tabs = [table(gate_w), table(up_w), table(down_w), table(gate_b), table(up_b), table(down_b)]
+        out = np.zeros((T, H), dtype=np.float32)
+        f = self.lib.port_moe_forward
+        f.argtypes = [C.c_int, C.c_int] + [C.c_uint] * 5 + [_vp] * 9 + [C.c_float, _vp]
+        f.restype = None
+        f(kind, {"q4_K": 12, "q4_0": 2}[qtype], T, H, I, E, top_k, _ptr(x), _ptr(router_w), _ptr(router_bias),
+          *[C.cast(t, C.c_void_p) if t is not None else None for t in tabs], alpha, _ptr(out))
+        return out
+
     def fp16_to_fp32(self, h: int) -> float:
         f = self.lib.port_fp16_to_fp32
         f.argtypes = [C.c_uint16]

@@ -1,0 +1,121 @@
+"""Mixture-of-experts layer: CPU checks of the restatement, GPU parity of the
+fused path. The reference has no test of its own for these layers; outputs are
+held to the path's tolerance (max-rel 2e-3), expert selection exactly."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+REL_TOL = 2e-3
+
+
+def make_layer(rng, H, I, E, distinct=None):
+    distinct = distinct or E
+    router = (rng.standard_normal((H, E)) * 0.02).astype(np.float32)
+    pool = [(O.random_q4_Kx8(rng, I, H), O.random_q4_Kx8(rng, I, H), O.random_q4_Kx8(rng, H, I)) for _ in range(distinct)]
+    gate = [pool[e % distinct][0] for e in range(E)]
+    up = [pool[e % distinct][1] for e in range(E)]
+    down = [pool[e % distinct][2] for e in range(E)]
+    return router, gate, up, down
+
+
+# ------------------------------------------------------------------ CPU
+def test_route_restatement_properties(port):
+    rng = np.random.default_rng(0)
+    T, H, E, k = 7, 256, 32, 4
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    router = (rng.standard_normal((H, E)) * 0.05).astype(np.float32)
+    idx, w = port.moe_route(x, router, k)
+    logits = x @ router
+    for t in range(T):
+        assert list(idx[t]) == list(np.argsort(-logits[t], kind="stable")[:k])  # softmax is monotone
+        assert abs(float(w[t].sum()) - 1.0) < 1e-5 and np.all(np.diff(w[t]) <= 0)
+        p = np.exp(logits[t] - logits[t].max())
+        p /= p.sum()
+        np.testing.assert_allclose(w[t], p[idx[t]] / p[idx[t]].sum(), rtol=1e-5)
+
+
+def test_forward_restatement_is_a_weighted_sum_of_expert_ffns(port):
+    rng = np.random.default_rng(1)
+    T, H, I, E, k = 3, 256, 256, 8, 2
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    router, gate, up, down = make_layer(rng, H, I, E)
+    out = port.moe_forward(x, router, gate, up, down, k)
+    idx, w = port.moe_route(x, router, k)
+    for t in range(T):
+        want = np.zeros(H, dtype=np.float32)
+        for e in sorted(idx[t]):
+            j = list(idx[t]).index(e)
+            g = port.gemm("q4_K", x[t:t + 1], gate[e], I)[0]
+            u = port.gemm("q4_K", x[t:t + 1], up[e], I)[0]
+            sig = (1.0 / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32)
+            a = (sig * g) * u
+            d = port.gemm("q4_K", a[None], down[e], H)[0]
+            want = want + d * w[t, j]
+        np.testing.assert_allclose(out[t], want, rtol=1e-4, atol=1e-4 * np.abs(want).max())
+
+
+# ------------------------------------------------------------------ GPU
+@pytest.fixture(scope="module")
+def be():
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from nntrainer_b200 import backend, build
+    build.build()
+    backend.init(0)
+    return backend
+
+
+def device_layer(be, router, gate, up, down, k):
+    import torch
+    cache = {}
+
+    def dev(a):
+        key = a.ctypes.data
+        if key not in cache:
+            cache[key] = torch.from_numpy(a).cuda()
+        return cache[key]
+
+    return be.MoeLayer(torch.from_numpy(router).cuda(), [dev(a) for a in gate], [dev(a) for a in up],
+                       [dev(a) for a in down], k)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 512, 256, 16, 4), (5, 512, 256, 16, 4), (33, 256, 512, 8, 2)])
+def test_moe_route_and_forward_match_checker(be, port, T, H, I, E, k):
+    import torch
+    rng = np.random.default_rng(T * 100 + E)
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    router, gate, up, down = make_layer(rng, H, I, E)
+    layer = device_layer(be, router, gate, up, down, k)
+    xd = torch.from_numpy(x).cuda()
+    idx, w = layer.route(xd)
+    ridx, rw = port.moe_route(x, router, k)
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), ridx), "expert selection must be identical"
+    np.testing.assert_allclose(w.cpu().numpy(), rw, rtol=1e-5)
+    got = layer.forward(xd).cpu().numpy()
+    want = port.moe_forward(x, router, gate, up, down, k)
+    assert np.isfinite(got).all()
+    assert np.max(np.abs(got - want)) <= REL_TOL * np.max(np.abs(want))
+    be.device_status()
+
+
+@pytest.mark.gpu
+def test_moe_qwen3_30b_a3b_shape_decode(be, port):
+    """One decode token through a layer with the Qwen3-30B-A3B MoE shape: hidden 2048, 128 experts, top-8,
+    expert intermediate 768 (8 distinct expert weight sets cycled to keep the fixture small)."""
+    import torch
+    rng = np.random.default_rng(30)
+    H, I, E, k = 2048, 768, 128, 8
+    x = rng.standard_normal((1, H)).astype(np.float32)
+    router, gate, up, down = make_layer(rng, H, I, E, distinct=8)
+    layer = device_layer(be, router, gate, up, down, k)
+    xd = torch.from_numpy(x).cuda()
+    idx, _ = layer.route(xd)
+    ridx, _ = port.moe_route(x, router, k)
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), ridx)
+    got = layer.forward(xd).cpu().numpy()
+    want = port.moe_forward(x, router, gate, up, down, k)
+    assert np.max(np.abs(got - want)) <= REL_TOL * np.max(np.abs(want))
+    be.device_status()
