@@ -11,7 +11,9 @@ programmatic dependent launch from one CUDA graph.
 
 With --gpus P > 1 the projection is N-split: the global weight is
 [4096*P, 4096], every rank holds a 4096-row shard (the same per-GPU work: weak
-scaling) and the output slices are all-gathered over NCCL after every GEMV.
+scaling) and every GEMV's epilogue stores its output slice straight into the
+gathered vector of every rank (peer stores over NVLink, arrival counters); the
+next GEMV waits on its counter. No collective library call on the data path.
 
 Prints ONE JSON line (rank 0). `value` = algorithmic GB/s of the whole job with
 inputs resident in HBM; `e2e` = the same metric through the host-pointer C ABI
@@ -269,28 +271,58 @@ def run_ours(args):
     dev = torch.device("cuda", local)
 
     base, how = make_base_weight()
-    host_ring = ring_host(base)
+    nsplit = world > 1 or args.nsplit
+
+    def shard(r, i):
+        """Weight shard of rank r for layer i: the base matrix with its row groups rotated (distinct memory per layer
+        and per rank, same statistics)."""
+        g = base.reshape(N_ROWS // 8, -1)
+        return np.ascontiguousarray(np.roll(g, 11 * i + 5 * r, axis=0)).reshape(-1)
+
+    host_ring = [shard(rank, i) for i in range(RING)]
     ring = [torch.from_numpy(w).to(dev) for w in host_ring]
     x0 = torch.from_numpy(np.random.default_rng(1).standard_normal(K_COLS).astype(np.float32)).to(dev)
-    # every step restarts from the same input, then ping-pongs between two buffers
-    # (with P ranks a buffer is the gathered [P*4096] vector and a rank reads its own slice)
-    gathered = [torch.zeros(world * N_ROWS, device=dev) for _ in range(2)]
     pdl = not args.no_pdl
-    lo, hi = rank * N_ROWS, (rank + 1) * N_ROWS
+    gathered = [torch.zeros(N_ROWS, device=dev) for _ in range(2)]
+    group = None
+    if nsplit:
+        from nntrainer_b200.nsplit import NSplitGroup
+        group = NSplitGroup(N_ROWS, RING)
 
     def step_body():
-        src = x0
+        sp = int(torch.cuda.current_stream().cuda_stream)
+        if group is not None:
+            # N-split: every GEMV stores its slice into all ranks' gathered vectors and the next one waits on the
+            # arrival counter -- no collective on the data path
+            group.bump_epoch(sp)
+            for i, W in enumerate(ring):
+                xp = x0.data_ptr() if i == 0 else group.input_ptr(i)
+                group.gemv("q4_K", K_COLS, xp, W.data_ptr(), i, sp, pdl=pdl)
+            return
+        src = x0  # every step restarts from the same input, then ping-pongs between two buffers
         for i, W in enumerate(ring):
             dst = gathered[i % 2]
-            if world == 1:
-                be.gemv("q4_K", N_ROWS, K_COLS, src, W, dst, pdl=pdl)
-            else:
-                be.gemv("q4_K", N_ROWS, K_COLS, src, W, dst[lo:hi], pdl=False)
-                dist.all_gather_into_tensor(dst, dst[lo:hi])
-            src = dst[lo:hi]
+            be.gemv("q4_K", N_ROWS, K_COLS, src, W, dst, pdl=pdl)
+            src = dst
 
     def renorm():
         pass
+
+    def verify_nsplit():
+        """After a full pass: every rank holds the gathered outputs of the last two layers; recompute the last layer's
+        slices of ALL ranks locally (plain single-GPU kernel) and require the same bits."""
+        g_prev, g_last = group.gathered_numpy(RING - 2), group.gathered_numpy(RING - 1)
+        for d in range(world):
+            xd = torch.from_numpy(g_prev[d * N_ROWS:(d + 1) * N_ROWS].copy()).to(dev)
+            Wd = torch.from_numpy(shard(d, RING - 1)).to(dev)
+            yd = torch.zeros(N_ROWS, device=dev)
+            be.gemv("q4_K", N_ROWS, K_COLS, xd, Wd, yd)
+            want = yd.cpu().numpy()
+            got = g_last[d * N_ROWS:(d + 1) * N_ROWS]
+            if not np.array_equal(want.view(np.uint32), got.view(np.uint32)):
+                raise AssertionError(f"rank {rank}: gathered slice of rank {d} differs from the single-GPU kernel")
+        be.device_status()
+        return True
 
     # one CUDA graph per step (single GPU): the launch loop is otherwise bound by the host
     graph = None
@@ -298,8 +330,10 @@ def run_ours(args):
     with torch.cuda.stream(stream):
         step_body()
         stream.synchronize()
-        renorm()
-        if world == 1 and not args.no_graph:
+        verified = verify_nsplit() if group is not None else None
+        if world > 1:
+            dist.barrier()
+        if not args.no_graph:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step_body()
@@ -340,7 +374,11 @@ def run_ours(args):
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        finite = bool(torch.isfinite(gathered[0]).all() and torch.isfinite(gathered[1]).all())
+        if group is not None:
+            finite = bool(np.isfinite(group.gathered_numpy(RING - 1)).all())
+            be.device_status()
+        else:
+            finite = bool(torch.isfinite(gathered[0]).all() and torch.isfinite(gathered[1]).all())
 
     # ---- end to end through the host-pointer C ABI: host x in, host y out, per GEMV
     e2e = None
@@ -388,8 +426,10 @@ def run_ours(args):
                                       "chained like decoder layers" % RING,
                           "l2": "inputs larger than L2: %d MB of distinct weights per step" % (RING * WEIGHT_BYTES // 2**20),
                           "launch": ("CUDA graph, " if graph is not None else "eager, ") +
-                                    ("programmatic dependent launch" if (pdl and world == 1) else "plain launches"),
-                          "parallelism": "single GPU" if world == 1 else f"N-split x{world} + NCCL all-gather per GEMV",
+                                    ("programmatic dependent launch" if pdl else "plain launches"),
+                          "parallelism": "single GPU" if group is None else
+                          f"N-split x{world}: global weight [{world * N_ROWS}, {K_COLS}], output slices stored into every "
+                          f"rank's gathered vector by the GEMV epilogue (peer stores + arrival counters), verified={verified}",
                           "outputs_finite": finite},
                "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                             "frac": round(achieved / peak, 4), "peak_source": which + " (copy bandwidth)",
@@ -399,6 +439,8 @@ def run_ours(args):
                "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
                "other_decode_gemv_shapes": others}
         print(json.dumps(out))
+    if group is not None:
+        group.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -410,6 +452,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
+    ap.add_argument("--nsplit", action="store_true", help="run the N-split exchange path even on one GPU")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other decode GEMV shapes")

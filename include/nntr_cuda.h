@@ -140,6 +140,44 @@ int nntr_cuda_gemm_q4_K_noalloc_dev(unsigned M, unsigned N, unsigned K, const fl
 int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
                        void *stream);
 
+/* ------------------------------------------- N-split over the GPUs of a node */
+
+/** Device memory and CUDA IPC for callers without a framework (zero-filled). */
+int nntr_cuda_malloc(void **p, size_t bytes);
+int nntr_cuda_free(void *p);
+/** Synchronous copy after a device synchronise; kind 1 = host to device, 2 = device to host, 3 = device to device. */
+int nntr_cuda_memcpy(void *dst, const void *src, size_t bytes, int kind);
+/** Export / map a device allocation made with nntr_cuda_malloc across the processes of one node. */
+int nntr_cuda_ipc_export(const void *dev_ptr, unsigned char handle[64]);
+int nntr_cuda_ipc_open(const unsigned char handle[64], void **dev_ptr);
+int nntr_cuda_ipc_close(void *dev_ptr);
+
+/** Column-wise (N) split of a projection over the GPUs of one node with the
+ *  all-gather fused into the GEMV. The reference has no multi-device path; this
+ *  shards what __ggml_q4_K_8x8_q8_K_GEMM (ggml_interface_omp.cpp:404-432) splits
+ *  over CPU threads. Rank r owns rows [r*N_local, (r+1)*N_local) of the weight;
+ *  its kernel stores its output slice directly into the gathered vector of EVERY
+ *  rank (y[d], peer memory mapped with nntr_cuda_ipc_open) and then adds 1 per
+ *  CTA to every rank's arrival counter (arrivals[d], a zeroed 8-byte word in rank
+ *  d's memory). Before it reads its activation, a kernel waits -- bounded; on
+ *  expiry it raises the device status word and returns -- until its own counter
+ *  shows that every rank has delivered all earlier layers:
+ *      ((*epoch - 1) * layers_per_epoch + layer) * CTAs-per-launch * n_ranks.
+ *  `epoch` is a device word bumped once (nntr_cuda_epoch_bump_dev) before every
+ *  pass over a fixed sequence of `layers_per_epoch` launches, `layer` the
+ *  position of this launch in the sequence; every rank must issue the same
+ *  sequence with the same shapes. Gathered vectors need two alternating buffers. */
+typedef struct {
+  int n_ranks, rank;                /* 1..8 */
+  float *y[8];                      /* gathered output vector of every rank for this launch */
+  unsigned long long *arrivals[8];  /* arrival counter of every rank */
+  const unsigned long long *epoch;  /* this rank's epoch word */
+  unsigned layers_per_epoch, layer;
+} nntr_exchange;
+int nntr_cuda_gemv_nsplit_dev(int qtype, unsigned N_local, unsigned K, const float *x, const void *B,
+                              const nntr_exchange *ex, unsigned flags, void *stream);
+int nntr_cuda_epoch_bump_dev(unsigned long long *epoch, void *stream);
+
 /* ------------------------------------------------------ mixture of experts */
 
 /** One MoE layer's parameters, all device pointers. Stands in for the weights

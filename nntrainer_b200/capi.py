@@ -46,6 +46,14 @@ SIGNATURES = {
     "nntr_cuda_gemm_q6_K_dev": (_i, _GEMM_DEV),
     "nntr_cuda_gemm_q4_K_noalloc_dev": (_i, [_u, _u, _u, _vp, _u, _vp, _u, _vp, _u, _vp]),
     "nntr_cuda_gemv_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _u, _vp]),
+    "nntr_cuda_malloc": (_i, [C.POINTER(C.c_void_p), _sz]),
+    "nntr_cuda_free": (_i, [_vp]),
+    "nntr_cuda_memcpy": (_i, [_vp, _vp, _sz, _i]),
+    "nntr_cuda_ipc_export": (_i, [_vp, _vp]),
+    "nntr_cuda_ipc_open": (_i, [_vp, C.POINTER(C.c_void_p)]),
+    "nntr_cuda_ipc_close": (_i, [_vp]),
+    "nntr_cuda_gemv_nsplit_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _u, _vp]),
+    "nntr_cuda_epoch_bump_dev": (_i, [_vp, _vp]),
     "nntr_cuda_moe_workspace_bytes": (_sz, [_vp, _u]),
     "nntr_cuda_moe_forward_dev": (_i, [_vp, _u, _vp, _vp, _vp, _sz, _vp]),
     "nntr_cuda_moe_route_dev": (_i, [_vp, _u, _vp, _vp, _vp, _vp, _sz, _vp]),
@@ -67,6 +75,12 @@ class MoeDesc(C.Structure):
                 ("n_experts", C.c_uint), ("top_k", C.c_uint), ("router_w", C.c_void_p), ("router_bias", C.c_void_p),
                 ("gate_w", C.c_void_p), ("up_w", C.c_void_p), ("down_w", C.c_void_p), ("gate_b", C.c_void_p),
                 ("up_b", C.c_void_p), ("down_b", C.c_void_p), ("alpha", C.c_float)]
+
+
+class Exchange(C.Structure):
+    """nntr_exchange of include/nntr_cuda.h."""
+    _fields_ = [("n_ranks", C.c_int), ("rank", C.c_int), ("y", C.c_void_p * 8), ("arrivals", C.c_void_p * 8),
+                ("epoch", C.c_void_p), ("layers_per_epoch", C.c_uint), ("layer", C.c_uint)]
 
 
 def declared_symbols() -> list[str]:

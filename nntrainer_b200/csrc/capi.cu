@@ -362,6 +362,60 @@ int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const 
   }
 }
 
+/* ---- plain device memory and CUDA IPC, for callers that do not bring a framework ---- */
+int nntr_cuda_malloc(void **p, size_t bytes) {
+  if (!p)
+    return set_error(NNTR_CUDA_ERR_INVALID, "malloc: null pointer");
+  NNTR_CHECK_CUDA(cudaMalloc(p, bytes ? bytes : 16));
+  return check_cuda(cudaMemset(*p, 0, bytes ? bytes : 16), "malloc: clear");
+}
+int nntr_cuda_free(void *p) { return check_cuda(cudaFree(p), "free"); }
+int nntr_cuda_memcpy(void *dst, const void *src, size_t bytes, int kind) {
+  if (kind < 1 || kind > 3)
+    return set_error(NNTR_CUDA_ERR_INVALID, "memcpy: kind must be 1 (host to device), 2 (device to host) or 3 (device to device)");
+  NNTR_CHECK_CUDA(cudaDeviceSynchronize());
+  return check_cuda(cudaMemcpy(dst, src, bytes, static_cast<cudaMemcpyKind>(kind)), "memcpy");
+}
+int nntr_cuda_ipc_export(const void *dev_ptr, unsigned char handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  NNTR_CHECK_CUDA(cudaIpcGetMemHandle(&h, const_cast<void *>(dev_ptr)));
+  memcpy(handle, &h, 64);
+  return NNTR_CUDA_OK;
+}
+int nntr_cuda_ipc_open(const unsigned char handle[64], void **dev_ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  return check_cuda(cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess), "ipc_open");
+}
+int nntr_cuda_ipc_close(void *dev_ptr) { return check_cuda(cudaIpcCloseMemHandle(dev_ptr), "ipc_close"); }
+
+int nntr_cuda_epoch_bump_dev(unsigned long long *epoch, void *stream) {
+  return launch_epoch_bump(epoch, static_cast<cudaStream_t>(stream));
+}
+
+int nntr_cuda_gemv_nsplit_dev(int qtype, unsigned N_local, unsigned K, const float *x, const void *B,
+                              const nntr_exchange *ex, unsigned flags, void *stream) {
+  if (qtype != NNTR_Q4_K)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_nsplit: only Q4_K weights so far (got qtype %d)", qtype);
+  int rc = check_weight_shape(qtype, N_local, K);
+  if (rc)
+    return rc;
+  if (!ex)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_nsplit: null exchange");
+  GemvExchange g = {};
+  g.n_ranks = ex->n_ranks;
+  g.rank = ex->rank;
+  for (int d = 0; d < 8; ++d) {
+    g.y[d] = ex->y[d];
+    g.flag[d] = ex->arrivals[d];
+  }
+  g.epoch = ex->epoch;
+  g.layers_per_epoch = ex->layers_per_epoch;
+  g.layer = ex->layer;
+  return launch_gemv_q4_K_nsplit(N_local, K, x, B, g, flags, static_cast<cudaStream_t>(stream));
+}
+
 int nntr_cuda_register_weight(const void *host_ptr, size_t bytes, int qtype, unsigned N, unsigned K) {
   int rc = check_weight_shape(qtype, N, K);
   if (rc)

@@ -226,6 +226,24 @@ struct GemvBatch {
   long long y_stride; // elements between the outputs of consecutive problems
 };
 
+/** N-split of a projection over the GPUs of one node, exchange fused into the GEMV: every rank computes the output
+ *  rows of its weight shard and its epilogue stores them straight into EVERY rank's gathered vector (y[d], peer
+ *  memory mapped through CUDA IPC) at slice_offset, then adds 1 to every rank's arrival counter (flag[d], in rank d's
+ *  memory). Before a kernel reads its activation it waits (bounded) until its own counter shows that all CTAs of all
+ *  ranks have delivered every earlier layer: target = ((epoch - 1) * layers_per_epoch + layer) * arrivals_per_layer,
+ *  epoch being a device word bumped (from 0) once before every pass over the fixed launch sequence.
+ *  n_ranks == 0: no exchange. */
+struct GemvExchange {
+  int n_ranks, rank;
+  float *y[8];
+  unsigned long long *flag[8];
+  const unsigned long long *epoch;
+  unsigned layers_per_epoch, layer;
+  unsigned arrivals_per_layer; // CTAs per launch x ranks (filled in by the launcher)
+  unsigned long long slice_offset;
+  int debug; // development switch (0 in normal use)
+};
+
 /* launchers implemented in the .cu files (host side, return NNTR_CUDA_* codes) */
 int launch_quantize_q8_K(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, int rule, cudaStream_t st);
 int launch_quantize_q8_0(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, cudaStream_t st);
@@ -234,6 +252,9 @@ int launch_dequantize_weight(int qtype, const void *w, float *y, int64_t N, int6
 int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
 int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
                              unsigned n_problems, GemvBatch batch, cudaStream_t st);
+int launch_gemv_q4_K_nsplit(unsigned N, unsigned K, const float *x, const void *B, GemvExchange ex, unsigned flags,
+                            cudaStream_t st);
+int launch_epoch_bump(unsigned long long *epoch, cudaStream_t st);
 int launch_gemv_q4_0(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
 int launch_gemv_q6_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
 /* M > 1 with activations already quantized to plain Q8 rows in `qa` */

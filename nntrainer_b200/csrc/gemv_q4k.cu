@@ -205,7 +205,7 @@ __device__ __forceinline__ void row_block_sums(const uint8_t *blk, const uint8_t
 
 __global__ void __launch_bounds__(GEMV_THREADS, 2)
 gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, float *__restrict__ y, int n_groups,
-                 int nb, int ngslot, GemvBatch batch) {
+                 int nb, int ngslot, GemvBatch batch, GemvExchange ex) {
   extern __shared__ __align__(128) uint8_t smem[];
   if (batch.w_table) { // batched launch: blockIdx.y picks the problem
     const int p = blockIdx.y;
@@ -296,7 +296,14 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
             a0 = __fmaf_rn(v.x, v.y, a0);
             a1 = __fmaf_rn(v.z, v.w, a1);
           }
-          y[(size_t)(g_first + gl) * 8 + r] = __fsub_rn(a0, a1);
+          const float v = __fsub_rn(a0, a1);
+          const size_t o = (size_t)(g_first + gl) * 8 + r;
+          if (ex.n_ranks == 0) {
+            y[o] = v;
+          } else { // N-split: store the slice straight into every rank's gathered vector (peer stores over NVLink)
+            for (int d = 0; d < ex.n_ranks; ++d)
+              ex.y[d][ex.slice_offset + o] = v;
+          }
         }
       }
       __syncwarp();
@@ -305,12 +312,43 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       if (*abort_flag)
         break;
     }
+    if (ex.n_ranks && !*abort_flag) {
+      // this CTA's share of the slice is written: make it visible system-wide, then tell every rank
+      if (!(ex.debug & 1))
+        __threadfence_system();
+      __syncwarp();
+      if (lane < ex.n_ranks && !(ex.debug & 2))
+        atomicAdd_system(ex.flag[lane], 1ull);
+    }
     trace_stamp(5);
   } else {
     // ----------------------------------------------------------- consumers
     pdl_wait();
+    if (ex.n_ranks && !(ex.debug & 4)) {
+      // the activation is complete once every CTA of every rank has delivered the previous layer
+      if (threadIdx.x == 0) {
+        const unsigned long long target =
+          ((unsigned long long)(*ex.epoch - 1) * ex.layers_per_epoch + ex.layer) * ex.arrivals_per_layer;
+        const volatile unsigned long long *f = ex.flag[ex.rank];
+        bool ok = false;
+        for (uint32_t it = 0; it < (1u << 24); ++it) {
+          if (*f >= target) {
+            ok = true;
+            break;
+          }
+          if (it > 64)
+            __nanosleep(64);
+        }
+        if (!ok) {
+          *abort_flag = 1;
+          atomicExch(&g_device_status, NNTR_CUDA_ERR_TIMEOUT);
+        }
+        __threadfence_system();
+      }
+      consumer_bar_sync();
+    }
     trace_stamp(2);
-    for (int b = warp; b < nb; b += CONSUMER_WARPS) {
+    for (int b = warp; b < nb && !*abort_flag; b += CONSUMER_WARPS) {
       const float *xs = x + b * QK_K + lane * 8;
       const float4 v0 = *reinterpret_cast<const float4 *>(xs);
       const float4 v1 = *reinterpret_cast<const float4 *>(xs + 4);
@@ -381,6 +419,27 @@ int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, floa
   return launch_gemv_q4_K_batched(N, K, x, B, y, flags, 1, none, st);
 }
 
+static GemvExchange g_no_exchange = {};
+static thread_local const GemvExchange *g_next_exchange = nullptr; // set by launch_gemv_q4_K_nsplit around its launch
+
+int launch_gemv_q4_K_nsplit(unsigned N, unsigned K, const float *x, const void *B, GemvExchange ex, unsigned flags,
+                            cudaStream_t st) {
+  if (ex.n_ranks < 1 || ex.n_ranks > 8 || ex.rank < 0 || ex.rank >= ex.n_ranks || !ex.epoch)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_nsplit: bad exchange description");
+  for (int d = 0; d < ex.n_ranks; ++d)
+    if (!ex.y[d] || !ex.flag[d])
+      return set_error(NNTR_CUDA_ERR_INVALID, "gemv_nsplit: null peer pointer for rank %d", d);
+  GemvBatch none = {};
+  ex.slice_offset = (unsigned long long)ex.rank * N;
+  // arrivals per layer at every rank = CTAs per launch (same on all ranks) x ranks; filled in by the launcher below
+  static thread_local GemvExchange tl_ex;
+  tl_ex = ex;
+  g_next_exchange = &tl_ex;
+  const int rc = launch_gemv_q4_K_batched(N, K, x, B, ex.y[ex.rank] + ex.slice_offset, flags, 1, none, st);
+  g_next_exchange = nullptr;
+  return rc;
+}
+
 /* n_problems > 1: `batch.w_table` (device memory) holds one weight pointer per problem, B is ignored. */
 int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
                              unsigned n_problems, GemvBatch batch, cudaStream_t st) {
@@ -430,9 +489,25 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
   cfg.attrs = attr;
   cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
   const BlockQ4Kx8 *Wp = static_cast<const BlockQ4Kx8 *>(B);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel, x, Wp, y, n_groups, nb, ngslot, batch);
+  GemvExchange ex = g_no_exchange;
+  if (g_next_exchange) {
+    ex = *g_next_exchange;
+    ex.arrivals_per_layer = (unsigned)grid * (unsigned)ex.n_ranks;
+    ex.debug = env_int("NNTR_CUDA_NSPLIT_DEBUG", 0);
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel, x, Wp, y, n_groups, nb, ngslot, batch, ex);
   count_launch();
   return check_cuda(e, "gemv_q4_K launch");
+}
+
+__global__ void epoch_bump_kernel(unsigned long long *epoch) { *epoch += 1; }
+
+int launch_epoch_bump(unsigned long long *epoch, cudaStream_t st) {
+  if (!epoch)
+    return set_error(NNTR_CUDA_ERR_INVALID, "epoch_bump: null pointer");
+  epoch_bump_kernel<<<1, 1, 0, st>>>(epoch);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "epoch_bump launch");
 }
 
 int read_device_status(int *out) {

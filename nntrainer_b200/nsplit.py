@@ -1,0 +1,147 @@
+"""Column-wise (N) split of dense projections over the GPUs of one node, one
+process per GPU, with the all-gather fused into the GEMV kernel.
+
+Dense projections and the lm_head shard by output rows (the 8-row-interleaved
+layout makes a shard a contiguous slice of the tensor's bytes). Every rank's
+GEMV epilogue stores its output slice straight into the gathered vector of every
+rank over NVLink (peer memory mapped with CUDA IPC) and bumps an arrival counter
+there; the next GEMV waits on its own counter. ``torch.distributed`` is used
+only to exchange the IPC handles and for barriers; no collective runs on the
+data path.
+
+Host-side helpers (``shard_rows``, ``exchange_targets``) are plain functions so
+that they can be tested on CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import capi
+from .capi import QTYPE, check, lib
+
+MAX_RANKS = 8
+
+
+def shard_rows(N: int, world: int, rank: int, qtype: str = "q4_K") -> tuple[int, int]:
+    """Rows [lo, hi) of an N-row projection owned by ``rank``: equal shards whose boundaries fall on multiples of 8
+    rows for the 8-row-interleaved formats (a shard must be whole row groups)."""
+    align = 8 if qtype in ("q4_K", "q4_0") else 1
+    if N % (world * align):
+        raise ValueError(f"N={N} does not split into {world} shards of whole {align}-row groups")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_bytes(qtype: str, N: int, K: int, world: int, rank: int) -> tuple[int, int]:
+    """Byte range of the tensor that holds the rank's rows."""
+    bs, bb = {"q4_0": (32, 18), "q4_K": (256, 144), "q6_K": (256, 210)}[qtype]
+    lo, hi = shard_rows(N, world, rank, qtype)
+    row = K // bs * bb
+    return lo * row, hi * row
+
+
+def exchange_targets(epoch: int, layers_per_epoch: int, layer: int, ctas: int, world: int) -> int:
+    """Arrival count a kernel waits for before reading its activation (mirrors the device-side formula)."""
+    return ((epoch - 1) * layers_per_epoch + layer) * ctas * world
+
+
+class NSplitGroup:
+    """Per-process state of an N-split group: two alternating gathered vectors, an arrival counter and an epoch
+    word in this rank's memory, and the peers' copies mapped through CUDA IPC."""
+
+    def __init__(self, n_local: int, layers_per_epoch: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self.dist, self.torch = dist, torch
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > MAX_RANKS:
+            raise ValueError("N-split groups span the GPUs of one node (at most 8 ranks)")
+        self.n_local, self.layers = n_local, layers_per_epoch
+        L = lib()
+        self._own = []
+        nbytes = self.world * n_local * 4
+
+        def alloc(n):
+            p = C.c_void_p()
+            check(L.nntr_cuda_malloc(C.byref(p), n))
+            self._own.append(p.value)
+            return p.value
+
+        self.buf = [alloc(nbytes), alloc(nbytes)]  # gathered vectors (ping-pong)
+        self.counter = alloc(8)
+        self.epoch = alloc(8)
+        # exchange IPC handles of buf[0], buf[1], counter
+        mine = []
+        for p in (self.buf[0], self.buf[1], self.counter):
+            h = (C.c_ubyte * 64)()
+            check(L.nntr_cuda_ipc_export(p, h))
+            mine.append(bytes(h))
+        if self.world > 1:
+            allh = [None] * self.world
+            dist.all_gather_object(allh, mine, group=group)
+        else:
+            allh = [mine]
+        self._opened = []
+        self.peer = []  # per rank: (buf0, buf1, counter) device pointers valid in THIS process
+        for r in range(self.world):
+            if r == self.rank:
+                self.peer.append((self.buf[0], self.buf[1], self.counter))
+                continue
+            ptrs = []
+            for hb in allh[r]:
+                p = C.c_void_p()
+                check(L.nntr_cuda_ipc_open((C.c_ubyte * 64).from_buffer_copy(hb), C.byref(p)))
+                self._opened.append(p.value)
+                ptrs.append(p.value)
+            self.peer.append(tuple(ptrs))
+        if self.world > 1:
+            dist.barrier(group=group)
+
+    def exchange(self, layer: int) -> capi.Exchange:
+        """Description of launch ``layer`` of the sequence: it writes gathered buffer layer % 2."""
+        ex = capi.Exchange()
+        ex.n_ranks, ex.rank = self.world, self.rank
+        for r in range(self.world):
+            ex.y[r] = self.peer[r][layer % 2]
+            ex.arrivals[r] = self.peer[r][2]
+        ex.epoch = self.epoch
+        ex.layers_per_epoch, ex.layer = self.layers, layer
+        return ex
+
+    def input_ptr(self, layer: int) -> int:
+        """Where launch ``layer`` (>= 1) finds its activation: this rank's slice of the previous gathered vector."""
+        return self.buf[(layer - 1) % 2] + self.rank * self.n_local * 4
+
+    def gathered_ptr(self, layer: int) -> int:
+        return self.buf[layer % 2]
+
+    def bump_epoch(self, stream: int) -> None:
+        check(lib().nntr_cuda_epoch_bump_dev(self.epoch, stream))
+
+    def gemv(self, qtype: str, K: int, x_ptr: int, w_ptr: int, layer: int, stream: int, pdl: bool = False) -> None:
+        ex = self.exchange(layer)
+        check(lib().nntr_cuda_gemv_nsplit_dev(QTYPE[qtype], self.n_local, K, x_ptr, w_ptr, C.byref(ex),
+                                              capi.GEMV_PDL if pdl else 0, stream))
+
+    def gathered_numpy(self, layer: int):
+        """Host copy of the gathered vector launch ``layer`` produced (synchronising; for checks)."""
+        import numpy as np
+        out = np.empty(self.world * self.n_local, dtype=np.float32)
+        check(lib().nntr_cuda_memcpy(out.ctypes.data, self.gathered_ptr(layer), out.nbytes, 2))
+        return out
+
+    def close(self) -> None:
+        L = lib()
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        for p in self._opened:
+            L.nntr_cuda_ipc_close(p)
+        self._opened = []
+        if self.world > 1:
+            self.dist.barrier()
+        for p in self._own:
+            L.nntr_cuda_free(p)
+        self._own = []
