@@ -156,23 +156,30 @@ int nntr_cuda_ipc_close(void *dev_ptr);
  *  all-gather fused into the GEMV. The reference has no multi-device path; this
  *  shards what __ggml_q4_K_8x8_q8_K_GEMM (ggml_interface_omp.cpp:404-432) splits
  *  over CPU threads. Rank r owns rows [r*N_local, (r+1)*N_local) of the weight;
- *  its kernel stores its output slice directly into the gathered vector of EVERY
- *  rank (y[d], peer memory mapped with nntr_cuda_ipc_open) and then adds 1 per
- *  CTA to every rank's arrival counter (arrivals[d], a zeroed 8-byte word in rank
- *  d's memory). Before it reads its activation, a kernel waits -- bounded; on
- *  expiry it raises the device status word and returns -- until its own counter
- *  shows that every rank has delivered all earlier layers:
- *      ((*epoch - 1) * layers_per_epoch + layer) * CTAs-per-launch * n_ranks.
+ *  its kernel stores each output as an 8-byte (fp32 value, launch number) pair
+ *  directly into the gathered vector of EVERY rank (y[d], 8 bytes per element,
+ *  peer memory mapped with nntr_cuda_ipc_open). The next launch takes such a
+ *  vector as its activation (x_tagged = 1, x points at the pairs) and polls the
+ *  number of every element it reads, so the exchange needs no fence and no
+ *  collective call. Gathered vectors alternate between two buffers; so that a
+ *  fast rank cannot overwrite what a slow one still reads, every CTA stores the
+ *  launch number into its slot of every rank's flag array (flags[d]:
+ *  NNTR_CUDA_NSPLIT_FLAG_BYTES zeroed bytes in rank d's memory) once it has read
+ *  its input, and no CTA stores outputs before all slots of its own array show
+ *  the previous launch. Launch number = (*epoch - 1) * layers_per_epoch + layer + 1:
  *  `epoch` is a device word bumped once (nntr_cuda_epoch_bump_dev) before every
  *  pass over a fixed sequence of `layers_per_epoch` launches, `layer` the
- *  position of this launch in the sequence; every rank must issue the same
- *  sequence with the same shapes. Gathered vectors need two alternating buffers. */
+ *  position of this launch in it; every rank issues the same sequence with the
+ *  same shapes. Every wait is bounded; on expiry the kernel raises the device
+ *  status word and returns. */
+#define NNTR_CUDA_NSPLIT_FLAG_BYTES (8 * 512 * 8)
 typedef struct {
   int n_ranks, rank;                /* 1..8 */
-  float *y[8];                      /* gathered output vector of every rank for this launch */
-  unsigned long long *arrivals[8];  /* arrival counter of every rank */
+  void *y[8];                       /* gathered (value, number) vector of every rank for this launch */
+  unsigned long long *flags[8];     /* flag array of every rank */
   const unsigned long long *epoch;  /* this rank's epoch word */
   unsigned layers_per_epoch, layer;
+  int x_tagged;                     /* the activation of this launch is a (value, number) vector */
 } nntr_exchange;
 int nntr_cuda_gemv_nsplit_dev(int qtype, unsigned N_local, unsigned K, const float *x, const void *B,
                               const nntr_exchange *ex, unsigned flags, void *stream);

@@ -407,12 +407,13 @@ int nntr_cuda_gemv_nsplit_dev(int qtype, unsigned N_local, unsigned K, const flo
   g.n_ranks = ex->n_ranks;
   g.rank = ex->rank;
   for (int d = 0; d < 8; ++d) {
-    g.y[d] = ex->y[d];
-    g.flag[d] = ex->arrivals[d];
+    g.y[d] = reinterpret_cast<uint2 *>(ex->y[d]);
+    g.flag[d] = ex->flags[d];
   }
   g.epoch = ex->epoch;
   g.layers_per_epoch = ex->layers_per_epoch;
   g.layer = ex->layer;
+  g.x_tagged = ex->x_tagged;
   return launch_gemv_q4_K_nsplit(N_local, K, x, B, g, flags, static_cast<cudaStream_t>(stream));
 }
 

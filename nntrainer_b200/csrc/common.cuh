@@ -226,22 +226,26 @@ struct GemvBatch {
   long long y_stride; // elements between the outputs of consecutive problems
 };
 
-/** N-split of a projection over the GPUs of one node, exchange fused into the GEMV: every rank computes the output
- *  rows of its weight shard and its epilogue stores them straight into EVERY rank's gathered vector (y[d], peer
- *  memory mapped through CUDA IPC) at slice_offset, then adds 1 to every rank's arrival counter (flag[d], in rank d's
- *  memory). Before a kernel reads its activation it waits (bounded) until its own counter shows that all CTAs of all
- *  ranks have delivered every earlier layer: target = ((epoch - 1) * layers_per_epoch + layer) * arrivals_per_layer,
- *  epoch being a device word bumped (from 0) once before every pass over the fixed launch sequence.
- *  n_ranks == 0: no exchange. */
+/** N-split of a projection over the GPUs of one node, exchange fused into the GEMV, without fences:
+ *   data   every rank computes the output rows of its weight shard and its epilogue stores each as an 8-byte
+ *          (value, launch number) pair straight into EVERY rank's gathered vector (y[d], peer memory mapped through
+ *          CUDA IPC) at slice_offset. A reader polls the number of every element it uses, so no ordering between
+ *          the stores is needed (x_tagged: this launch's activation is such a vector).
+ *   reuse  gathered vectors alternate between two buffers; launch seq overwrites what launch seq - 1 read. When a CTA
+ *          has finished reading its input it stores seq into slot [rank][CTA] of every rank's flag array (flag[d],
+ *          NSPLIT_MAX_CTAS slots per source rank); an epilogue stores nothing before all slots of its own array show
+ *          seq - 1.
+ *  seq = (epoch - 1) * layers_per_epoch + layer + 1, epoch being a device word bumped (from 0) once before every pass
+ *  over the fixed launch sequence. Every wait is bounded. n_ranks == 0: no exchange. */
+constexpr int NSPLIT_MAX_CTAS = 512;
 struct GemvExchange {
   int n_ranks, rank;
-  float *y[8];
+  uint2 *y[8];
   unsigned long long *flag[8];
   const unsigned long long *epoch;
   unsigned layers_per_epoch, layer;
-  unsigned arrivals_per_layer; // CTAs per launch x ranks (filled in by the launcher)
   unsigned long long slice_offset;
-  int debug; // development switch (0 in normal use)
+  int x_tagged;
 };
 
 /* launchers implemented in the .cu files (host side, return NNTR_CUDA_* codes) */

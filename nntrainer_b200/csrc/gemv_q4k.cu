@@ -283,6 +283,38 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     // ------------------------------------------------------------ epilogue
     pdl_wait(); // y may still be read by the previous kernel until it has finished
     const int j = lane >> 3, r = lane & 7;
+    uint32_t tag = 0;
+    if (ex.n_ranks) {
+      // N-split. Launch number seq writes gathered buffer seq % 2 on every rank. A rank reads that buffer as the input
+      // of launch seq - 1, so before the first store every CTA of every rank must have said "launch seq - 1: done
+      // reading" (a relaxed store into its flag slot, see the consumers; a peer may already be one launch ahead, hence
+      // >=). The poll runs while the consumer warps work, and it is bounded.
+      const unsigned long long seq = (unsigned long long)(*ex.epoch - 1) * ex.layers_per_epoch + ex.layer + 1;
+      tag = (uint32_t)seq;
+      if (seq > 1 && ex.n_ranks > 1) {
+        // slots of the other ranks only: this rank's own launch seq - 1 has finished (stream order). All of a lane's
+        // loads are issued together; the round is repeated (bounded) while any slot is still behind.
+        const int per_rank = (int)gridDim.x, n_slots = (ex.n_ranks - 1) * per_rank;
+        bool all_ok = false;
+        for (uint32_t it = 0; it < (1u << 20) && !all_ok; ++it) {
+          bool mine = true;
+          for (int t = lane; t < n_slots; t += 32) {
+            int src = t / per_rank;
+            src += (src >= ex.rank);
+            const volatile unsigned long long *slot =
+              ex.flag[ex.rank] + (size_t)src * NSPLIT_MAX_CTAS + (t - (t / per_rank) * per_rank);
+            mine = mine && (*slot >= seq - 1);
+          }
+          all_ok = __all_sync(FULL, mine);
+          if (!all_ok && it > 4)
+            __nanosleep(200);
+        }
+        if (!all_ok) {
+          *abort_flag = 1;
+          atomicExch(&g_device_status, NNTR_CUDA_ERR_TIMEOUT);
+        }
+      }
+    }
     for (int gl0 = 0; gl0 < ng; gl0 += 4) {
       const int gl = gl0 + j;
       if (gl < ng) {
@@ -300,9 +332,14 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
           const size_t o = (size_t)(g_first + gl) * 8 + r;
           if (ex.n_ranks == 0) {
             y[o] = v;
-          } else { // N-split: store the slice straight into every rank's gathered vector (peer stores over NVLink)
-            for (int d = 0; d < ex.n_ranks; ++d)
-              ex.y[d][ex.slice_offset + o] = v;
+          } else {
+            // (value, launch number) in one 8-byte store straight into every rank's gathered vector: the reader checks
+            // the number of every element it uses, so no fence orders these stores against anything
+            for (int d = 0; d < ex.n_ranks; ++d) {
+              volatile uint2 *dst = ex.y[d] + ex.slice_offset + o;
+              asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag)
+                           : "memory");
+            }
           }
         }
       }
@@ -312,46 +349,66 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       if (*abort_flag)
         break;
     }
-    if (ex.n_ranks && !*abort_flag) {
-      // this CTA's share of the slice is written: make it visible system-wide, then tell every rank
-      if (!(ex.debug & 1))
-        __threadfence_system();
-      __syncwarp();
-      if (lane < ex.n_ranks && !(ex.debug & 2))
-        atomicAdd_system(ex.flag[lane], 1ull);
-    }
     trace_stamp(5);
   } else {
     // ----------------------------------------------------------- consumers
     pdl_wait();
-    if (ex.n_ranks && !(ex.debug & 4)) {
-      // the activation is complete once every CTA of every rank has delivered the previous layer
-      if (threadIdx.x == 0) {
-        const unsigned long long target =
-          ((unsigned long long)(*ex.epoch - 1) * ex.layers_per_epoch + ex.layer) * ex.arrivals_per_layer;
-        const volatile unsigned long long *f = ex.flag[ex.rank];
-        bool ok = false;
-        for (uint32_t it = 0; it < (1u << 24); ++it) {
-          if (*f >= target) {
-            ok = true;
-            break;
+    trace_stamp(2);
+    const uint32_t in_tag =
+      ex.n_ranks ? (uint32_t)((unsigned long long)(*ex.epoch - 1) * ex.layers_per_epoch + ex.layer) : 0u;
+    for (int b = warp; b < nb && !*abort_flag; b += CONSUMER_WARPS) {
+      float4 v0, v1;
+      if (ex.x_tagged) {
+        // the activation arrives as (value, launch number) pairs stored by the previous launch of every rank:
+        // poll (bounded) until all eight elements of the lane carry that launch's number
+        const uint4 *xs = reinterpret_cast<const uint4 *>(x) + (size_t)(b * QK_K + lane * 8) / 2;
+        // cheap wait first: one lane polls the number of the block's last element (8 bytes per round instead of
+        // 2 KB), then everything is read and every number checked; a stale element sends the warp round again
+        {
+          const volatile uint32_t *probe = reinterpret_cast<const volatile uint32_t *>(x) + 2 * (size_t)(b * QK_K + 255) + 1;
+          bool seen = false;
+          for (uint32_t it = 0; it < (1u << 22) && !seen; ++it) {
+            uint32_t t = 0;
+            if (lane == 0)
+              t = *probe;
+            seen = __shfl_sync(FULL, t, 0) == in_tag;
+            if (!seen && it > 4)
+              __nanosleep(100);
           }
-          if (it > 64)
-            __nanosleep(64);
+        }
+        bool ok = false;
+        for (uint32_t it = 0; it < (1u << 20) && !ok; ++it) {
+          uint4 e[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(e[i].x), "=r"(e[i].y), "=r"(e[i].z), "=r"(e[i].w)
+                         : "l"(xs + i)
+                         : "memory");
+          bool mine = true;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            mine = mine && e[i].y == in_tag && e[i].w == in_tag;
+          ok = __all_sync(FULL, mine);
+          if (ok) {
+            v0 = make_float4(__uint_as_float(e[0].x), __uint_as_float(e[0].z), __uint_as_float(e[1].x),
+                             __uint_as_float(e[1].z));
+            v1 = make_float4(__uint_as_float(e[2].x), __uint_as_float(e[2].z), __uint_as_float(e[3].x),
+                             __uint_as_float(e[3].z));
+          } else if (it > 2) {
+            __nanosleep(200);
+          }
         }
         if (!ok) {
           *abort_flag = 1;
           atomicExch(&g_device_status, NNTR_CUDA_ERR_TIMEOUT);
+          break;
         }
-        __threadfence_system();
+      } else {
+        const float *xs = x + b * QK_K + lane * 8;
+        v0 = *reinterpret_cast<const float4 *>(xs);
+        v1 = *reinterpret_cast<const float4 *>(xs + 4);
       }
-      consumer_bar_sync();
-    }
-    trace_stamp(2);
-    for (int b = warp; b < nb && !*abort_flag; b += CONSUMER_WARPS) {
-      const float *xs = x + b * QK_K + lane * 8;
-      const float4 v0 = *reinterpret_cast<const float4 *>(xs);
-      const float4 v1 = *reinterpret_cast<const float4 *>(xs + 4);
       const Q8KLane qv = q8K_quantize_warp(v0, v1, lane, 0);
       uint8_t *dst = act + b * ACT_STRIDE;
       *reinterpret_cast<uint2 *>(dst + 8 * lane) = make_uint2(qv.w0, qv.w1);
@@ -363,6 +420,12 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
         *reinterpret_cast<float *>(dst + 272) = qv.d;
     }
     consumer_bar_sync();
+    if (ex.n_ranks && threadIdx.x < ex.n_ranks && !*abort_flag) {
+      // this CTA has finished reading its input: tell every rank (relaxed store, nothing needs to be ordered after it)
+      const unsigned long long seq = (unsigned long long)in_tag + 1;
+      volatile unsigned long long *slot = ex.flag[threadIdx.x] + (size_t)ex.rank * NSPLIT_MAX_CTAS + blockIdx.x;
+      *slot = seq;
+    }
     trace_stamp(3);
 
     const int j = lane >> 3, r = lane & 7;
@@ -435,7 +498,7 @@ int launch_gemv_q4_K_nsplit(unsigned N, unsigned K, const float *x, const void *
   static thread_local GemvExchange tl_ex;
   tl_ex = ex;
   g_next_exchange = &tl_ex;
-  const int rc = launch_gemv_q4_K_batched(N, K, x, B, ex.y[ex.rank] + ex.slice_offset, flags, 1, none, st);
+  const int rc = launch_gemv_q4_K_batched(N, K, x, B, reinterpret_cast<float *>(ex.y[ex.rank]), flags, 1, none, st);
   g_next_exchange = nullptr;
   return rc;
 }
@@ -492,8 +555,8 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
   GemvExchange ex = g_no_exchange;
   if (g_next_exchange) {
     ex = *g_next_exchange;
-    ex.arrivals_per_layer = (unsigned)grid * (unsigned)ex.n_ranks;
-    ex.debug = env_int("NNTR_CUDA_NSPLIT_DEBUG", 0);
+    if (grid > (unsigned)NSPLIT_MAX_CTAS)
+      return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_nsplit: %u CTAs exceed the %d flag slots per rank", grid, NSPLIT_MAX_CTAS);
   }
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel, x, Wp, y, n_groups, nb, ngslot, batch, ex);
   count_launch();

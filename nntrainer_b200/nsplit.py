@@ -4,12 +4,13 @@ process per GPU, with the all-gather fused into the GEMV kernel.
 Dense projections and the lm_head shard by output rows (the 8-row-interleaved
 layout makes a shard a contiguous slice of the tensor's bytes). Every rank's
 GEMV epilogue stores its output slice straight into the gathered vector of every
-rank over NVLink (peer memory mapped with CUDA IPC) and bumps an arrival counter
-there; the next GEMV waits on its own counter. ``torch.distributed`` is used
+rank over NVLink (peer memory mapped with CUDA IPC) as (value, launch number)
+pairs; the next GEMV polls the numbers of the elements it reads. No fence, no
+collective call. ``torch.distributed`` is used
 only to exchange the IPC handles and for barriers; no collective runs on the
 data path.
 
-Host-side helpers (``shard_rows``, ``exchange_targets``) are plain functions so
+Host-side helpers (``shard_rows``, ``sequence_number``) are plain functions so
 that they can be tested on CPU.
 """
 from __future__ import annotations
@@ -40,13 +41,14 @@ def shard_bytes(qtype: str, N: int, K: int, world: int, rank: int) -> tuple[int,
     return lo * row, hi * row
 
 
-def exchange_targets(epoch: int, layers_per_epoch: int, layer: int, ctas: int, world: int) -> int:
-    """Arrival count a kernel waits for before reading its activation (mirrors the device-side formula)."""
-    return ((epoch - 1) * layers_per_epoch + layer) * ctas * world
+def sequence_number(epoch: int, layers_per_epoch: int, layer: int) -> int:
+    """Sequence number a launch publishes in its flag slots; it waits for every slot to show this number minus one
+    (mirrors the device-side formula; the first launch ever, number 1, waits for nothing)."""
+    return (epoch - 1) * layers_per_epoch + layer + 1
 
 
 class NSplitGroup:
-    """Per-process state of an N-split group: two alternating gathered vectors, an arrival counter and an epoch
+    """Per-process state of an N-split group: two alternating gathered vectors, a flag array and an epoch
     word in this rank's memory, and the peers' copies mapped through CUDA IPC."""
 
     def __init__(self, n_local: int, layers_per_epoch: int, group=None):
@@ -61,7 +63,7 @@ class NSplitGroup:
         self.n_local, self.layers = n_local, layers_per_epoch
         L = lib()
         self._own = []
-        nbytes = self.world * n_local * 4
+        nbytes = self.world * n_local * 8  # (fp32 value, launch number) per element
 
         def alloc(n):
             p = C.c_void_p()
@@ -70,7 +72,7 @@ class NSplitGroup:
             return p.value
 
         self.buf = [alloc(nbytes), alloc(nbytes)]  # gathered vectors (ping-pong)
-        self.counter = alloc(8)
+        self.counter = alloc(8 * 512 * 8)  # flag array: [source rank][source CTA] sequence numbers
         self.epoch = alloc(8)
         # exchange IPC handles of buf[0], buf[1], counter
         mine = []
@@ -99,20 +101,23 @@ class NSplitGroup:
         if self.world > 1:
             dist.barrier(group=group)
 
-    def exchange(self, layer: int) -> capi.Exchange:
+    def exchange(self, layer: int, x_tagged: bool = True) -> capi.Exchange:
         """Description of launch ``layer`` of the sequence: it writes gathered buffer layer % 2."""
         ex = capi.Exchange()
         ex.n_ranks, ex.rank = self.world, self.rank
         for r in range(self.world):
             ex.y[r] = self.peer[r][layer % 2]
-            ex.arrivals[r] = self.peer[r][2]
+            ex.flags[r] = self.peer[r][2]
         ex.epoch = self.epoch
         ex.layers_per_epoch, ex.layer = self.layers, layer
+        ex.x_tagged = 1 if x_tagged else 0
         return ex
 
-    def input_ptr(self, layer: int) -> int:
-        """Where launch ``layer`` (>= 1) finds its activation: this rank's slice of the previous gathered vector."""
-        return self.buf[(layer - 1) % 2] + self.rank * self.n_local * 4
+    def input_ptr(self, layer: int, src_rank: int | None = None) -> int:
+        """Where launch ``layer`` (>= 1) finds its activation: the slice rank ``src_rank`` (default: this rank)
+        contributed to the previous gathered vector."""
+        r = self.rank if src_rank is None else src_rank
+        return self.buf[(layer - 1) % 2] + r * self.n_local * 8
 
     def gathered_ptr(self, layer: int) -> int:
         return self.buf[layer % 2]
@@ -120,17 +125,20 @@ class NSplitGroup:
     def bump_epoch(self, stream: int) -> None:
         check(lib().nntr_cuda_epoch_bump_dev(self.epoch, stream))
 
-    def gemv(self, qtype: str, K: int, x_ptr: int, w_ptr: int, layer: int, stream: int, pdl: bool = False) -> None:
-        ex = self.exchange(layer)
+    def gemv(self, qtype: str, K: int, x_ptr: int, w_ptr: int, layer: int, stream: int, pdl: bool = False,
+             x_tagged: bool = True) -> None:
+        """Launch ``layer`` of the sequence. ``x_ptr`` is this rank's slice of the previous gathered vector
+        (``input_ptr``, tagged pairs) or, with ``x_tagged=False``, a plain fp32 vector."""
+        ex = self.exchange(layer, x_tagged)
         check(lib().nntr_cuda_gemv_nsplit_dev(QTYPE[qtype], self.n_local, K, x_ptr, w_ptr, C.byref(ex),
                                               capi.GEMV_PDL if pdl else 0, stream))
 
     def gathered_numpy(self, layer: int):
         """Host copy of the gathered vector launch ``layer`` produced (synchronising; for checks)."""
         import numpy as np
-        out = np.empty(self.world * self.n_local, dtype=np.float32)
-        check(lib().nntr_cuda_memcpy(out.ctypes.data, self.gathered_ptr(layer), out.nbytes, 2))
-        return out
+        raw = np.empty(2 * self.world * self.n_local, dtype=np.float32)
+        check(lib().nntr_cuda_memcpy(raw.ctypes.data, self.gathered_ptr(layer), raw.nbytes, 2))
+        return np.ascontiguousarray(raw[0::2])  # drop the launch numbers
 
     def close(self) -> None:
         L = lib()

@@ -36,11 +36,12 @@ def test_a_shard_is_a_byte_slice_and_gives_the_matching_output_slice(port, q, ge
         assert np.array_equal(part.view(np.uint32), full[lo:hi].view(np.uint32))
 
 
-def test_exchange_target_counts_all_earlier_layers():
-    # 148 CTAs per launch, 2 ranks, 48 launches per pass: launch 0 of pass 1 waits for nothing,
-    # launch 5 of pass 3 for two whole passes plus five launches
-    assert nsplit.exchange_targets(1, 48, 0, 148, 2) == 0
-    assert nsplit.exchange_targets(3, 48, 5, 148, 2) == (2 * 48 + 5) * 148 * 2
+def test_sequence_numbers_are_consecutive_across_passes():
+    # 48 launches per pass: the last launch of pass 2 and the first of pass 3 are consecutive,
+    # so a launch always waits for "its number minus one" whatever its position
+    assert nsplit.sequence_number(1, 48, 0) == 1
+    assert nsplit.sequence_number(2, 48, 47) + 1 == nsplit.sequence_number(3, 48, 0)
+    assert [nsplit.sequence_number(1, 3, i) for i in range(3)] + [nsplit.sequence_number(2, 3, 0)] == [1, 2, 3, 4]
 
 
 def _rank_main(rank, world, port, q):
