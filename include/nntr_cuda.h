@@ -95,8 +95,23 @@ int nntr_cuda_dequantize_row_dev(int qtype, const void *x, float *y, int64_t k, 
  *  values equal dequantize_row_* applied to the un-interleaved rows. */
 int nntr_cuda_dequantize_weight_dev(int qtype, const void *w, float *y, int64_t N, int64_t K, void *stream);
 
-/** Bytes of scratch a *_dev GEMM call needs for its quantized activations. */
+/** Bytes of scratch a *_dev GEMM call needs for its quantized activations
+ *  (enough for whichever path nntr_cuda_set_gemm_path selects). */
 size_t nntr_cuda_gemm_workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K);
+
+/** Which kernels serve Q4_K GEMMs with M > 1 (process-wide):
+ *   EXACT   integer dot products on the CUDA cores with the reference's exact
+ *           floating-point chain: C equals the CPU result bit for bit;
+ *   TENSOR  tcgen05 int8 tensor-core kernel (needs N % 128 == 0): exact integer
+ *           sums, one rounding more per super-block in the fp32 combination, C
+ *           within max-rel 2e-3 of the CPU result (the tolerance the CPU path's
+ *           own SIMD variants have among themselves);
+ *   AUTO    TENSOR where it applies and M >= 32, else EXACT (the default).
+ *  There is no CPU counterpart: the reference picks its SIMD variant at build time. */
+#define NNTR_CUDA_GEMM_PATH_AUTO 0
+#define NNTR_CUDA_GEMM_PATH_EXACT 1
+#define NNTR_CUDA_GEMM_PATH_TENSOR 2
+int nntr_cuda_set_gemm_path(int path);
 
 /** C[M][N] = A[M][K] x W^T with W a quantized [N][K] weight (device pointers).
  *  Same argument meaning as cpu_backend.h:937-977 gemm_q4_0 / gemm_q4_K /

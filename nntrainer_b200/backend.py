@@ -84,6 +84,15 @@ def _gemm(qtype: str, M: int, N: int, K: int, A, lda: int, B, ldb: int, C, ldc: 
     return C
 
 
+GEMM_PATHS = {"auto": 0, "exact": 1, "tensor": 2}
+
+
+def set_gemm_path(path: str) -> None:
+    """Kernels that serve Q4_K GEMMs with M > 1: "exact" (CUDA-core integer dot products, bit-identical to the CPU
+    result), "tensor" (tcgen05 int8 MMA, within the path's tolerance) or "auto" (tensor from 32 rows up)."""
+    check(lib().nntr_cuda_set_gemm_path(GEMM_PATHS[path]))
+
+
 def gemm_q4_0(M, N, K, A, lda, B, ldb, C, ldc, workspace=None):
     """cpu_backend.h:937 -- C[M,N] = A[M,K] x W^T, W = Q4_0 (8-row interleaved)."""
     return _gemm("q4_0", M, N, K, A, lda, B, ldb, C, ldc, workspace)

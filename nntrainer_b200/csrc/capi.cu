@@ -15,6 +15,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <algorithm>
 #include <atomic>
 #include <map>
 #include <mutex>
@@ -157,12 +158,24 @@ static int grow(void *&p, size_t &cap, size_t need) {
 }
 
 /* --------------------------------------------------------- GEMM dispatch */
-static size_t workspace_bytes(int qtype, unsigned M, unsigned K) {
+static std::atomic<int> g_gemm_path{NNTR_CUDA_GEMM_PATH_AUTO};
+constexpr unsigned TENSOR_PATH_MIN_M = 32; // below this the dp4a kernels win (a 128-row activation tile is mostly padding)
+
+static bool use_tensor_path(int qtype, unsigned M, unsigned N, unsigned K) {
+  const int path = g_gemm_path.load(std::memory_order_relaxed);
+  if (path == NNTR_CUDA_GEMM_PATH_EXACT || !umma_supported(qtype, M, N, K))
+    return false;
+  return path == NNTR_CUDA_GEMM_PATH_TENSOR || M >= TENSOR_PATH_MIN_M;
+}
+
+static size_t workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K) {
   if (M <= 1)
     return 0;
   if (qtype == NNTR_Q4_0)
     return (size_t)M * (K / 32) * sizeof(BlockQ80);
-  return (size_t)M * (K / 256) * sizeof(BlockQ8K);
+  const size_t rows = (size_t)M * (K / 256) * sizeof(BlockQ8K);
+  // large enough for either path, whichever the path setting selects at call time
+  return umma_supported(qtype, M, N, K) ? std::max(rows, umma_workspace_bytes(M, K)) : rows;
 }
 
 static int gemm_dev(int qtype, unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C,
@@ -186,7 +199,7 @@ static int gemm_dev(int qtype, unsigned M, unsigned N, unsigned K, const float *
   }
   if (ldc < N)
     return set_error(NNTR_CUDA_ERR_INVALID, "gemm: ldc (%u) < N (%u)", ldc, N);
-  const size_t need = workspace_bytes(qtype, M, K);
+  const size_t need = workspace_bytes(qtype, M, N, K);
   if (!ws || ws_bytes < need)
     return set_error(NNTR_CUDA_ERR_INVALID, "gemm: workspace of %zu bytes needed, %zu given", need, ws_bytes);
   if (reinterpret_cast<uintptr_t>(ws) & 15)
@@ -194,6 +207,8 @@ static int gemm_dev(int qtype, unsigned M, unsigned N, unsigned K, const float *
   /* Rows below 4*floor(M/4) are quantized the way the reference's 4-row
    * quantizer does it, the last M%4 rows the way its row quantizer does
    * (ggml_interface_omp.cpp:433-461). */
+  if (use_tensor_path(qtype, M, N, K))
+    return launch_gemm_q4_K_umma(M, N, K, A, B, C, ldc, ws, st);
   const unsigned M4 = (M / 4) * 4;
   if (qtype == NNTR_Q4_0) {
     rc = launch_quantize_q8_0(A, K, ws, M, K, st);
@@ -244,7 +259,7 @@ static int gemm_host(int qtype, unsigned M, unsigned N, unsigned K, const float 
    * result is dense [M][N]; the copy back reproduces those strides. */
   const size_t bytesA = (size_t)M * K * sizeof(float), bytesC = (size_t)M * N * sizeof(float);
   if ((rc = grow(c->dA, c->capA, bytesA)) || (rc = grow(c->dC, c->capC, bytesC)) ||
-      (rc = grow(c->dQ, c->capQ, workspace_bytes(qtype, M, K))))
+      (rc = grow(c->dQ, c->capQ, workspace_bytes(qtype, M, N, K))))
     return rc;
   NNTR_CHECK_CUDA(cudaMemcpyAsync(c->dA, A, bytesA, cudaMemcpyHostToDevice, c->stream));
   rc = gemm_dev(qtype, M, N, K, static_cast<const float *>(c->dA), dB, static_cast<float *>(c->dC), N, c->dQ,
@@ -304,6 +319,8 @@ int nntr_cuda_device_status(void) {
   int rc = read_device_status(&v);
   if (rc)
     return rc;
+  if (!v && (rc = read_umma_status(&v)))
+    return rc;
   if (v)
     return set_error(v, "a device kernel gave up on a bounded wait (status %d)", v);
   return NNTR_CUDA_OK;
@@ -323,8 +340,14 @@ int nntr_cuda_dequantize_weight_dev(int qtype, const void *w, float *y, int64_t 
 }
 
 size_t nntr_cuda_gemm_workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K) {
-  (void)N;
-  return workspace_bytes(qtype, M, K);
+  return workspace_bytes(qtype, M, N, K);
+}
+
+int nntr_cuda_set_gemm_path(int path) {
+  if (path != NNTR_CUDA_GEMM_PATH_AUTO && path != NNTR_CUDA_GEMM_PATH_EXACT && path != NNTR_CUDA_GEMM_PATH_TENSOR)
+    return set_error(NNTR_CUDA_ERR_INVALID, "set_gemm_path: unknown path %d", path);
+  g_gemm_path.store(path, std::memory_order_relaxed);
+  return NNTR_CUDA_OK;
 }
 
 int nntr_cuda_gemm_q4_K_dev(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B,

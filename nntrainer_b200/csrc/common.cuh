@@ -248,6 +248,13 @@ struct GemvExchange {
   int x_tagged;
 };
 
+/* Activation tiles of the tensor-core GEMM: per (128 activation rows, super-block) the Q8_K values in the MMA operand
+ * layout, then the rows' scales, then their sums of 32 (see quantize_q8_K_tiles_kernel in gemm_umma.cu). */
+constexpr int UMMA_TILE_M = 128;
+constexpr int UMMA_AQS_BYTES = 128 * 256;
+constexpr int UMMA_AMETA_BYTES = 128 * 4 + 128 * 8 * 2;
+constexpr int UMMA_ATILE_BYTES = UMMA_AQS_BYTES + UMMA_AMETA_BYTES;
+
 /* launchers implemented in the .cu files (host side, return NNTR_CUDA_* codes) */
 int launch_quantize_q8_K(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, int rule, cudaStream_t st);
 int launch_quantize_q8_0(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, cudaStream_t st);
@@ -266,6 +273,12 @@ int launch_gemm_q4_K(unsigned M, unsigned N, unsigned K, const void *qa, const v
                      cudaStream_t st);
 int launch_gemm_q4_0(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
                      cudaStream_t st);
+/* tensor-core path (gemm_umma.cu): quantizes the fp32 activations itself, into ws */
+bool umma_supported(int qtype, unsigned M, unsigned N, unsigned K);
+size_t umma_workspace_bytes(unsigned M, unsigned K);
+int launch_gemm_q4_K_umma(unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C, unsigned ldc,
+                          void *ws, cudaStream_t st);
+int read_umma_status(int *out);
 int launch_gemm_q6_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
                      cudaStream_t st);
 

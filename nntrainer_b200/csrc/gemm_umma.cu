@@ -1,0 +1,446 @@
+// SPDX-License-Identifier: Apache-2.0
+/**
+ * @file  gemm_umma.cu
+ * @brief Prefill GEMM (M >= 32 activation rows) for Q4_K weights on the 5th
+ *        generation tensor cores: tcgen05.mma kind::i8 with the accumulators
+ *        in tensor memory.
+ *
+ * What is computed. The same quantity as the reference's
+ * nntr_gemm_q4_K_8x8_q8_K / nntr_gemv_q4_K_8x8_q8_K
+ * (nntr_ggml_impl.cpp, called from __ggml_q4_K_8x8_q8_K_GEMM,
+ * ggml_interface_omp.cpp:380-470): per super-block of 256 weights
+ *     I = sum_k q_k * sc_{sub(k)} * a_k        (integer)
+ *     J = sum_sub min_sub * (sum of the a_k of that sub-block)   (integer)
+ *     out += d_a * (d_w * I - dmin_w * J)
+ * with the activations quantized to Q8_K by the same rules as the exact path.
+ * The integers I and J are exact; the floating-point combination uses one
+ * rounding more per super-block than the reference's chain, so results agree
+ * with the reference within the path's tolerance (max-rel 2e-3), not bit for
+ * bit. The dp4a kernels of gemm_dp4a.cu remain the bit-exact path.
+ *
+ * How. sc is a 6-bit number, q a 4-bit one: q*sc does not fit a byte. The
+ * scale is split, sc = 16*(sc >> 4) + (sc & 15), which gives two unsigned
+ * 8-bit operands W_lo = q*(sc & 15) <= 225 and W_hi = q*(sc >> 4) <= 45 and
+ * I = W_lo.a + 16 * W_hi.a: two u8 x s8 -> s32 MMAs into two accumulators.
+ *
+ * One CTA owns a tile of 128 weight rows x 128 activation rows and walks the
+ * K dimension one super-block (256) at a time:
+ *   warps 0-3   producers: thread r expands weight row r of the super-block
+ *               (nibbles x split scales) into the two operand tiles in shared
+ *               memory, K-major core-matrix layout without swizzle; thread 0
+ *               also starts the bulk copy of the activation tile, which the
+ *               quantizer already wrote in that layout.
+ *   warp 4      one thread issues 8 K-steps x 2 MMAs (128x128x32 each) and
+ *               commits them to the "stage free" and "accumulator full"
+ *               barriers.
+ *   warps 5-12  drain: tcgen05.ld of both accumulators, I = lo + 16*hi, the
+ *               mins term with two-way 16-bit dot products, scale and add into
+ *               64 fp32 registers per thread; after the last super-block the
+ *               tile of C is written (coalesced along N).
+ * Two operand stages and two accumulator buffers (2 x 256 of the 512 tensor
+ * memory columns) let expansion, MMA and drain of consecutive super-blocks
+ * overlap. Every wait is bounded; a wait that runs out raises the device
+ * status word and the CTA leaves through the common tail, which frees the
+ * tensor memory.
+ *
+ * Cost model per CTA and super-block: 16 MMAs of 128x128x32 = 1024 tensor
+ * cycles; the drain is ~12 instructions per output = ~1500 issue cycles, so
+ * the kernel is bound by the drain's instruction issue, not by the tensor
+ * pipe or by HBM (weights are read once per 128 activation rows).
+ */
+#include "common.cuh"
+
+namespace nntr {
+
+namespace {
+
+constexpr int TILE_N = 128;          // weight rows per CTA (MMA M, tensor memory lanes)
+constexpr int TILE_M = UMMA_TILE_M;  // activation rows per CTA (MMA N, tensor memory columns)
+constexpr int OPERAND_BYTES = 128 * 256; // one 128-row x 256-byte operand tile
+constexpr int STAGE_BYTES = 3 * OPERAND_BYTES;
+constexpr int N_STAGES = 2;
+constexpr int META_SLOTS = 4;
+constexpr int WMETA_BYTES = 128 * 16; // per weight row: 8 mins, d*1, dmin*1
+constexpr int PRODUCER_THREADS = 128;
+constexpr int MMA_WARP = 4;
+constexpr int DRAIN_WARP0 = 5;
+constexpr int DRAIN_WARPS = 8;
+constexpr int CTA_THREADS = (DRAIN_WARP0 + DRAIN_WARPS) * 32; // 416
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t WAIT_POLLS_UMMA = 1u << 22;
+
+constexpr int OFF_AMETA = N_STAGES * STAGE_BYTES;
+constexpr int OFF_WMETA = OFF_AMETA + META_SLOTS * UMMA_AMETA_BYTES;
+constexpr int OFF_BARS = OFF_WMETA + META_SLOTS * WMETA_BYTES;
+constexpr int SMEM_BYTES = OFF_BARS + 128;
+
+__device__ int g_umma_status = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+/** Bounded wait: false (abort flag and device status raised) when the phase did not complete in time. */
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  for (uint32_t it = 0; it < WAIT_POLLS_UMMA; ++it) {
+    if (mbar_try_wait(bar, parity))
+      return true;
+    if (it > 2048) {
+      if (*abort_flag)
+        return false;
+      __nanosleep(32);
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(&g_umma_status, NNTR_CUDA_ERR_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+/** Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; lbo = bytes between the two
+ *  core matrices of one 32-byte K step, sbo = bytes between 8-row groups. */
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)((lbo >> 4) & 0x3fff) << 16) |
+         ((uint64_t)((sbo >> 4) & 0x3fff) << 32) | ((uint64_t)1 << 46);
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+/** scales and mins of row j for the 8 sub-blocks of a block_q4_Kx8, packed: sc[i] in byte i of (sc_lo, sc_hi) */
+__device__ __forceinline__ void row_scales(const BlockQ4Kx8 *blk, int j, uint32_t (&sc)[8], uint32_t &mins_a,
+                                           uint32_t &mins_b) {
+  uint32_t mm[8];
+#pragma unroll
+  for (int sb = 0; sb < 8; ++sb) {
+    const uint32_t *g = reinterpret_cast<const uint32_t *>(blk->scales + 12 * sb);
+    const uint32_t w0 = __ldg(g), w1 = __ldg(g + 1), w2 = __ldg(g + 2);
+    // bytes 0-3: low 6 bits = scales of rows 0-3, top 2 bits = high bits of the scales of rows 4-7
+    // bytes 4-7: low 6 bits = mins of rows 0-3, top 2 bits = high bits of the mins of rows 4-7
+    // bytes 8-11: low nibble = scales of rows 4-7 (low 4 bits), high nibble = mins of rows 4-7 (low 4 bits)
+    const int sh = 8 * (j & 3);
+    const uint32_t b0 = (w0 >> sh) & 0xff, b1 = (w1 >> sh) & 0xff, b2 = (w2 >> sh) & 0xff;
+    if (j < 4) {
+      sc[sb] = b0 & 63;
+      mm[sb] = b1 & 63;
+    } else {
+      sc[sb] = (b2 & 0xf) | ((b0 >> 6) << 4);
+      mm[sb] = (b2 >> 4) | ((b1 >> 6) << 4);
+    }
+  }
+  mins_a = mm[0] | (mm[1] << 8) | (mm[2] << 16) | (mm[3] << 24);
+  mins_b = mm[4] | (mm[5] << 8) | (mm[6] << 16) | (mm[7] << 24);
+}
+
+__global__ void __launch_bounds__(CTA_THREADS, 1)
+gemm_q4_K_umma_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__restrict__ W, float *__restrict__ C,
+                      int ldc, int M, int nb) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + OFF_BARS);
+  // bars: [0,1] full, [2,3] empty, [4,5] acc_full, [6,7] acc_empty, [8..11] meta_full
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BARS + 96);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + OFF_BARS + 104);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int mt = blockIdx.x, nt = blockIdx.y;
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = smem_u32(bars);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(BAR(0 + s), PRODUCER_THREADS + 1); // 128 expanded rows + the thread that armed the bulk copy
+      mbar_init(BAR(2 + s), 1);                    // MMAs of the stage retired
+      mbar_init(BAR(4 + s), 1);                    // accumulator buffer complete
+      mbar_init(BAR(6 + s), DRAIN_WARPS);          // accumulator buffer drained
+    }
+    for (int i = 0; i < META_SLOTS; ++i)
+      mbar_init(BAR(8 + i), PRODUCER_THREADS + 1); // per-row and per-activation-row constants of a super-block
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp < MMA_WARP) {
+    /* ------------------------------ producers ------------------------------ */
+    const int r = tid;                                   // weight row inside the tile
+    const int j = r & 7;                                 // row inside its 8-row group
+    const BlockQ4Kx8 *wrow = W + (size_t)(nt * (TILE_N / 8) + (r >> 3)) * nb;
+    const uint8_t *asrc = atiles + (size_t)mt * nb * UMMA_ATILE_BYTES;
+    uint2 q[16];
+#pragma unroll
+    for (int c = 0; c < 16; ++c)
+      q[c] = ldg_stream_u2(wrow->qs + (c * 8 + j) * 8);
+    for (int b = 0; b < nb; ++b) {
+      const int s = b & 1, u = b >> 1;
+      const BlockQ4Kx8 *blk = wrow + b;
+      uint32_t sc[8], mins_a, mins_b;
+      row_scales(blk, j, sc, mins_a, mins_b);
+      const float dw = half_bits_to_float(blk->d[j]), dmw = half_bits_to_float(blk->dmin[j]);
+      if (u > 0 && !mbar_wait(BAR(2 + s), (u - 1) & 1, abort_flag))
+        break;
+      if (tid == 0) {
+        mbar_expect_tx(BAR(0 + s), UMMA_AQS_BYTES);
+        bulk_g2s(sbase + s * STAGE_BYTES + 2 * OPERAND_BYTES, asrc + (size_t)b * UMMA_ATILE_BYTES, UMMA_AQS_BYTES,
+                 BAR(0 + s));
+        // slot b % 4 was last read by the drain of super-block b - 4, which ended before the MMAs of b - 2 began
+        mbar_expect_tx(BAR(8 + (b & 3)), UMMA_AMETA_BYTES);
+        bulk_g2s(sbase + OFF_AMETA + (b & 3) * UMMA_AMETA_BYTES, asrc + (size_t)b * UMMA_ATILE_BYTES + UMMA_AQS_BYTES,
+                 UMMA_AMETA_BYTES, BAR(8 + (b & 3)));
+      }
+      *reinterpret_cast<uint4 *>(smem + OFF_WMETA + (b & 3) * WMETA_BYTES + r * 16) =
+        make_uint4(mins_a, mins_b, __float_as_uint(dw), __float_as_uint(dmw));
+      mbar_arrive(BAR(8 + (b & 3)));
+      uint8_t *wlo = smem + s * STAGE_BYTES + r * 16;
+      uint8_t *whi = wlo + OPERAND_BYTES;
+#pragma unroll
+      for (int cp = 0; cp < 8; ++cp) { // chunk pair (2cp, 2cp+1): 16 consecutive row bytes
+        const int p = cp >> 1;         // 64-element group
+        const uint32_t sa = sc[2 * p], sb = sc[2 * p + 1];
+        const uint32_t sa_lo = sa & 15, sa_hi = sa >> 4, sb_lo = sb & 15, sb_hi = sb >> 4;
+        const uint2 w0 = q[2 * cp], w1 = q[2 * cp + 1];
+        const uint32_t l0 = w0.x & 0x0f0f0f0fu, l1 = w0.y & 0x0f0f0f0fu, l2 = w1.x & 0x0f0f0f0fu,
+                       l3 = w1.y & 0x0f0f0f0fu;
+        const uint32_t h0 = (w0.x >> 4) & 0x0f0f0f0fu, h1 = (w0.y >> 4) & 0x0f0f0f0fu, h2 = (w1.x >> 4) & 0x0f0f0f0fu,
+                       h3 = (w1.y >> 4) & 0x0f0f0f0fu;
+        // low nibbles: elements 64p + 16(cp&1) .. +15 (sub-block 2p); high nibbles: the same + 32 (sub-block 2p+1)
+        const int kc_l = 4 * p + (cp & 1), kc_h = kc_l + 2;
+        *reinterpret_cast<uint4 *>(wlo + kc_l * 2048) = make_uint4(l0 * sa_lo, l1 * sa_lo, l2 * sa_lo, l3 * sa_lo);
+        *reinterpret_cast<uint4 *>(whi + kc_l * 2048) = make_uint4(l0 * sa_hi, l1 * sa_hi, l2 * sa_hi, l3 * sa_hi);
+        *reinterpret_cast<uint4 *>(wlo + kc_h * 2048) = make_uint4(h0 * sb_lo, h1 * sb_lo, h2 * sb_lo, h3 * sb_lo);
+        *reinterpret_cast<uint4 *>(whi + kc_h * 2048) = make_uint4(h0 * sb_hi, h1 * sb_hi, h2 * sb_hi, h3 * sb_hi);
+      }
+      if (b + 1 < nb) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c)
+          q[c] = ldg_stream_u2(blk[1].qs + (c * 8 + j) * 8);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(BAR(0 + s));
+    }
+  } else if (warp == MMA_WARP) {
+    /* ------------------------------ MMA issue ------------------------------ */
+    if (lane == 0) {
+      // D = S32, A = U8, B = S8, both K-major, N = 128 columns, M = 128 lanes
+      const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(TILE_M >> 3) << 17) |
+                             ((uint32_t)(TILE_N >> 4) << 24);
+      for (int b = 0; b < nb; ++b) {
+        const int s = b & 1, u = b >> 1;
+        if (!mbar_wait(BAR(0 + s), u & 1, abort_flag))
+          break;
+        if (u > 0 && !mbar_wait(BAR(6 + s), (u - 1) & 1, abort_flag))
+          break;
+        tc_fence_after();
+        const uint32_t st = sbase + s * STAGE_BYTES;
+        const uint32_t acc_lo = tmem + s * 256, acc_hi = acc_lo + 128;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t db = umma_desc(st + 2 * OPERAND_BYTES + ks * 4096, 2048, 128);
+          umma_i8(acc_lo, umma_desc(st + ks * 4096, 2048, 128), db, idesc, ks > 0);
+          umma_i8(acc_hi, umma_desc(st + OPERAND_BYTES + ks * 4096, 2048, 128), db, idesc, ks > 0);
+        }
+        umma_commit(BAR(2 + s)); // operand stage may be overwritten
+        umma_commit(BAR(4 + s)); // accumulators of this super-block complete
+      }
+    }
+    __syncwarp();
+  } else {
+    /* -------------------------------- drain -------------------------------- */
+    const int dw_id = warp - DRAIN_WARP0;
+    const int quad = warp & 3;     // tensor memory lanes this warp may read: 32*quad ..
+    const int half = dw_id >> 2;   // columns 64*half ..
+    const int n = quad * 32 + lane; // weight row inside the tile
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i)
+      acc[i] = 0.f;
+    bool ok = true;
+    for (int b = 0; b < nb; ++b) {
+      const int s = b & 1, u = b >> 1;
+      if (!mbar_wait(BAR(4 + s), u & 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      if (!mbar_wait(BAR(8 + (b & 3)), (b >> 2) & 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint4 wm = *reinterpret_cast<const uint4 *>(smem + OFF_WMETA + (b & 3) * WMETA_BYTES + n * 16);
+      const float dw = __uint_as_float(wm.z), dmw = __uint_as_float(wm.w);
+      const uint8_t *am = smem + OFF_AMETA + (b & 3) * UMMA_AMETA_BYTES;
+      const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16) + s * 256 + half * 64;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t lo[16], hi[16];
+        tmem_ld16(trow + ch * 16, lo);
+        tmem_ld16(trow + 128 + ch * 16, hi);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int m = half * 64 + ch * 16 + i;
+          const float da = reinterpret_cast<const float *>(am)[m];
+          const uint4 bs = reinterpret_cast<const uint4 *>(am + 512)[m];
+          const int I = (int)lo[i] + ((int)hi[i] << 4);
+          int J = __dp2a_lo((int)bs.x, (int)wm.x, 0);
+          J = __dp2a_hi((int)bs.y, (int)wm.x, J);
+          J = __dp2a_lo((int)bs.z, (int)wm.y, J);
+          J = __dp2a_hi((int)bs.w, (int)wm.y, J);
+          const float t = fmaf((float)I, dw, -((float)J * dmw));
+          acc[ch * 16 + i] = fmaf(t, da, acc[ch * 16 + i]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(BAR(6 + s));
+    }
+    if (ok) {
+      const int m_base = mt * TILE_M + half * 64;
+      float *crow = C + (size_t)nt * TILE_N + n;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const int m = m_base + i;
+        if (m < M)
+          crow[(size_t)m * ldc] = acc[i];
+      }
+    }
+  }
+
+  /* common tail: on an abort give copies and MMAs in flight time to land before the memory is released */
+  if (*abort_flag)
+    for (int i = 0; i < 1000; ++i)
+      __nanosleep(1000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+}
+
+/* Activation quantizer for the tensor path: Q8_K values written straight into the operand layout, one tile of
+ * UMMA_ATILE_BYTES per (128 activation rows, super-block):
+ *   [0, 32768)       values, core-matrix layout: element k of row m at (k/16)*2048 + m*16 + k%16
+ *   [32768, 33280)   d of the 128 rows (fp32)
+ *   [33280, 35328)   sums of the 8 groups of 32 values, int16[128][8]
+ * Rows at or beyond M are written as zeros. One warp per (row, super-block); rows below M4 use the sign rule of the
+ * reference's 4-row quantizer, the others that of its row quantizer. */
+__global__ void __launch_bounds__(256)
+quantize_q8_K_tiles_kernel(const float *__restrict__ x, int64_t ldx, uint8_t *__restrict__ tiles, int M, int M4,
+                           int Mpad, int nb) {
+  const int lane = threadIdx.x & 31;
+  const int64_t blk = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (blk >= (int64_t)Mpad * nb)
+    return;
+  // consecutive warps take consecutive rows of one super-block, so a CTA's stores fall into one tile
+  const int b = (int)(blk / Mpad);
+  const int row = (int)(blk - (int64_t)b * Mpad);
+  uint8_t *tile = tiles + ((size_t)(row / UMMA_TILE_M) * nb + b) * UMMA_ATILE_BYTES;
+  const int m = row % UMMA_TILE_M;
+  Q8KLane q;
+  if (row < M) {
+    const float *src = x + (int64_t)row * ldx + (int64_t)b * QK_K + lane * 8;
+    const float4 a = *reinterpret_cast<const float4 *>(src);
+    const float4 c = *reinterpret_cast<const float4 *>(src + 4);
+    q = q8K_quantize_warp(a, c, lane, row < M4 ? 1 : 0);
+  } else {
+    q.w0 = q.w1 = 0u;
+    q.sum8 = 0;
+    q.d = 0.f;
+  }
+  *reinterpret_cast<uint2 *>(tile + (lane >> 1) * 2048 + m * 16 + (lane & 1) * 8) = make_uint2(q.w0, q.w1);
+  int s32 = q.sum8 + __shfl_xor_sync(FULL, q.sum8, 1);
+  s32 += __shfl_xor_sync(FULL, s32, 2);
+  if ((lane & 3) == 0)
+    reinterpret_cast<int16_t *>(tile + UMMA_AQS_BYTES + 512)[m * 8 + (lane >> 2)] = (int16_t)s32;
+  if (lane == 0)
+    reinterpret_cast<float *>(tile + UMMA_AQS_BYTES)[m] = q.d;
+}
+
+} // namespace
+
+size_t umma_workspace_bytes(unsigned M, unsigned K) {
+  return (size_t)((M + UMMA_TILE_M - 1) / UMMA_TILE_M) * (K / QK_K) * UMMA_ATILE_BYTES;
+}
+
+bool umma_supported(int qtype, unsigned M, unsigned N, unsigned K) {
+  return qtype == NNTR_Q4_K && M >= 2 && N % TILE_N == 0 && K % QK_K == 0 && K > 0;
+}
+
+int launch_gemm_q4_K_umma(unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C, unsigned ldc,
+                          void *ws, cudaStream_t st) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  NNTR_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemm_q4_K_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set[dev] = true;
+  }
+  const int nb = (int)(K / QK_K);
+  const int mtiles = (int)((M + UMMA_TILE_M - 1) / UMMA_TILE_M), Mpad = mtiles * UMMA_TILE_M;
+  const unsigned M4 = (M / 4) * 4;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(ws) & 15))
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm (tensor path): activations and workspace must be 16-byte aligned");
+  const int64_t nwarps = (int64_t)Mpad * nb;
+  quantize_q8_K_tiles_kernel<<<(unsigned)((nwarps + 7) / 8), 256, 0, st>>>(A, K, static_cast<uint8_t *>(ws), (int)M,
+                                                                         (int)M4, Mpad, nb);
+  count_launch();
+  NNTR_CHECK_CUDA(cudaGetLastError());
+  dim3 grid(mtiles, N / TILE_N);
+  gemm_q4_K_umma_kernel<<<grid, CTA_THREADS, SMEM_BYTES, st>>>(static_cast<const uint8_t *>(ws),
+                                                               static_cast<const BlockQ4Kx8 *>(B), C, (int)ldc, (int)M,
+                                                               nb);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "gemm_q4_K tensor-path launch");
+}
+
+int read_umma_status(int *out) {
+  int v = 0;
+  NNTR_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_umma_status, sizeof(int)));
+  *out = v;
+  return NNTR_CUDA_OK;
+}
+
+} // namespace nntr
