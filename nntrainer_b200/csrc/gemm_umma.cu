@@ -30,13 +30,14 @@
  *               memory, K-major core-matrix layout without swizzle; thread 0
  *               also starts the bulk copy of the activation tile, which the
  *               quantizer already wrote in that layout.
- *   warp 4      one thread issues 8 K-steps x 2 MMAs (128x128x32 each) and
+ *   warps 4-19  drain: tcgen05.ld of both accumulators (8 columns at a time,
+ *               the next 8 in flight while these are combined), I = lo + 16*hi,
+ *               the mins term with two-way 16-bit dot products, scale and add
+ *               into 32 fp32 registers per thread; after the last super-block
+ *               the tile of C is written (coalesced along N).
+ *   warp 20     one thread issues 8 K-steps x 2 MMAs (128x128x32 each) and
  *               commits them to the "stage free" and "accumulator full"
  *               barriers.
- *   warps 5-12  drain: tcgen05.ld of both accumulators, I = lo + 16*hi, the
- *               mins term with two-way 16-bit dot products, scale and add into
- *               64 fp32 registers per thread; after the last super-block the
- *               tile of C is written (coalesced along N).
  * Two operand stages and two accumulator buffers (2 x 256 of the 512 tensor
  * memory columns) let expansion, MMA and drain of consecutive super-blocks
  * overlap. Every wait is bounded; a wait that runs out raises the device
@@ -61,20 +62,25 @@ constexpr int STAGE_BYTES = 3 * OPERAND_BYTES;
 constexpr int N_STAGES = 2;
 constexpr int META_SLOTS = 4;
 constexpr int WMETA_BYTES = 128 * 16; // per weight row: 8 mins, d*1, dmin*1
-constexpr int PRODUCER_THREADS = 128;
-constexpr int MMA_WARP = 4;
-constexpr int DRAIN_WARP0 = 5;
-constexpr int DRAIN_WARPS = 8;
-constexpr int CTA_THREADS = (DRAIN_WARP0 + DRAIN_WARPS) * 32; // 416
+constexpr int PRODUCER_THREADS = 256; // two per weight row
+constexpr int DRAIN_WARP0 = PRODUCER_THREADS / 32;
+constexpr int DRAIN_WARPS = 16;                   // 4 lane quadrants x 4 column groups
+constexpr int DRAIN_COLS = 4 * TILE_M / DRAIN_WARPS; // activation rows (columns) per drain warp: 32
+constexpr int MMA_WARP = DRAIN_WARP0 + DRAIN_WARPS;
+constexpr int CTA_THREADS = (MMA_WARP + 1) * 32; // 800
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t WAIT_POLLS_UMMA = 1u << 22;
+constexpr uint32_t WAIT_POLLS_UMMA = 1u << 18; // x (up to ~4 us parked per try): a lost signal costs a second at most
 
 constexpr int OFF_AMETA = N_STAGES * STAGE_BYTES;
 constexpr int OFF_WMETA = OFF_AMETA + META_SLOTS * UMMA_AMETA_BYTES;
-constexpr int OFF_BARS = OFF_WMETA + META_SLOTS * WMETA_BYTES;
-constexpr int SMEM_BYTES = OFF_BARS + 128;
+constexpr int HEAD_SLOTS = 4;
+constexpr int HEAD_BYTES = 16 * 128; // d, dmin and packed scales of the tile's 16 row groups
+constexpr int OFF_HEAD = OFF_WMETA + META_SLOTS * WMETA_BYTES;
+constexpr int OFF_BARS = OFF_HEAD + HEAD_SLOTS * HEAD_BYTES;
+constexpr int SMEM_BYTES = OFF_BARS + 256;
 
 __device__ int g_umma_status = 0;
+
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -89,10 +95,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile("{\n\t.reg .pred p;\n\t"
-               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
                "selp.u32 %0, 1, 0, p;\n\t}"
                : "=r"(ok)
-               : "r"(bar), "r"(parity)
+               : "r"(bar), "r"(parity), "r"(4000u) /* let the hardware park the thread for up to ~4 us per try */
                : "memory");
   return ok != 0;
 }
@@ -139,42 +145,51 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-/** scales and mins of row j for the 8 sub-blocks of a block_q4_Kx8, packed: sc[i] in byte i of (sc_lo, sc_hi) */
-__device__ __forceinline__ void row_scales(const BlockQ4Kx8 *blk, int j, uint32_t (&sc)[8], uint32_t &mins_a,
-                                           uint32_t &mins_b) {
-  uint32_t mm[8];
+/** Scales and mins of row j for four consecutive sub-blocks of a block_q4_Kx8, from their 48 packed bytes in shared
+ *  memory (12 per sub-block; get_scale_min_k4 with the row in place of the sub-block index). mins: one byte each. */
+__device__ __forceinline__ void row_scales_half(const uint8_t *scales, int j, uint32_t (&sc)[4], uint32_t &mins) {
+  mins = 0;
 #pragma unroll
-  for (int sb = 0; sb < 8; ++sb) {
-    const uint32_t *g = reinterpret_cast<const uint32_t *>(blk->scales + 12 * sb);
-    const uint32_t w0 = __ldg(g), w1 = __ldg(g + 1), w2 = __ldg(g + 2);
+  for (int sb = 0; sb < 4; ++sb) {
+    const uint32_t *g = reinterpret_cast<const uint32_t *>(scales + 12 * sb);
     // bytes 0-3: low 6 bits = scales of rows 0-3, top 2 bits = high bits of the scales of rows 4-7
     // bytes 4-7: low 6 bits = mins of rows 0-3, top 2 bits = high bits of the mins of rows 4-7
     // bytes 8-11: low nibble = scales of rows 4-7 (low 4 bits), high nibble = mins of rows 4-7 (low 4 bits)
     const int sh = 8 * (j & 3);
-    const uint32_t b0 = (w0 >> sh) & 0xff, b1 = (w1 >> sh) & 0xff, b2 = (w2 >> sh) & 0xff;
+    const uint32_t b0 = (g[0] >> sh) & 0xff, b1 = (g[1] >> sh) & 0xff, b2 = (g[2] >> sh) & 0xff;
+    uint32_t m;
     if (j < 4) {
       sc[sb] = b0 & 63;
-      mm[sb] = b1 & 63;
+      m = b1 & 63;
     } else {
       sc[sb] = (b2 & 0xf) | ((b0 >> 6) << 4);
-      mm[sb] = (b2 >> 4) | ((b1 >> 6) << 4);
+      m = (b2 >> 4) | ((b1 >> 6) << 4);
     }
+    mins |= m << (8 * sb);
   }
-  mins_a = mm[0] | (mm[1] << 8) | (mm[2] << 16) | (mm[3] << 24);
-  mins_b = mm[4] | (mm[5] << 8) | (mm[6] << 16) | (mm[7] << 24);
 }
 
-__global__ void __launch_bounds__(CTA_THREADS, 1)
+__global__ void __maxnreg__(72)
 gemm_q4_K_umma_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__restrict__ W, float *__restrict__ C,
-                      int ldc, int M, int nb) {
+                      int ldc, int M, int nb, int c_vec4) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + OFF_BARS);
-  // bars: [0,1] full, [2,3] empty, [4,5] acc_full, [6,7] acc_empty, [8..11] meta_full
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BARS + 96);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + OFF_BARS + 104);
+  // bars: [0,1] full, [2,3] empty, [4,5] acc_full, [6,7] acc_empty, [8..11] meta_full, [12..15] head_full
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BARS + 128);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + OFF_BARS + 136);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int mt = blockIdx.x, nt = blockIdx.y;
@@ -191,6 +206,8 @@ gemm_q4_K_umma_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__re
     }
     for (int i = 0; i < META_SLOTS; ++i)
       mbar_init(BAR(8 + i), PRODUCER_THREADS + 1); // per-row and per-activation-row constants of a super-block
+    for (int i = 0; i < HEAD_SLOTS; ++i)
+      mbar_init(BAR(12 + i), PRODUCER_THREADS); // block headers of a super-block in shared memory (every producer)
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -204,22 +221,41 @@ gemm_q4_K_umma_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__re
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp < MMA_WARP) {
+  if (warp < PRODUCER_THREADS / 32) {
     /* ------------------------------ producers ------------------------------ */
-    const int r = tid;                                   // weight row inside the tile
-    const int j = r & 7;                                 // row inside its 8-row group
+    const int r = tid & (TILE_N - 1); // weight row inside the tile
+    const int h = tid >> 7;           // which half of the row's super-block: sub-blocks 4h .. 4h+3
+    const int j = r & 7;              // row inside its 8-row group
     const BlockQ4Kx8 *wrow = W + (size_t)(nt * (TILE_N / 8) + (r >> 3)) * nb;
     const uint8_t *asrc = atiles + (size_t)mt * nb * UMMA_ATILE_BYTES;
-    uint2 q[16];
+    /* The first 128 bytes of every block_q4_Kx8 (d, dmin, packed scales) travel two super-blocks ahead through a
+     * ring of HEAD_SLOTS slots: thread t < 128 copies 16 bytes of group t/8. Every producer thread arrives on the
+     * slot's barrier once per iteration, so a slot is rewritten only after all its readers have moved on. */
+    const uint8_t *head_src = reinterpret_cast<const uint8_t *>(wrow) + (tid & 7) * 16;
+    const uint32_t head_dst = sbase + OFF_HEAD + (r >> 3) * 128 + (tid & 7) * 16;
+    auto fetch_head = [&](int b) {
+      if (b < nb && h == 0)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(head_dst + (b % HEAD_SLOTS) * HEAD_BYTES),
+                     "l"(head_src + (size_t)b * sizeof(BlockQ4Kx8))
+                     : "memory");
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch_head(0);
+    fetch_head(1);
+    uint2 q[8]; // chunks 8h .. 8h+7 of the row: 64 nibble bytes
 #pragma unroll
-    for (int c = 0; c < 16; ++c)
-      q[c] = ldg_stream_u2(wrow->qs + (c * 8 + j) * 8);
+    for (int c = 0; c < 8; ++c)
+      q[c] = ldg_stream_u2(wrow->qs + ((8 * h + c) * 8 + j) * 8);
     for (int b = 0; b < nb; ++b) {
       const int s = b & 1, u = b >> 1;
-      const BlockQ4Kx8 *blk = wrow + b;
-      uint32_t sc[8], mins_a, mins_b;
-      row_scales(blk, j, sc, mins_a, mins_b);
-      const float dw = half_bits_to_float(blk->d[j]), dmw = half_bits_to_float(blk->dmin[j]);
+      fetch_head(b + 2);
+      asm volatile("cp.async.wait_group 2;" ::: "memory");
+      mbar_arrive(BAR(12 + b % HEAD_SLOTS)); // my 16 bytes of header b have landed (or I had none to fetch)
+      if (!mbar_wait(BAR(12 + b % HEAD_SLOTS), (b / HEAD_SLOTS) & 1, abort_flag))
+        break;
+      const uint8_t *head = smem + OFF_HEAD + (b % HEAD_SLOTS) * HEAD_BYTES + (r >> 3) * 128;
+      uint32_t sc[4], mins;
+      row_scales_half(head + 32 + 48 * h, j, sc, mins);
       if (u > 0 && !mbar_wait(BAR(2 + s), (u - 1) & 1, abort_flag))
         break;
       if (tid == 0) {
@@ -231,42 +267,49 @@ gemm_q4_K_umma_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__re
         bulk_g2s(sbase + OFF_AMETA + (b & 3) * UMMA_AMETA_BYTES, asrc + (size_t)b * UMMA_ATILE_BYTES + UMMA_AQS_BYTES,
                  UMMA_AMETA_BYTES, BAR(8 + (b & 3)));
       }
-      *reinterpret_cast<uint4 *>(smem + OFF_WMETA + (b & 3) * WMETA_BYTES + r * 16) =
-        make_uint4(mins_a, mins_b, __float_as_uint(dw), __float_as_uint(dmw));
+      { // per-row constants of this super-block for the drain: {mins 0-3, mins 4-7, d, dmin}
+        uint32_t *wm = reinterpret_cast<uint32_t *>(smem + OFF_WMETA + (b & 3) * WMETA_BYTES + r * 16);
+        wm[h] = mins;
+        if (h == 0)
+          *reinterpret_cast<uint2 *>(wm + 2) =
+            make_uint2(__float_as_uint(half_bits_to_float(reinterpret_cast<const uint16_t *>(head)[j])),
+                       __float_as_uint(half_bits_to_float(reinterpret_cast<const uint16_t *>(head + 16)[j])));
+      }
       mbar_arrive(BAR(8 + (b & 3)));
-      uint8_t *wlo = smem + s * STAGE_BYTES + r * 16;
-      uint8_t *whi = wlo + OPERAND_BYTES;
+      uint8_t *wlo = smem + s * STAGE_BYTES + r * 16; // row r of the 256-row operand tile
+      uint8_t *whi = wlo + TILE_N * 16;               // row 128 + r
+      const uint8_t *nq = wrow[b + 1 < nb ? b + 1 : b].qs + (64 * h + j) * 8; // the last iteration re-reads its block
 #pragma unroll
-      for (int cp = 0; cp < 8; ++cp) { // chunk pair (2cp, 2cp+1): 16 consecutive row bytes
-        const int p = cp >> 1;         // 64-element group
-        const uint32_t sa = sc[2 * p], sb = sc[2 * p + 1];
+      for (int cl = 0; cl < 4; ++cl) { // chunk pair 4h + cl: 16 consecutive row bytes
+        const int pl = cl >> 1;        // 64-element group 2h + pl
+        const uint32_t sa = sc[2 * pl], sb = sc[2 * pl + 1];
         const uint32_t sa_lo = sa & 15, sa_hi = sa >> 4, sb_lo = sb & 15, sb_hi = sb >> 4;
-        const uint2 w0 = q[2 * cp], w1 = q[2 * cp + 1];
+        const uint2 w0 = q[2 * cl], w1 = q[2 * cl + 1];
+        // the registers just consumed receive the same chunks of the next super-block: a whole iteration to land
+        q[2 * cl] = ldg_stream_u2(nq + (2 * cl) * 64);
+        q[2 * cl + 1] = ldg_stream_u2(nq + (2 * cl + 1) * 64);
         const uint32_t l0 = w0.x & 0x0f0f0f0fu, l1 = w0.y & 0x0f0f0f0fu, l2 = w1.x & 0x0f0f0f0fu,
                        l3 = w1.y & 0x0f0f0f0fu;
         const uint32_t h0 = (w0.x >> 4) & 0x0f0f0f0fu, h1 = (w0.y >> 4) & 0x0f0f0f0fu, h2 = (w1.x >> 4) & 0x0f0f0f0fu,
                        h3 = (w1.y >> 4) & 0x0f0f0f0fu;
-        // low nibbles: elements 64p + 16(cp&1) .. +15 (sub-block 2p); high nibbles: the same + 32 (sub-block 2p+1)
-        const int kc_l = 4 * p + (cp & 1), kc_h = kc_l + 2;
-        *reinterpret_cast<uint4 *>(wlo + kc_l * 2048) = make_uint4(l0 * sa_lo, l1 * sa_lo, l2 * sa_lo, l3 * sa_lo);
-        *reinterpret_cast<uint4 *>(whi + kc_l * 2048) = make_uint4(l0 * sa_hi, l1 * sa_hi, l2 * sa_hi, l3 * sa_hi);
-        *reinterpret_cast<uint4 *>(wlo + kc_h * 2048) = make_uint4(h0 * sb_lo, h1 * sb_lo, h2 * sb_lo, h3 * sb_lo);
-        *reinterpret_cast<uint4 *>(whi + kc_h * 2048) = make_uint4(h0 * sb_hi, h1 * sb_hi, h2 * sb_hi, h3 * sb_hi);
-      }
-      if (b + 1 < nb) {
-#pragma unroll
-        for (int c = 0; c < 16; ++c)
-          q[c] = ldg_stream_u2(blk[1].qs + (c * 8 + j) * 8);
+        // low nibbles: elements 64p + 16(cl&1) .. +15 (sub-block 2p); high nibbles: the same + 32 (sub-block 2p+1)
+        const int kc_l = 4 * (2 * h + pl) + (cl & 1), kc_h = kc_l + 2;
+        *reinterpret_cast<uint4 *>(wlo + kc_l * 4096) = make_uint4(l0 * sa_lo, l1 * sa_lo, l2 * sa_lo, l3 * sa_lo);
+        *reinterpret_cast<uint4 *>(whi + kc_l * 4096) = make_uint4(l0 * sa_hi, l1 * sa_hi, l2 * sa_hi, l3 * sa_hi);
+        *reinterpret_cast<uint4 *>(wlo + kc_h * 4096) = make_uint4(h0 * sb_lo, h1 * sb_lo, h2 * sb_lo, h3 * sb_lo);
+        *reinterpret_cast<uint4 *>(whi + kc_h * 4096) = make_uint4(h0 * sb_hi, h1 * sb_hi, h2 * sb_hi, h3 * sb_hi);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(BAR(0 + s));
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   } else if (warp == MMA_WARP) {
     /* ------------------------------ MMA issue ------------------------------ */
     if (lane == 0) {
-      // D = S32, A = U8, B = S8, both K-major, N = 128 columns, M = 128 lanes
-      const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(TILE_M >> 3) << 17) |
-                             ((uint32_t)(TILE_N >> 4) << 24);
+      // D = S32; A = the activations (S8, 128 rows = tensor memory lanes); B = the expanded weights (U8, 256 rows =
+      // columns: 0..127 the low-scale part, 128..255 the high-scale part); both K-major
+      const uint32_t idesc = (2u << 4) | (1u << 7) | (0u << 10) | ((uint32_t)(2 * TILE_N >> 3) << 17) |
+                             ((uint32_t)(TILE_M >> 4) << 24);
       for (int b = 0; b < nb; ++b) {
         const int s = b & 1, u = b >> 1;
         if (!mbar_wait(BAR(0 + s), u & 1, abort_flag))
@@ -275,13 +318,10 @@ gemm_q4_K_umma_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__re
           break;
         tc_fence_after();
         const uint32_t st = sbase + s * STAGE_BYTES;
-        const uint32_t acc_lo = tmem + s * 256, acc_hi = acc_lo + 128;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t db = umma_desc(st + 2 * OPERAND_BYTES + ks * 4096, 2048, 128);
-          umma_i8(acc_lo, umma_desc(st + ks * 4096, 2048, 128), db, idesc, ks > 0);
-          umma_i8(acc_hi, umma_desc(st + OPERAND_BYTES + ks * 4096, 2048, 128), db, idesc, ks > 0);
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          umma_i8(tmem + s * 256, umma_desc(st + 2 * OPERAND_BYTES + ks * 4096, 2048, 128),
+                  umma_desc(st + ks * 8192, 4096, 128), idesc, ks > 0);
         umma_commit(BAR(2 + s)); // operand stage may be overwritten
         umma_commit(BAR(4 + s)); // accumulators of this super-block complete
       }
@@ -289,48 +329,48 @@ gemm_q4_K_umma_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__re
     __syncwarp();
   } else {
     /* -------------------------------- drain -------------------------------- */
-    const int dw_id = warp - DRAIN_WARP0;
-    const int quad = warp & 3;     // tensor memory lanes this warp may read: 32*quad ..
-    const int half = dw_id >> 2;   // columns 64*half ..
-    const int n = quad * 32 + lane; // weight row inside the tile
-    float acc[64];
+    const int quad = warp & 3;                  // tensor memory lanes this warp may read: 32*quad ..
+    const int cgrp = (warp - DRAIN_WARP0) >> 2; // weight rows DRAIN_COLS*cgrp .. of the tile
+    const int m = quad * 32 + lane;             // activation row inside the tile = tensor memory lane
+    constexpr int MAGIC = 0x4B400000;           // bits of 12582912.0f: MAGIC + J read as a float is 12582912 + J
+    float acc[DRAIN_COLS];
 #pragma unroll
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < DRAIN_COLS; ++i)
       acc[i] = 0.f;
     bool ok = true;
     for (int b = 0; b < nb; ++b) {
       const int s = b & 1, u = b >> 1;
-      if (!mbar_wait(BAR(4 + s), u & 1, abort_flag)) {
-        ok = false;
-        break;
-      }
-      if (!mbar_wait(BAR(8 + (b & 3)), (b >> 2) & 1, abort_flag)) {
+      if (!mbar_wait(BAR(8 + (b & 3)), (b >> 2) & 1, abort_flag) || !mbar_wait(BAR(4 + s), u & 1, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint4 wm = *reinterpret_cast<const uint4 *>(smem + OFF_WMETA + (b & 3) * WMETA_BYTES + n * 16);
-      const float dw = __uint_as_float(wm.z), dmw = __uint_as_float(wm.w);
+      const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16) + s * 256 + cgrp * DRAIN_COLS;
+      uint32_t lo[2][4], hi[2][4];
+      tmem_ld4(trow, lo[0]);
+      tmem_ld4(trow + 128, hi[0]);
       const uint8_t *am = smem + OFF_AMETA + (b & 3) * UMMA_AMETA_BYTES;
-      const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16) + s * 256 + half * 64;
+      const float da = reinterpret_cast<const float *>(am)[m];
+      const uint4 bs = reinterpret_cast<const uint4 *>(am + 512)[m]; // this row's 8 sums of 32
+      const uint4 *wmeta = reinterpret_cast<const uint4 *>(smem + OFF_WMETA + (b & 3) * WMETA_BYTES) + cgrp * DRAIN_COLS;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t lo[16], hi[16];
-        tmem_ld16(trow + ch * 16, lo);
-        tmem_ld16(trow + 128 + ch * 16, hi);
+      for (int ch = 0; ch < DRAIN_COLS / 4; ++ch) {
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (ch + 1 < DRAIN_COLS / 4) { // next 4 columns travel while these are combined
+          tmem_ld4(trow + (ch + 1) * 4, lo[(ch + 1) & 1]);
+          tmem_ld4(trow + 128 + (ch + 1) * 4, hi[(ch + 1) & 1]);
+        }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int m = half * 64 + ch * 16 + i;
-          const float da = reinterpret_cast<const float *>(am)[m];
-          const uint4 bs = reinterpret_cast<const uint4 *>(am + 512)[m];
-          const int I = (int)lo[i] + ((int)hi[i] << 4);
-          int J = __dp2a_lo((int)bs.x, (int)wm.x, 0);
+        for (int i = 0; i < 4; ++i) {
+          const uint4 wm = wmeta[ch * 4 + i]; // weight row's 8 mins, d, dmin (same address in every lane)
+          const int I = (int)lo[ch & 1][i] + ((int)hi[ch & 1][i] << 4);
+          int J = __dp2a_lo((int)bs.x, (int)wm.x, MAGIC);
           J = __dp2a_hi((int)bs.y, (int)wm.x, J);
           J = __dp2a_lo((int)bs.z, (int)wm.y, J);
           J = __dp2a_hi((int)bs.w, (int)wm.y, J);
-          const float t = fmaf((float)I, dw, -((float)J * dmw));
-          acc[ch * 16 + i] = fmaf(t, da, acc[ch * 16 + i]);
+          const float fJ = __int_as_float(J) - 12582912.0f;
+          const float t = fmaf((float)I, __uint_as_float(wm.z), -(fJ * __uint_as_float(wm.w)));
+          acc[ch * 4 + i] = fmaf(t, da, acc[ch * 4 + i]);
         }
       }
       tc_fence_before();
@@ -338,14 +378,17 @@ gemm_q4_K_umma_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__re
       if (lane == 0)
         mbar_arrive(BAR(6 + s));
     }
-    if (ok) {
-      const int m_base = mt * TILE_M + half * 64;
-      float *crow = C + (size_t)nt * TILE_N + n;
+    const int row = mt * TILE_M + m;
+    if (ok && row < M) {
+      float *dst = C + (size_t)row * ldc + nt * TILE_N + cgrp * DRAIN_COLS;
+      if (c_vec4) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const int m = m_base + i;
-        if (m < M)
-          crow[(size_t)m * ldc] = acc[i];
+        for (int i = 0; i < DRAIN_COLS; i += 4)
+          *reinterpret_cast<float4 *>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < DRAIN_COLS; ++i)
+          dst[i] = acc[i];
       }
     }
   }
@@ -428,10 +471,11 @@ int launch_gemm_q4_K_umma(unsigned M, unsigned N, unsigned K, const float *A, co
                                                                          (int)M4, Mpad, nb);
   count_launch();
   NNTR_CHECK_CUDA(cudaGetLastError());
+  const int c_vec4 = (ldc % 4 == 0) && !(reinterpret_cast<uintptr_t>(C) & 15);
   dim3 grid(mtiles, N / TILE_N);
   gemm_q4_K_umma_kernel<<<grid, CTA_THREADS, SMEM_BYTES, st>>>(static_cast<const uint8_t *>(ws),
                                                                static_cast<const BlockQ4Kx8 *>(B), C, (int)ldc, (int)M,
-                                                               nb);
+                                                               nb, c_vec4);
   count_launch();
   return check_cuda(cudaGetLastError(), "gemm_q4_K tensor-path launch");
 }
