@@ -268,6 +268,11 @@ int launch_gemv_q4_K_nsplit(unsigned N, unsigned K, const float *x, const void *
 int launch_epoch_bump(unsigned long long *epoch, cudaStream_t st);
 int launch_gemv_q4_0(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
 int launch_gemv_q6_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
+/* bulk-copy ring version (gemv_q6k.cu); launch_gemv_q6_K dispatches to it when the shape fits */
+bool gemv_q6_K_stream_supported(unsigned N, unsigned K);
+int launch_gemv_q6_K_stream(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
+                            cudaStream_t st, unsigned *rows_done);
+int read_q6_status(int *out);
 /* M > 1 with activations already quantized to plain Q8 rows in `qa` */
 int launch_gemm_q4_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
                      cudaStream_t st);

@@ -26,6 +26,8 @@
  * These kernels are correct for every shape; they are bandwidth-efficient for
  * small M and compute-bound (CUDA-core dp4a) for large M.
  */
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace nntr {
@@ -414,7 +416,21 @@ int launch_gemv_q4_0(unsigned N, unsigned K, const float *x, const void *B, floa
 }
 
 int launch_gemv_q6_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st) {
-  (void)flags;
+  // the streaming kernel takes every shape whose rows group into 16-byte aligned stages; the rest stays here
+  static const bool stream_off = [] {
+    const char *e = getenv("NNTR_CUDA_Q6K_STREAM");
+    return e && e[0] == '0';
+  }();
+  if (!stream_off && x && B && y && N && !(reinterpret_cast<uintptr_t>(B) & 15) && gemv_q6_K_stream_supported(N, K)) {
+    unsigned done = 0;
+    const int rc = launch_gemv_q6_K_stream(N, K, x, B, y, flags, st, &done);
+    if (rc || done == N)
+      return rc;
+    // the last rows (less than one stage of the ring) go through the kernel below
+    B = static_cast<const uint8_t *>(B) + (size_t)done * (K / QK_K) * sizeof(BlockQ6K);
+    y += done;
+    N -= done;
+  }
   if (!x || !B || !y || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(B) & 1))
     return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q6_K: null or misaligned pointer");
   if (N == 0)

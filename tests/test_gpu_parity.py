@@ -136,6 +136,20 @@ def test_gemv_matches_checker(be, port, q, gen, N, K):
     assert np.array_equal(bits(got), bits(want)), "GEMV is expected to reproduce the reference bit for bit"
 
 
+@pytest.mark.parametrize("N,K", [(1516, 2560), (1000, 2048), (30, 2560), (620, 1792)])
+def test_gemv_q6_K_streaming_kernel_row_groupings(be, port, N, K):
+    """Q6_K decode GEMV with the lm_head's K: 10 (or 8, 7) super-blocks per row, i.e. three (four) whole rows per warp
+    step with idle lanes, stages of 12 (or 16) rows, and a last partial stage that the plain kernel finishes."""
+    rng = np.random.default_rng(N + K)
+    B = O.random_q6_K(rng, N, K)
+    x = acts(rng, 1, K)
+    want = port.gemm("q6_K", x, B, N)[0]
+    y = torch.full((N,), float("nan"), device="cuda")
+    be.gemm_q6_K(1, N, K, dev(x), K, dev(B), N, y, N)
+    be.device_status()
+    assert np.array_equal(bits(y.cpu().numpy()), bits(want))
+
+
 @pytest.mark.parametrize("q", ["q4_K", "q4_0", "q6_K"])
 def test_gemv_golden(be, golden, q):
     B = golden[f"{q}_x8"] if q != "q6_K" else golden[f"{q}_plain"]
