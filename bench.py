@@ -250,6 +250,48 @@ def other_shapes(be, torch, dev, peak, steps=20):
 
 
 # --------------------------------------------------------------------------
+# prefill GEMM sweep (Q4_K weights, tensor-core path), reported beside the headline
+# --------------------------------------------------------------------------
+PREFILL_SWEEP = [(64, 24576, 4096), (256, 24576, 4096), (1024, 24576, 4096)]  # (M, N, K): fused gate+up projection
+NOMINAL_INT8_TOPS = 4500.0  # dense int8, per GPU (nominal; no measured int8 figure is provided)
+
+
+def prefill_gemm_shapes(be, torch, dev, steps=10):
+    """Q4_K x Q8_K GEMM through the device entry point (activation quantizer + tcgen05 kernel per call), three distinct
+    copies of the weight in rotation (170 MB > L2), CUDA events on the launching stream. effective = 2*M*N*K / time;
+    mma = twice that (the 6-bit scale is split in two 8-bit operands, so the tensor pipe does two passes)."""
+    from oracle import oracle as O
+    out = []
+    rng = np.random.default_rng(11)
+    for M, N, K in PREFILL_SWEEP:
+        base = torch.from_numpy(O.random_q4_Kx8(rng, N, K)).to(dev)
+        mats = [base, torch.roll(base, 4099 * 16), torch.roll(base, 2 * 4099 * 16)]
+        A = torch.randn(M, K, device=dev)
+        C = torch.empty(M, N, device=dev)
+        ws = torch.empty(be.gemm_workspace_bytes("q4_K", M, N, K), dtype=torch.uint8, device=dev)
+        be.set_gemm_path("auto")
+        for W in mats:
+            be.gemm_q4_K(M, N, K, A, K, W, N, C, N, ws)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            for W in mats:
+                be.gemm_q4_K(M, N, K, A, K, W, N, C, N, ws)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (steps * len(mats))
+        eff = 2.0 * M * N * K / (us * 1e-6) / 1e12
+        out.append({"M": M, "N": N, "K": K, "qtype": "q4_K", "path": "tcgen05 kind::i8", "us_per_call": round(us, 1),
+                    "effective_TOP/s": round(eff, 1), "mma_TOP/s": round(2 * eff, 1),
+                    "mma_frac_of_nominal_int8": round(2 * eff / NOMINAL_INT8_TOPS, 4)})
+        del mats, base, A, C, ws
+        torch.cuda.empty_cache()
+    be.device_status()
+    return out
+
+
+# --------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------
 def run_ours(args):
@@ -417,6 +459,7 @@ def run_ours(args):
         per_launch_us = ms * 1e3 / (args.steps * RING)
         achieved = ALG_BYTES / (per_launch_us * 1e-6) / 1e9
         others = other_shapes(be, torch, dev, peak) if (world == 1 and not args.no_extra) else None
+        prefill = prefill_gemm_shapes(be, torch, dev) if (world == 1 and not args.no_extra) else None
         cpu_desc = None
         if world == 1 and not args.no_cpu:
             _, cpu_desc, _ = cpu_reference_gbps(host_ring, args.cpu_seconds)
@@ -440,7 +483,7 @@ def run_ours(args):
                             "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_BYTES,
                             "kernel": "gemv_q4_K_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
                "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
-               "other_decode_gemv_shapes": others}
+               "other_decode_gemv_shapes": others, "prefill_gemm_sweep": prefill}
         print(json.dumps(out))
     if group is not None:
         group.close()

@@ -84,6 +84,11 @@ def _gemm(qtype: str, M: int, N: int, K: int, A, lda: int, B, ldb: int, C, ldc: 
     return C
 
 
+def gemm_workspace_bytes(qtype: str, M: int, N: int, K: int) -> int:
+    """Scratch a device-pointer GEMM call needs for its quantized activations."""
+    return int(lib().nntr_cuda_gemm_workspace_bytes(QTYPE[qtype], M, N, K))
+
+
 GEMM_PATHS = {"auto": 0, "exact": 1, "tensor": 2}
 
 
