@@ -113,6 +113,13 @@ size_t nntr_cuda_gemm_workspace_bytes(int qtype, unsigned M, unsigned N, unsigne
 #define NNTR_CUDA_GEMM_PATH_TENSOR 2
 int nntr_cuda_set_gemm_path(int path);
 
+/** Measures the device's dense int8 tensor-core rate with a stream of the MMA
+ *  instruction the TENSOR path uses (tcgen05.mma kind::i8, 128 x 256 x 32) on
+ *  every SM: *tops = TOP/s at 2 ops per multiply-accumulate, *clk_per_mma
+ *  (may be null) = SM clocks per instruction on the first SM. Blocking; takes a
+ *  few milliseconds. Measurement aid: no counterpart on the CPU path. */
+int nntr_cuda_measure_int8_peak(double *tops, double *clk_per_mma);
+
 /** C[M][N] = A[M][K] x W^T with W a quantized [N][K] weight (device pointers).
  *  Same argument meaning as cpu_backend.h:937-977 gemm_q4_0 / gemm_q4_K /
  *  gemm_q6_K -> GI/ggml_interface_omp.cpp:303,404,506: lda and ldb are ignored,

@@ -89,6 +89,14 @@ def gemm_workspace_bytes(qtype: str, M: int, N: int, K: int) -> int:
     return int(lib().nntr_cuda_gemm_workspace_bytes(QTYPE[qtype], M, N, K))
 
 
+def measure_int8_peak() -> tuple[float, float]:
+    """(dense int8 TOP/s of the device, SM clocks per 128x256x32 MMA), measured with the GEMM's own MMA instruction."""
+    import ctypes as C
+    tops, clk = C.c_double(), C.c_double()
+    check(lib().nntr_cuda_measure_int8_peak(C.byref(tops), C.byref(clk)))
+    return tops.value, clk.value
+
+
 GEMM_PATHS = {"auto": 0, "exact": 1, "tensor": 2}
 
 

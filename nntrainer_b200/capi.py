@@ -42,6 +42,7 @@ SIGNATURES = {
     "nntr_cuda_dequantize_weight_dev": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
     "nntr_cuda_gemm_workspace_bytes": (_sz, [_i, _u, _u, _u]),
     "nntr_cuda_set_gemm_path": (_i, [_i]),
+    "nntr_cuda_measure_int8_peak": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "nntr_cuda_gemm_q4_K_dev": (_i, _GEMM_DEV),
     "nntr_cuda_gemm_q4_0_dev": (_i, _GEMM_DEV),
     "nntr_cuda_gemm_q6_K_dev": (_i, _GEMM_DEV),

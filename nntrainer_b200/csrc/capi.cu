@@ -345,6 +345,8 @@ size_t nntr_cuda_gemm_workspace_bytes(int qtype, unsigned M, unsigned N, unsigne
   return workspace_bytes(qtype, M, N, K);
 }
 
+int nntr_cuda_measure_int8_peak(double *tops, double *clk_per_mma) { return measure_int8_peak(tops, clk_per_mma); }
+
 int nntr_cuda_set_gemm_path(int path) {
   if (path != NNTR_CUDA_GEMM_PATH_AUTO && path != NNTR_CUDA_GEMM_PATH_EXACT && path != NNTR_CUDA_GEMM_PATH_TENSOR)
     return set_error(NNTR_CUDA_ERR_INVALID, "set_gemm_path: unknown path %d", path);

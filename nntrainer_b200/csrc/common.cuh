@@ -284,6 +284,8 @@ size_t umma_workspace_bytes(unsigned M, unsigned K);
 int launch_gemm_q4_K_umma(unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C, unsigned ldc,
                           void *ws, cudaStream_t st);
 int read_umma_status(int *out);
+/* dense int8 tensor-core rate of the current device, measured (umma_peak.cu) */
+int measure_int8_peak(double *tops_out, double *clk_per_mma_out);
 int launch_gemm_q6_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
                      cudaStream_t st);
 

@@ -100,3 +100,12 @@ def test_prefill_size_property_linearity_in_activation_scale(be):
     # (both below 4*floor(M/4)), so the values must be identical
     c3 = run(be, "tensor", 132, N, K, A[:132].contiguous(), B)
     assert np.array_equal(c3[:132].view(np.uint32), c1[:132].view(np.uint32))
+
+
+def test_int8_peak_measurement_is_plausible(be):
+    """The int8 rate the prefill fraction is quoted against: a dense tcgen05 kind::i8 stream on every SM. A B200 is
+    specified at 4.5 POP/s dense; anything outside 1.5 .. 6 POP/s means the measurement is not doing the work."""
+    tops, clk = be.measure_int8_peak()
+    be.device_status()
+    assert 1500.0 < tops < 6000.0
+    assert 100.0 < clk < 400.0  # 128 x 256 x 32 multiply-accumulates per instruction
