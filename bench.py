@@ -495,6 +495,47 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """Small single-kernel cases for profiler captures (a few hundred MB on the device, a handful of launches)."""
+    import torch
+    from nntrainer_b200 import backend as be
+    from nntrainer_b200 import build as nb_build
+    from oracle import oracle as O
+    nb_build.build()
+    be.init(0)
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(3)
+    reps = max(1, args.steps if args.steps < 100 else 5)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.case == "prefill":
+        M, N, K = 512, 4096, 4096
+        W = torch.from_numpy(O.random_q4_Kx8(rng, N, K)).to(dev)
+        A = torch.randn(M, K, device=dev)
+        C = torch.empty(M, N, device=dev)
+        ws = torch.empty(be.gemm_workspace_bytes("q4_K", M, N, K), dtype=torch.uint8, device=dev)
+        be.set_gemm_path("tensor")
+        call = lambda: be.gemm_q4_K(M, N, K, A, K, W, N, C, N, ws)
+        work = {"case": "prefill", "M": M, "N": N, "K": K, "qtype": "q4_K", "ops": 2.0 * M * N * K}
+    else:  # lm_head
+        N, K = 151936, 2560
+        W = torch.from_numpy(O.random_q6_K(rng, N, K)).to(dev)
+        x = torch.randn(1, K, device=dev)
+        y = torch.empty(1, N, device=dev)
+        call = lambda: be.gemm_q6_K(1, N, K, x, K, W, N, y, N)
+        work = {"case": "lm_head", "N": N, "K": K, "qtype": "q6_K", "bytes": N * (K // 256) * 210 + 4 * K + 4 * N}
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    be.device_status()
+    work["us_per_call"] = round(e0.elapsed_time(e1) * 1e3 / reps, 2)
+    print(json.dumps(work))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -511,9 +552,13 @@ def main():
     ap.add_argument("--ring", type=int, default=RING, help="distinct weight matrices per step (default keeps every launch out of L2)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the GEMV kernel from an ncu capture (reported as roofline.traffic)")
+    ap.add_argument("--case", default=None, choices=["prefill", "lm_head"],
+                    help="run one small single-kernel case (profiler captures) instead of the benchmark")
     args = ap.parse_args()
     globals()["RING"] = args.ring
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
