@@ -220,6 +220,9 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
   const uint32_t bars = smem_u32(smem + L.bars);
   const uint32_t full0 = bars, empty0 = bars + 8 * NSTAGE, done0 = bars + 16 * NSTAGE,
                  free0 = bars + 16 * NSTAGE + 8 * ngslot;
+  const uint32_t xread_bar = smem_u32(smem + L.abort_flag + 8); // N-split: the consumers have read the activation
+  // launch >= 1 of an N-split sequence whose activation arrives as numbered elements
+  const bool chained_by_tags = ex.n_ranks && (ex.x_tagged & 1) && !(ex.x_tagged & 2) && ex.layer > 0;
   const int slot_mask = ngslot - 1;
   const int slot_shift = 31 - __clz(ngslot);
 
@@ -233,6 +236,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    mbar_init(xread_bar, 1);
     for (int i = 0; i < NSTAGE; ++i) {
       mbar_init(full0 + 8 * i, 1);
       mbar_init(empty0 + 8 * i, 2); // the two warps that read a stage
@@ -281,33 +285,49 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     }
   } else if (warp == EPILOGUE_WARP) {
     // ------------------------------------------------------------ epilogue
-    pdl_wait(); // y may still be read by the previous kernel until it has finished
+    // Launches of an N-split sequence after the first are ordered by the data itself (numbered elements, "done
+    // reading" flags), not by kernel boundaries: they do not wait for the previous grid to drain.
+    unsigned long long epoch_early = 0;
+    if (ex.n_ranks && ex.layer > 0)
+      epoch_early = *reinterpret_cast<const volatile unsigned long long *>(ex.epoch);
+    if (!chained_by_tags)
+      pdl_wait(); // y may still be read by the previous kernel until it has finished
     const int j = lane >> 3, r = lane & 7;
     uint32_t tag = 0;
     if (ex.n_ranks) {
       // N-split. Launch number seq writes gathered buffer seq % 2 on every rank. A rank reads that buffer as the input
-      // of launch seq - 1, so before the first store every CTA of every rank must have said "launch seq - 1: done
-      // reading" (a relaxed store into its flag slot, see the consumers; a peer may already be one launch ahead, hence
-      // >=). The poll runs while the consumer warps work, and it is bounded.
-      const unsigned long long seq = (unsigned long long)(*ex.epoch - 1) * ex.layers_per_epoch + ex.layer + 1;
+      // of launch seq - 1, so before the first store every rank (this one included) must have said "launch seq - 1:
+      // done reading". Two levels: the CTAs of a rank count themselves on a local counter once their consumers have
+      // read the input; the last one stores the launch number into ONE slot per destination rank, so a waiting
+      // epilogue polls n_ranks words instead of one per CTA of every rank. Every wait is bounded.
+      const unsigned long long seq =
+        ((ex.layer > 0 ? epoch_early : *ex.epoch) - 1) * ex.layers_per_epoch + ex.layer + 1;
       tag = (uint32_t)seq;
-      if (seq > 1 && ex.n_ranks > 1) {
-        // slots of the other ranks only: this rank's own launch seq - 1 has finished (stream order). All of a lane's
-        // loads are issued together; the round is repeated (bounded) while any slot is still behind.
-        const int per_rank = (int)gridDim.x, n_slots = (ex.n_ranks - 1) * per_rank;
+      bool last = false;
+      if (mbar_wait(xread_bar, 0, abort_flag)) {
+        if (lane == 0) {
+          unsigned long long *cnt = ex.flag[ex.rank] + (size_t)ex.rank * NSPLIT_MAX_CTAS + NSPLIT_MAX_CTAS / 2 + (seq & 1);
+          last = atomicAdd(cnt, 1ull) == (unsigned long long)gridDim.x - 1;
+          if (last)
+            atomicExch(cnt, 0ull); // launch seq + 2 counts here again, long after every CTA of this launch has
+        }
+        last = __shfl_sync(FULL, last, 0);
+        if (last && lane < ex.n_ranks) {
+          volatile unsigned long long *slot = ex.flag[lane] + (size_t)ex.rank * NSPLIT_MAX_CTAS;
+          *slot = seq;
+        }
+      }
+      if (seq > 1) {
         bool all_ok = false;
-        for (uint32_t it = 0; it < (1u << 20) && !all_ok; ++it) {
+        for (uint32_t it = 0; it < (1u << 21) && !all_ok; ++it) {
           bool mine = true;
-          for (int t = lane; t < n_slots; t += 32) {
-            int src = t / per_rank;
-            src += (src >= ex.rank);
-            const volatile unsigned long long *slot =
-              ex.flag[ex.rank] + (size_t)src * NSPLIT_MAX_CTAS + (t - (t / per_rank) * per_rank);
-            mine = mine && (*slot >= seq - 1);
+          if (lane < ex.n_ranks) {
+            const volatile unsigned long long *slot = ex.flag[ex.rank] + (size_t)lane * NSPLIT_MAX_CTAS;
+            mine = *slot >= seq - 1; // a peer may already be one launch ahead
           }
           all_ok = __all_sync(FULL, mine);
           if (!all_ok && it > 4)
-            __nanosleep(200);
+            __nanosleep(100);
         }
         if (!all_ok) {
           *abort_flag = 1;
@@ -352,13 +372,18 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     trace_stamp(5);
   } else {
     // ----------------------------------------------------------- consumers
-    pdl_wait();
+    // the epoch word changes only between passes (before launch 0), so later launches read it while they wait
+    unsigned long long epoch_early = 0;
+    if (ex.n_ranks && ex.layer > 0)
+      epoch_early = *reinterpret_cast<const volatile unsigned long long *>(ex.epoch);
+    if (!chained_by_tags)
+      pdl_wait();
     trace_stamp(2);
     const uint32_t in_tag =
-      ex.n_ranks ? (uint32_t)((unsigned long long)(*ex.epoch - 1) * ex.layers_per_epoch + ex.layer) : 0u;
+      ex.n_ranks ? (uint32_t)(((ex.layer > 0 ? epoch_early : *ex.epoch) - 1) * ex.layers_per_epoch + ex.layer) : 0u;
     for (int b = warp; b < nb && !*abort_flag; b += CONSUMER_WARPS) {
       float4 v0, v1;
-      if (ex.x_tagged) {
+      if (ex.x_tagged & 1) {
         // the activation arrives as (value, launch number) pairs stored by the previous launch of every rank:
         // poll (bounded) until all eight elements of the lane carry that launch's number
         const uint4 *xs = reinterpret_cast<const uint4 *>(x) + (size_t)(b * QK_K + lane * 8) / 2;
@@ -372,8 +397,8 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
             if (lane == 0)
               t = *probe;
             seen = __shfl_sync(FULL, t, 0) == in_tag;
-            if (!seen && it > 4)
-              __nanosleep(100);
+            if (!seen && it > 8)
+              __nanosleep(40);
           }
         }
         bool ok = false;
@@ -395,8 +420,8 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
                              __uint_as_float(e[1].z));
             v1 = make_float4(__uint_as_float(e[2].x), __uint_as_float(e[2].z), __uint_as_float(e[3].x),
                              __uint_as_float(e[3].z));
-          } else if (it > 2) {
-            __nanosleep(200);
+          } else if (it > 4) {
+            __nanosleep(40);
           }
         }
         if (!ok) {
@@ -420,12 +445,8 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
         *reinterpret_cast<float *>(dst + 272) = qv.d;
     }
     consumer_bar_sync();
-    if (ex.n_ranks && threadIdx.x < ex.n_ranks && !*abort_flag) {
-      // this CTA has finished reading its input: tell every rank (relaxed store, nothing needs to be ordered after it)
-      const unsigned long long seq = (unsigned long long)in_tag + 1;
-      volatile unsigned long long *slot = ex.flag[threadIdx.x] + (size_t)ex.rank * NSPLIT_MAX_CTAS + blockIdx.x;
-      *slot = seq;
-    }
+    if (ex.n_ranks && threadIdx.x == 0)
+      mbar_arrive(xread_bar); // this CTA has finished reading its input: the epilogue warp counts it (see there)
     trace_stamp(3);
 
     const int j = lane >> 3, r = lane & 7;
@@ -497,6 +518,11 @@ int launch_gemv_q4_K_nsplit(unsigned N, unsigned K, const float *x, const void *
   // arrivals per layer at every rank = CTAs per launch (same on all ranks) x ranks; filled in by the launcher below
   static thread_local GemvExchange tl_ex;
   tl_ex = ex;
+  // Launches after the first are ordered by the numbered elements and the flags alone; whether they also wait for the
+  // previous grid to drain is a tuning choice: measured faster without the wait on one GPU (-0.75 us per launch),
+  // slower on two (+0.6 us), so the default keeps the wait whenever peers are involved.
+  if (env_int("NNTR_NSPLIT_GRID_WAIT", ex.n_ranks > 1 ? 1 : 0))
+    tl_ex.x_tagged |= 2;
   g_next_exchange = &tl_ex;
   const int rc = launch_gemv_q4_K_batched(N, K, x, B, reinterpret_cast<float *>(ex.y[ex.rank]), flags, 1, none, st);
   g_next_exchange = nullptr;
