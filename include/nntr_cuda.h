@@ -245,6 +245,31 @@ int nntr_cuda_moe_forward_dev(const nntr_moe_desc *d, unsigned tokens, const flo
 int nntr_cuda_moe_route_dev(const nntr_moe_desc *d, unsigned tokens, const float *x, int *idx_out, float *w_out,
                             void *workspace, size_t workspace_bytes, void *stream);
 
+/** Expert parallelism over the GPUs of one node (one process per GPU): rank r
+ *  owns experts [r*E/P, (r+1)*E/P); the tables of nntr_moe_desc hold NULL for
+ *  the experts of other ranks. The activation x is the same on every rank (it
+ *  comes out of a gathered projection), so every rank routes identically; only
+ *  the owner of a selected expert runs its FFN, and its down projection stores
+ *  the outputs as (value, call number) pairs straight into EVERY rank's buffer
+ *  `out[d]` over NVLink (peer memory mapped through CUDA IPC). Each rank then
+ *  combines all experts of all tokens in ascending expert order, waiting for the
+ *  numbered elements: y is complete and bit-identical on every rank, and equal
+ *  to the single-GPU result. No collective call. Every wait is bounded.
+ *   out[d]        rank d's buffer of nntr_cuda_moe_ep_buffer_bytes(desc, tokens) (zeroed once)
+ *   heartbeat[d]  rank d's array of 8 words (zeroed once): "rank s has started call n"
+ *   epoch, layers_per_epoch, layer   call numbering as in nntr_exchange: number =
+ *                 (epoch - 1) * layers_per_epoch + layer + 1; all ranks make the same calls in the same order */
+typedef struct {
+  int n_ranks, rank;
+  void *out[8];
+  unsigned long long *heartbeat[8];
+  const unsigned long long *epoch;
+  unsigned layers_per_epoch, layer;
+} nntr_moe_ep;
+size_t nntr_cuda_moe_ep_buffer_bytes(const nntr_moe_desc *d, unsigned tokens);
+int nntr_cuda_moe_forward_ep_dev(const nntr_moe_desc *d, const nntr_moe_ep *ep, unsigned tokens, const float *x,
+                                 float *y, void *workspace, size_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------ host-pointer entry points */
 
 /** Upload a weight tensor's bytes to device memory once, keyed by its host

@@ -201,7 +201,8 @@ class MoeLayer:
         import ctypes as C
         torch = _torch()
         self.H, self.E = router_w.shape
-        self.I = gate_w[0].numel() * _BLOCK[qtype][0] // _BLOCK[qtype][1] // self.H
+        first = next(w for w in gate_w if w is not None)  # experts of other ranks are None under expert parallelism
+        self.I = first.numel() * _BLOCK[qtype][0] // _BLOCK[qtype][1] // self.H
         self.top_k = top_k
         self._keep = [router_w, gate_w, up_w, down_w, router_bias, gate_b, up_b, down_b]
         dev = router_w.device
@@ -209,7 +210,7 @@ class MoeLayer:
         def table(ts):
             if ts is None:
                 return None
-            t = torch.tensor([x.data_ptr() for x in ts], dtype=torch.int64, device=dev)
+            t = torch.tensor([x.data_ptr() if x is not None else 0 for x in ts], dtype=torch.int64, device=dev)
             self._keep.append(t)
             return t
 
@@ -235,6 +236,41 @@ class MoeLayer:
         ws = self._workspace(T)
         check(lib().nntr_cuda_moe_forward_dev(self._C.byref(self.desc), T, x.data_ptr(), y.data_ptr(), ws.data_ptr(),
                                               ws.numel(), _stream()))
+        return y
+
+    def enable_expert_parallel(self, max_tokens: int, layers_per_epoch: int = 1, group=None):
+        """Expert parallelism over the ranks of ``group`` (one process per GPU). This rank must have been built with
+        None in place of the weights of experts it does not own (``nsplit.expert_range``). Allocates the exchange
+        buffers for calls of up to ``max_tokens`` tokens and maps the peers'."""
+        from .nsplit import PeerBuffers
+        C = self._C
+        nbytes = int(lib().nntr_cuda_moe_ep_buffer_bytes(C.byref(self.desc), max_tokens))
+        self._ep_buf = PeerBuffers([nbytes, 64, 8], group)  # expert outputs (two alternating), heartbeat words, epoch
+        self._ep_tokens, self._ep_layers = max_tokens, layers_per_epoch
+        return self
+
+    def forward_ep(self, x, layer: int = 0, bump_epoch: bool = True):
+        """Expert-parallel forward: every rank passes the same x and gets the complete y. ``layer`` numbers the call
+        inside a pass of ``layers_per_epoch`` calls; ``bump_epoch`` starts a new pass (every rank alike)."""
+        torch = _torch()
+        C = self._C
+        T = x.shape[0]
+        if T != self._ep_tokens:
+            raise ValueError("expert-parallel calls use the token count the buffers were sized for")
+        pb = self._ep_buf
+        if bump_epoch:
+            check(lib().nntr_cuda_epoch_bump_dev(pb.ptr(pb.rank, 2), _stream()))
+        ep = capi.MoeEp()
+        ep.n_ranks, ep.rank = pb.world, pb.rank
+        for r in range(pb.world):
+            ep.out[r] = pb.ptr(r, 0)
+            ep.heartbeat[r] = pb.ptr(r, 1)
+        ep.epoch = pb.ptr(pb.rank, 2)
+        ep.layers_per_epoch, ep.layer = self._ep_layers, layer
+        y = torch.empty((T, self.H), dtype=torch.float32, device=x.device)
+        ws = self._workspace(T)
+        check(lib().nntr_cuda_moe_forward_ep_dev(C.byref(self.desc), C.byref(ep), T, x.data_ptr(), y.data_ptr(),
+                                                 ws.data_ptr(), ws.numel(), _stream()))
         return y
 
     def route(self, x):

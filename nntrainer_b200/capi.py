@@ -59,6 +59,8 @@ SIGNATURES = {
     "nntr_cuda_moe_workspace_bytes": (_sz, [_vp, _u]),
     "nntr_cuda_moe_forward_dev": (_i, [_vp, _u, _vp, _vp, _vp, _sz, _vp]),
     "nntr_cuda_moe_route_dev": (_i, [_vp, _u, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "nntr_cuda_moe_ep_buffer_bytes": (_sz, [_vp, _u]),
+    "nntr_cuda_moe_forward_ep_dev": (_i, [_vp, _vp, _u, _vp, _vp, _vp, _sz, _vp]),
     "nntr_cuda_register_weight": (_i, [_vp, _sz, _i, _u, _u]),
     "nntr_cuda_unregister_weight": (_i, [_vp]),
     "nntr_cuda_weight_device_ptr": (_vp, [_vp]),
@@ -83,6 +85,12 @@ class Exchange(C.Structure):
     """nntr_exchange of include/nntr_cuda.h."""
     _fields_ = [("n_ranks", C.c_int), ("rank", C.c_int), ("y", C.c_void_p * 8), ("flags", C.c_void_p * 8),
                 ("epoch", C.c_void_p), ("layers_per_epoch", C.c_uint), ("layer", C.c_uint), ("x_tagged", C.c_int)]
+
+
+class MoeEp(C.Structure):
+    """nntr_moe_ep of include/nntr_cuda.h."""
+    _fields_ = [("n_ranks", C.c_int), ("rank", C.c_int), ("out", C.c_void_p * 8), ("heartbeat", C.c_void_p * 8),
+                ("epoch", C.c_void_p), ("layers_per_epoch", C.c_uint), ("layer", C.c_uint)]
 
 
 def declared_symbols() -> list[str]:

@@ -246,6 +246,11 @@ struct GemvExchange {
   unsigned layers_per_epoch, layer;
   unsigned long long slice_offset;
   int x_tagged;
+  /* Expert-parallel MoE (batched launch): outputs of the problems this rank owns go, numbered, into every rank's
+   * buffer at problem * y_stride (+ parity_stride for odd launch numbers: two buffers in alternation); no "done
+   * reading" flags -- the ranks stay in step through the heartbeat words of the MoE kernels (moe.cu). */
+  int no_flags;
+  unsigned long long parity_stride;
 };
 
 /* Activation tiles of the tensor-core GEMM: per (128 activation rows, super-block) the Q8_K values in the MMA operand
@@ -265,6 +270,9 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
                              unsigned n_problems, GemvBatch batch, cudaStream_t st);
 int launch_gemv_q4_K_nsplit(unsigned N, unsigned K, const float *x, const void *B, GemvExchange ex, unsigned flags,
                             cudaStream_t st);
+int launch_gemv_q4_K_batched_publish(unsigned N, unsigned K, const float *x, unsigned n_problems, GemvBatch batch,
+                                     GemvExchange ex, cudaStream_t st);
+int read_moe_status(int *out);
 int launch_epoch_bump(unsigned long long *epoch, cudaStream_t st);
 int launch_gemv_q4_0(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
 int launch_gemv_q6_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);

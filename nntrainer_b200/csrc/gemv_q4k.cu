@@ -212,6 +212,12 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     x += (long long)(p / batch.x_div) * batch.x_stride;
     y += (long long)p * batch.y_stride;
   }
+  if (batch.w_table) {
+    // the table is written by the kernel launched just before; a null entry marks a problem another rank owns
+    pdl_wait();
+    if (batch.w_table[blockIdx.y] == nullptr)
+      return;
+  }
   const SmemLayout L = smem_layout(nb, ngslot);
   uint8_t *ring = smem + L.ring;
   uint8_t *act = smem + L.act;
@@ -294,7 +300,12 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       pdl_wait(); // y may still be read by the previous kernel until it has finished
     const int j = lane >> 3, r = lane & 7;
     uint32_t tag = 0;
-    if (ex.n_ranks) {
+    unsigned long long ex_off = ex.slice_offset;
+    if (ex.n_ranks && ex.no_flags) {
+      const unsigned long long seq = (*ex.epoch - 1) * ex.layers_per_epoch + ex.layer + 1;
+      tag = (uint32_t)seq;
+      ex_off = (unsigned long long)blockIdx.y * (unsigned long long)batch.y_stride + (seq & 1) * ex.parity_stride;
+    } else if (ex.n_ranks) {
       // N-split. Launch number seq writes gathered buffer seq % 2 on every rank. A rank reads that buffer as the input
       // of launch seq - 1, so before the first store every rank (this one included) must have said "launch seq - 1:
       // done reading". Two levels: the CTAs of a rank count themselves on a local counter once their consumers have
@@ -356,7 +367,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
             // (value, launch number) in one 8-byte store straight into every rank's gathered vector: the reader checks
             // the number of every element it uses, so no fence orders these stores against anything
             for (int d = 0; d < ex.n_ranks; ++d) {
-              volatile uint2 *dst = ex.y[d] + ex.slice_offset + o;
+              volatile uint2 *dst = ex.y[d] + ex_off + o;
               asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag)
                            : "memory");
             }
@@ -445,7 +456,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
         *reinterpret_cast<float *>(dst + 272) = qv.d;
     }
     consumer_bar_sync();
-    if (ex.n_ranks && threadIdx.x == 0)
+    if (ex.n_ranks && !ex.no_flags && threadIdx.x == 0)
       mbar_arrive(xread_bar); // this CTA has finished reading its input: the epilogue warp counts it (see there)
     trace_stamp(3);
 
@@ -504,7 +515,28 @@ int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, floa
 }
 
 static GemvExchange g_no_exchange = {};
-static thread_local const GemvExchange *g_next_exchange = nullptr; // set by launch_gemv_q4_K_nsplit around its launch
+static thread_local const GemvExchange *g_next_exchange = nullptr; // set by the exchange launchers around their launch
+int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
+                             unsigned n_problems, GemvBatch batch, cudaStream_t st);
+
+/* Batched launch whose epilogue publishes each problem's outputs, numbered, into every rank's buffer (expert-parallel
+ * MoE). ex.no_flags must be set; problems with a null table entry are skipped. */
+int launch_gemv_q4_K_batched_publish(unsigned N, unsigned K, const float *x, unsigned n_problems, GemvBatch batch,
+                                     GemvExchange ex, cudaStream_t st) {
+  if (ex.n_ranks < 1 || ex.n_ranks > 8 || ex.rank < 0 || ex.rank >= ex.n_ranks || !ex.epoch || !ex.no_flags)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_batched_publish: bad exchange description");
+  for (int d = 0; d < ex.n_ranks; ++d)
+    if (!ex.y[d])
+      return set_error(NNTR_CUDA_ERR_INVALID, "gemv_batched_publish: null peer pointer for rank %d", d);
+  static thread_local GemvExchange tl_ex;
+  tl_ex = ex;
+  tl_ex.x_tagged = 0;
+  g_next_exchange = &tl_ex;
+  const int rc =
+    launch_gemv_q4_K_batched(N, K, x, nullptr, reinterpret_cast<float *>(ex.y[ex.rank]), 0, n_problems, batch, st);
+  g_next_exchange = nullptr;
+  return rc;
+}
 
 int launch_gemv_q4_K_nsplit(unsigned N, unsigned K, const float *x, const void *B, GemvExchange ex, unsigned flags,
                             cudaStream_t st) {

@@ -28,6 +28,15 @@
 
 namespace nntr {
 
+/* device-side view of nntr_moe_ep (all-zero: single GPU) */
+struct MoeEp {
+  int n_ranks, rank;
+  unsigned long long *hb[8]; // hb[d]: rank d's heartbeat words, one per source rank
+  const unsigned long long *epoch;
+  unsigned layers_per_epoch, layer;
+  unsigned long long parity_stride; // elements between the two alternating expert-output buffers
+};
+
 constexpr int ROUTER_WARPS = 8;
 constexpr int MAX_E_PER_LANE = 8; // up to 256 experts
 
@@ -36,9 +45,15 @@ __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, const float *__restrict__ bias, int H, int E,
                   int topk, const void *const *__restrict__ gate_w, const void *const *__restrict__ up_w,
                   const void *const *__restrict__ down_w, int *__restrict__ idx_out, float *__restrict__ w_out,
-                  const void **__restrict__ gu_table, const void **__restrict__ dn_table) {
+                  const void **__restrict__ gu_table, const void **__restrict__ dn_table, MoeEp ep) {
   extern __shared__ float rsm[]; // [ROUTER_WARPS][E]
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (ep.n_ranks && t == 0 && threadIdx.x < ep.n_ranks) {
+    // heartbeat: "this rank has started layer call seq", i.e. it has finished combining seq - 1 (stream order)
+    const unsigned long long seq = (*ep.epoch - 1) * ep.layers_per_epoch + ep.layer + 1;
+    volatile unsigned long long *slot = ep.hb[threadIdx.x] + ep.rank;
+    *slot = seq;
+  }
   const float *xt = x + (size_t)t * H;
   const int per = (E + 31) / 32;
   float acc[MAX_E_PER_LANE];
@@ -143,12 +158,14 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
 /* a[p][i] from the gate / up GEMV outputs gu[2p][i], gu[2p+1][i] */
 __global__ void moe_act_kernel(const float *__restrict__ gu, float *__restrict__ a, const int *__restrict__ idx,
                                const float *const *__restrict__ gate_b, const float *const *__restrict__ up_b, int kind,
-                               float alpha, int I, long total) {
+                               float alpha, int I, long total, int e_lo, int e_hi) {
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total)
     return;
   const long p = i / I;
   const int c = (int)(i - p * I);
+  if (idx[p] < e_lo || idx[p] >= e_hi)
+    return; // expert owned by another rank
   float g = gu[(2 * p) * I + c], u = gu[(2 * p + 1) * I + c];
   float r;
   if (kind == 0) {
@@ -194,6 +211,70 @@ __global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__re
   y[i] = acc;
 }
 
+/* Expert-parallel combine: the expert outputs arrive as (value, call number) pairs stored by the owning ranks' down
+ * projections into this rank's buffer (two buffers in alternation). First the heartbeat of every rank for this call
+ * (all ranks run the same calls in the same order; a rank that is a call ahead can then not overwrite a buffer still
+ * being read), then per expert, ascending, the element with this call's number. Every wait is bounded. */
+__global__ void moe_combine_ep_kernel(const uint2 *__restrict__ eo, const int *__restrict__ idx,
+                                      const float *__restrict__ w, const float *const *__restrict__ down_b,
+                                      float *__restrict__ y, int H, int topk, long total, MoeEp ep, int *status) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned long long seq = (*ep.epoch - 1) * ep.layers_per_epoch + ep.layer + 1;
+  if (threadIdx.x < ep.n_ranks) {
+    const volatile unsigned long long *slot = ep.hb[ep.rank] + threadIdx.x;
+    bool ok = false;
+    for (uint32_t it = 0; it < (1u << 22) && !ok; ++it) {
+      ok = *slot >= seq;
+      if (!ok && it > 16)
+        __nanosleep(64);
+    }
+    if (!ok)
+      atomicExch(status, NNTR_CUDA_ERR_TIMEOUT);
+  }
+  __syncthreads();
+  if (i >= total)
+    return;
+  const long t = i / H;
+  const int h = (int)(i - t * H);
+  const uint2 *buf = eo + (seq & 1) * ep.parity_stride;
+  const uint32_t tag = (uint32_t)seq;
+  float acc = 0.f;
+  int last = -1;
+  for (int k = 0; k < topk; ++k) {
+    int best = 0x7fffffff, bj = -1;
+    for (int j = 0; j < topk; ++j) {
+      const int e = idx[t * topk + j];
+      if (e > last && e < best) {
+        best = e;
+        bj = j;
+      }
+    }
+    if (bj < 0)
+      break;
+    last = best;
+    const volatile uint2 *src = buf + (t * topk + bj) * H + h;
+    uint32_t vx = 0, vy = 0;
+    bool ok = false;
+    for (uint32_t it = 0; it < (1u << 22) && !ok; ++it) {
+      asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(vx), "=r"(vy) : "l"(src) : "memory");
+      ok = vy == tag;
+      if (!ok && it > 16)
+        __nanosleep(64);
+    }
+    if (!ok) {
+      atomicExch(status, NNTR_CUDA_ERR_TIMEOUT);
+      break;
+    }
+    float v = __uint_as_float(vx);
+    if (down_b)
+      v = __fadd_rn(v, down_b[best][h]);
+    acc = __fadd_rn(acc, __fmul_rn(v, w[t * topk + bj]));
+  }
+  y[i] = acc;
+}
+
+static __device__ int g_moe_status = 0;
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct MoeWs {
@@ -231,8 +312,8 @@ extern "C" size_t nntr_cuda_moe_workspace_bytes(const nntr_moe_desc *d, unsigned
   return moe_ws(tokens, d->hidden, d->inter, d->top_k).total;
 }
 
-extern "C" int nntr_cuda_moe_forward_dev(const nntr_moe_desc *d, unsigned tokens, const float *x, float *y,
-                                         void *workspace, size_t workspace_bytes, void *stream) {
+static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned tokens, const float *x, float *y,
+                       void *workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!d || !x || !y)
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: null pointer");
   if (d->qtype != NNTR_Q4_K)
@@ -249,10 +330,29 @@ extern "C" int nntr_cuda_moe_forward_dev(const nntr_moe_desc *d, unsigned tokens
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: null weight table");
   if (tokens == 0)
     return NNTR_CUDA_OK;
+  MoeEp ep = {};
+  int e_lo = 0, e_hi = (int)E;
+  if (epd) {
+    if (epd->n_ranks < 1 || epd->n_ranks > 8 || epd->rank < 0 || epd->rank >= epd->n_ranks || !epd->epoch ||
+        E % (unsigned)epd->n_ranks)
+      return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward_ep: bad rank description (experts must divide by ranks)");
+    ep.n_ranks = epd->n_ranks;
+    ep.rank = epd->rank;
+    for (int r = 0; r < epd->n_ranks; ++r) {
+      if (!epd->out[r] || !epd->heartbeat[r])
+        return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward_ep: null peer pointer for rank %d", r);
+      ep.hb[r] = epd->heartbeat[r];
+    }
+    ep.epoch = epd->epoch;
+    ep.layers_per_epoch = epd->layers_per_epoch;
+    ep.layer = epd->layer;
+    ep.parity_stride = (unsigned long long)tokens * K * H;
+    e_lo = (int)(E / epd->n_ranks) * epd->rank;
+    e_hi = e_lo + (int)(E / epd->n_ranks);
+  }
   const MoeWs s = moe_ws(tokens, H, I, K);
   if (!workspace || workspace_bytes < s.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: workspace of %zu bytes (256-byte aligned) needed", s.total);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t *ws = static_cast<uint8_t *>(workspace);
   int *idx = reinterpret_cast<int *>(ws + s.idx);
   float *w = reinterpret_cast<float *>(ws + s.w);
@@ -264,7 +364,7 @@ extern "C" int nntr_cuda_moe_forward_dev(const nntr_moe_desc *d, unsigned tokens
   const unsigned P = tokens * K;
 
   moe_router_kernel<<<tokens, ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float), st>>>(
-    x, d->router_w, d->router_bias, (int)H, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx, w, gu_tab, dn_tab);
+    x, d->router_w, d->router_bias, (int)H, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx, w, gu_tab, dn_tab, ep);
   count_launch();
   NNTR_CHECK_CUDA(cudaGetLastError());
 
@@ -275,21 +375,72 @@ extern "C" int nntr_cuda_moe_forward_dev(const nntr_moe_desc *d, unsigned tokens
 
   const long n_act = (long)P * I;
   moe_act_kernel<<<(unsigned)((n_act + 255) / 256), 256, 0, st>>>(gu, act, idx, d->gate_b, d->up_b, d->kind, d->alpha,
-                                                                  (int)I, n_act);
+                                                                  (int)I, n_act, e_lo, e_hi);
   count_launch();
   NNTR_CHECK_CUDA(cudaGetLastError());
 
   GemvBatch b2 = {dn_tab, (long long)I, 1, (long long)H};
-  rc = launch_gemv_q4_K_batched(H, I, act, nullptr, dn, 0, P, b2, st);
+  const long n_out = (long)tokens * H;
+  if (!epd) {
+    rc = launch_gemv_q4_K_batched(H, I, act, nullptr, dn, 0, P, b2, st);
+    if (rc)
+      return rc;
+    moe_combine_kernel<<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dn, idx, w, d->kind == 1 ? d->down_b : nullptr,
+                                                                        y, (int)H, (int)K, n_out);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "moe_combine launch");
+  }
+  /* expert parallel: the down projections of the experts this rank owns store their outputs, numbered, into every
+   * rank's buffer; the combine waits for the numbers */
+  GemvExchange ex = {};
+  ex.n_ranks = epd->n_ranks;
+  ex.rank = epd->rank;
+  for (int r = 0; r < epd->n_ranks; ++r)
+    ex.y[r] = static_cast<uint2 *>(epd->out[r]);
+  ex.epoch = epd->epoch;
+  ex.layers_per_epoch = epd->layers_per_epoch;
+  ex.layer = epd->layer;
+  ex.no_flags = 1;
+  ex.parity_stride = ep.parity_stride;
+  rc = launch_gemv_q4_K_batched_publish(H, I, act, P, b2, ex, st);
   if (rc)
     return rc;
-
-  const long n_out = (long)tokens * H;
-  moe_combine_kernel<<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dn, idx, w, d->kind == 1 ? d->down_b : nullptr, y,
-                                                                      (int)H, (int)K, n_out);
+  int *status = nullptr;
+  NNTR_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_moe_status));
+  moe_combine_ep_kernel<<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(
+    static_cast<const uint2 *>(epd->out[epd->rank]), idx, w, d->kind == 1 ? d->down_b : nullptr, y, (int)H, (int)K,
+    n_out, ep, status);
   count_launch();
-  return check_cuda(cudaGetLastError(), "moe_combine launch");
+  return check_cuda(cudaGetLastError(), "moe_combine_ep launch");
 }
+
+extern "C" int nntr_cuda_moe_forward_dev(const nntr_moe_desc *d, unsigned tokens, const float *x, float *y,
+                                         void *workspace, size_t workspace_bytes, void *stream) {
+  return moe_forward(d, nullptr, tokens, x, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t nntr_cuda_moe_ep_buffer_bytes(const nntr_moe_desc *d, unsigned tokens) {
+  if (!d)
+    return 0;
+  return (size_t)2 * tokens * d->top_k * d->hidden * sizeof(uint2); // two alternating buffers of (value, number) pairs
+}
+
+extern "C" int nntr_cuda_moe_forward_ep_dev(const nntr_moe_desc *d, const nntr_moe_ep *ep, unsigned tokens,
+                                            const float *x, float *y, void *workspace, size_t workspace_bytes,
+                                            void *stream) {
+  if (!ep)
+    return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward_ep: null rank description");
+  return moe_forward(d, ep, tokens, x, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+namespace nntr {
+int read_moe_status(int *out) {
+  int v = 0;
+  NNTR_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_moe_status, sizeof(int)));
+  *out = v;
+  return NNTR_CUDA_OK;
+}
+} // namespace nntr
 
 extern "C" int nntr_cuda_moe_route_dev(const nntr_moe_desc *d, unsigned tokens, const float *x, int *idx_out,
                                        float *w_out, void *workspace, size_t workspace_bytes, void *stream) {
@@ -306,7 +457,7 @@ extern "C" int nntr_cuda_moe_route_dev(const nntr_moe_desc *d, unsigned tokens, 
   uint8_t *ws = static_cast<uint8_t *>(workspace);
   moe_router_kernel<<<tokens, ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
     x, d->router_w, d->router_bias, (int)d->hidden, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx_out, w_out,
-    reinterpret_cast<const void **>(ws + s.gu_tab), reinterpret_cast<const void **>(ws + s.dn_tab));
+    reinterpret_cast<const void **>(ws + s.gu_tab), reinterpret_cast<const void **>(ws + s.dn_tab), MoeEp{});
   count_launch();
   return check_cuda(cudaGetLastError(), "moe_router launch");
 }

@@ -47,6 +47,73 @@ def sequence_number(epoch: int, layers_per_epoch: int, layer: int) -> int:
     return (epoch - 1) * layers_per_epoch + layer + 1
 
 
+def expert_range(n_experts: int, world: int, rank: int) -> tuple[int, int]:
+    """Experts [lo, hi) owned by ``rank`` under expert parallelism: equal contiguous blocks."""
+    if n_experts % world:
+        raise ValueError(f"{n_experts} experts do not split evenly over {world} ranks")
+    per = n_experts // world
+    return rank * per, (rank + 1) * per
+
+
+class PeerBuffers:
+    """Device buffers of this rank (zeroed) and the same buffers of every peer mapped through CUDA IPC.
+    ``sizes``: bytes of each buffer. ``ptr(r, i)`` is buffer i of rank r as a device pointer valid in this process."""
+
+    def __init__(self, sizes, group=None):
+        import torch
+        import torch.distributed as dist
+        self.dist, self.torch, self.group = dist, torch, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > MAX_RANKS:
+            raise ValueError("peer buffers span the GPUs of one node (at most 8 ranks)")
+        L = lib()
+        self._own, mine = [], []
+        for n in sizes:
+            p = C.c_void_p()
+            check(L.nntr_cuda_malloc(C.byref(p), n))
+            self._own.append(p.value)
+            h = (C.c_ubyte * 64)()
+            check(L.nntr_cuda_ipc_export(p.value, h))
+            mine.append(bytes(h))
+        if self.world > 1:
+            allh = [None] * self.world
+            dist.all_gather_object(allh, mine, group=group)
+        else:
+            allh = [mine]
+        self._opened, self._ptrs = [], []
+        for r in range(self.world):
+            if r == self.rank:
+                self._ptrs.append(list(self._own))
+                continue
+            row = []
+            for hb in allh[r]:
+                p = C.c_void_p()
+                check(L.nntr_cuda_ipc_open((C.c_ubyte * 64).from_buffer_copy(hb), C.byref(p)))
+                self._opened.append(p.value)
+                row.append(p.value)
+            self._ptrs.append(row)
+        if self.world > 1:
+            dist.barrier(group=group)
+
+    def ptr(self, rank: int, i: int) -> int:
+        return self._ptrs[rank][i]
+
+    def close(self) -> None:
+        L = lib()
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier(group=self.group)
+        for p in self._opened:
+            L.nntr_cuda_ipc_close(p)
+        self._opened = []
+        if self.world > 1:
+            self.dist.barrier(group=self.group)
+        for p in self._own:
+            L.nntr_cuda_free(p)
+        self._own = []
+
+
 class NSplitGroup:
     """Per-process state of an N-split group: two alternating gathered vectors, a flag array and an epoch
     word in this rank's memory, and the peers' copies mapped through CUDA IPC."""
