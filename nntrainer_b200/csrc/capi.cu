@@ -325,6 +325,8 @@ int nntr_cuda_device_status(void) {
     return rc;
   if (!v && (rc = read_moe_status(&v)))
     return rc;
+  if (!v && (rc = read_q40_status(&v)))
+    return rc;
   if (v)
     return set_error(v, "a device kernel gave up on a bounded wait (status %d)", v);
   return NNTR_CUDA_OK;

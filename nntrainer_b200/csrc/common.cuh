@@ -281,6 +281,13 @@ bool gemv_q6_K_stream_supported(unsigned N, unsigned K);
 int launch_gemv_q6_K_stream(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
                             cudaStream_t st, unsigned *rows_done);
 int read_q6_status(int *out);
+/* bulk-copy ring version for Q4_0 (gemv_q40.cu) */
+bool gemv_q4_0_stream_supported(unsigned N, unsigned K);
+int launch_gemv_q4_0_stream(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
+                            cudaStream_t st);
+int launch_gemv_q4_0_batched(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
+                             unsigned n_problems, GemvBatch batch, cudaStream_t st);
+int read_q40_status(int *out);
 /* M > 1 with activations already quantized to plain Q8 rows in `qa` */
 int launch_gemm_q4_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
                      cudaStream_t st);

@@ -398,7 +398,12 @@ int launch_gemm_q6_K(unsigned M, unsigned N, unsigned K, const void *qa, const v
 }
 
 int launch_gemv_q4_0(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st) {
-  (void)flags;
+  static const bool stream_off = [] {
+    const char *e = getenv("NNTR_CUDA_Q40_STREAM");
+    return e && e[0] == '0';
+  }();
+  if (!stream_off && x && B && y && N && !(reinterpret_cast<uintptr_t>(B) & 15) && gemv_q4_0_stream_supported(N, K))
+    return launch_gemv_q4_0_stream(N, K, x, B, y, flags, st);
   if (!x || !B || !y || (reinterpret_cast<uintptr_t>(x) & 15))
     return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_0: null or misaligned pointer");
   if (N == 0)

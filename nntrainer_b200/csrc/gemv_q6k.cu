@@ -114,6 +114,22 @@ __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { asm volatile("st
 /** signed byte k of w, sign-extended */
 __device__ __forceinline__ int sbyte(uint32_t w, int k) { return (int)(w << (24 - 8 * k)) >> 24; }
 
+/** Bounded wait until the producer has armed stage t (see `armed` in the kernel). */
+__device__ __forceinline__ bool wait_armed(volatile int *armed, int t, volatile int *abort_flag) {
+  for (uint32_t it = 0; it < Q6_WAIT_POLLS; ++it) {
+    if (*armed > t)
+      return true;
+    if (it > 64) {
+      if (*abort_flag)
+        return false;
+      __nanosleep(64);
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(&g_q6_status, NNTR_CUDA_ERR_TIMEOUT);
+  return false;
+}
+
 /** whole rows a warp takes per step: lane = block of a row; at most four rows (8 chain lanes each) */
 __host__ __device__ inline int q6_rows_per_step(int nb) { return 32 / nb < 4 ? 32 / nb : 4; }
 
@@ -151,6 +167,10 @@ gemv_q6_K_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, flo
   auto FULL_BAR = [&](int s) { return bar0 + 8u * s; };                   // stage bytes landed
   auto FREE_BAR = [&](int s) { return bar0 + 8u * (Q6_MAX_STAGES + s); }; // every step of the stage done
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.bars + 2 * Q6_MAX_STAGES * 8);
+  // Number of stages the producer has armed so far. A consumer may be more than a ring ahead of the producer; a parity
+  // wait on a slot that is still two uses behind would succeed at once, so a consumer first waits (bounded) until its
+  // stage has been armed -- from then on the slot's barrier is in the phase the consumer means.
+  volatile int *armed = abort_flag + 1;
 
   // this CTA's contiguous share of the stages
   const int s_lo = (int)((long long)n_stages_total * blockIdx.x / gridDim.x);
@@ -163,6 +183,7 @@ gemv_q6_K_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, flo
       mbar_init(FREE_BAR(s), steps);
     }
     *abort_flag = 0;
+    *armed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -178,6 +199,8 @@ gemv_q6_K_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, flo
         mbar_expect_tx(FULL_BAR(s), (uint32_t)stage_bytes);
         bulk_g2s(sm0 + L.ring + (uint32_t)s * (uint32_t)(stage_bytes + 16), src + (size_t)i * stage_bytes,
                  (uint32_t)stage_bytes, FULL_BAR(s));
+        __threadfence_block();
+        *armed = i + 1;
       }
     }
     __syncwarp();
@@ -214,7 +237,7 @@ gemv_q6_K_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, flo
     for (long long g = warp; g < total_steps; g += Q6_CONSUMER_WARPS) {
       const int i = (int)(g / steps), st = (int)(g - (long long)i * steps);
       const int s = i % n_ring, use = i / n_ring;
-      if (!mbar_wait(FULL_BAR(s), use & 1, abort_flag))
+      if (!wait_armed(armed, i, abort_flag) || !mbar_wait(FULL_BAR(s), use & 1, abort_flag))
         break;
       if (work) {
         const int t = st * active + lane; // block inside the stage

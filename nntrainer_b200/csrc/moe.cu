@@ -316,16 +316,20 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
                        void *workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!d || !x || !y)
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: null pointer");
-  if (d->qtype != NNTR_Q4_K)
-    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "moe_forward: expert weights must be Q4_K (got qtype %d)", d->qtype);
+  if (d->qtype != NNTR_Q4_K && d->qtype != NNTR_Q4_0)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "moe_forward: expert weights must be Q4_K or Q4_0 (got qtype %d)", d->qtype);
+  if (d->qtype == NNTR_Q4_0 && epd)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "moe_forward_ep: expert parallelism is built for Q4_K experts only");
   if (d->kind != 0 && d->kind != 1)
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: kind must be 0 (Qwen) or 1 (GPT-OSS)");
   if (d->kind == 1 && (!d->gate_b || !d->up_b || !d->down_b))
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: kind 1 needs the three expert bias tables");
   const unsigned H = d->hidden, I = d->inter, E = d->n_experts, K = d->top_k;
-  if (H == 0 || H % 256 || I == 0 || I % 256 || E == 0 || E > 32 * MAX_E_PER_LANE || K == 0 || K > E || K > 32)
+  const unsigned kmul = d->qtype == NNTR_Q4_K ? 256 : 32; // K of a projection must be whole blocks of the format
+  if (H == 0 || H % kmul || H % 8 || I == 0 || I % kmul || I % 8 || E == 0 || E > 32 * MAX_E_PER_LANE || K == 0 || K > E ||
+      K > 32)
     return set_error(NNTR_CUDA_ERR_INVALID,
-                     "moe_forward: need hidden %% 256 == 0, inter %% 256 == 0, experts <= 256, top_k <= min(experts, 32)");
+                     "moe_forward: need hidden and inter multiples of %u, experts <= 256, top_k <= min(experts, 32)", kmul);
   if (!d->router_w || !d->gate_w || !d->up_w || !d->down_w)
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: null weight table");
   if (tokens == 0)
@@ -369,7 +373,8 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
   NNTR_CHECK_CUDA(cudaGetLastError());
 
   GemvBatch b1 = {gu_tab, (long long)H, (int)(2 * K), (long long)I};
-  int rc = launch_gemv_q4_K_batched(I, H, x, nullptr, gu, 0, 2 * P, b1, st);
+  int rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched(I, H, x, nullptr, gu, 0, 2 * P, b1, st)
+                                 : launch_gemv_q4_0_batched(I, H, x, nullptr, gu, 0, 2 * P, b1, st);
   if (rc)
     return rc;
 
@@ -382,7 +387,8 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
   GemvBatch b2 = {dn_tab, (long long)I, 1, (long long)H};
   const long n_out = (long)tokens * H;
   if (!epd) {
-    rc = launch_gemv_q4_K_batched(H, I, act, nullptr, dn, 0, P, b2, st);
+    rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched(H, I, act, nullptr, dn, 0, P, b2, st)
+                               : launch_gemv_q4_0_batched(H, I, act, nullptr, dn, 0, P, b2, st);
     if (rc)
       return rc;
     moe_combine_kernel<<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dn, idx, w, d->kind == 1 ? d->down_b : nullptr,

@@ -150,6 +150,35 @@ def test_gemv_q6_K_streaming_kernel_row_groupings(be, port, N, K):
     assert np.array_equal(bits(y.cpu().numpy()), bits(want))
 
 
+@pytest.mark.parametrize("N,K", [(21312, 1024), (24576, 4096), (2880, 2880), (5760, 2880)])
+def test_gemv_q4_0_streaming_kernel_many_row_groups(be, port, N, K):
+    """Q4_0 decode GEMV where every CTA owns more row groups than it has consumer warps (warps run ahead of the
+    producer by more than the ring), one and two stages per row group, and K = 2880 (a last stage of 26 blocks and a
+    quantizer pass that is masked beyond K)."""
+    rng = np.random.default_rng(N + K)
+    B = O.random_q4_0x8(rng, N, K)
+    x = acts(rng, 1, K)
+    want = port.gemm("q4_0", x, B, N)[0]
+    y = torch.full((N,), float("nan"), device="cuda")
+    be.gemm_q4_0(1, N, K, dev(x), K, dev(B), N, y, N)
+    be.device_status()
+    assert np.array_equal(bits(y.cpu().numpy()), bits(want))
+
+
+def test_gemv_q6_K_streaming_kernel_full_lm_head_rows(be, port):
+    """Q6_K decode GEMV with ~68 stages per CTA (consumer warps far ahead of the producer): N = 118400, K = 2560."""
+    rng = np.random.default_rng(77)
+    N, K = 118400, 2560
+    base = O.random_q6_K(rng, 4736, K)
+    B = np.tile(base, N // 4736)  # rows repeat with period 4736: cheap to generate, cheap to check
+    x = acts(rng, 1, K)
+    want = np.tile(port.gemm("q6_K", x, base, 4736)[0], N // 4736)
+    y = torch.full((N,), float("nan"), device="cuda")
+    be.gemm_q6_K(1, N, K, dev(x), K, dev(B), N, y, N)
+    be.device_status()
+    assert np.array_equal(bits(y.cpu().numpy()), bits(want))
+
+
 @pytest.mark.parametrize("q", ["q4_K", "q4_0", "q6_K"])
 def test_gemv_golden(be, golden, q):
     B = golden[f"{q}_x8"] if q != "q6_K" else golden[f"{q}_plain"]

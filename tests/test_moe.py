@@ -119,3 +119,31 @@ def test_moe_qwen3_30b_a3b_shape_decode(be, port):
     want = port.moe_forward(x, router, gate, up, down, k)
     assert np.max(np.abs(got - want)) <= REL_TOL * np.max(np.abs(want))
     be.device_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T", [1, 6])
+def test_gpt_oss_form_with_q4_0_experts_matches_checker(be, port, T):
+    """GPT-OSS MoE form (router bias, expert biases, clamped-free (up + 1) * gate * sigmoid(alpha * gate)) with Q4_0
+    expert weights and a hidden size that is a multiple of 32 but not of 256 (2880 in the model; 352 here)."""
+    import torch
+    rng = np.random.default_rng(40 + T)
+    H, I, E, k, alpha = 352, 352, 8, 4, 1.702
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    router = (rng.standard_normal((H, E)) * 0.02).astype(np.float32)
+    rbias = (rng.standard_normal(E) * 0.01).astype(np.float32)
+    gate = [O.random_q4_0x8(rng, I, H) for _ in range(E)]
+    up = [O.random_q4_0x8(rng, I, H) for _ in range(E)]
+    down = [O.random_q4_0x8(rng, H, I) for _ in range(E)]
+    gb = [(rng.standard_normal(I) * 0.1).astype(np.float32) for _ in range(E)]
+    ub = [(rng.standard_normal(I) * 0.1).astype(np.float32) for _ in range(E)]
+    db = [(rng.standard_normal(H) * 0.1).astype(np.float32) for _ in range(E)]
+    cu = lambda arrs: [torch.from_numpy(a).cuda() for a in arrs]
+    layer = be.MoeLayer(torch.from_numpy(router).cuda(), cu(gate), cu(up), cu(down), k, qtype="q4_0", kind=1,
+                        router_bias=torch.from_numpy(rbias).cuda(), gate_b=cu(gb), up_b=cu(ub), down_b=cu(db), alpha=alpha)
+    got = layer.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+    want = port.moe_forward(x, router, gate, up, down, k, qtype="q4_0", kind=1, router_bias=rbias, gate_b=gb, up_b=ub,
+                            down_b=db, alpha=alpha)
+    assert np.isfinite(got).all()
+    assert np.max(np.abs(got - want)) <= REL_TOL * np.max(np.abs(want))
+    be.device_status()
