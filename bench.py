@@ -250,6 +250,64 @@ def other_shapes(be, torch, dev, peak, steps=20):
 
 
 # --------------------------------------------------------------------------
+# one decode token through all projections of a Qwen3-4B-shaped decoder (weights only: the quantized matmul path)
+# --------------------------------------------------------------------------
+QWEN3_4B = {"layers": 36, "hidden": 2560, "q_dim": 4096, "kv_dim": 1024, "inter": 9728, "vocab": 151936}
+
+
+def decode_step_qwen3_4b(be, torch, dev, peak, steps=10):
+    """Per layer four Q4_K GEMVs (fused q|k|v 6144x2560, o 2560x4096, fused gate|up 19456x2560, down 2560x9728), then
+    the Q6_K lm_head 151936x2560: 145 launches, 2.36 GB of distinct weights, one CUDA graph with programmatic dependent
+    launch, launches ordered like the layers of a decoder. Attention, norms and sampling are outside the quantized
+    matmul path and are not run; tok/s is therefore the ceiling this path allows, not a whole-model figure. Every GEMV
+    reads a fixed random activation of its input size, so values stay finite with random weights."""
+    from oracle import oracle as O
+    c = QWEN3_4B
+    shapes = [(c["q_dim"] + 2 * c["kv_dim"], c["hidden"]), (c["hidden"], c["q_dim"]), (2 * c["inter"], c["hidden"]),
+              (c["hidden"], c["inter"])]
+    rng = np.random.default_rng(21)
+    bases = [torch.from_numpy(O.random_q4_Kx8(rng, N, K)).to(dev) for N, K in shapes]
+    layers = [[torch.roll(b, 1152 * (7 * l + 3)) if l else b for b in bases] for l in range(c["layers"])]  # whole blocks
+    head = torch.from_numpy(O.random_q6_K(rng, c["vocab"], c["hidden"])).to(dev)
+    xs = {K: torch.randn(K, device=dev) for K in {k for _, k in shapes}}
+    ys = [torch.zeros(N, device=dev) for N, _ in shapes]
+    logits = torch.zeros(c["vocab"], device=dev)
+    wbytes = c["layers"] * sum(int(N * K * 144 / 256) for N, K in shapes) + c["vocab"] * (c["hidden"] // 256) * 210
+
+    def one_token():
+        for l in range(c["layers"]):
+            for (N, K), W, y in zip(shapes, layers[l], ys):
+                be.gemv("q4_K", N, K, xs[K], W, y, pdl=True)
+        be.gemv("q6_K", c["vocab"], c["hidden"], xs[c["hidden"]], head, logits, pdl=True)
+
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        one_token()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            one_token()
+        for _ in range(3):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            g.replay()
+        e1.record(stream)
+        stream.synchronize()
+    be.device_status()
+    ms = e0.elapsed_time(e1) / steps
+    finite = bool(torch.isfinite(logits).all().item())
+    out = {"shape": "Qwen3-4B decode, projections + lm_head (attention/norms not run)", "launches_per_token": 4 * c["layers"] + 1,
+           "weight_bytes_per_token": wbytes, "ms_per_token": round(ms, 4), "tok/s": round(1e3 / ms, 1),
+           "GB/s": round(wbytes / (ms * 1e-3) / 1e9, 1), "frac_of_hbm_peak": round(wbytes / (ms * 1e-3) / 1e9 / peak, 4),
+           "ceiling_tok/s_at_hbm_peak": round(peak * 1e9 / wbytes, 1), "outputs_finite": finite}
+    del layers, bases, head
+    torch.cuda.empty_cache()
+    return out
+
+
+# --------------------------------------------------------------------------
 # prefill GEMM sweep (Q4_K weights, tensor-core path), reported beside the headline
 # --------------------------------------------------------------------------
 PREFILL_SWEEP = [(64, 24576, 4096), (256, 24576, 4096), (1024, 24576, 4096)]  # (M, N, K): fused gate+up projection
@@ -464,6 +522,7 @@ def run_ours(args):
         achieved = ALG_BYTES / (per_launch_us * 1e-6) / 1e9
         others = other_shapes(be, torch, dev, peak) if (world == 1 and not args.no_extra) else None
         prefill = prefill_gemm_shapes(be, torch, dev) if (world == 1 and not args.no_extra) else None
+        decode = decode_step_qwen3_4b(be, torch, dev, peak) if (world == 1 and not args.no_extra) else None
         cpu_desc = None
         if world == 1 and not args.no_cpu:
             _, cpu_desc, _ = cpu_reference_gbps(host_ring, args.cpu_seconds)
@@ -487,7 +546,8 @@ def run_ours(args):
                             "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_BYTES,
                             "kernel": "gemv_q4_K_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
                "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
-               "other_decode_gemv_shapes": others, "prefill_gemm_sweep": prefill}
+               "other_decode_gemv_shapes": others, "prefill_gemm_sweep": prefill,
+               "decode_step": decode}
         print(json.dumps(out))
     if group is not None:
         group.close()

@@ -187,11 +187,10 @@ def test_gemv_golden(be, golden, q):
     assert np.array_equal(bits(y.cpu().numpy()), bits(golden[f"{q}_gemv"][0]))
 
 
-@pytest.mark.parametrize("slices", [1, 2, 4, 8])
-def test_gemv_q4_K_every_k_split_gives_same_bits(be, port, slices, monkeypatch):
-    monkeypatch.setenv("NNTR_CUDA_GEMV_SLICES", str(slices))
-    rng = np.random.default_rng(slices)
-    N, K = 264, 2560  # 33 row groups, 10 super-blocks: ragged against 8 warps and against the slices
+def test_gemv_q4_K_ragged_row_groups(be, port):
+    """33 row groups of 10 super-blocks: ragged against the consumer warps, the ring stages and the CTAs' shares."""
+    rng = np.random.default_rng(3)
+    N, K = 264, 2560
     B = O.random_q4_Kx8(rng, N, K)
     x = acts(rng, 1, K)
     y = torch.zeros(N, device="cuda")
