@@ -308,6 +308,76 @@ def decode_step_qwen3_4b(be, torch, dev, peak, steps=10):
 
 
 # --------------------------------------------------------------------------
+# one decode token through the MoE layers of a Qwen3-30B-A3B-shaped decoder, expert-parallel over the ranks
+# --------------------------------------------------------------------------
+QWEN3_30B_A3B = {"layers": 48, "hidden": 2048, "experts": 128, "top_k": 8, "inter": 768}
+
+
+def moe_decode_step(be, torch, dev, world, rank, steps=10):
+    """48 MoE layers (router fp32 [2048,128], top-8 of 128 Q4_K experts with intermediate 768), batch 1: every layer's
+    output is the next layer's input. With more than one rank the experts are split evenly (expert parallelism, the
+    owners' down projections store their outputs into every rank's buffer; no collective call). Expert weights: 16
+    distinct sets per projection rotated into distinct device memory for every (layer, expert) this rank owns --
+    340 MB per layer in total, so L2 cannot serve a layer. Attention is outside the path and not run."""
+    from oracle import oracle as O
+    from nntrainer_b200 import nsplit
+    c = QWEN3_30B_A3B
+    H, I, E, k, Lc = c["hidden"], c["inter"], c["experts"], c["top_k"], c["layers"]
+    rng = np.random.default_rng(31)
+    pool = [[torch.from_numpy(O.random_q4_Kx8(rng, n, kk)).to(dev) for _ in range(16)] for n, kk in ((I, H), (I, H), (H, I))]
+    lo, hi = nsplit.expert_range(E, world, rank)
+
+    def owned(kind, l):
+        return [torch.roll(pool[kind][(e + l) % 16], 1152 * (1 + e + 131 * l)) if lo <= e < hi else None for e in range(E)]
+
+    layers = []
+    for l in range(Lc):
+        router = (torch.randn(H, E, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + l)) * 0.02)
+        layers.append(be.MoeLayer(router, owned(0, l), owned(1, l), owned(2, l), k))
+    if world > 1:
+        layers[0].enable_expert_parallel(1, layers_per_epoch=Lc)
+        for ly in layers[1:]:
+            ly.enable_expert_parallel(1, share_with=layers[0])
+    x0 = torch.randn(1, H, device=dev, generator=torch.Generator(device=dev).manual_seed(7))
+
+    def one_token():
+        x = x0
+        for l, ly in enumerate(layers):
+            y = ly.forward_ep(x, layer=l, bump_epoch=(l == 0)) if world > 1 else ly.forward(x)
+            x = torch.nn.functional.layer_norm(y, (H,))  # one kernel: keeps magnitudes finite through 48 random layers
+        return x
+
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        out = one_token()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            out = one_token()
+        for _ in range(3):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            g.replay()
+        e1.record(stream)
+        stream.synchronize()
+    be.device_status()
+    ms = e0.elapsed_time(e1) / steps
+    active = Lc * k * 3 * int(I * H * 144 / 256) + Lc * H * E * 4  # expert weights touched + routers, per token
+    res = {"shape": "Qwen3-30B-A3B decode, 48 MoE layers (attention not run)", "ranks": world,
+           "parallelism": "single GPU" if world == 1 else f"expert parallel x{world}",
+           "ms_per_token": round(ms, 4), "us_per_layer": round(ms * 1e3 / Lc, 2), "layers_per_s": round(Lc * 1e3 / ms, 1),
+           "weight_bytes_touched_per_token": active, "outputs_finite": bool(torch.isfinite(out).all().item()),
+           "checksum": float(out.double().sum().item())}
+    if world > 1:
+        layers[0]._ep_buf.close()
+    del layers, pool
+    torch.cuda.empty_cache()
+    return res
+
+
+# --------------------------------------------------------------------------
 # prefill GEMM sweep (Q4_K weights, tensor-core path), reported beside the headline
 # --------------------------------------------------------------------------
 PREFILL_SWEEP = [(64, 24576, 4096), (256, 24576, 4096), (1024, 24576, 4096)]  # (M, N, K): fused gate+up projection
@@ -514,6 +584,15 @@ def run_ours(args):
         for W in host_ring:
             be.unregister_weight(W)
 
+    # the MoE decode step runs on every rank (expert parallel when there is more than one); a failure there must not
+    # take the headline down with it
+    moe = None
+    if not args.no_extra and not args.no_moe:
+        try:
+            moe = moe_decode_step(be, torch, dev, world, rank)
+        except Exception as exc:  # noqa: BLE001
+            moe = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
     if rank == 0:
         peak, which = measured_peak()
         total_bytes = world * args.steps * RING * ALG_BYTES
@@ -547,7 +626,7 @@ def run_ours(args):
                             "kernel": "gemv_q4_K_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
                "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
                "other_decode_gemv_shapes": others, "prefill_gemm_sweep": prefill,
-               "decode_step": decode}
+               "decode_step": decode, "moe_decode_step": moe}
         print(json.dumps(out))
     if group is not None:
         group.close()
@@ -608,6 +687,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other decode GEMV shapes")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer end-to-end leg (profiling runs)")
+    ap.add_argument("--no-moe", action="store_true", help="skip the MoE decode step")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--ring", type=int, default=RING, help="distinct weight matrices per step (default keeps every launch out of L2)")
     ap.add_argument("--traffic", type=float, default=None,

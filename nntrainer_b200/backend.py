@@ -238,12 +238,16 @@ class MoeLayer:
                                               ws.numel(), _stream()))
         return y
 
-    def enable_expert_parallel(self, max_tokens: int, layers_per_epoch: int = 1, group=None):
+    def enable_expert_parallel(self, max_tokens: int, layers_per_epoch: int = 1, group=None, share_with=None):
         """Expert parallelism over the ranks of ``group`` (one process per GPU). This rank must have been built with
         None in place of the weights of experts it does not own (``nsplit.expert_range``). Allocates the exchange
-        buffers for calls of up to ``max_tokens`` tokens and maps the peers'."""
+        buffers for calls of ``max_tokens`` tokens and maps the peers'; the layers of one model pass
+        ``share_with=<first layer>`` and use its buffers in turn (calls are numbered per pass)."""
         from .nsplit import PeerBuffers
         C = self._C
+        if share_with is not None:
+            self._ep_buf, self._ep_tokens, self._ep_layers = share_with._ep_buf, share_with._ep_tokens, share_with._ep_layers
+            return self
         nbytes = int(lib().nntr_cuda_moe_ep_buffer_bytes(C.byref(self.desc), max_tokens))
         self._ep_buf = PeerBuffers([nbytes, 64, 8], group)  # expert outputs (two alternating), heartbeat words, epoch
         self._ep_tokens, self._ep_layers = max_tokens, layers_per_epoch

@@ -34,8 +34,9 @@
  * Per 256 weights a lane spends ~500 instructions (6-bit unpack is ~5x the work
  * of Q4_K): on this part the kernel is bound by instruction issue and latency,
  * not by HBM. Algorithmic bytes per launch: N * nb * 210 (weights) + 4K (x) +
- * 4N (y). Rows beyond the last whole stage are left to the caller (the dp4a
- * kernel of gemm_dp4a.cu takes them).
+ * 4N (y). Rows beyond the last whole stage form one short stage for the last
+ * CTA when their byte size is a multiple of 16; otherwise they are left to the
+ * caller (the dp4a kernel of gemm_dp4a.cu takes them).
  */
 #include "common.cuh"
 
@@ -155,7 +156,7 @@ __host__ __device__ inline Q6Layout q6_layout(int nb, int stage_bytes, int stage
 
 __global__ void __launch_bounds__(Q6_THREADS, 1)
 gemv_q6_K_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, float *__restrict__ y, int n_stages_total,
-                 int rows_per_stage, int nb, int n_ring) {
+                 int rows_per_stage, int nb, int n_ring, int tail_rows) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int stage_blocks = rows_per_stage * nb, stage_bytes = stage_blocks * (int)sizeof(BlockQ6K);
   const int rows_per_step = q6_rows_per_step(nb), active = rows_per_step * nb; // lanes at work in a step
@@ -176,6 +177,10 @@ gemv_q6_K_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, flo
   const int s_lo = (int)((long long)n_stages_total * blockIdx.x / gridDim.x);
   const int s_hi = (int)((long long)n_stages_total * (blockIdx.x + 1) / gridDim.x);
   const int my_stages = s_hi - s_lo;
+  // rows beyond the last whole stage (fewer than rows_per_stage, a 16-byte multiple of bytes): one short extra stage
+  // for the last CTA
+  const int my_tail = (blockIdx.x == gridDim.x - 1) ? tail_rows : 0;
+  const int tail_steps = (my_tail + rows_per_step - 1) / rows_per_step;
 
   if (tid == 0) {
     for (int s = 0; s < n_ring; ++s) {
@@ -202,6 +207,17 @@ gemv_q6_K_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, flo
         __threadfence_block();
         *armed = i + 1;
       }
+      if (my_tail && !*abort_flag) {
+        const int i = my_stages, s = i % n_ring, use = i / n_ring;
+        if (use == 0 || mbar_wait(FREE_BAR(s), (use - 1) & 1, abort_flag)) {
+          const uint32_t bytes = (uint32_t)(my_tail * nb) * (uint32_t)sizeof(BlockQ6K);
+          mbar_expect_tx(FULL_BAR(s), bytes);
+          bulk_g2s(sm0 + L.ring + (uint32_t)s * (uint32_t)(stage_bytes + 16), src + (size_t)i * stage_bytes, bytes,
+                   FULL_BAR(s));
+          __threadfence_block();
+          *armed = i + 1;
+        }
+      }
     }
     __syncwarp();
   } else {
@@ -224,21 +240,23 @@ gemv_q6_K_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, flo
     }
     asm volatile("bar.sync 1, %0;" ::"n"(Q6_CONSUMER_WARPS * 32) : "memory");
 
-    const bool work = lane < active;
     const int b = lane % nb;                                // super-block of the lane's row
     const uint32_t ab = sm0 + L.act + (uint32_t)b * Q6_ACT_STRIDE;
     const uint32_t myrec = sm0 + L.rec + (uint32_t)((warp * 32 + lane) * Q6_REC_WORDS * 4);
     // chain role: 8 lanes per row of the step
     const int crow = lane >> 3, cl = lane & 7;
-    const bool chain = crow < rows_per_step;
     const uint32_t crec = sm0 + L.rec + (uint32_t)((warp * 32 + crow * nb) * Q6_REC_WORDS * 4) + 4 * cl;
 
-    const long long total_steps = (long long)my_stages * steps;
+    const long long total_steps = (long long)my_stages * steps + tail_steps;
     for (long long g = warp; g < total_steps; g += Q6_CONSUMER_WARPS) {
-      const int i = (int)(g / steps), st = (int)(g - (long long)i * steps);
+      const int i = (int)(g / steps), st = (int)(g - (long long)i * steps); // the tail's steps follow the last stage's
       const int s = i % n_ring, use = i / n_ring;
       if (!wait_armed(armed, i, abort_flag) || !mbar_wait(FULL_BAR(s), use & 1, abort_flag))
         break;
+      // rows of this step: rows_per_step, fewer in the last step of the short stage
+      const int step_rows = (i < my_stages || my_tail - st * rows_per_step >= rows_per_step) ? rows_per_step
+                                                                                            : my_tail - st * rows_per_step;
+      const bool work = lane < step_rows * nb, chain = crow < step_rows;
       if (work) {
         const int t = st * active + lane; // block inside the stage
         const uint32_t off = (uint32_t)t * 210u;
@@ -387,7 +405,11 @@ int launch_gemv_q6_K_stream(unsigned N, unsigned K, const float *x, const void *
     attr_done[dev & 63] = true;
   }
   const int n_stages_total = (int)(N / rs);
-  *rows_done = (unsigned)n_stages_total * (unsigned)rs;
+  // the rows left over form one short stage inside the kernel when their byte size is a multiple of 16
+  int tail_rows = (int)(N - (unsigned)n_stages_total * (unsigned)rs);
+  if ((tail_rows * nb) % 8)
+    tail_rows = 0;
+  *rows_done = (unsigned)n_stages_total * (unsigned)rs + (unsigned)tail_rows;
   const int sms = sm_count();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(n_stages_total < sms ? n_stages_total : sms));
@@ -400,7 +422,7 @@ int launch_gemv_q6_K_stream(unsigned N, unsigned K, const float *x, const void *
   cfg.attrs = attr;
   cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q6_K_kernel, x, static_cast<const uint8_t *>(B), y, n_stages_total, rs,
-                                     nb, ring);
+                                     nb, ring, tail_rows);
   count_launch();
   return check_cuda(e, "gemv_q6_K launch");
 }

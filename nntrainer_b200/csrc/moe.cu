@@ -38,17 +38,22 @@ struct MoeEp {
 };
 
 constexpr int ROUTER_WARPS = 8;
+constexpr int ROUTER_SLICES = 8; // CTAs per token
 constexpr int MAX_E_PER_LANE = 8; // up to 256 experts
 
-/* one CTA per token */
+/* ROUTER_SLICES CTAs per token: each sums its slice of the hidden dimension into partial logits (the router weight
+ * is a megabyte per layer: one CTA alone would be bound by the latency of its own loads); the CTA that arrives last on
+ * the token's counter adds the partials in slice order and does softmax, top-k and the tables. */
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, const float *__restrict__ bias, int H, int E,
                   int topk, const void *const *__restrict__ gate_w, const void *const *__restrict__ up_w,
                   const void *const *__restrict__ down_w, int *__restrict__ idx_out, float *__restrict__ w_out,
-                  const void **__restrict__ gu_table, const void **__restrict__ dn_table, MoeEp ep) {
+                  const void **__restrict__ gu_table, const void **__restrict__ dn_table, float *__restrict__ rpart,
+                  unsigned *__restrict__ rcount, MoeEp ep) {
   extern __shared__ float rsm[]; // [ROUTER_WARPS][E]
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (ep.n_ranks && t == 0 && threadIdx.x < ep.n_ranks) {
+  __shared__ bool is_last;
+  const int t = blockIdx.x, sl = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (ep.n_ranks && t == 0 && sl == 0 && threadIdx.x < ep.n_ranks) {
     // heartbeat: "this rank has started layer call seq", i.e. it has finished combining seq - 1 (stream order)
     const unsigned long long seq = (*ep.epoch - 1) * ep.layers_per_epoch + ep.layer + 1;
     volatile unsigned long long *slot = ep.hb[threadIdx.x] + ep.rank;
@@ -60,22 +65,49 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
 #pragma unroll
   for (int i = 0; i < MAX_E_PER_LANE; ++i)
     acc[i] = 0.f;
-  const int h0 = (int)(((long long)warp * H) / ROUTER_WARPS), h1 = (int)(((long long)(warp + 1) * H) / ROUTER_WARPS);
-  for (int h = h0; h < h1; ++h) {
-    const float xv = xt[h];
-    const float *row = wr + (size_t)h * E;
+  const int nw = ROUTER_SLICES * ROUTER_WARPS, wi = sl * ROUTER_WARPS + warp;
+  const int h0 = (int)(((long long)wi * H) / nw), h1 = (int)(((long long)(wi + 1) * H) / nw);
+  for (int h = h0; h < h1; h += 4) { // four rows in flight per lane
+    float xv[4], wv[4][MAX_E_PER_LANE];
 #pragma unroll
-    for (int i = 0; i < MAX_E_PER_LANE; ++i)
-      if (i < per && lane + 32 * i < E)
-        acc[i] = fmaf(xv, row[lane + 32 * i], acc[i]);
+    for (int u = 0; u < 4; ++u) {
+      const int hh = h + u < h1 ? h + u : h1 - 1;
+      xv[u] = h + u < h1 ? xt[hh] : 0.f;
+      const float *row = wr + (size_t)hh * E;
+#pragma unroll
+      for (int i = 0; i < MAX_E_PER_LANE; ++i)
+        wv[u][i] = (i < per && lane + 32 * i < E) ? row[lane + 32 * i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int i = 0; i < MAX_E_PER_LANE; ++i)
+        acc[i] = fmaf(xv[u], wv[u][i], acc[i]);
   }
 #pragma unroll
   for (int i = 0; i < MAX_E_PER_LANE; ++i)
     if (i < per && lane + 32 * i < E)
       rsm[warp * E + lane + 32 * i] = acc[i];
   __syncthreads();
-  if (warp != 0)
+  float *mine = rpart + ((size_t)t * ROUTER_SLICES + sl) * E;
+  for (int e = threadIdx.x; e < E; e += ROUTER_WARPS * 32) {
+    float s = 0.f;
+    for (int w = 0; w < ROUTER_WARPS; ++w)
+      s += rsm[w * E + e];
+    mine[e] = s;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned old = atomicAdd(rcount + t, 1u);
+    is_last = old == ROUTER_SLICES - 1;
+    if (is_last)
+      rcount[t] = 0; // ready for the next call
+  }
+  __syncthreads();
+  if (!is_last || warp != 0)
     return;
+  __threadfence();
   // ---- warp 0: logits, softmax, top-k
   float p[MAX_E_PER_LANE];
   float mx = -INFINITY;
@@ -85,8 +117,8 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
     const int e = lane + 32 * i;
     if (i < per && e < E) {
       float s = 0.f;
-      for (int w = 0; w < ROUTER_WARPS; ++w)
-        s += rsm[w * E + e];
+      for (int w = 0; w < ROUTER_SLICES; ++w)
+        s += __ldcg(rpart + ((size_t)t * ROUTER_SLICES + w) * E + e);
       p[i] = s + (bias ? bias[e] : 0.f);
       mx = fmaxf(mx, p[i]);
     }
@@ -278,9 +310,9 @@ static __device__ int g_moe_status = 0;
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct MoeWs {
-  size_t idx, w, gu_tab, dn_tab, gu, act, dn, total;
+  size_t idx, w, gu_tab, dn_tab, rpart, rcount, gu, act, dn, total;
 };
-static MoeWs moe_ws(unsigned T, unsigned H, unsigned I, unsigned topk) {
+static MoeWs moe_ws(unsigned T, unsigned H, unsigned I, unsigned topk, unsigned E = 256) {
   MoeWs s;
   const size_t P = (size_t)T * topk;
   size_t o = 0;
@@ -292,6 +324,10 @@ static MoeWs moe_ws(unsigned T, unsigned H, unsigned I, unsigned topk) {
   o = align_up(o + 2 * P * 8, 256);
   s.dn_tab = o;
   o = align_up(o + P * 8, 256);
+  s.rpart = o; // sized for the largest expert count so that the layout does not depend on it
+  o = align_up(o + (size_t)T * ROUTER_SLICES * E * 4, 256);
+  s.rcount = o;
+  o = align_up(o + (size_t)T * 4, 256);
   s.gu = o;
   o = align_up(o + 2 * P * I * 4, 256);
   s.act = o;
@@ -367,14 +403,19 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
   float *dn = reinterpret_cast<float *>(ws + s.dn);
   const unsigned P = tokens * K;
 
-  moe_router_kernel<<<tokens, ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float), st>>>(
-    x, d->router_w, d->router_bias, (int)H, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx, w, gu_tab, dn_tab, ep);
+  NNTR_CHECK_CUDA(cudaMemsetAsync(ws + s.rcount, 0, (size_t)tokens * 4, st));
+  moe_router_kernel<<<dim3(tokens, ROUTER_SLICES), ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float), st>>>(
+    x, d->router_w, d->router_bias, (int)H, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx, w, gu_tab, dn_tab,
+    reinterpret_cast<float *>(ws + s.rpart), reinterpret_cast<unsigned *>(ws + s.rcount), ep);
   count_launch();
   NNTR_CHECK_CUDA(cudaGetLastError());
 
   GemvBatch b1 = {gu_tab, (long long)H, (int)(2 * K), (long long)I};
-  int rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched(I, H, x, nullptr, gu, 0, 2 * P, b1, st)
-                                 : launch_gemv_q4_0_batched(I, H, x, nullptr, gu, 0, 2 * P, b1, st);
+  // programmatic dependent launch: the batched kernels wait for the grid before them as their first action, so only
+  // their launch latency overlaps the previous kernel
+  const unsigned pdl = NNTR_CUDA_GEMV_PDL;
+  int rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched(I, H, x, nullptr, gu, pdl, 2 * P, b1, st)
+                                 : launch_gemv_q4_0_batched(I, H, x, nullptr, gu, pdl, 2 * P, b1, st);
   if (rc)
     return rc;
 
@@ -387,8 +428,8 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
   GemvBatch b2 = {dn_tab, (long long)I, 1, (long long)H};
   const long n_out = (long)tokens * H;
   if (!epd) {
-    rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched(H, I, act, nullptr, dn, 0, P, b2, st)
-                               : launch_gemv_q4_0_batched(H, I, act, nullptr, dn, 0, P, b2, st);
+    rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched(H, I, act, nullptr, dn, pdl, P, b2, st)
+                               : launch_gemv_q4_0_batched(H, I, act, nullptr, dn, pdl, P, b2, st);
     if (rc)
       return rc;
     moe_combine_kernel<<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dn, idx, w, d->kind == 1 ? d->down_b : nullptr,
@@ -461,9 +502,12 @@ extern "C" int nntr_cuda_moe_route_dev(const nntr_moe_desc *d, unsigned tokens, 
   if (!workspace || workspace_bytes < s.gu || (reinterpret_cast<uintptr_t>(workspace) & 255))
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_route: workspace too small");
   uint8_t *ws = static_cast<uint8_t *>(workspace);
-  moe_router_kernel<<<tokens, ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+  NNTR_CHECK_CUDA(cudaMemsetAsync(ws + s.rcount, 0, (size_t)tokens * 4, static_cast<cudaStream_t>(stream)));
+  moe_router_kernel<<<dim3(tokens, ROUTER_SLICES), ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float),
+                      static_cast<cudaStream_t>(stream)>>>(
     x, d->router_w, d->router_bias, (int)d->hidden, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx_out, w_out,
-    reinterpret_cast<const void **>(ws + s.gu_tab), reinterpret_cast<const void **>(ws + s.dn_tab), MoeEp{});
+    reinterpret_cast<const void **>(ws + s.gu_tab), reinterpret_cast<const void **>(ws + s.dn_tab),
+    reinterpret_cast<float *>(ws + s.rpart), reinterpret_cast<unsigned *>(ws + s.rcount), MoeEp{});
   count_launch();
   return check_cuda(cudaGetLastError(), "moe_router launch");
 }
