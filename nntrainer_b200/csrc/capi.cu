@@ -262,13 +262,25 @@ static int gemm_host(int qtype, unsigned M, unsigned N, unsigned K, const float 
       (rc = grow(c->dQ, c->capQ, workspace_bytes(qtype, M, N, K))))
     return rc;
   NNTR_CHECK_CUDA(cudaMemcpyAsync(c->dA, A, bytesA, cudaMemcpyHostToDevice, c->stream));
-  rc = gemm_dev(qtype, M, N, K, static_cast<const float *>(c->dA), dB, static_cast<float *>(c->dC), N, c->dQ,
-                c->capQ, c->stream);
+  /* Decode (M == 1) with C in page-locked, device-mapped host memory: the kernel's epilogue writes the result straight
+   * into the caller's buffer (16 KB of posted writes) instead of a device buffer plus a copy back. The activation
+   * still travels by copy: every CTA reads all of x, which must not cross the host link 148 times. */
+  float *c_direct = nullptr;
+  if (M == 1) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, C) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
+      c_direct = static_cast<float *>(attr.devicePointer);
+    else
+      (void)cudaGetLastError();
+  }
+  rc = gemm_dev(qtype, M, N, K, static_cast<const float *>(c->dA), dB, c_direct ? c_direct : static_cast<float *>(c->dC),
+                N, c->dQ, c->capQ, c->stream);
   if (rc)
     return rc;
   const unsigned M4 = (M == 1 || qtype == NNTR_Q6_K) ? M : (M / 4) * 4; // rows written with stride ldc
   if (M == 1) {
-    NNTR_CHECK_CUDA(cudaMemcpyAsync(C, c->dC, bytesC, cudaMemcpyDeviceToHost, c->stream));
+    if (!c_direct)
+      NNTR_CHECK_CUDA(cudaMemcpyAsync(C, c->dC, bytesC, cudaMemcpyDeviceToHost, c->stream));
   } else {
     if (M4)
       NNTR_CHECK_CUDA(cudaMemcpy2DAsync(C, (size_t)ldc * sizeof(float), c->dC, (size_t)N * sizeof(float),

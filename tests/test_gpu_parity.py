@@ -235,6 +235,22 @@ def test_host_pointer_gemv_and_weight_cache(be, port, q, gen):
     be.unregister_weight(B)
 
 
+@pytest.mark.parametrize("q,gen", [("q4_K", O.random_q4_Kx8), ("q4_0", O.random_q4_0x8), ("q6_K", O.random_q6_K)])
+def test_host_pointer_gemv_into_page_locked_output(be, port, q, gen):
+    """Decode through the host-pointer entry point with the result buffer in page-locked host memory: the kernel writes
+    it directly (no device buffer, no copy back); same bits as with an ordinary buffer."""
+    rng = np.random.default_rng(23)
+    N, K = 1024, 1024
+    B = gen(rng, N, K)
+    x = acts(rng, 1, K)
+    want = port.gemm(q, x, B, N)
+    xh = torch.from_numpy(x).pin_memory()
+    yh = torch.full((1, N), float("nan")).pin_memory()
+    getattr(be, f"gemm_{q}")(1, N, K, xh.numpy(), K, B, N, yh.numpy(), N)
+    assert np.array_equal(bits(yh.numpy()), bits(want))
+    be.unregister_weight(B)
+
+
 # ------------------------------------------------------------------- GEMM
 @pytest.mark.parametrize("q,gen", [("q4_K", O.random_q4_Kx8), ("q4_0", O.random_q4_0x8), ("q6_K", O.random_q6_K)])
 @pytest.mark.parametrize("M", [2, 3, 4, 5, 8, 13, 64, 67])
