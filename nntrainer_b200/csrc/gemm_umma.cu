@@ -50,6 +50,7 @@
  * pipe or by HBM (weights are read once per 128 activation rows).
  */
 #include "common.cuh"
+#include "pipeline.cuh"
 
 namespace nntr {
 
@@ -81,47 +82,13 @@ constexpr int SMEM_BYTES = OFF_BARS + 256;
 
 __device__ int g_umma_status = 0;
 
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-               "selp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok)
-               : "r"(bar), "r"(parity), "r"(4000u) /* let the hardware park the thread for up to ~4 us per try */
-               : "memory");
-  return ok != 0;
-}
-/** Bounded wait: false (abort flag and device status raised) when the phase did not complete in time. */
+/** Bounded wait (pipeline.cuh); raises this file's status word when it runs out. */
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  for (uint32_t it = 0; it < WAIT_POLLS_UMMA; ++it) {
-    if (mbar_try_wait(bar, parity))
-      return true;
-    if (it > 2048) {
-      if (*abort_flag)
-        return false;
-      __nanosleep(32);
-    }
-  }
-  *abort_flag = 1;
-  atomicExch(&g_umma_status, NNTR_CUDA_ERR_TIMEOUT);
-  return false;
+  return mbar_wait_bounded(bar, parity, abort_flag, &g_umma_status, WAIT_POLLS_UMMA, 2048, 4000);
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
+
+
+/** Bounded wait: false (abort flag and device status raised) when the phase did not complete in time. */
 
 /** Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; lbo = bytes between the two
  *  core matrices of one 32-byte K step, sbo = bytes between 8-row groups. */

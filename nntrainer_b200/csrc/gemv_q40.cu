@@ -31,6 +31,7 @@
  * Algorithmic bytes per launch: N * K/32 * 18 (weights) + 4K (x) + 4N (y).
  */
 #include "common.cuh"
+#include "pipeline.cuh"
 
 namespace nntr {
 
@@ -46,72 +47,12 @@ constexpr int Q40_SMEM_BUDGET = 200 * 1024;
 
 __device__ int g_q40_status = 0;
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-               "selp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok)
-               : "r"(bar), "r"(parity)
-               : "memory");
-  return ok != 0;
-}
-/** Bounded wait: false (abort flag and device status raised) when the phase did not complete in time. */
+/** Bounded wait (pipeline.cuh); raises this file's status word when it runs out. */
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  for (uint32_t it = 0; it < Q40_WAIT_POLLS; ++it) {
-    if (mbar_try_wait(bar, parity))
-      return true;
-    if (it > 1024) {
-      if (*abort_flag)
-        return false;
-      __nanosleep(32);
-    }
-  }
-  *abort_flag = 1;
-  atomicExch(&g_q40_status, NNTR_CUDA_ERR_TIMEOUT);
-  return false;
+  return mbar_wait_bounded(bar, parity, abort_flag, &g_q40_status, Q40_WAIT_POLLS, 1024);
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) { // unsigned bytes (a) x signed bytes (b)
-  int d;
-  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-/* explicit shared-space accesses by 32-bit address: keeps every access on the shared-memory path */
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
 
-__device__ __forceinline__ void sts64(uint32_t a, uint32_t v0, uint32_t v1) {
-  asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a), "r"(v0), "r"(v1) : "memory");
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-  return v;
-}
+
 
 /** Bounded wait until the producer has armed stage t (see `armed` in the kernel). */
 __device__ __forceinline__ bool wait_armed(volatile int *armed, int t, volatile int *abort_flag) {

@@ -36,6 +36,7 @@
  * Every wait is bounded: on expiry the kernel raises a status word and leaves.
  */
 #include "common.cuh"
+#include "pipeline.cuh"
 
 namespace nntr {
 
@@ -77,6 +78,12 @@ constexpr int ACT_STRIDE = 288; // per 256 activations: 256 B q8 | 8 x int16 sum
 static_assert(NSTAGE * STAGE_BLOCKS == STEP_BLOCKS, "a consumer warp always reads the same ring slot");
 constexpr uint32_t WAIT_POLLS = 1u << 22;
 
+/** Bounded wait (pipeline.cuh); raises this file's status word when it runs out. */
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  return mbar_wait_bounded(bar, parity, abort_flag, &g_device_status, WAIT_POLLS, 1024);
+}
+
+
 struct SmemLayout {
   uint32_t ring, act, part, bars, abort_flag, total;
 };
@@ -104,58 +111,10 @@ __host__ __device__ inline int pick_ngslot(int nb) {
   return n;
 }
 
-/* ---- mbarrier / bulk-copy primitives (shared::cta addresses as 32-bit) ---- */
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-               "selp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok)
-               : "r"(bar), "r"(parity)
-               : "memory");
-  return ok != 0;
-}
-/** Bounded wait. Returns false (and raises the CTA's abort flag and the device
- *  status word) if the phase did not complete within WAIT_POLLS polls. */
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  for (uint32_t it = 0; it < WAIT_POLLS; ++it) {
-    if (mbar_try_wait(bar, parity))
-      return true;
-    if (it > 1024) {
-      if (*abort_flag)
-        return false;
-      __nanosleep(32);
-    }
-  }
-  *abort_flag = 1;
-  atomicExch(&g_device_status, NNTR_CUDA_ERR_TIMEOUT);
-  return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
 __device__ __forceinline__ void consumer_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
 }
 
-/** 4-way dot product of unsigned bytes (a) with signed bytes (b), accumulated in c */
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
-  int d;
-  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
 
 /** Integer sums of one super-block (in shared memory at blk) for output row r:
  *      I = sum_sb sc*dot32,  J = sum_sb m*bsum32.

@@ -9,6 +9,7 @@
  *        with nothing else running.
  */
 #include "common.cuh"
+#include "pipeline.cuh"
 
 namespace nntr {
 
@@ -16,7 +17,6 @@ namespace {
 
 constexpr int PEAK_SMEM = 64 * 1024 + 32 * 1024; // B: 256 rows x 256 B, A: 128 rows x 256 B
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
   return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)((lbo >> 4) & 0x3fff) << 16) |
          ((uint64_t)((sbo >> 4) & 0x3fff) << 32) | ((uint64_t)1 << 46);
