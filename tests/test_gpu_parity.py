@@ -290,6 +290,34 @@ def test_host_pointer_gemm_ldc_quirk(be, port):
     be.unregister_weight(B)
 
 
+# ------------------------------------------------------------ edge cases
+@pytest.mark.parametrize("q,gen", [("q4_K", O.random_q4_Kx8), ("q4_0", O.random_q4_0x8), ("q6_K", O.random_q6_K)])
+def test_empty_zero_and_padded_calls(be, port, q, gen):
+    """M == 0 and N == 0 return without touching the output; an all-zero activation gives exact zeros (the reference's
+    zero-scale blocks); a device GEMM with ldc > N leaves the padding columns alone."""
+    rng = np.random.default_rng(31)
+    N, K = 64, 512
+    B = gen(rng, N, K)
+    Bd = dev(B)
+    C = torch.full((4, N), float("nan"), device="cuda")
+    getattr(be, f"gemm_{q}")(0, N, K, torch.zeros((1, K), device="cuda"), K, Bd, N, C, N)
+    getattr(be, f"gemm_{q}")(1, 0, K, torch.zeros((1, K), device="cuda"), K, Bd, 0, C, N)
+    assert torch.isnan(C).all()
+    y = torch.full((1, N), float("nan"), device="cuda")
+    getattr(be, f"gemm_{q}")(1, N, K, torch.zeros((1, K), device="cuda"), K, Bd, N, y, N)
+    assert np.array_equal(bits(y.cpu().numpy()), bits(port.gemm(q, np.zeros((1, K), np.float32), B, N)))
+    M, ldc = 6, N + 8
+    A = acts(rng, M, K)
+    Cp = torch.full((M, ldc), float("nan"), device="cuda")
+    be.set_gemm_path("exact")
+    getattr(be, f"gemm_{q}")(M, N, K, dev(A), K, Bd, N, Cp, ldc)
+    be.set_gemm_path("auto")
+    got = Cp.cpu().numpy()
+    assert np.array_equal(bits(got[:, :N]), bits(port.gemm(q, A, B, N)))
+    assert np.isnan(got[:, N:]).all()
+    be.device_status()
+
+
 # ------------------------------------------------- full-size property checks
 def test_full_size_gemv_linearity_in_weights_scale(be):
     """cfg-sized GEMV (N=K=4096): doubling every fp16 block scale doubles the
