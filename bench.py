@@ -655,6 +655,15 @@ def run_case(args):
         be.set_gemm_path("tensor")
         call = lambda: be.gemm_q4_K(M, N, K, A, K, W, N, C, N, ws)
         work = {"case": "prefill", "M": M, "N": N, "K": K, "qtype": "q4_K", "ops": 2.0 * M * N * K}
+    elif args.case == "moe_layer":
+        H, I, E, k = 2048, 768, 128, 8
+        mk = lambda n, kk: torch.from_numpy(O.random_q4_Kx8(rng, n, kk)).to(dev)
+        pool = [(mk(I, H), mk(I, H), mk(H, I)) for _ in range(8)]
+        layer = be.MoeLayer(torch.randn(H, E, device=dev) * 0.02, [pool[e % 8][0] for e in range(E)],
+                            [pool[e % 8][1] for e in range(E)], [pool[e % 8][2] for e in range(E)], k)
+        x = torch.randn(1, H, device=dev)
+        call = lambda: layer.forward(x)
+        work = {"case": "moe_layer", "hidden": H, "inter": I, "experts": E, "top_k": k, "tokens": 1}
     else:  # lm_head
         N, K = 151936, 2560
         W = torch.from_numpy(O.random_q6_K(rng, N, K)).to(dev)
@@ -692,7 +701,7 @@ def main():
     ap.add_argument("--ring", type=int, default=RING, help="distinct weight matrices per step (default keeps every launch out of L2)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the GEMV kernel from an ncu capture (reported as roofline.traffic)")
-    ap.add_argument("--case", default=None, choices=["prefill", "lm_head"],
+    ap.add_argument("--case", default=None, choices=["prefill", "lm_head", "moe_layer"],
                     help="run one small single-kernel case (profiler captures) instead of the benchmark")
     args = ap.parse_args()
     globals()["RING"] = args.ring

@@ -191,6 +191,8 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
 __global__ void moe_act_kernel(const float *__restrict__ gu, float *__restrict__ a, const int *__restrict__ idx,
                                const float *const *__restrict__ gate_b, const float *const *__restrict__ up_b, int kind,
                                float alpha, int I, long total, int e_lo, int e_hi) {
+  pdl_wait(); // launched with programmatic stream serialization: everything it reads comes from the grid before it
+  pdl_launch_dependents();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total)
     return;
@@ -216,6 +218,7 @@ __global__ void moe_act_kernel(const float *__restrict__ gu, float *__restrict__
 __global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__restrict__ idx, const float *__restrict__ w,
                                    const float *const *__restrict__ down_b, float *__restrict__ y, int H, int topk,
                                    long total) {
+  pdl_wait();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total)
     return;
@@ -250,6 +253,7 @@ __global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__re
 __global__ void moe_combine_ep_kernel(const uint2 *__restrict__ eo, const int *__restrict__ idx,
                                       const float *__restrict__ w, const float *const *__restrict__ down_b,
                                       float *__restrict__ y, int H, int topk, long total, MoeEp ep, int *status) {
+  pdl_wait();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const unsigned long long seq = (*ep.epoch - 1) * ep.layers_per_epoch + ep.layer + 1;
   if (threadIdx.x < ep.n_ranks) {
@@ -308,6 +312,22 @@ __global__ void moe_combine_ep_kernel(const uint2 *__restrict__ eo, const int *_
 static __device__ int g_moe_status = 0;
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+/** Launch with programmatic stream serialization: the grid may be scheduled while its predecessor drains; the kernel
+ *  calls pdl_wait() before it touches anything the predecessor wrote. */
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 struct MoeWs {
   size_t idx, w, gu_tab, dn_tab, rpart, rcount, gu, act, dn, total;
@@ -420,10 +440,9 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
     return rc;
 
   const long n_act = (long)P * I;
-  moe_act_kernel<<<(unsigned)((n_act + 255) / 256), 256, 0, st>>>(gu, act, idx, d->gate_b, d->up_b, d->kind, d->alpha,
-                                                                  (int)I, n_act, e_lo, e_hi);
+  NNTR_CHECK_CUDA(launch_pdl(moe_act_kernel, (unsigned)((n_act + 255) / 256), 256, st, gu, act, idx, d->gate_b, d->up_b,
+                             d->kind, d->alpha, (int)I, n_act, e_lo, e_hi));
   count_launch();
-  NNTR_CHECK_CUDA(cudaGetLastError());
 
   GemvBatch b2 = {dn_tab, (long long)I, 1, (long long)H};
   const long n_out = (long)tokens * H;
@@ -432,10 +451,10 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
                                : launch_gemv_q4_0_batched(H, I, act, nullptr, dn, pdl, P, b2, st);
     if (rc)
       return rc;
-    moe_combine_kernel<<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dn, idx, w, d->kind == 1 ? d->down_b : nullptr,
-                                                                        y, (int)H, (int)K, n_out);
+    const cudaError_t e = launch_pdl(moe_combine_kernel, (unsigned)((n_out + 255) / 256), 256, st, dn, idx, w,
+                                     d->kind == 1 ? d->down_b : nullptr, y, (int)H, (int)K, n_out);
     count_launch();
-    return check_cuda(cudaGetLastError(), "moe_combine launch");
+    return check_cuda(e, "moe_combine launch");
   }
   /* expert parallel: the down projections of the experts this rank owns store their outputs, numbered, into every
    * rank's buffer; the combine waits for the numbers */
@@ -454,11 +473,11 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
     return rc;
   int *status = nullptr;
   NNTR_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_moe_status));
-  moe_combine_ep_kernel<<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(
-    static_cast<const uint2 *>(epd->out[epd->rank]), idx, w, d->kind == 1 ? d->down_b : nullptr, y, (int)H, (int)K,
-    n_out, ep, status);
+  const cudaError_t e = launch_pdl(moe_combine_ep_kernel, (unsigned)((n_out + 255) / 256), 256, st,
+                                   static_cast<const uint2 *>(epd->out[epd->rank]), idx, w,
+                                   d->kind == 1 ? d->down_b : nullptr, y, (int)H, (int)K, n_out, ep, status);
   count_launch();
-  return check_cuda(cudaGetLastError(), "moe_combine_ep launch");
+  return check_cuda(e, "moe_combine_ep launch");
 }
 
 extern "C" int nntr_cuda_moe_forward_dev(const nntr_moe_desc *d, unsigned tokens, const float *x, float *y,
