@@ -38,11 +38,11 @@ struct MoeEp {
 };
 
 constexpr int ROUTER_WARPS = 8;
-constexpr int ROUTER_SLICES = 8; // CTAs per token
+constexpr int ROUTER_SLICES = 32; // CTAs per token
 constexpr int MAX_E_PER_LANE = 8; // up to 256 experts
 
 /* ROUTER_SLICES CTAs per token: each sums its slice of the hidden dimension into partial logits (the router weight
- * is a megabyte per layer: one CTA alone would be bound by the latency of its own loads); the CTA that arrives last on
+ * is a megabyte per layer: a few CTAs alone would be bound by the latency of their own loads); the CTA that arrives last on
  * the token's counter adds the partials in slice order and does softmax, top-k and the tables. */
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, const float *__restrict__ bias, int H, int E,
@@ -224,24 +224,45 @@ __global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__re
     return;
   const long t = i / H;
   const int h = (int)(i - t * H);
+  // the token's experts in ascending order (top_k <= 32: a bitmask of taken slots), then eight values in flight at a
+  // time, added in that order
+  int ids[32];
+  for (int j = 0; j < topk; ++j)
+    ids[j] = idx[t * topk + j];
   float acc = 0.f;
-  int last = -1;
-  for (int k = 0; k < topk; ++k) { // selection sort over at most a handful of experts
-    int best = 0x7fffffff, bj = -1;
-    for (int j = 0; j < topk; ++j) {
-      const int e = idx[t * topk + j];
-      if (e > last && e < best) {
-        best = e;
-        bj = j;
+  unsigned taken = 0;
+  for (int k0 = 0; k0 < topk; k0 += 8) {
+    int sel[8], se[8];
+    float v[8], ww[8];
+    const int n = topk - k0 < 8 ? topk - k0 : 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      sel[k] = -1;
+      se[k] = 0;
+      if (k < n) {
+        int best = 0x7fffffff, bj = -1;
+        for (int j = 0; j < topk; ++j)
+          if (!((taken >> j) & 1u) && ids[j] < best) {
+            best = ids[j];
+            bj = j;
+          }
+        taken |= 1u << bj;
+        sel[k] = bj;
+        se[k] = best;
       }
     }
-    if (bj < 0)
-      break;
-    last = best;
-    float v = dn[(t * topk + bj) * H + h];
-    if (down_b)
-      v = __fadd_rn(v, down_b[best][h]);
-    acc = __fadd_rn(acc, __fmul_rn(v, w[t * topk + bj]));
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (sel[k] >= 0) {
+        v[k] = dn[(t * topk + sel[k]) * H + h];
+        ww[k] = w[t * topk + sel[k]];
+        if (down_b)
+          v[k] = __fadd_rn(v[k], down_b[se[k]][h]);
+      }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (sel[k] >= 0)
+        acc = __fadd_rn(acc, __fmul_rn(v[k], ww[k]));
   }
   y[i] = acc;
 }
