@@ -100,17 +100,23 @@ int nntr_cuda_dequantize_weight_dev(int qtype, const void *w, float *y, int64_t 
 size_t nntr_cuda_gemm_workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K);
 
 /** Which kernels serve Q4_K GEMMs with M > 1 (process-wide):
- *   EXACT   integer dot products on the CUDA cores with the reference's exact
- *           floating-point chain: C equals the CPU result bit for bit;
- *   TENSOR  tcgen05 int8 tensor-core kernel (needs N % 128 == 0): exact integer
- *           sums, one rounding more per super-block in the fp32 combination, C
- *           within max-rel 2e-3 of the CPU result (the tolerance the CPU path's
- *           own SIMD variants have among themselves);
- *   AUTO    TENSOR where it applies and M >= 32, else EXACT (the default).
+ *   EXACT       integer dot products on the CUDA cores with the reference's exact
+ *               floating-point chain: C equals the CPU result bit for bit;
+ *   TENSOR      tcgen05 int8 tensor-core kernel (needs N % 128 == 0): exact
+ *               integer sums, one rounding more per super-block in the fp32
+ *               combination (measured 1e-6 from the CPU result);
+ *   TENSOR_F16  tcgen05 fp16 tensor-core kernel (needs N % 256 == 0): weights
+ *               and quantized activations are dequantized to fp16 operands, the
+ *               products summed in fp32 (measured 4e-4 from the CPU result; the
+ *               path's stated tolerance is max-rel 2e-3); the fastest;
+ *   AUTO        from 32 rows up TENSOR_F16 where it applies, else TENSOR where
+ *               that applies, else EXACT (the default).
+ *  A path that does not apply to a call falls back to EXACT.
  *  There is no CPU counterpart: the reference picks its SIMD variant at build time. */
 #define NNTR_CUDA_GEMM_PATH_AUTO 0
 #define NNTR_CUDA_GEMM_PATH_EXACT 1
 #define NNTR_CUDA_GEMM_PATH_TENSOR 2
+#define NNTR_CUDA_GEMM_PATH_TENSOR_F16 3
 int nntr_cuda_set_gemm_path(int path);
 
 /** Measures the device's dense int8 tensor-core rate with a stream of the MMA

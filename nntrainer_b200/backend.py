@@ -97,12 +97,13 @@ def measure_int8_peak() -> tuple[float, float]:
     return tops.value, clk.value
 
 
-GEMM_PATHS = {"auto": 0, "exact": 1, "tensor": 2}
+GEMM_PATHS = {"auto": 0, "exact": 1, "tensor": 2, "tensor_f16": 3}
 
 
 def set_gemm_path(path: str) -> None:
     """Kernels that serve Q4_K GEMMs with M > 1: "exact" (CUDA-core integer dot products, bit-identical to the CPU
-    result), "tensor" (tcgen05 int8 MMA, within the path's tolerance) or "auto" (tensor from 32 rows up)."""
+    result), "tensor" (tcgen05 int8 MMA, integer sums exact), "tensor_f16" (tcgen05 fp16 MMA on dequantized operands,
+    the fastest, within the path's tolerance) or "auto" (a tensor path from 32 rows up)."""
     check(lib().nntr_cuda_set_gemm_path(GEMM_PATHS[path]))
 
 

@@ -161,11 +161,20 @@ static int grow(void *&p, size_t &cap, size_t need) {
 static std::atomic<int> g_gemm_path{NNTR_CUDA_GEMM_PATH_AUTO};
 constexpr unsigned TENSOR_PATH_MIN_M = 32; // below this the dp4a kernels win (a 128-row activation tile is mostly padding)
 
-static bool use_tensor_path(int qtype, unsigned M, unsigned N, unsigned K) {
+/* 0: exact CUDA-core kernels, 1: integer tensor path (kind::i8), 2: fp16 tensor path (kind::f16) */
+static int pick_gemm_kernel(int qtype, unsigned M, unsigned N, unsigned K) {
   const int path = g_gemm_path.load(std::memory_order_relaxed);
-  if (path == NNTR_CUDA_GEMM_PATH_EXACT || !umma_supported(qtype, M, N, K))
-    return false;
-  return path == NNTR_CUDA_GEMM_PATH_TENSOR || M >= TENSOR_PATH_MIN_M;
+  if (path == NNTR_CUDA_GEMM_PATH_EXACT)
+    return 0;
+  if (path == NNTR_CUDA_GEMM_PATH_TENSOR)
+    return umma_supported(qtype, M, N, K) ? 1 : 0;
+  if (path == NNTR_CUDA_GEMM_PATH_TENSOR_F16)
+    return umma_f16_supported(qtype, M, N, K) ? 2 : 0;
+  if (M < TENSOR_PATH_MIN_M) // auto
+    return 0;
+  if (umma_f16_supported(qtype, M, N, K))
+    return 2;
+  return umma_supported(qtype, M, N, K) ? 1 : 0;
 }
 
 static size_t workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K) {
@@ -174,8 +183,13 @@ static size_t workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K) {
   if (qtype == NNTR_Q4_0)
     return (size_t)M * (K / 32) * sizeof(BlockQ80);
   const size_t rows = (size_t)M * (K / 256) * sizeof(BlockQ8K);
-  // large enough for either path, whichever the path setting selects at call time
-  return umma_supported(qtype, M, N, K) ? std::max(rows, umma_workspace_bytes(M, K)) : rows;
+  // large enough for every path the setting may select at call time
+  size_t need = rows;
+  if (umma_supported(qtype, M, N, K))
+    need = std::max(need, umma_workspace_bytes(M, K));
+  if (umma_f16_supported(qtype, M, N, K))
+    need = std::max(need, umma_f16_workspace_bytes(M, K));
+  return need;
 }
 
 static int gemm_dev(int qtype, unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C,
@@ -207,8 +221,14 @@ static int gemm_dev(int qtype, unsigned M, unsigned N, unsigned K, const float *
   /* Rows below 4*floor(M/4) are quantized the way the reference's 4-row
    * quantizer does it, the last M%4 rows the way its row quantizer does
    * (ggml_interface_omp.cpp:433-461). */
-  if (use_tensor_path(qtype, M, N, K))
+  switch (pick_gemm_kernel(qtype, M, N, K)) {
+  case 1:
     return launch_gemm_q4_K_umma(M, N, K, A, B, C, ldc, ws, st);
+  case 2:
+    return launch_gemm_q4_K_f16(M, N, K, A, B, C, ldc, ws, st);
+  default:
+    break;
+  }
   const unsigned M4 = (M / 4) * 4;
   if (qtype == NNTR_Q4_0) {
     rc = launch_quantize_q8_0(A, K, ws, M, K, st);
@@ -339,6 +359,8 @@ int nntr_cuda_device_status(void) {
     return rc;
   if (!v && (rc = read_q40_status(&v)))
     return rc;
+  if (!v && (rc = read_f16_status(&v)))
+    return rc;
   if (v)
     return set_error(v, "a device kernel gave up on a bounded wait (status %d)", v);
   return NNTR_CUDA_OK;
@@ -364,7 +386,8 @@ size_t nntr_cuda_gemm_workspace_bytes(int qtype, unsigned M, unsigned N, unsigne
 int nntr_cuda_measure_int8_peak(double *tops, double *clk_per_mma) { return measure_int8_peak(tops, clk_per_mma); }
 
 int nntr_cuda_set_gemm_path(int path) {
-  if (path != NNTR_CUDA_GEMM_PATH_AUTO && path != NNTR_CUDA_GEMM_PATH_EXACT && path != NNTR_CUDA_GEMM_PATH_TENSOR)
+  if (path != NNTR_CUDA_GEMM_PATH_AUTO && path != NNTR_CUDA_GEMM_PATH_EXACT && path != NNTR_CUDA_GEMM_PATH_TENSOR &&
+      path != NNTR_CUDA_GEMM_PATH_TENSOR_F16)
     return set_error(NNTR_CUDA_ERR_INVALID, "set_gemm_path: unknown path %d", path);
   g_gemm_path.store(path, std::memory_order_relaxed);
   return NNTR_CUDA_OK;

@@ -61,10 +61,12 @@ def test_no_device_means_error_not_fallback(L):
 
 def test_workspace_sizes(L):
     assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_K, 1, 4096, 4096) == 0
-    # N % 128 == 0: room for the tensor path's activation tiles (128 rows x 256 values + scales + sums per super-block)
-    assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_K, 64, 4096, 4096) == max(64 * 16 * 292, 1 * 16 * (32768 + 2560))
+    # N % 256 == 0: room for the fp16 tensor path's activation tiles (128 rows x K halves)
+    assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_K, 64, 4096, 4096) == 128 * 4096 * 2
+    # N % 128 == 0 only: the integer tensor path's tiles (128 rows x 256 values + scales + sums per super-block)
+    assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_K, 64, 4224, 4096) == max(64 * 16 * 292, 1 * 16 * (32768 + 2560))
     assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_K, 64, 4104, 4096) == 64 * 16 * 292
-    assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_K, 129, 4096, 256) == 2 * (32768 + 2560)
+    assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_K, 129, 4224, 256) == 2 * (32768 + 2560)
     assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_0, 64, 4096, 4096) == 64 * 128 * 34
     assert L.nntr_cuda_gemm_workspace_bytes(capi.Q6_K, 3, 8, 2560) == 3 * 10 * 292
     assert L.nntr_cuda_set_gemm_path(7) == capi.ERR_INVALID and L.nntr_cuda_set_gemm_path(0) == 0

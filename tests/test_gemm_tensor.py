@@ -102,6 +102,36 @@ def test_prefill_size_property_linearity_in_activation_scale(be):
     assert np.array_equal(c3[:132].view(np.uint32), c1[:132].view(np.uint32))
 
 
+@pytest.mark.parametrize("M,N,K", [(2, 256, 256), (33, 256, 512), (128, 256, 2048), (129, 512, 768), (300, 256, 1280)])
+def test_fp16_tensor_gemm_matches_checker(be, port, M, N, K):
+    """tcgen05 kind::f16 path: weights and quantized activations dequantized to fp16 operands, fp32 accumulation.
+    Bar: the path's stated tolerance; in practice a few 1e-4 (two fp16 roundings per product)."""
+    rng = np.random.default_rng(M * 11 + N)
+    B = O.random_q4_Kx8(rng, N, K)
+    A = acts(rng, max(M, 4), K)[:M]
+    want = port.gemm("q4_K", A, B, N)
+    Ad, Bd = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    got = run(be, "tensor_f16", M, N, K, Ad, Bd)
+    assert np.isfinite(got).all()
+    assert max_rel(got, want) <= REL_TOL
+    assert max_rel(got, want) <= 1e-3, "expected error of fp16 operands is a few 1e-4"
+
+
+def test_fp16_tensor_gemm_strides_padding_and_auto_choice(be, port):
+    rng = np.random.default_rng(15)
+    M, N, K, ldc = 40, 256, 512, 288
+    B = O.random_q4_Kx8(rng, N, K)
+    A = acts(rng, M, K)
+    Ad, Bd = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    got = run(be, "tensor_f16", M, N, K, Ad, Bd, ldc=ldc)
+    want = port.gemm("q4_K", A, B, N)
+    assert max_rel(got[:, :N], want) <= REL_TOL
+    assert np.isnan(got[:, N:]).all(), "columns beyond N are not touched"
+    # auto: N % 256 == 0 and M >= 32 -> the fp16 path
+    auto = run(be, "auto", M, N, K, Ad, Bd, ldc=ldc)
+    assert np.array_equal(auto[:, :N].view(np.uint32), got[:, :N].view(np.uint32))
+
+
 def test_int8_peak_measurement_is_plausible(be):
     """The int8 rate the prefill fraction is quoted against: a dense tcgen05 kind::i8 stream on every SM. A B200 is
     specified at 4.5 POP/s dense; anything outside 1.5 .. 6 POP/s means the measurement is not doing the work."""
