@@ -385,40 +385,60 @@ NOMINAL_INT8_TOPS = 4500.0  # dense int8, per GPU (nominal, for context)
 
 
 def prefill_gemm_shapes(be, torch, dev, steps=10):
-    """Q4_K x Q8_K GEMM through the device entry point (activation quantizer + tcgen05 kernel per call), three distinct
-    copies of the weight in rotation (170 MB > L2), CUDA events on the launching stream. effective = 2*M*N*K / time;
-    mma = twice that (the 6-bit scale is split in two 8-bit operands, so the tensor pipe does two passes)."""
+    """Q4_K x Q8_K GEMM through the device entry point (activation quantizer + tensor-core kernel per call), three
+    distinct copies of the weight in rotation (170 MB > L2), CUDA events on the launching stream. Two kernels:
+    "tensor_f16" (tcgen05 kind::f16 on operands dequantized to fp16; the default from 32 rows up) against the measured
+    bf16 GEMM peaks of MEASURED_PEAKS.json, and "tensor" (tcgen05 kind::i8, integer sums exact) against the int8 rate
+    measured now with a stream of the same MMA instruction; its tensor pipe does two passes (the 6-bit scale is split
+    in two 8-bit operands), so mma = 2 x effective."""
     from oracle import oracle as O
     out = []
     rng = np.random.default_rng(11)
-    peak_tops, clk_per_mma = be.measure_int8_peak()  # stream of the same MMA instruction on every SM, measured now
+    peak_i8, clk_per_mma = be.measure_int8_peak()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp = json.load(f)
+        peak_f16, peak_f16_sus, src = float(mp["bf16_tflops"]), float(mp["bf16_tflops_sustained"]), "measured (cuBLAS bf16)"
+    except Exception:
+        peak_f16, peak_f16_sus, src = 1590.0, 1400.0, "fallback"
     for M, N, K in PREFILL_SWEEP:
         base = torch.from_numpy(O.random_q4_Kx8(rng, N, K)).to(dev)
         mats = [base, torch.roll(base, 4099 * 16), torch.roll(base, 2 * 4099 * 16)]
         A = torch.randn(M, K, device=dev)
         C = torch.empty(M, N, device=dev)
         ws = torch.empty(be.gemm_workspace_bytes("q4_K", M, N, K), dtype=torch.uint8, device=dev)
-        be.set_gemm_path("auto")
-        for W in mats:
-            be.gemm_q4_K(M, N, K, A, K, W, N, C, N, ws)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
+        row = {"M": M, "N": N, "K": K, "qtype": "q4_K"}
+        for path in ("tensor_f16", "tensor"):
+            be.set_gemm_path(path)
             for W in mats:
                 be.gemm_q4_K(M, N, K, A, K, W, N, C, N, ws)
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (steps * len(mats))
-        eff = 2.0 * M * N * K / (us * 1e-6) / 1e12
-        out.append({"M": M, "N": N, "K": K, "qtype": "q4_K", "path": "tcgen05 kind::i8", "us_per_call": round(us, 1),
-                    "effective_TOP/s": round(eff, 1), "mma_TOP/s": round(2 * eff, 1),
-                    "int8_peak_TOP/s": round(peak_tops, 1), "int8_peak_source": "measured (tcgen05.mma kind::i8 stream)",
-                    "clk_per_128x256x32_mma": round(clk_per_mma, 1),
-                    "mma_frac_of_measured_int8": round(2 * eff / peak_tops, 4),
-                    "mma_frac_of_nominal_int8": round(2 * eff / NOMINAL_INT8_TOPS, 4)})
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                for W in mats:
+                    be.gemm_q4_K(M, N, K, A, K, W, N, C, N, ws)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (steps * len(mats))
+            eff = 2.0 * M * N * K / (us * 1e-6) / 1e12
+            if path == "tensor_f16":
+                row["fp16_path"] = {"kernel": "tcgen05 kind::f16, fp16 operands", "us_per_call": round(us, 1),
+                                    "TFLOP/s": round(eff, 1), "peak_TFLOP/s_burst": peak_f16,
+                                    "peak_TFLOP/s_sustained": peak_f16_sus, "peak_source": src,
+                                    "frac_of_burst_peak": round(eff / peak_f16, 4),
+                                    "frac_of_sustained_peak": round(eff / peak_f16_sus, 4)}
+            else:
+                row["int8_path"] = {"kernel": "tcgen05 kind::i8, integer sums exact", "us_per_call": round(us, 1),
+                                    "effective_TOP/s": round(eff, 1), "mma_TOP/s": round(2 * eff, 1),
+                                    "int8_peak_TOP/s": round(peak_i8, 1),
+                                    "int8_peak_source": "measured (tcgen05.mma kind::i8 stream)",
+                                    "clk_per_128x256x32_mma": round(clk_per_mma, 1),
+                                    "mma_frac_of_measured_int8": round(2 * eff / peak_i8, 4)}
+        out.append(row)
         del mats, base, A, C, ws
         torch.cuda.empty_cache()
+    be.set_gemm_path("auto")
     be.device_status()
     return out
 
@@ -647,7 +667,7 @@ def run_case(args):
     reps = max(1, args.steps if args.steps < 100 else 5)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if args.case in ("prefill", "prefill_f16"):
-        M, N, K = 512, 4096, 4096
+        M, N, K = (512, 4096, 4096) if args.case == "prefill" else (256, 24576, 4096)
         W = torch.from_numpy(O.random_q4_Kx8(rng, N, K)).to(dev)
         A = torch.randn(M, K, device=dev)
         C = torch.empty(M, N, device=dev)

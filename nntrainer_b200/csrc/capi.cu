@@ -172,9 +172,14 @@ static int pick_gemm_kernel(int qtype, unsigned M, unsigned N, unsigned K) {
     return umma_f16_supported(qtype, M, N, K) ? 2 : 0;
   if (M < TENSOR_PATH_MIN_M) // auto
     return 0;
-  if (umma_f16_supported(qtype, M, N, K))
+  // auto: the fp16 path is the faster kernel per tile but cuts the problem into 256 x 256 tiles; when those would
+  // leave most SMs idle the integer path's 128 x 128 tiles win
+  const bool f16_ok = umma_f16_supported(qtype, M, N, K), i8_ok = umma_supported(qtype, M, N, K);
+  const unsigned mt = (M + 127) / 128;
+  const unsigned tiles_f16 = ((mt + 1) / 2) * (N / 256);
+  if (f16_ok && (tiles_f16 >= (unsigned)sm_count() / 2 || !i8_ok))
     return 2;
-  return umma_supported(qtype, M, N, K) ? 1 : 0;
+  return i8_ok ? 1 : 0;
 }
 
 static size_t workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K) {

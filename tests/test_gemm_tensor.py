@@ -127,9 +127,16 @@ def test_fp16_tensor_gemm_strides_padding_and_auto_choice(be, port):
     want = port.gemm("q4_K", A, B, N)
     assert max_rel(got[:, :N], want) <= REL_TOL
     assert np.isnan(got[:, N:]).all(), "columns beyond N are not touched"
-    # auto: N % 256 == 0 and M >= 32 -> the fp16 path
+    # auto with a single 256 x 256 tile: most SMs would idle, so the integer path's 128 x 128 tiles are chosen
     auto = run(be, "auto", M, N, K, Ad, Bd, ldc=ldc)
-    assert np.array_equal(auto[:, :N].view(np.uint32), got[:, :N].view(np.uint32))
+    i8 = run(be, "tensor", M, N, K, Ad, Bd, ldc=ldc)
+    assert np.array_equal(auto[:, :N].view(np.uint32), i8[:, :N].view(np.uint32))
+    # auto with enough tiles for the machine: the fp16 path
+    N2 = 256 * 80
+    B2 = torch.from_numpy(O.random_q4_Kx8(rng, N2, K)).cuda()
+    auto2 = run(be, "auto", M, N2, K, Ad, B2)
+    f16 = run(be, "tensor_f16", M, N2, K, Ad, B2)
+    assert np.array_equal(auto2.view(np.uint32), f16.view(np.uint32))
 
 
 def test_int8_peak_measurement_is_plausible(be):
