@@ -186,6 +186,14 @@ gemm_q4_K_f16_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__res
 #pragma unroll
       for (int i = 0; i < 6; ++i)
         g[i] = __ldg(reinterpret_cast<const uint32_t *>(wrow[nst >> 2].scales + 24 * (nst & 3)) + i);
+      { // weights are read once from HBM: pull the lines of three stages ahead into L2 so that the loads above hit it
+        const int fst = st + 3 < n_stages ? st + 3 : n_stages - 1;
+        const uint8_t *fq = wrow[fst >> 2].qs + ((fst & 3) * 32 + 16 * hsel + j) * 8;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(fq));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(fq + 64));
+        if ((fst & 3) == 0 && hsel == 0 && j == 0)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow + (fst >> 2))); // d, dmin, scales: the block's first 128 bytes
+      }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const uint2 w2 = q[c];
