@@ -185,8 +185,10 @@ static int pick_gemm_kernel(int qtype, unsigned M, unsigned N, unsigned K) {
 static size_t workspace_bytes(int qtype, unsigned M, unsigned N, unsigned K) {
   if (M <= 1)
     return 0;
-  if (qtype == NNTR_Q4_0)
-    return (size_t)M * (K / 32) * sizeof(BlockQ80);
+  if (qtype == NNTR_Q4_0) {
+    const size_t rows0 = (size_t)M * (K / 32) * sizeof(BlockQ80);
+    return umma_f16_supported(qtype, M, N, K) ? std::max(rows0, umma_f16_workspace_bytes(M, K)) : rows0;
+  }
   const size_t rows = (size_t)M * (K / 256) * sizeof(BlockQ8K);
   // large enough for every path the setting may select at call time
   size_t need = rows;
@@ -230,7 +232,7 @@ static int gemm_dev(int qtype, unsigned M, unsigned N, unsigned K, const float *
   case 1:
     return launch_gemm_q4_K_umma(M, N, K, A, B, C, ldc, ws, st);
   case 2:
-    return launch_gemm_q4_K_f16(M, N, K, A, B, C, ldc, ws, st);
+    return launch_gemm_f16(qtype, M, N, K, A, B, C, ldc, ws, st);
   default:
     break;
   }

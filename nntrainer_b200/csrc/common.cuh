@@ -302,8 +302,8 @@ int read_umma_status(int *out);
 /* tensor-core path with fp16 operands (gemm_umma_f16.cu): also quantizes the activations itself, into ws */
 bool umma_f16_supported(int qtype, unsigned M, unsigned N, unsigned K);
 size_t umma_f16_workspace_bytes(unsigned M, unsigned K);
-int launch_gemm_q4_K_f16(unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C, unsigned ldc,
-                         void *ws, cudaStream_t st);
+int launch_gemm_f16(int qtype, unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C, unsigned ldc,
+                    void *ws, cudaStream_t st);
 int read_f16_status(int *out);
 /* dense int8 tensor-core rate of the current device, measured (umma_peak.cu) */
 int measure_int8_peak(double *tops_out, double *clk_per_mma_out);

@@ -1,7 +1,7 @@
 // SPDX-License-Identifier: Apache-2.0
 /**
  * @file  gemm_umma_f16.cu
- * @brief Prefill GEMM for Q4_K weights with both operands dequantized to fp16
+ * @brief Prefill GEMM for Q4_K and Q4_0 weights with both operands dequantized to fp16
  *        on the fly: tcgen05.mma kind::f16, fp32 accumulators in tensor memory,
  *        no work per super-block outside the tensor pipe.
  *
@@ -14,7 +14,10 @@
  * the tensor core. Measured against the reference chain on random-byte weights:
  * max-rel 3.5e-4 (bar 2e-3). This is the fast prefill path; the integer-exact
  * tensor path (gemm_umma.cu) and the bit-exact CUDA-core path (gemm_dp4a.cu)
- * stay selectable.
+ * stay selectable. Q4_0 weights (nntr_gemm_q4_0_8x8_q8_0, nntr_ggml_impl.cpp:650-3259) take the same route:
+ * w = (q4 - 8) * d as one half-precision multiply, a = fp16(fp32(d_a) * q8) with the Q8_0 quantizer, a stage of 64
+ * being two 32-weight blocks; their 32-element block scale would force an integer kernel to leave the tensor pipe at
+ * every MMA K step.
  *
  * Why fp16 operands: folding the per-sub-block scales and mins into the weight
  * values removes every per-super-block step from the CUDA cores -- no split of
@@ -107,9 +110,20 @@ __device__ __forceinline__ uint32_t expand2(uint32_t nib2, __half2 d, __half2 ne
   return *reinterpret_cast<const uint32_t *>(&w);
 }
 
+/** (n_a, n_b) of a Q4_0 word whose nibbles already had their XOR 8 undone, as half2: (n - 8) * d */
+__device__ __forceinline__ uint32_t expand2_q40(uint32_t nib2, __half2 d) {
+  const uint32_t biased = nib2 | 0x64006400u;
+  const __half2 x = __hsub2(*reinterpret_cast<const __half2 *>(&biased), __half2half2(__ushort_as_half(0x6408))); // - 1032
+  const __half2 w = __hmul2(x, d);
+  return *reinterpret_cast<const uint32_t *>(&w);
+}
+
+/* QT = NNTR_Q4_K: W is block_q4_Kx8, a stage is one pair of sub-blocks (n_stages = 4 * K/256).
+ * QT = NNTR_Q4_0: W is block_q4_0x8, a stage is two 32-weight blocks (n_stages = K/64). */
+template <int QT>
 __global__ void __launch_bounds__(F16_THREADS, 1)
-gemm_q4_K_f16_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__restrict__ W, float *__restrict__ C, int ldc,
-                     int M, int nb, int m_tiles, int c_vec4) {
+gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ Wb, float *__restrict__ C, int ldc, int M,
+                int n_stages, int m_tiles, int c_vec4) {
   extern __shared__ __align__(128) uint8_t smem[];
   // bars: [0..3] full, [4..7] empty, [8] tile complete
   const uint32_t sbase = smem_u32(smem);
@@ -122,7 +136,6 @@ gemm_q4_K_f16_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__res
   // weights of a stage feed two MMAs, which halves the expansion work per output
   const int mt = 2 * blockIdx.x, nt = blockIdx.y;
   const bool two = mt + 1 < m_tiles;
-  const int n_stages = nb * 4;
 
   if (tid == 0) {
     for (int s = 0; s < F16_STAGES; ++s) {
@@ -148,8 +161,10 @@ gemm_q4_K_f16_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__res
     const int r = tid & (F16_TILE_N - 1); // weight row inside the tile
     const int hsel = tid >> 8;            // which half of the stage's 32 nibble bytes: chunks 2*hsel, 2*hsel + 1
     const int j = r & 7;                  // row inside its 8-row group
-    const BlockQ4Kx8 *wrow = W + (size_t)(nt * (F16_TILE_N / 8) + (r >> 3)) * nb;
     const uint8_t *asrc = atiles + (size_t)mt * n_stages * F16_A_BYTES;
+    bool ok = true;
+    if constexpr (QT == NNTR_Q4_K) {
+    const BlockQ4Kx8 *wrow = reinterpret_cast<const BlockQ4Kx8 *>(Wb) + (size_t)(nt * (F16_TILE_N / 8) + (r >> 3)) * (n_stages / 4);
     uint2 q[2];
 #pragma unroll
     for (int c = 0; c < 2; ++c)
@@ -159,7 +174,6 @@ gemm_q4_K_f16_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__res
 #pragma unroll
     for (int i = 0; i < 6; ++i)
       g[i] = __ldg(reinterpret_cast<const uint32_t *>(wrow->scales) + i);
-    bool ok = true;
     for (int st = 0; st < n_stages && ok; ++st) {
       const int s = st % F16_STAGES, use = st / F16_STAGES;
       float sc0, mn0, sc1, mn1;
@@ -213,6 +227,47 @@ gemm_q4_K_f16_kernel(const uint8_t *__restrict__ atiles, const BlockQ4Kx8 *__res
       dmw = ndmw;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(BAR(s));
+    }
+    } else {
+      const BlockQ40x8 *wrow = reinterpret_cast<const BlockQ40x8 *>(Wb) + (size_t)(nt * (F16_TILE_N / 8) + (r >> 3)) * (n_stages * 2);
+      // this thread expands block 2*st + hsel of the row: 16 nibble bytes = four words = four 16-byte chunks of halves
+      const BlockQ40x8 *blk = wrow + hsel;
+      uint2 qa = ldg_stream_u2(blk->qs + j * 8), qb = ldg_stream_u2(blk->qs + 64 + j * 8);
+      uint16_t dbits = blk->d[j];
+      for (int st = 0; st < n_stages && ok; ++st) {
+        const int s = st % F16_STAGES, use = st / F16_STAGES;
+        const __half2 d2 = __half2half2(__ushort_as_half(dbits));
+        if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        if (tid == 0) {
+          mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
+          bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
+          if (two)
+            bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES + F16_A_BYTES,
+                     asrc + ((size_t)n_stages + st) * F16_A_BYTES, F16_A_BYTES, BAR(s));
+        }
+        uint8_t *wdst = smem + s * F16_STAGE_BYTES + r * 16 + (4 * hsel) * (F16_TILE_N * 16);
+        const uint32_t w[4] = {qa.x ^ 0x88888888u, qa.y ^ 0x88888888u, qb.x ^ 0x88888888u, qb.y ^ 0x88888888u};
+        // the next stage's block travels while this one is expanded; three stages ahead goes to L2
+        const BlockQ40x8 *nblk = wrow + 2 * (st + 1 < n_stages ? st + 1 : st) + hsel;
+        qa = ldg_stream_u2(nblk->qs + j * 8);
+        qb = ldg_stream_u2(nblk->qs + 64 + j * 8);
+        dbits = nblk->d[j];
+        if (j == 0) {
+          const BlockQ40x8 *fblk = wrow + 2 * (st + 3 < n_stages ? st + 3 : n_stages - 1) + hsel;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(fblk));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(fblk) + 128));
+        }
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) // chunk wi: elements 4wi + {0,2,1,3} then 16 + 4wi + {0,2,1,3} of the block
+          *reinterpret_cast<uint4 *>(wdst + wi * (F16_TILE_N * 16)) =
+            make_uint4(expand2_q40(w[wi] & 0x000f000fu, d2), expand2_q40((w[wi] >> 8) & 0x000f000fu, d2),
+                       expand2_q40((w[wi] >> 4) & 0x000f000fu, d2), expand2_q40((w[wi] >> 12) & 0x000f000fu, d2));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(BAR(s));
+      }
     }
     /* ------------------------------ epilogue ------------------------------- */
     if (ok && mbar_wait(BAR(8), 0, abort_flag)) {
@@ -327,6 +382,51 @@ quantize_q8_K_f16_tiles_kernel(const float *__restrict__ x, int64_t ldx, uint8_t
   }
 }
 
+/* Activation tiles for Q4_0 weights: Q8_0 quantization (32-element blocks, fp16 scale; the x86 SIMD form the
+ * reference's GEMM uses), values fp16(fp32(d_a) * q8), same tile geometry. A stage is two blocks; chunk 4h + wi of stage
+ * st holds the elements 4wi + {0,2,1,3} and 16 + 4wi + {0,2,1,3} of block 2 st + h. One warp per (row, 256 elements);
+ * K % 64 == 0, elements at or beyond K belong to no stage. */
+__global__ void __launch_bounds__(256)
+quantize_q8_0_f16_tiles_kernel(const float *__restrict__ x, int64_t ldx, uint8_t *__restrict__ tiles, int M, int Mpad,
+                               int K) {
+  const int lane = threadIdx.x & 31;
+  const int nu = (K + 255) / 256, n_stages = K / 64;
+  const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (unit >= (int64_t)Mpad * nu)
+    return;
+  const int u = (int)(unit / Mpad);
+  const int row = (int)(unit - (int64_t)u * Mpad);
+  const int m = row % F16_TILE_M;
+  const int e0 = u * 256 + lane * 8;
+  const bool valid = e0 < K;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), c = a;
+  if (valid && row < M) {
+    const float *src = x + (int64_t)row * ldx + e0;
+    a = *reinterpret_cast<const float4 *>(src);
+    c = *reinterpret_cast<const float4 *>(src + 4);
+  }
+  const Q80Lane q = q80_quantize_warp(a, c);
+  if (!valid)
+    return;
+  const float d = half_bits_to_float(q.d_bits);
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[i] = __fmul_rn(d, (float)(int)(int8_t)(q.w0 >> (8 * i)));
+    v[4 + i] = __fmul_rn(d, (float)(int)(int8_t)(q.w1 >> (8 * i)));
+  }
+  // lane's elements: block (lane/4) of the unit, e = 8*(lane%4) + i inside it
+  const int st = u * 4 + (lane >> 3), h = (lane >> 2) & 1, hf = (lane & 3) >> 1, wi0 = 2 * (lane & 1);
+  uint8_t *tile = tiles + ((size_t)(row / F16_TILE_M) * n_stages + st) * F16_A_BYTES;
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    const __half2 lo = __floats2half2_rn(v[4 * h2 + 0], v[4 * h2 + 2]);
+    const __half2 hi = __floats2half2_rn(v[4 * h2 + 1], v[4 * h2 + 3]);
+    *reinterpret_cast<uint2 *>(tile + (4 * h + wi0 + h2) * (F16_TILE_M * 16) + m * 16 + hf * 8) =
+      make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+  }
+}
+
 } // namespace
 
 size_t umma_f16_workspace_bytes(unsigned M, unsigned K) {
@@ -334,35 +434,50 @@ size_t umma_f16_workspace_bytes(unsigned M, unsigned K) {
 }
 
 bool umma_f16_supported(int qtype, unsigned M, unsigned N, unsigned K) {
-  return qtype == NNTR_Q4_K && M >= 2 && N % F16_TILE_N == 0 && K % QK_K == 0 && K > 0;
+  if (M < 2 || N % F16_TILE_N || K == 0)
+    return false;
+  return (qtype == NNTR_Q4_K && K % QK_K == 0) || (qtype == NNTR_Q4_0 && K % F16_KS == 0);
 }
 
-int launch_gemm_q4_K_f16(unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C, unsigned ldc,
-                         void *ws, cudaStream_t st) {
+int launch_gemm_f16(int qtype, unsigned M, unsigned N, unsigned K, const float *A, const void *B, float *C, unsigned ldc,
+                    void *ws, cudaStream_t st) {
   static bool attr_set[64] = {};
   int dev = 0;
   NNTR_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemm_q4_K_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F16_SMEM));
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<NNTR_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, F16_SMEM));
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<NNTR_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, F16_SMEM));
     attr_set[dev] = true;
   }
-  const int nb = (int)(K / QK_K);
   const int mtiles = (int)((M + F16_TILE_M - 1) / F16_TILE_M), Mpad = mtiles * F16_TILE_M;
-  const unsigned M4 = (M / 4) * 4;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(ws) & 15))
     return set_error(NNTR_CUDA_ERR_INVALID, "gemm (fp16 tensor path): activations and workspace must be 16-byte aligned");
-  const int64_t nwarps = (int64_t)Mpad * nb;
-  quantize_q8_K_f16_tiles_kernel<<<(unsigned)((nwarps + 7) / 8), 256, 0, st>>>(A, K, static_cast<uint8_t *>(ws), (int)M,
-                                                                             (int)M4, Mpad, nb);
-  count_launch();
-  NNTR_CHECK_CUDA(cudaGetLastError());
   const int c_vec4 = (ldc % 4 == 0) && !(reinterpret_cast<uintptr_t>(C) & 15);
   dim3 grid((mtiles + 1) / 2, N / F16_TILE_N);
-  gemm_q4_K_f16_kernel<<<grid, F16_THREADS, F16_SMEM, st>>>(static_cast<const uint8_t *>(ws),
-                                                            static_cast<const BlockQ4Kx8 *>(B), C, (int)ldc, (int)M, nb,
-                                                            mtiles, c_vec4);
+  const int n_stages = (int)(K / F16_KS);
+  if (qtype == NNTR_Q4_K) {
+    const int nb = (int)(K / QK_K);
+    const unsigned M4 = (M / 4) * 4;
+    const int64_t nwarps = (int64_t)Mpad * nb;
+    quantize_q8_K_f16_tiles_kernel<<<(unsigned)((nwarps + 7) / 8), 256, 0, st>>>(A, K, static_cast<uint8_t *>(ws), (int)M,
+                                                                               (int)M4, Mpad, nb);
+    count_launch();
+    NNTR_CHECK_CUDA(cudaGetLastError());
+    gemm_f16_kernel<NNTR_Q4_K><<<grid, F16_THREADS, F16_SMEM, st>>>(static_cast<const uint8_t *>(ws),
+                                                                    static_cast<const uint8_t *>(B), C, (int)ldc, (int)M,
+                                                                    n_stages, mtiles, c_vec4);
+  } else {
+    const int64_t nwarps = (int64_t)Mpad * ((K + 255) / 256);
+    quantize_q8_0_f16_tiles_kernel<<<(unsigned)((nwarps + 7) / 8), 256, 0, st>>>(A, K, static_cast<uint8_t *>(ws), (int)M,
+                                                                               Mpad, (int)K);
+    count_launch();
+    NNTR_CHECK_CUDA(cudaGetLastError());
+    gemm_f16_kernel<NNTR_Q4_0><<<grid, F16_THREADS, F16_SMEM, st>>>(static_cast<const uint8_t *>(ws),
+                                                                    static_cast<const uint8_t *>(B), C, (int)ldc, (int)M,
+                                                                    n_stages, mtiles, c_vec4);
+  }
   count_launch();
-  return check_cuda(cudaGetLastError(), "gemm_q4_K fp16 tensor-path launch");
+  return check_cuda(cudaGetLastError(), "gemm fp16 tensor-path launch");
 }
 
 int read_f16_status(int *out) {

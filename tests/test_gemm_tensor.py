@@ -139,6 +139,31 @@ def test_fp16_tensor_gemm_strides_padding_and_auto_choice(be, port):
     assert np.array_equal(auto2.view(np.uint32), f16.view(np.uint32))
 
 
+@pytest.mark.parametrize("M,N,K", [(33, 256, 512), (128, 256, 2880), (129, 512, 704), (300, 256, 1280)])
+def test_fp16_tensor_gemm_q4_0_matches_checker(be, port, M, N, K):
+    """Q4_0 weights through the fp16 tensor path (the default from 32 rows up when N % 256 == 0 and K % 64 == 0): Q8_0
+    activations and (q - 8) * d weights as fp16 operands; K = 2880 and 704 are not multiples of 256."""
+    rng = np.random.default_rng(M * 13 + K)
+    B = O.random_q4_0x8(rng, N, K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    A[1, :64] = 0.0
+    want = port.gemm("q4_0", A, B, N)
+    Ad, Bd = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    C = torch.full((M, N), float("nan"), device="cuda")
+    be.set_gemm_path("auto")
+    be.gemm_q4_0(M, N, K, Ad, K, Bd, N, C, N)
+    be.device_status()
+    got = C.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert max_rel(got, want) <= 1e-3
+    be.set_gemm_path("exact")
+    Ce = torch.full((M, N), float("nan"), device="cuda")
+    be.gemm_q4_0(M, N, K, Ad, K, Bd, N, Ce, N)
+    be.set_gemm_path("auto")
+    assert np.array_equal(Ce.cpu().numpy().view(np.uint32), want.view(np.uint32)), "the exact path stays bit-exact"
+    assert not np.array_equal(got.view(np.uint32), want.view(np.uint32)), "auto took the tensor path"
+
+
 def test_int8_peak_measurement_is_plausible(be):
     """The int8 rate the prefill fraction is quoted against: a dense tcgen05 kind::i8 stream on every SM. A B200 is
     specified at 4.5 POP/s dense; anything outside 1.5 .. 6 POP/s means the measurement is not doing the work."""
