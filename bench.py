@@ -438,27 +438,35 @@ def prefill_gemm_shapes(be, torch, dev, steps=10):
         out.append(row)
         del mats, base, A, C, ws
         torch.cuda.empty_cache()
-    # Q4_0 weights, same shapes: the fp16 kernel (its integer form would leave the tensor pipe every 32 of K)
-    for M, N, K in PREFILL_SWEEP:
-        base = torch.from_numpy(O.random_q4_0x8(rng, N, K)).to(dev)
-        mats = [base, torch.roll(base, 4099 * 16), torch.roll(base, 2 * 4099 * 16)]
+    # Q4_0 weights, same shapes: the fp16 kernel (its integer form would leave the tensor pipe every 32 of K);
+    # Q6_K weights on the Qwen3-4B lm_head (N = 151936 ends inside a 256-row tile; 319 MB of weights, one copy)
+    cases = [("q4_0", s) for s in PREFILL_SWEEP] + [("q6_K", (64, 151936, 2560)), ("q6_K", (256, 151936, 2560))]
+    for qt, (M, N, K) in cases:
+        if qt == "q4_0":
+            base = torch.from_numpy(O.random_q4_0x8(rng, N, K)).to(dev)
+            mats = [base, torch.roll(base, 4099 * 16), torch.roll(base, 2 * 4099 * 16)]
+        else:
+            base = torch.from_numpy(O.random_q6_K(rng, 4736, K)).to(dev).reshape(-1).repeat(N // 4736 + 1)
+            base = base[:N * (K // 256) * 210].contiguous()
+            mats = [base]
+        gemm = be.gemm_q4_0 if qt == "q4_0" else be.gemm_q6_K
         A = torch.randn(M, K, device=dev)
         C = torch.empty(M, N, device=dev)
-        ws = torch.empty(be.gemm_workspace_bytes("q4_0", M, N, K), dtype=torch.uint8, device=dev)
+        ws = torch.empty(be.gemm_workspace_bytes(qt, M, N, K), dtype=torch.uint8, device=dev)
         be.set_gemm_path("tensor_f16")
         for W in mats:
-            be.gemm_q4_0(M, N, K, A, K, W, N, C, N, ws)
+            gemm(M, N, K, A, K, W, N, C, N, ws)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             for W in mats:
-                be.gemm_q4_0(M, N, K, A, K, W, N, C, N, ws)
+                gemm(M, N, K, A, K, W, N, C, N, ws)
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (steps * len(mats))
         eff = 2.0 * M * N * K / (us * 1e-6) / 1e12
-        out.append({"M": M, "N": N, "K": K, "qtype": "q4_0",
+        out.append({"M": M, "N": N, "K": K, "qtype": qt,
                     "fp16_path": {"kernel": "tcgen05 kind::f16, fp16 operands", "us_per_call": round(us, 1),
                                   "TFLOP/s": round(eff, 1), "peak_TFLOP/s_burst": peak_f16,
                                   "peak_TFLOP/s_sustained": peak_f16_sus, "peak_source": src,

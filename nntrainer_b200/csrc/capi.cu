@@ -176,7 +176,7 @@ static int pick_gemm_kernel(int qtype, unsigned M, unsigned N, unsigned K) {
   // leave most SMs idle the integer path's 128 x 128 tiles win
   const bool f16_ok = umma_f16_supported(qtype, M, N, K), i8_ok = umma_supported(qtype, M, N, K);
   const unsigned mt = (M + 127) / 128;
-  const unsigned tiles_f16 = ((mt + 1) / 2) * (N / 256);
+  const unsigned tiles_f16 = ((mt + 1) / 2) * ((N + 255) / 256);
   if (f16_ok && (tiles_f16 >= (unsigned)sm_count() / 2 || !i8_ok))
     return 2;
   return i8_ok ? 1 : 0;

@@ -119,11 +119,14 @@ __device__ __forceinline__ uint32_t expand2_q40(uint32_t nib2, __half2 d) {
 }
 
 /* QT = NNTR_Q4_K: W is block_q4_Kx8, a stage is one pair of sub-blocks (n_stages = 4 * K/256).
- * QT = NNTR_Q4_0: W is block_q4_0x8, a stage is two 32-weight blocks (n_stages = K/64). */
+ * QT = NNTR_Q4_0: W is block_q4_0x8, a stage is two 32-weight blocks (n_stages = K/64).
+ * QT = NNTR_Q6_K: W is plain rows of block_q6_K (210 bytes, 2-byte aligned); stage (b, h, s2) of super-block b holds
+ *                 the quarters s2 and s2 + 2 of its 128-element half h (the two quarters that share the bytes ql[64h +
+ *                 32 s2 ..] as low and high nibbles); n_stages = 4 * K/256. N may end inside the last 256-row tile. */
 template <int QT>
 __global__ void __launch_bounds__(F16_THREADS, 1)
 gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ Wb, float *__restrict__ C, int ldc, int M,
-                int n_stages, int m_tiles, int c_vec4) {
+                int N, int n_stages, int m_tiles, int c_vec4) {
   extern __shared__ __align__(128) uint8_t smem[];
   // bars: [0..3] full, [4..7] empty, [8] tile complete
   const uint32_t sbase = smem_u32(smem);
@@ -228,6 +231,78 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(BAR(s));
     }
+    } else if constexpr (QT == NNTR_Q6_K) {
+      const int n_row = nt * F16_TILE_N + r;
+      const bool have_row = n_row < N;
+      const int nb = n_stages / 4;
+      const uint8_t *wrow = Wb + (size_t)(have_row ? n_row : 0) * nb * sizeof(BlockQ6K);
+      // this thread: bytes l = 16*hsel .. +15 of the stage's 32 ql bytes and 32 qh bytes (four words each), read as five
+      // aligned words and funnel-shifted (blocks are 2-byte aligned)
+      uint32_t rl[5], rh[5];
+      uint32_t scd = 0; // the two scales (bytes 0, 1) and d (bytes 2, 3) of the stage
+      auto fetch = [&](int st) {
+        const int b = st >> 2, h = (st >> 1) & 1, s2 = st & 1;
+        const uint8_t *blk = wrow + (size_t)b * sizeof(BlockQ6K);
+        const uint8_t *pl = blk + 64 * h + 32 * s2 + 16 * hsel, *ph = blk + 128 + 32 * h + 16 * hsel;
+        const uint32_t *al = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(pl) & ~(uintptr_t)3);
+        const uint32_t *ah = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(ph) & ~(uintptr_t)3);
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+          rl[k] = __ldg(al + k);
+          rh[k] = __ldg(ah + k);
+        }
+        const uint32_t s_lo = blk[192 + 8 * h + 2 * s2 + hsel], s_hi = blk[192 + 8 * h + 2 * (s2 + 2) + hsel];
+        scd = s_lo | (s_hi << 8) | ((uint32_t) * reinterpret_cast<const uint16_t *>(blk + 208) << 16);
+      };
+      fetch(0);
+      for (int st = 0; st < n_stages && ok; ++st) {
+        const int s = st % F16_STAGES, use = st / F16_STAGES, s2 = st & 1;
+        const uint32_t sh = (uint32_t)((reinterpret_cast<uintptr_t>(wrow) + (size_t)(st >> 2) * sizeof(BlockQ6K)) & 2) * 8;
+        uint32_t ql[4], qh[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          ql[k] = __funnelshift_r(rl[k], rl[k + 1], sh);
+          qh[k] = __funnelshift_r(rh[k], rh[k + 1], sh);
+        }
+        const float d = half_bits_to_float((uint16_t)(scd >> 16));
+        const __half2 d_lo = __float2half2_rn(d * (float)(int)(int8_t)(scd & 0xff));
+        const __half2 d_hi = __float2half2_rn(d * (float)(int)(int8_t)((scd >> 8) & 0xff));
+        if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        if (tid == 0) {
+          mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
+          bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
+          if (two)
+            bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES + F16_A_BYTES,
+                     asrc + ((size_t)n_stages + st) * F16_A_BYTES, F16_A_BYTES, BAR(s));
+        }
+        fetch(st + 1 < n_stages ? st + 1 : st); // the next stage travels while this one is expanded
+        uint8_t *wdst = smem + s * F16_STAGE_BYTES + r * 16 + (4 * hsel) * (F16_TILE_N * 16);
+        const __half2 off = __half2half2(__ushort_as_half(0x6420)); // 1024 + 32
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t l = ql[i], hq = qh[i];
+          // two high bits of the 6-bit value: qh bits (2 s2, 2 s2 + 1) for the low-nibble quarter, (2 s2 + 4, + 5) for the
+          // high-nibble quarter, moved to bits 4-5 of each half
+          const uint32_t hl02 = (s2 ? (hq << 2) : (hq << 4)) & 0x00300030u, hl13 = (s2 ? (hq >> 6) : (hq >> 4)) & 0x00300030u;
+          const uint32_t hh02 = (s2 ? (hq >> 2) : hq) & 0x00300030u, hh13 = (s2 ? (hq >> 10) : (hq >> 8)) & 0x00300030u;
+          const uint32_t t0 = (l & 0x000f000fu) | hl02 | 0x64006400u, t1 = ((l >> 8) & 0x000f000fu) | hl13 | 0x64006400u;
+          const uint32_t t2 = ((l >> 4) & 0x000f000fu) | hh02 | 0x64006400u, t3 = ((l >> 12) & 0x000f000fu) | hh13 | 0x64006400u;
+          const __half2 w0 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t0), off), d_lo);
+          const __half2 w1 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t1), off), d_lo);
+          const __half2 w2 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t2), off), d_hi);
+          const __half2 w3 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t3), off), d_hi);
+          uint4 o = make_uint4(*reinterpret_cast<const uint32_t *>(&w0), *reinterpret_cast<const uint32_t *>(&w1),
+                               *reinterpret_cast<const uint32_t *>(&w2), *reinterpret_cast<const uint32_t *>(&w3));
+          if (!have_row)
+            o = make_uint4(0u, 0u, 0u, 0u); // rows beyond N: zero weights (their columns are not stored either)
+          *reinterpret_cast<uint4 *>(wdst + i * (F16_TILE_N * 16)) = o;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(BAR(s));
+      }
     } else {
       const BlockQ40x8 *wrow = reinterpret_cast<const BlockQ40x8 *>(Wb) + (size_t)(nt * (F16_TILE_N / 8) + (r >> 3)) * (n_stages * 2);
       // this thread expands block 2*st + hsel of the row: 16 nibble bytes = four words = four 16-byte chunks of halves
@@ -282,7 +357,8 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
           uint32_t v[16];
           tmem_ld16(trow + ch * 16, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (row < M) {
+          const int col0 = nt * F16_TILE_N + cg * 64 + ch * 16;
+          if (row < M && col0 + 16 <= N) {
             if (c_vec4) {
 #pragma unroll
               for (int i = 0; i < 16; i += 4)
@@ -294,6 +370,11 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
               for (int i = 0; i < 16; ++i)
                 dst[ch * 16 + i] = __uint_as_float(v[i]);
             }
+          } else if (row < M) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (col0 + i < N)
+                dst[ch * 16 + i] = __uint_as_float(v[i]);
           }
         }
       }
@@ -346,7 +427,7 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
  * the 4-row quantizer's sign rule). Rows at or beyond M are zero. One warp per (row, super-block). */
 __global__ void __launch_bounds__(256)
 quantize_q8_K_f16_tiles_kernel(const float *__restrict__ x, int64_t ldx, uint8_t *__restrict__ tiles, int M, int M4,
-                               int Mpad, int nb) {
+                               int Mpad, int nb, int q6_order) {
   const int lane = threadIdx.x & 31;
   const int64_t blk = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (blk >= (int64_t)Mpad * nb)
@@ -371,7 +452,14 @@ quantize_q8_K_f16_tiles_kernel(const float *__restrict__ x, int64_t ldx, uint8_t
       v[i] = 0.f;
   }
   // lane's elements 8*lane + i: p = lane/8, half = (lane%8)/4, wi = 2*(lane%4) + i/4, position j = i%4 -> slot {0,2,1,3}
-  const int p = lane >> 3, hf = (lane & 7) >> 2, wi0 = 2 * (lane & 3);
+  int p = lane >> 3, hf = (lane & 7) >> 2, wi0 = 2 * (lane & 3);
+  if (q6_order) {
+    // Q6_K stages: element e = 8*lane + i: half h = lane/16, quarter w = (lane%16)/4, l = 8*(lane%4) + i inside it;
+    // stage 2h + w%2, slot half w/2, chunk 4*(l/16) + (l%16)/4
+    p = 2 * (lane >> 4) + ((lane >> 2) & 1);
+    hf = (lane >> 3) & 1;
+    wi0 = 4 * ((lane >> 1) & 1) + 2 * (lane & 1);
+  }
   uint8_t *tile = tiles + ((size_t)(row / F16_TILE_M) * (nb * 4) + (size_t)b * 4 + p) * F16_A_BYTES;
 #pragma unroll
   for (int h2 = 0; h2 < 2; ++h2) {
@@ -434,7 +522,11 @@ size_t umma_f16_workspace_bytes(unsigned M, unsigned K) {
 }
 
 bool umma_f16_supported(int qtype, unsigned M, unsigned N, unsigned K) {
-  if (M < 2 || N % F16_TILE_N || K == 0)
+  if (M < 2 || K == 0 || N == 0)
+    return false;
+  if (qtype == NNTR_Q6_K) // plain rows: any N; the last tile may be ragged
+    return K % QK_K == 0;
+  if (N % F16_TILE_N)
     return false;
   return (qtype == NNTR_Q4_K && K % QK_K == 0) || (qtype == NNTR_Q4_0 && K % F16_KS == 0);
 }
@@ -447,25 +539,33 @@ int launch_gemm_f16(int qtype, unsigned M, unsigned N, unsigned K, const float *
   if (dev < 64 && !attr_set[dev]) {
     NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<NNTR_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, F16_SMEM));
     NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<NNTR_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, F16_SMEM));
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemm_f16_kernel<NNTR_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, F16_SMEM));
     attr_set[dev] = true;
   }
   const int mtiles = (int)((M + F16_TILE_M - 1) / F16_TILE_M), Mpad = mtiles * F16_TILE_M;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(ws) & 15))
     return set_error(NNTR_CUDA_ERR_INVALID, "gemm (fp16 tensor path): activations and workspace must be 16-byte aligned");
   const int c_vec4 = (ldc % 4 == 0) && !(reinterpret_cast<uintptr_t>(C) & 15);
-  dim3 grid((mtiles + 1) / 2, N / F16_TILE_N);
+  dim3 grid((mtiles + 1) / 2, (N + F16_TILE_N - 1) / F16_TILE_N);
   const int n_stages = (int)(K / F16_KS);
-  if (qtype == NNTR_Q4_K) {
+  if (qtype == NNTR_Q4_K || qtype == NNTR_Q6_K) {
     const int nb = (int)(K / QK_K);
-    const unsigned M4 = (M / 4) * 4;
+    // Q4_K: rows below 4*floor(M/4) with the 4-row quantizer's sign rule; Q6_K: the row quantizer for every row
+    // (ggml_interface_omp.cpp:545-551)
+    const unsigned M4 = qtype == NNTR_Q4_K ? (M / 4) * 4 : 0;
     const int64_t nwarps = (int64_t)Mpad * nb;
     quantize_q8_K_f16_tiles_kernel<<<(unsigned)((nwarps + 7) / 8), 256, 0, st>>>(A, K, static_cast<uint8_t *>(ws), (int)M,
-                                                                               (int)M4, Mpad, nb);
+                                                                               (int)M4, Mpad, nb, qtype == NNTR_Q6_K);
     count_launch();
     NNTR_CHECK_CUDA(cudaGetLastError());
-    gemm_f16_kernel<NNTR_Q4_K><<<grid, F16_THREADS, F16_SMEM, st>>>(static_cast<const uint8_t *>(ws),
-                                                                    static_cast<const uint8_t *>(B), C, (int)ldc, (int)M,
-                                                                    n_stages, mtiles, c_vec4);
+    if (qtype == NNTR_Q4_K)
+      gemm_f16_kernel<NNTR_Q4_K><<<grid, F16_THREADS, F16_SMEM, st>>>(static_cast<const uint8_t *>(ws),
+                                                                      static_cast<const uint8_t *>(B), C, (int)ldc, (int)M,
+                                                                      (int)N, n_stages, mtiles, c_vec4);
+    else
+      gemm_f16_kernel<NNTR_Q6_K><<<grid, F16_THREADS, F16_SMEM, st>>>(static_cast<const uint8_t *>(ws),
+                                                                      static_cast<const uint8_t *>(B), C, (int)ldc, (int)M,
+                                                                      (int)N, n_stages, mtiles, c_vec4);
   } else {
     const int64_t nwarps = (int64_t)Mpad * ((K + 255) / 256);
     quantize_q8_0_f16_tiles_kernel<<<(unsigned)((nwarps + 7) / 8), 256, 0, st>>>(A, K, static_cast<uint8_t *>(ws), (int)M,
@@ -474,7 +574,7 @@ int launch_gemm_f16(int qtype, unsigned M, unsigned N, unsigned K, const float *
     NNTR_CHECK_CUDA(cudaGetLastError());
     gemm_f16_kernel<NNTR_Q4_0><<<grid, F16_THREADS, F16_SMEM, st>>>(static_cast<const uint8_t *>(ws),
                                                                     static_cast<const uint8_t *>(B), C, (int)ldc, (int)M,
-                                                                    n_stages, mtiles, c_vec4);
+                                                                    (int)N, n_stages, mtiles, c_vec4);
   }
   count_launch();
   return check_cuda(cudaGetLastError(), "gemm fp16 tensor-path launch");

@@ -69,5 +69,5 @@ def test_workspace_sizes(L):
     assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_K, 129, 4224, 256) == 2 * (32768 + 2560)
     assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_0, 64, 4096, 4096) == 128 * 4096 * 2  # fp16 tiles (N % 256 == 0)
     assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_0, 64, 4104, 4096) == 64 * 128 * 34
-    assert L.nntr_cuda_gemm_workspace_bytes(capi.Q6_K, 3, 8, 2560) == 3 * 10 * 292
+    assert L.nntr_cuda_gemm_workspace_bytes(capi.Q6_K, 3, 8, 2560) == 128 * 2560 * 2  # fp16 tiles (any N)
     assert L.nntr_cuda_set_gemm_path(7) == capi.ERR_INVALID and L.nntr_cuda_set_gemm_path(0) == 0

@@ -164,6 +164,34 @@ def test_fp16_tensor_gemm_q4_0_matches_checker(be, port, M, N, K):
     assert not np.array_equal(got.view(np.uint32), want.view(np.uint32)), "auto took the tensor path"
 
 
+@pytest.mark.parametrize("M,N,K", [(33, 256, 512), (64, 300, 256), (129, 1000, 768), (300, 514, 1280), (40, 97, 2560)])
+def test_fp16_tensor_gemm_q6_K_matches_checker(be, port, M, N, K):
+    """Q6_K weights (plain 210-byte rows) through the fp16 tensor path: (q - 32) * fp16(d * scale) weights, Q8_K
+    activations of the row quantizer. N need not be a multiple of the 256-row tile: rows past N are zero operands and
+    their columns are never stored (the padding of C must survive)."""
+    rng = np.random.default_rng(M * 17 + N)
+    B = O.random_q6_K(rng, N, K)
+    A = acts(rng, max(M, 4), K)[:M]
+    want = port.gemm("q6_K", A, B, N)
+    Ad, Bd = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    ldc = N + 3
+    C = torch.full((M, ldc), float("nan"), device="cuda")
+    be.set_gemm_path("auto")
+    be.gemm_q6_K(M, N, K, Ad, K, Bd, N, C, ldc)
+    be.device_status()
+    got = C.cpu().numpy()
+    assert np.isnan(got[:, N:]).all(), "columns beyond N are left alone"
+    got = got[:, :N]
+    assert np.isfinite(got).all()
+    assert max_rel(got, want) <= 1e-3
+    be.set_gemm_path("exact")
+    Ce = torch.full((M, N), float("nan"), device="cuda")
+    be.gemm_q6_K(M, N, K, Ad, K, Bd, N, Ce, N)
+    be.set_gemm_path("auto")
+    assert np.array_equal(Ce.cpu().numpy().view(np.uint32), want.view(np.uint32)), "the exact path stays bit-exact"
+    assert not np.array_equal(got.view(np.uint32), want.view(np.uint32)), "auto took the tensor path"
+
+
 def test_int8_peak_measurement_is_plausible(be):
     """The int8 rate the prefill fraction is quoted against: a dense tcgen05 kind::i8 stream on every SM. A B200 is
     specified at 4.5 POP/s dense; anything outside 1.5 .. 6 POP/s means the measurement is not doing the work."""
