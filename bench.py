@@ -711,6 +711,15 @@ def run_case(args):
         be.set_gemm_path("tensor" if args.case == "prefill" else "tensor_f16")
         call = lambda: be.gemm_q4_K(M, N, K, A, K, W, N, C, N, ws)
         work = {"case": args.case, "M": M, "N": N, "K": K, "qtype": "q4_K", "ops": 2.0 * M * N * K}
+    elif args.case == "lm_head_prefill":
+        M, N, K = 256, 151936, 2560
+        W = torch.from_numpy(O.random_q6_K(rng, N, K)).to(dev)
+        A = torch.randn(M, K, device=dev)
+        C = torch.empty(M, N, device=dev)
+        ws = torch.empty(be.gemm_workspace_bytes("q6_K", M, N, K), dtype=torch.uint8, device=dev)
+        be.set_gemm_path("tensor_f16")
+        call = lambda: be.gemm_q6_K(M, N, K, A, K, W, N, C, N, ws)
+        work = {"case": args.case, "M": M, "N": N, "K": K, "qtype": "q6_K", "ops": 2.0 * M * N * K}
     elif args.case == "moe_layer":
         H, I, E, k = 2048, 768, 128, 8
         mk = lambda n, kk: torch.from_numpy(O.random_q4_Kx8(rng, n, kk)).to(dev)
@@ -757,7 +766,7 @@ def main():
     ap.add_argument("--ring", type=int, default=RING, help="distinct weight matrices per step (default keeps every launch out of L2)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the GEMV kernel from an ncu capture (reported as roofline.traffic)")
-    ap.add_argument("--case", default=None, choices=["prefill", "prefill_f16", "lm_head", "moe_layer"],
+    ap.add_argument("--case", default=None, choices=["prefill", "prefill_f16", "lm_head", "lm_head_prefill", "moe_layer"],
                     help="run one small single-kernel case (profiler captures) instead of the benchmark")
     args = ap.parse_args()
     globals()["RING"] = args.ring

@@ -142,7 +142,7 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
 
   if (tid == 0) {
     for (int s = 0; s < F16_STAGES; ++s) {
-      mbar_init(BAR(s), F16_PRODUCERS + 1); // every producer thread + the one that armed the activation copy
+      mbar_init(BAR(s), F16_PRODUCERS / 32 + 1); // every producer warp + the thread that armed the activation copy
       mbar_init(BAR(4 + s), 1);             // MMAs of the stage retired
     }
     mbar_init(BAR(8), 1);
@@ -184,10 +184,11 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
       scale_min_row(g[3], g[4], g[5], j, sc1, mn1);
       const __half2 d_lo = __float2half2_rn(dw * sc0), d_hi = __float2half2_rn(dw * sc1);
       const __half2 m_lo = __float2half2_rn(-(dmw * mn0)), m_hi = __float2half2_rn(-(dmw * mn1));
-      if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag)) {
+      if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag))
         ok = false;
+      ok = __all_sync(0xffffffffu, ok); // the warp leaves together: its lanes meet at the arrive below
+      if (!ok)
         break;
-      }
       if (tid == 0) {
         mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
         bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
@@ -229,79 +230,90 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
       dw = ndw;
       dmw = ndmw;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(BAR(s));
+      __syncwarp(); // every lane's writes are fenced; one arrival per warp keeps the barrier word off the critical path
+      if (lane == 0)
+        mbar_arrive(BAR(s));
     }
     } else if constexpr (QT == NNTR_Q6_K) {
       const int n_row = nt * F16_TILE_N + r;
-      const bool have_row = n_row < N;
-      const int nb = n_stages / 4;
+      const bool have_row = n_row < N; // rows beyond N: scale 0, so zero weights (their columns are not stored either)
+      const int nb = n_stages / 4, n_groups = n_stages / 2;
       const uint8_t *wrow = Wb + (size_t)(have_row ? n_row : 0) * nb * sizeof(BlockQ6K);
-      // this thread: bytes l = 16*hsel .. +15 of the stage's 32 ql bytes and 32 qh bytes (four words each), read as five
-      // aligned words and funnel-shifted (blocks are 2-byte aligned)
-      uint32_t rl[5], rh[5];
-      uint32_t scd = 0; // the two scales (bytes 0, 1) and d (bytes 2, 3) of the stage
-      auto fetch = [&](int st) {
-        const int b = st >> 2, h = (st >> 1) & 1, s2 = st & 1;
+      // A group is the two stages of one half h of a super-block: they share the 32 qh bytes. This thread: bytes
+      // 16*hsel .. +15 of each stage's 32 ql bytes and of the qh bytes, each read as five aligned words and
+      // funnel-shifted (blocks are 2-byte aligned), the four scales of its 16-element slices, and d.
+      uint32_t rl[2][5], rh[5], rs = 0, rd = 0;
+      auto fetch = [&](int g) {
+        const int b = g >> 1, h = g & 1;
         const uint8_t *blk = wrow + (size_t)b * sizeof(BlockQ6K);
-        const uint8_t *pl = blk + 64 * h + 32 * s2 + 16 * hsel, *ph = blk + 128 + 32 * h + 16 * hsel;
-        const uint32_t *al = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(pl) & ~(uintptr_t)3);
-        const uint32_t *ah = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(ph) & ~(uintptr_t)3);
+        const uint32_t *al =
+          reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(blk + 64 * h + 16 * hsel) & ~(uintptr_t)3);
+        const uint32_t *ah =
+          reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(blk + 128 + 32 * h + 16 * hsel) & ~(uintptr_t)3);
 #pragma unroll
         for (int k = 0; k < 5; ++k) {
-          rl[k] = __ldg(al + k);
+          rl[0][k] = __ldg(al + k);
+          rl[1][k] = __ldg(al + 8 + k);
           rh[k] = __ldg(ah + k);
         }
-        const uint32_t s_lo = blk[192 + 8 * h + 2 * s2 + hsel], s_hi = blk[192 + 8 * h + 2 * (s2 + 2) + hsel];
-        scd = s_lo | (s_hi << 8) | ((uint32_t) * reinterpret_cast<const uint16_t *>(blk + 208) << 16);
+        const uint8_t *sc = blk + 192 + 8 * h + hsel; // scale of quarter w: sc[2 w]
+        rs = (uint32_t)__ldg(sc) | ((uint32_t)__ldg(sc + 2) << 8) | ((uint32_t)__ldg(sc + 4) << 16) | ((uint32_t)__ldg(sc + 6) << 24);
+        rd = __ldg(reinterpret_cast<const uint16_t *>(blk + 208));
       };
       fetch(0);
-      for (int st = 0; st < n_stages && ok; ++st) {
-        const int s = st % F16_STAGES, use = st / F16_STAGES, s2 = st & 1;
-        const uint32_t sh = (uint32_t)((reinterpret_cast<uintptr_t>(wrow) + (size_t)(st >> 2) * sizeof(BlockQ6K)) & 2) * 8;
-        uint32_t ql[4], qh[4];
+      for (int g = 0; g < n_groups && ok; ++g) {
+        const uint32_t sh = (uint32_t)((reinterpret_cast<uintptr_t>(wrow) + (size_t)(g >> 1) * sizeof(BlockQ6K)) & 2) * 8;
+        uint32_t ql[2][4], qh[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          ql[k] = __funnelshift_r(rl[k], rl[k + 1], sh);
+          ql[0][k] = __funnelshift_r(rl[0][k], rl[0][k + 1], sh);
+          ql[1][k] = __funnelshift_r(rl[1][k], rl[1][k + 1], sh);
           qh[k] = __funnelshift_r(rh[k], rh[k + 1], sh);
         }
-        const float d = half_bits_to_float((uint16_t)(scd >> 16));
-        const __half2 d_lo = __float2half2_rn(d * (float)(int)(int8_t)(scd & 0xff));
-        const __half2 d_hi = __float2half2_rn(d * (float)(int)(int8_t)((scd >> 8) & 0xff));
-        if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag)) {
-          ok = false;
-          break;
-        }
-        if (tid == 0) {
-          mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
-          bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
-          if (two)
-            bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES + F16_A_BYTES,
-                     asrc + ((size_t)n_stages + st) * F16_A_BYTES, F16_A_BYTES, BAR(s));
-        }
-        fetch(st + 1 < n_stages ? st + 1 : st); // the next stage travels while this one is expanded
-        uint8_t *wdst = smem + s * F16_STAGE_BYTES + r * 16 + (4 * hsel) * (F16_TILE_N * 16);
-        const __half2 off = __half2half2(__ushort_as_half(0x6420)); // 1024 + 32
+        const float d = have_row ? half_bits_to_float((uint16_t)rd) : 0.f;
+        const uint32_t scs = rs;
+        fetch(g + 1 < n_groups ? g + 1 : g); // the next group travels while this one is expanded
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t l = ql[i], hq = qh[i];
-          // two high bits of the 6-bit value: qh bits (2 s2, 2 s2 + 1) for the low-nibble quarter, (2 s2 + 4, + 5) for the
-          // high-nibble quarter, moved to bits 4-5 of each half
-          const uint32_t hl02 = (s2 ? (hq << 2) : (hq << 4)) & 0x00300030u, hl13 = (s2 ? (hq >> 6) : (hq >> 4)) & 0x00300030u;
-          const uint32_t hh02 = (s2 ? (hq >> 2) : hq) & 0x00300030u, hh13 = (s2 ? (hq >> 10) : (hq >> 8)) & 0x00300030u;
-          const uint32_t t0 = (l & 0x000f000fu) | hl02 | 0x64006400u, t1 = ((l >> 8) & 0x000f000fu) | hl13 | 0x64006400u;
-          const uint32_t t2 = ((l >> 4) & 0x000f000fu) | hh02 | 0x64006400u, t3 = ((l >> 12) & 0x000f000fu) | hh13 | 0x64006400u;
-          const __half2 w0 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t0), off), d_lo);
-          const __half2 w1 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t1), off), d_lo);
-          const __half2 w2 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t2), off), d_hi);
-          const __half2 w3 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t3), off), d_hi);
-          uint4 o = make_uint4(*reinterpret_cast<const uint32_t *>(&w0), *reinterpret_cast<const uint32_t *>(&w1),
-                               *reinterpret_cast<const uint32_t *>(&w2), *reinterpret_cast<const uint32_t *>(&w3));
-          if (!have_row)
-            o = make_uint4(0u, 0u, 0u, 0u); // rows beyond N: zero weights (their columns are not stored either)
-          *reinterpret_cast<uint4 *>(wdst + i * (F16_TILE_N * 16)) = o;
+        for (int s2 = 0; s2 < 2; ++s2) {
+          const int st = 2 * g + s2, s = st % F16_STAGES, use = st / F16_STAGES;
+          const __half2 d_lo = __float2half2_rn(d * (float)(int)(int8_t)(scs >> (8 * s2)));
+          const __half2 d_hi = __float2half2_rn(d * (float)(int)(int8_t)(scs >> (8 * s2 + 16)));
+          if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag))
+            ok = false;
+          ok = __all_sync(0xffffffffu, ok); // the warp leaves together: its lanes meet at the arrive below
+          if (!ok)
+            break;
+          if (tid == 0) {
+            mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
+            bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
+            if (two)
+              bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES + F16_A_BYTES,
+                       asrc + ((size_t)n_stages + st) * F16_A_BYTES, F16_A_BYTES, BAR(s));
+          }
+          uint8_t *wdst = smem + s * F16_STAGE_BYTES + r * 16 + (4 * hsel) * (F16_TILE_N * 16);
+          const __half2 off = __half2half2(__ushort_as_half(0x6420)); // 1024 + 32
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t l = ql[s2][i], hq = qh[i];
+            // the 6-bit values as bytes: low nibbles + qh bits (2 s2, 2 s2 + 1) for quarter s2, high nibbles + qh bits
+            // (2 s2 + 4, + 5) for quarter s2 + 2; a byte permute with 0x64 makes (1024 + q) halves: elements {0, 2}, {1, 3}
+            const uint32_t qlo = (l & 0x0f0f0f0fu) | ((hq << (4 - 2 * s2)) & 0x30303030u);
+            const uint32_t qhi = ((l >> 4) & 0x0f0f0f0fu) | ((hq >> (2 * s2)) & 0x30303030u);
+            const uint32_t t0 = __byte_perm(qlo, 0x64646464u, 0x4240), t1 = __byte_perm(qlo, 0x64646464u, 0x4341);
+            const uint32_t t2 = __byte_perm(qhi, 0x64646464u, 0x4240), t3 = __byte_perm(qhi, 0x64646464u, 0x4341);
+            const __half2 w0 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t0), off), d_lo);
+            const __half2 w1 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t1), off), d_lo);
+            const __half2 w2 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t2), off), d_hi);
+            const __half2 w3 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&t3), off), d_hi);
+            *reinterpret_cast<uint4 *>(wdst + i * (F16_TILE_N * 16)) =
+              make_uint4(*reinterpret_cast<const uint32_t *>(&w0), *reinterpret_cast<const uint32_t *>(&w1),
+                         *reinterpret_cast<const uint32_t *>(&w2), *reinterpret_cast<const uint32_t *>(&w3));
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp(); // every lane's writes are fenced; one arrival per warp keeps the barrier word off the critical path
+          if (lane == 0)
+            mbar_arrive(BAR(s));
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(BAR(s));
       }
     } else {
       const BlockQ40x8 *wrow = reinterpret_cast<const BlockQ40x8 *>(Wb) + (size_t)(nt * (F16_TILE_N / 8) + (r >> 3)) * (n_stages * 2);
@@ -312,10 +324,11 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
       for (int st = 0; st < n_stages && ok; ++st) {
         const int s = st % F16_STAGES, use = st / F16_STAGES;
         const __half2 d2 = __half2half2(__ushort_as_half(dbits));
-        if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag)) {
+        if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag))
           ok = false;
+        ok = __all_sync(0xffffffffu, ok); // the warp leaves together: its lanes meet at the arrive below
+        if (!ok)
           break;
-        }
         if (tid == 0) {
           mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
           bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
@@ -341,7 +354,9 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
             make_uint4(expand2_q40(w[wi] & 0x000f000fu, d2), expand2_q40((w[wi] >> 8) & 0x000f000fu, d2),
                        expand2_q40((w[wi] >> 4) & 0x000f000fu, d2), expand2_q40((w[wi] >> 12) & 0x000f000fu, d2));
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(BAR(s));
+        __syncwarp(); // every lane's writes are fenced; one arrival per warp keeps the barrier word off the critical path
+        if (lane == 0)
+          mbar_arrive(BAR(s));
       }
     }
     /* ------------------------------ epilogue ------------------------------- */
