@@ -105,7 +105,8 @@ size_t nntr_cuda_gemm_workspace_bytes(int qtype, unsigned M, unsigned N, unsigne
  *   TENSOR      tcgen05 int8 tensor-core kernel (needs N % 128 == 0): exact
  *               integer sums, one rounding more per super-block in the fp32
  *               combination (measured 1e-6 from the CPU result);
- *   TENSOR_F16  tcgen05 fp16 tensor-core kernel (needs N % 256 == 0): weights
+ *   TENSOR_F16  tcgen05 fp16 tensor-core kernel (Q4_K and Q4_0 weights need
+ *               N % 256 == 0, Q6_K weights take any N): weights
  *               and quantized activations are dequantized to fp16 operands, the
  *               products summed in fp32 (measured 4e-4 from the CPU result; the
  *               path's stated tolerance is max-rel 2e-3); the fastest;

@@ -261,9 +261,15 @@ def test_gemm_matches_checker(be, port, q, gen, M):
     A = acts(rng, M, K)
     want = port.gemm(q, A, B, N)
     C = torch.full((M, N), float("nan"), device="cuda")
-    getattr(be, f"gemm_{q}")(M, N, K, dev(A), K, dev(B), N, C, N)
+    getattr(be, f"gemm_{q}")(M, N, K, dev(A), K, dev(B), N, C, N)  # default path (tensor cores from 32 rows up where they apply)
+    assert max_rel(C.cpu().numpy(), want) <= REL_TOL
+    be.set_gemm_path("exact")
+    try:
+        C.fill_(float("nan"))
+        getattr(be, f"gemm_{q}")(M, N, K, dev(A), K, dev(B), N, C, N)
+    finally:
+        be.set_gemm_path("auto")
     got = C.cpu().numpy()
-    assert max_rel(got, want) <= REL_TOL
     assert np.array_equal(bits(got), bits(want)), "dp4a GEMM is expected to reproduce the reference bit for bit"
 
 
