@@ -33,11 +33,12 @@
  *               logic op each ((w >> s) & 0x000F000F | 0x64006400 is
  *               (1024 + n_lo, 1024 + n_hi)), so the K order inside a stage is
  *               the order that unpack produces; the activation tiles are written
- *               in the same order (a dot product does not care). The thread
- *               that ends up first also starts the bulk copy of the activation
- *               stage. After the last stage the same warps are the epilogue:
- *               tcgen05.ld of the tile, float4 stores of C.
+ *               in the same order (a dot product does not care). After the
+ *               last stage the same warps are the epilogue: tcgen05.ld of the
+ *               tile, float4 stores of C.
  *   warp 16     one thread issues 8 MMAs (128 x 256 x 16) per stage.
+ *   warp 17     one thread starts the bulk copies of the activation stages, each
+ *               as soon as the MMAs that read its slot have retired.
  * Three stages of 64 KB, both accumulators (512 columns) in tensor memory. Every wait is bounded (pipeline.cuh).
  */
 #include "common.cuh"
@@ -58,7 +59,8 @@ constexpr int F16_STAGE_BYTES = F16_W_BYTES + 2 * F16_A_BYTES; // weights + two 
 constexpr int F16_STAGES = 3;
 constexpr int F16_PRODUCERS = 512; // two per weight row
 constexpr int F16_MMA_WARP = F16_PRODUCERS / 32;
-constexpr int F16_THREADS = (F16_MMA_WARP + 1) * 32; // 544
+constexpr int F16_COPY_WARP = F16_MMA_WARP + 1;
+constexpr int F16_THREADS = (F16_COPY_WARP + 1) * 32; // 576
 constexpr int F16_OFF_BARS = F16_STAGES * F16_STAGE_BYTES;
 constexpr int F16_SMEM = F16_OFF_BARS + 128;
 constexpr uint32_t F16_POLLS = 1u << 22;
@@ -142,7 +144,7 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
 
   if (tid == 0) {
     for (int s = 0; s < F16_STAGES; ++s) {
-      mbar_init(BAR(s), F16_PRODUCERS / 32 + 1); // every producer warp + the thread that armed the activation copy
+      mbar_init(BAR(s), F16_PRODUCERS / 32 + 1); // every producer warp + the copy warp's thread that armed the activation copy
       mbar_init(BAR(4 + s), 1);             // MMAs of the stage retired
     }
     mbar_init(BAR(8), 1);
@@ -164,60 +166,56 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
     const int r = tid & (F16_TILE_N - 1); // weight row inside the tile
     const int hsel = tid >> 8;            // which half of the stage's 32 nibble bytes: chunks 2*hsel, 2*hsel + 1
     const int j = r & 7;                  // row inside its 8-row group
-    const uint8_t *asrc = atiles + (size_t)mt * n_stages * F16_A_BYTES;
     bool ok = true;
     if constexpr (QT == NNTR_Q4_K) {
     const BlockQ4Kx8 *wrow = reinterpret_cast<const BlockQ4Kx8 *>(Wb) + (size_t)(nt * (F16_TILE_N / 8) + (r >> 3)) * (n_stages / 4);
-    uint2 q[2];
+    // A stage's inputs in registers: this thread's 16 nibble bytes (two 8-byte chunks), the two 12-byte scale groups of
+    // the stage (sub-blocks 2p: low nibbles, 2p+1: high nibbles), d and dmin of the row. Two such sets rotate, so a
+    // stage's loads are issued two stages before they are used: one stage alone does not cover the L2 latency.
+    struct StageIn {
+      uint2 q[2];
+      uint32_t g[6];
+      float dw, dmw;
+    };
+    auto fetch = [&](StageIn &in, int st) {
+      const BlockQ4Kx8 *blk = wrow + (st >> 2);
+      const uint8_t *nq = blk->qs + ((st & 3) * 32 + 16 * hsel + j) * 8;
 #pragma unroll
-    for (int c = 0; c < 2; ++c)
-      q[c] = ldg_stream_u2(wrow->qs + ((2 * hsel + c) * 8 + j) * 8);
-    float dw = half_bits_to_float(wrow->d[j]), dmw = half_bits_to_float(wrow->dmin[j]);
-    uint32_t g[6]; // the two 12-byte scale groups of the stage: sub-blocks 2p (low nibbles) and 2p+1 (high nibbles)
-#pragma unroll
-    for (int i = 0; i < 6; ++i)
-      g[i] = __ldg(reinterpret_cast<const uint32_t *>(wrow->scales) + i);
-    for (int st = 0; st < n_stages && ok; ++st) {
-      const int s = st % F16_STAGES, use = st / F16_STAGES;
-      float sc0, mn0, sc1, mn1;
-      scale_min_row(g[0], g[1], g[2], j, sc0, mn0);
-      scale_min_row(g[3], g[4], g[5], j, sc1, mn1);
-      const __half2 d_lo = __float2half2_rn(dw * sc0), d_hi = __float2half2_rn(dw * sc1);
-      const __half2 m_lo = __float2half2_rn(-(dmw * mn0)), m_hi = __float2half2_rn(-(dmw * mn1));
-      if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag))
-        ok = false;
-      ok = __all_sync(0xffffffffu, ok); // the warp leaves together: its lanes meet at the arrive below
-      if (!ok)
-        break;
-      if (tid == 0) {
-        mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
-        bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
-        if (two)
-          bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES + F16_A_BYTES,
-                   asrc + ((size_t)n_stages + st) * F16_A_BYTES, F16_A_BYTES, BAR(s));
-      }
-      uint8_t *wdst = smem + s * F16_STAGE_BYTES + r * 16;
-      // the next stage's nibbles travel while these are expanded
-      const int nst = st + 1 < n_stages ? st + 1 : st;
-      const uint8_t *nq = wrow[nst >> 2].qs + ((nst & 3) * 32 + 16 * hsel + j) * 8;
-      const float ndw = half_bits_to_float(wrow[nst >> 2].d[j]), ndmw = half_bits_to_float(wrow[nst >> 2].dmin[j]);
+      for (int c = 0; c < 2; ++c)
+        in.q[c] = ldg_stream_u2(nq + c * 64);
 #pragma unroll
       for (int i = 0; i < 6; ++i)
-        g[i] = __ldg(reinterpret_cast<const uint32_t *>(wrow[nst >> 2].scales + 24 * (nst & 3)) + i);
-      { // weights are read once from HBM: pull the lines of three stages ahead into L2 so that the loads above hit it
-        const int fst = st + 3 < n_stages ? st + 3 : n_stages - 1;
+        in.g[i] = __ldg(reinterpret_cast<const uint32_t *>(blk->scales + 24 * (st & 3)) + i);
+      in.dw = half_bits_to_float(blk->d[j]);
+      in.dmw = half_bits_to_float(blk->dmin[j]);
+    };
+    auto stage = [&](StageIn &in, int st) {
+      const int s = st % F16_STAGES, use = st / F16_STAGES;
+      float sc0, mn0, sc1, mn1;
+      scale_min_row(in.g[0], in.g[1], in.g[2], j, sc0, mn0);
+      scale_min_row(in.g[3], in.g[4], in.g[5], j, sc1, mn1);
+      const __half2 d_lo = __float2half2_rn(in.dw * sc0), d_hi = __float2half2_rn(in.dw * sc1);
+      const __half2 m_lo = __float2half2_rn(-(in.dmw * mn0)), m_hi = __float2half2_rn(-(in.dmw * mn1));
+      const uint2 w[2] = {in.q[0], in.q[1]};
+      fetch(in, st + 2 < n_stages ? st + 2 : n_stages - 1); // the set is free again: the stage after next travels
+      { // weights are read once from HBM: pull the lines of five stages ahead into L2 so that the loads above hit it
+        const int fst = st + 5 < n_stages ? st + 5 : n_stages - 1;
         const uint8_t *fq = wrow[fst >> 2].qs + ((fst & 3) * 32 + 16 * hsel + j) * 8;
         asm volatile("prefetch.global.L2 [%0];" ::"l"(fq));
         asm volatile("prefetch.global.L2 [%0];" ::"l"(fq + 64));
         if ((fst & 3) == 0 && hsel == 0 && j == 0)
           asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow + (fst >> 2))); // d, dmin, scales: the block's first 128 bytes
       }
+      if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag))
+        ok = false;
+      ok = __all_sync(0xffffffffu, ok); // the warp leaves together: its lanes meet at the arrive below
+      if (!ok)
+        return;
+      uint8_t *wdst = smem + s * F16_STAGE_BYTES + r * 16;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const uint2 w2 = q[c];
-        q[c] = ldg_stream_u2(nq + c * 64);
         // word -> 8 halves in the order [lo b0, lo b2, lo b1, lo b3, hi b0, hi b2, hi b1, hi b3]
-        const uint32_t wx = w2.x, wy = w2.y;
+        const uint32_t wx = w[c].x, wy = w[c].y;
         const uint4 o0 = make_uint4(expand2(wx & 0x000f000fu, d_lo, m_lo), expand2((wx >> 8) & 0x000f000fu, d_lo, m_lo),
                                     expand2((wx >> 4) & 0x000f000fu, d_hi, m_hi),
                                     expand2((wx >> 12) & 0x000f000fu, d_hi, m_hi));
@@ -227,12 +225,18 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
         *reinterpret_cast<uint4 *>(wdst + (4 * hsel + 2 * c) * (F16_TILE_N * 16)) = o0;
         *reinterpret_cast<uint4 *>(wdst + (4 * hsel + 2 * c + 1) * (F16_TILE_N * 16)) = o1;
       }
-      dw = ndw;
-      dmw = ndmw;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp(); // every lane's writes are fenced; one arrival per warp keeps the barrier word off the critical path
       if (lane == 0)
         mbar_arrive(BAR(s));
+    };
+    StageIn in0, in1;
+    fetch(in0, 0);
+    fetch(in1, 1); // n_stages is a multiple of 4
+    for (int st = 0; st < n_stages && ok; st += 2) {
+      stage(in0, st);
+      if (ok)
+        stage(in1, st + 1);
     }
     } else if constexpr (QT == NNTR_Q6_K) {
       const int n_row = nt * F16_TILE_N + r;
@@ -283,13 +287,6 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
           ok = __all_sync(0xffffffffu, ok); // the warp leaves together: its lanes meet at the arrive below
           if (!ok)
             break;
-          if (tid == 0) {
-            mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
-            bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
-            if (two)
-              bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES + F16_A_BYTES,
-                       asrc + ((size_t)n_stages + st) * F16_A_BYTES, F16_A_BYTES, BAR(s));
-          }
           uint8_t *wdst = smem + s * F16_STAGE_BYTES + r * 16 + (4 * hsel) * (F16_TILE_N * 16);
           const __half2 off = __half2half2(__ushort_as_half(0x6420)); // 1024 + 32
 #pragma unroll
@@ -329,13 +326,6 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
         ok = __all_sync(0xffffffffu, ok); // the warp leaves together: its lanes meet at the arrive below
         if (!ok)
           break;
-        if (tid == 0) {
-          mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
-          bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
-          if (two)
-            bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES + F16_A_BYTES,
-                     asrc + ((size_t)n_stages + st) * F16_A_BYTES, F16_A_BYTES, BAR(s));
-        }
         uint8_t *wdst = smem + s * F16_STAGE_BYTES + r * 16 + (4 * hsel) * (F16_TILE_N * 16);
         const uint32_t w[4] = {qa.x ^ 0x88888888u, qa.y ^ 0x88888888u, qb.x ^ 0x88888888u, qb.y ^ 0x88888888u};
         // the next stage's block travels while this one is expanded; three stages ahead goes to L2
@@ -394,6 +384,24 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
         }
       }
     }
+  } else if (warp == F16_COPY_WARP) {
+    /* -------------------------- activation copies -------------------------- */
+    // A warp of its own keeps the activation stages as far ahead as the ring allows: a slot's copy starts the moment
+    // its MMAs have retired, whatever the producers are doing.
+    if (lane == 0) {
+      const uint8_t *asrc = atiles + (size_t)mt * n_stages * F16_A_BYTES;
+      for (int st = 0; st < n_stages; ++st) {
+        const int s = st % F16_STAGES, use = st / F16_STAGES;
+        if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag))
+          break;
+        mbar_expect_tx(BAR(s), (two ? 2 : 1) * F16_A_BYTES);
+        bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES, asrc + (size_t)st * F16_A_BYTES, F16_A_BYTES, BAR(s));
+        if (two)
+          bulk_g2s(sbase + s * F16_STAGE_BYTES + F16_W_BYTES + F16_A_BYTES, asrc + ((size_t)n_stages + st) * F16_A_BYTES,
+                   F16_A_BYTES, BAR(s));
+      }
+    }
+    __syncwarp();
   } else {
     /* ------------------------------ MMA issue ------------------------------ */
     if (lane == 0) {
