@@ -614,7 +614,7 @@ def run_ours(args):
 
     # ---- end to end through the host-pointer C ABI: host x in, host y out, per GEMV
     e2e = None
-    if world == 1 and rank == 0 and not args.no_e2e:
+    if not args.no_e2e:  # every rank: its own slice of the global weight, host x in, host y slice out; max over ranks
         xh = torch.empty((1, K_COLS), dtype=torch.float32).pin_memory()
         yh = torch.empty((1, N_ROWS), dtype=torch.float32).pin_memory()
         xh.copy_(x0.cpu()[None])
@@ -626,6 +626,8 @@ def run_ours(args):
             for W in host_ring:
                 be.gemm_q4_K(1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS)
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         tt0 = time.perf_counter()
         for _ in range(e2e_steps):
             for W in host_ring:
@@ -633,10 +635,15 @@ def run_ours(args):
                 np.multiply(yn, 0.78, out=xn)  # chain on the host (one cheap pass; 0.78 keeps the magnitude level)
         torch.cuda.synchronize()
         dt = time.perf_counter() - tt0
-        e2e = {"value": round(e2e_steps * RING * ALG_BYTES / dt / 1e9, 2), "unit": "GB/s",
-               "h2d_bytes_per_step": RING * 4 * K_COLS, "d2h_bytes_per_step": RING * 4 * N_ROWS,
+        if world > 1:
+            t = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        e2e = {"value": round(world * e2e_steps * RING * ALG_BYTES / dt / 1e9, 2), "unit": "GB/s",
+               "h2d_bytes_per_step": world * RING * 4 * K_COLS, "d2h_bytes_per_step": world * RING * 4 * N_ROWS,
                "us_per_call": round(dt / (e2e_steps * RING) * 1e6, 2),
-               "api": "nntr_cuda_gemm_q4_K (host pointers, weights cached in HBM)"}
+               "api": "nntr_cuda_gemm_q4_K (host pointers, weights cached in HBM)" +
+                      ("" if world == 1 else f"; every rank on its own row slice, host x in and host y slice out, no gather")}
         for W in host_ring:
             be.unregister_weight(W)
 
