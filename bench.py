@@ -615,36 +615,56 @@ def run_ours(args):
     # ---- end to end through the host-pointer C ABI: host x in, host y out, per GEMV
     e2e = None
     if not args.no_e2e:  # every rank: its own slice of the global weight, host x in, host y slice out; max over ranks
-        xh = torch.empty((1, K_COLS), dtype=torch.float32).pin_memory()
-        yh = torch.empty((1, N_ROWS), dtype=torch.float32).pin_memory()
-        xh.copy_(x0.cpu()[None])
-        xn, yn = xh.numpy(), yh.numpy()
-        for W in host_ring:
-            be.register_weight("q4_K", W, N_ROWS, K_COLS)
-        e2e_steps = max(1, min(args.steps, 20))
-        for _ in range(2):
-            for W in host_ring:
-                be.gemm_q4_K(1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        tt0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            for W in host_ring:
-                be.gemm_q4_K(1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS)
-                np.multiply(yn, 0.78, out=xn)  # chain on the host (one cheap pass; 0.78 keeps the magnitude level)
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - tt0
-        if world > 1:
-            t = torch.tensor([dt], device=dev, dtype=torch.float64)
+        def all_ok(ok):  # every rank reaches this, whatever happened to it before
+            if world == 1:
+                return ok
+            t = torch.tensor([0.0 if ok else 1.0], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t.item())
-        e2e = {"value": round(world * e2e_steps * RING * ALG_BYTES / dt / 1e9, 2), "unit": "GB/s",
-               "h2d_bytes_per_step": world * RING * 4 * K_COLS, "d2h_bytes_per_step": world * RING * 4 * N_ROWS,
-               "us_per_call": round(dt / (e2e_steps * RING) * 1e6, 2),
-               "api": "nntr_cuda_gemm_q4_K (host pointers, weights cached in HBM)" +
-                      ("" if world == 1 else f"; every rank on its own row slice, host x in and host y slice out, no gather")}
-        for W in host_ring:
+            return float(t.item()) == 0.0
+
+        err, registered = None, []
+        try:
+            xh = torch.empty((1, K_COLS), dtype=torch.float32).pin_memory()
+            yh = torch.empty((1, N_ROWS), dtype=torch.float32).pin_memory()
+            xh.copy_(x0.cpu()[None])
+            xn, yn = xh.numpy(), yh.numpy()
+            for W in host_ring:
+                be.register_weight("q4_K", W, N_ROWS, K_COLS)
+                registered.append(W)
+            for _ in range(2):
+                for W in host_ring:
+                    be.gemm_q4_K(1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS)
+            torch.cuda.synchronize()
+        except Exception as exc:  # noqa: BLE001
+            err = f"{type(exc).__name__}: {exc}"[:300]
+        e2e_steps = max(1, min(args.steps, 20))
+        dt = 0.0
+        if all_ok(err is None):
+            if world > 1:
+                dist.barrier()
+            try:
+                tt0 = time.perf_counter()
+                for _ in range(e2e_steps):
+                    for W in host_ring:
+                        be.gemm_q4_K(1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS)
+                        np.multiply(yn, 0.78, out=xn)  # chain on the host (one cheap pass; 0.78 keeps the magnitude level)
+                torch.cuda.synchronize()
+                dt = time.perf_counter() - tt0
+            except Exception as exc:  # noqa: BLE001
+                err = f"{type(exc).__name__}: {exc}"[:300]
+            if world > 1:
+                t = torch.tensor([dt], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                dt = float(t.item())
+        if all_ok(err is None) and dt > 0.0:
+            e2e = {"value": round(world * e2e_steps * RING * ALG_BYTES / dt / 1e9, 2), "unit": "GB/s",
+                   "h2d_bytes_per_step": world * RING * 4 * K_COLS, "d2h_bytes_per_step": world * RING * 4 * N_ROWS,
+                   "us_per_call": round(dt / (e2e_steps * RING) * 1e6, 2),
+                   "api": "nntr_cuda_gemm_q4_K (host pointers, weights cached in HBM)" +
+                          ("" if world == 1 else "; every rank on its own row slice, host x in and host y slice out, no gather")}
+        else:
+            e2e = {"error": err or "the end-to-end leg failed on another rank"}
+        for W in registered:
             be.unregister_weight(W)
 
     # the MoE decode step runs on every rank (expert parallel when there is more than one); a failure there must not
