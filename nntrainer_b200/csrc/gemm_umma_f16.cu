@@ -314,30 +314,34 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
       }
     } else {
       const BlockQ40x8 *wrow = reinterpret_cast<const BlockQ40x8 *>(Wb) + (size_t)(nt * (F16_TILE_N / 8) + (r >> 3)) * (n_stages * 2);
-      // this thread expands block 2*st + hsel of the row: 16 nibble bytes = four words = four 16-byte chunks of halves
-      const BlockQ40x8 *blk = wrow + hsel;
-      uint2 qa = ldg_stream_u2(blk->qs + j * 8), qb = ldg_stream_u2(blk->qs + 64 + j * 8);
-      uint16_t dbits = blk->d[j];
-      for (int st = 0; st < n_stages && ok; ++st) {
+      // this thread expands block 2*st + hsel of the row: 16 nibble bytes = four words = four 16-byte chunks of halves.
+      // Two register sets rotate: a stage's loads are issued two stages before they are used.
+      struct StageIn {
+        uint2 qa, qb;
+        uint16_t dbits;
+      };
+      auto fetch = [&](StageIn &in, int st) {
+        const BlockQ40x8 *blk = wrow + 2 * st + hsel;
+        in.qa = ldg_stream_u2(blk->qs + j * 8);
+        in.qb = ldg_stream_u2(blk->qs + 64 + j * 8);
+        in.dbits = __ldg(&blk->d[j]);
+      };
+      auto stage = [&](StageIn &in, int st) {
         const int s = st % F16_STAGES, use = st / F16_STAGES;
-        const __half2 d2 = __half2half2(__ushort_as_half(dbits));
+        const __half2 d2 = __half2half2(__ushort_as_half(in.dbits));
+        const uint32_t w[4] = {in.qa.x ^ 0x88888888u, in.qa.y ^ 0x88888888u, in.qb.x ^ 0x88888888u, in.qb.y ^ 0x88888888u};
+        fetch(in, st + 2 < n_stages ? st + 2 : n_stages - 1); // the set is free again: the stage after next travels
+        if (j == 0) { // five stages ahead goes to L2
+          const BlockQ40x8 *fblk = wrow + 2 * (st + 5 < n_stages ? st + 5 : n_stages - 1) + hsel;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(fblk));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(fblk) + 128));
+        }
         if (use > 0 && !mbar_wait(BAR(4 + s), (use - 1) & 1, abort_flag))
           ok = false;
         ok = __all_sync(0xffffffffu, ok); // the warp leaves together: its lanes meet at the arrive below
         if (!ok)
-          break;
+          return;
         uint8_t *wdst = smem + s * F16_STAGE_BYTES + r * 16 + (4 * hsel) * (F16_TILE_N * 16);
-        const uint32_t w[4] = {qa.x ^ 0x88888888u, qa.y ^ 0x88888888u, qb.x ^ 0x88888888u, qb.y ^ 0x88888888u};
-        // the next stage's block travels while this one is expanded; three stages ahead goes to L2
-        const BlockQ40x8 *nblk = wrow + 2 * (st + 1 < n_stages ? st + 1 : st) + hsel;
-        qa = ldg_stream_u2(nblk->qs + j * 8);
-        qb = ldg_stream_u2(nblk->qs + 64 + j * 8);
-        dbits = nblk->d[j];
-        if (j == 0) {
-          const BlockQ40x8 *fblk = wrow + 2 * (st + 3 < n_stages ? st + 3 : n_stages - 1) + hsel;
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(fblk));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(fblk) + 128));
-        }
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) // chunk wi: elements 4wi + {0,2,1,3} then 16 + 4wi + {0,2,1,3} of the block
           *reinterpret_cast<uint4 *>(wdst + wi * (F16_TILE_N * 16)) =
@@ -347,6 +351,14 @@ gemm_f16_kernel(const uint8_t *__restrict__ atiles, const uint8_t *__restrict__ 
         __syncwarp(); // every lane's writes are fenced; one arrival per warp keeps the barrier word off the critical path
         if (lane == 0)
           mbar_arrive(BAR(s));
+      };
+      StageIn in0, in1;
+      fetch(in0, 0);
+      fetch(in1, n_stages > 1 ? 1 : 0);
+      for (int st = 0; st < n_stages && ok; st += 2) { // n_stages may be odd (K = 2880)
+        stage(in0, st);
+        if (ok && st + 1 < n_stages)
+          stage(in1, st + 1);
       }
     }
     /* ------------------------------ epilogue ------------------------------- */
