@@ -40,26 +40,6 @@
 
 namespace nntr {
 
-#ifdef NNTR_TRACE
-/* development aid: per-CTA time stamps of the kernel's phases (off in the library build) */
-__device__ unsigned long long *g_trace = nullptr;
-__device__ __forceinline__ void trace_stamp(int slot) {
-  if (g_trace && (threadIdx.x & 31) == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_trace[blockIdx.x * 8 + slot] = t;
-  }
-}
-/* fine-grained: clock64 stamps of warp 0 of CTA 0 */
-__device__ long long g_fine[64];
-__device__ __forceinline__ void fine_stamp(int i) {
-  if (blockIdx.x == 0 && threadIdx.x == 0 && i < 64)
-    g_fine[i] = clock64();
-}
-#else
-__device__ __forceinline__ void trace_stamp(int) {}
-__device__ __forceinline__ void fine_stamp(int) {}
-#endif
 
 /** raised (non-zero) by a kernel whose bounded wait expired */
 __device__ int g_device_status = 0;
@@ -213,7 +193,6 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  trace_stamp(0);
   pdl_launch_dependents();
 
   if (warp == PRODUCER_WARP) {
@@ -339,7 +318,6 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       if (*abort_flag)
         break;
     }
-    trace_stamp(5);
   } else {
     // ----------------------------------------------------------- consumers
     // the epoch word changes only between passes (before launch 0), so later launches read it while they wait
@@ -348,7 +326,6 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       epoch_early = *reinterpret_cast<const volatile unsigned long long *>(ex.epoch);
     if (!chained_by_tags)
       pdl_wait();
-    trace_stamp(2);
     const uint32_t in_tag =
       ex.n_ranks ? (uint32_t)(((ex.layer > 0 ? epoch_early : *ex.epoch) - 1) * ex.layers_per_epoch + ex.layer) : 0u;
     for (int b = warp; b < nb && !*abort_flag; b += CONSUMER_WARPS) {
@@ -417,7 +394,6 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     consumer_bar_sync();
     if (ex.n_ranks && !ex.no_flags && threadIdx.x == 0)
       mbar_arrive(xread_bar); // this CTA has finished reading its input: the epilogue warp counts it (see there)
-    trace_stamp(3);
 
     const int j = lane >> 3, r = lane & 7;
     const int st = warp >> 1;                // this warp's ring slot, every step
@@ -459,7 +435,6 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
         ++gl;
       }
     }
-    trace_stamp(4);
   }
 }
 

@@ -39,6 +39,17 @@ static void expert_gemv(int qtype, unsigned N, unsigned K, const float *x, const
 
 extern "C" {
 
+/* Tensor::topK on one row (nntrainer/tensor/float_tensor.cpp:1155-1160): the same std::partial_sort call with the same
+ * comparator, so equal values come out in whatever order the library's heap leaves them. */
+void port_topk(const float *p, unsigned width, unsigned k, uint32_t *idx_out) {
+  std::vector<size_t> idx(width);
+  std::iota(idx.begin(), idx.end(), 0);
+  const float *B = p;
+  std::partial_sort(idx.begin(), idx.begin() + k, idx.end(), [&B](size_t i1, size_t i2) { return B[i1] > B[i2]; });
+  for (unsigned i = 0; i < k; ++i)
+    idx_out[i] = (uint32_t)idx[i];
+}
+
 /* Routing only: indices [T][topk] and normalised weights [T][topk] in the order topK returns them. */
 void port_moe_route(unsigned T, unsigned H, unsigned E, unsigned topk, const float *x, const float *router_w,
                     const float *router_bias, uint32_t *idx_out, float *w_out) {

@@ -35,10 +35,17 @@ _vp = C.c_void_p
 _GEMM_SIG = [C.c_uint, C.c_uint, C.c_uint, _vp, C.c_uint, _vp, C.c_uint, _vp, C.c_uint]
 
 
+def reference_root() -> str:
+    """Root of a checkout of the reference project: $NNTR_REFERENCE_ROOT, else a
+    directory named ``reference`` beside this repository; "" when neither exists."""
+    cand = os.environ.get("NNTR_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "nntrainer", "tensor", "cpu_backend")) else ""
+
+
 def build(ref: bool = True) -> None:
     """Compile the checkers (make -C oracle). The reference build is skipped by
-    the Makefile when no checkout is present."""
-    subprocess.run(["make", "-C", HERE, "port"] + (["ref"] if ref else []),
+    the Makefile when no checkout is present (prebuilt files are then kept)."""
+    subprocess.run(["make", "-C", HERE, "port"] + (["ref", f"REF={reference_root()}"] if ref else []),
                    check=True, stdout=subprocess.DEVNULL)
 
 
@@ -125,6 +132,82 @@ class _Lib:
         return float(getattr(self.lib, f"{self.prefix}vec_dot_q6_K_q8_K")(K, _ptr(w), _ptr(a)))
 
 
+
+    # -- helpers around the matmuls (x86/avx2_impl.cpp; restated in glue_port.c) ------------------------------
+    def _f(self, name, argtypes, restype=None):
+        f = getattr(self.lib, self.prefix + name)
+        f.argtypes, f.restype = argtypes, restype
+        return f
+
+    def swiglu(self, gate, up, alpha=None):
+        """X = (gate / (1 + exp(-[alpha*]gate))) * up, the reference's table+cubic exp (avx2_impl.cpp:906,950)."""
+        gate = np.ascontiguousarray(gate, dtype=np.float32).ravel()
+        up = np.ascontiguousarray(up, dtype=np.float32).ravel()
+        out = np.empty_like(gate)
+        if self.prefix == "ref_":
+            if alpha is None:
+                self._f("swiglu", [C.c_uint, _vp, _vp, _vp])(gate.size, _ptr(out), _ptr(gate), _ptr(up))
+            else:
+                self._f("swiglu_alpha", [C.c_uint, _vp, _vp, _vp, C.c_float])(gate.size, _ptr(out), _ptr(gate), _ptr(up), alpha)
+        else:
+            self._f("swiglu", [C.c_uint, _vp, _vp, _vp, C.c_int, C.c_float])(
+                gate.size, _ptr(out), _ptr(gate), _ptr(up), 0 if alpha is None else 1, 0.0 if alpha is None else alpha)
+        return out
+
+    def softmax_rows(self, qk, start_row, end_row, sink=None, inplace_form=True):
+        """softmax over cache rows per head; qk is [rows, heads] (copied). inplace_form picks softmax_row_inplace
+        (decode, avx2_impl.cpp:1299) or softmax_row (prefill, :1429)."""
+        qk = np.array(qk, dtype=np.float32, order="C")
+        sk = None if sink is None else np.ascontiguousarray(sink, dtype=np.float32)
+        name = "softmax_row_inplace" if inplace_form else "softmax_row"
+        self._f(name, [_vp, C.c_size_t, C.c_size_t, C.c_size_t, _vp], None if self.prefix == "ref_" else C.c_int)(
+            _ptr(qk), start_row, end_row, qk.shape[1], _ptr(sk))
+        return qk
+
+    def compute_kcaches(self, q, kcache, num_rows, n_kv, head_dim, gqa, window):
+        """scores [min(num_rows, window), n_kv*gqa] of one query row against the fp16 key cache (avx2_impl.cpp:1595)."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        kc = np.ascontiguousarray(kcache, dtype=np.uint16)
+        out = np.zeros((min(num_rows, window), n_kv * gqa), dtype=np.float32)
+        if self.prefix == "ref_":
+            self._f("compute_kcaches", [_vp, _vp, _vp] + [C.c_int] * 5 + [C.c_size_t])(
+                _ptr(q), _ptr(kc), _ptr(out), num_rows, n_kv, head_dim, gqa, 8, window)
+        else:
+            assert self._f("compute_kcaches", [_vp, _vp, _vp] + [C.c_int] * 4 + [C.c_size_t], C.c_int)(
+                _ptr(q), _ptr(kc), _ptr(out), num_rows, n_kv, head_dim, gqa, window) == 0
+        return out
+
+    def compute_vcache(self, row_num, probs, vcache, n_kv, gqa, head_dim, window):
+        """out [n_kv*gqa, head_dim] = probabilities x fp16 value cache (avx2_impl.cpp:1512)."""
+        pr = np.ascontiguousarray(probs, dtype=np.float32)
+        vc = np.ascontiguousarray(vcache, dtype=np.uint16)
+        out = np.zeros((n_kv * gqa, head_dim), dtype=np.float32)
+        rc = self._f("compute_fp16vcache_fp32_transposed", [C.c_int, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_size_t],
+                     None if self.prefix == "ref_" else C.c_int)(row_num, _ptr(pr), _ptr(vc), _ptr(out), n_kv, gqa, head_dim, window)
+        assert not rc
+        return out
+
+    def rotary(self, x, dim, cos, sin, to_fp16=False, only_convert=False):
+        """compute_rotary_emb_value (avx2_impl.cpp:1652) on a copy of x [width]; returns fp32 (in place form) or
+        uint16 fp16 bits."""
+        x = np.array(x, dtype=np.float32, order="C").ravel()
+        out = np.zeros(x.size, dtype=np.uint16) if to_fp16 else None
+        cs = np.ascontiguousarray(cos, dtype=np.float32)
+        sn = np.ascontiguousarray(sin, dtype=np.float32)
+        self._f("compute_rotary_emb_value", [C.c_uint, C.c_uint, C.c_uint, _vp, _vp, _vp, _vp, C.c_int])(
+            x.size, dim, dim // 2, _ptr(x), _ptr(out), _ptr(cs), _ptr(sn), 1 if only_convert else 0)
+        return out if to_fp16 else x
+
+    def rms_norm_wrt_width(self, x, width, eps):
+        """rms_norm_wrt_width_fp32_intrinsic (avx2_impl.cpp:1751) over rows of `width`."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty_like(x)
+        rc = self._f("rms_norm_wrt_width", [_vp, _vp, C.c_size_t, C.c_size_t, C.c_float],
+                     None if self.prefix == "ref_" else C.c_int)(_ptr(x), _ptr(y), x.size // width, width, eps)
+        assert not rc
+        return y
+
+
 class Ref(_Lib):
     """The reference's own code. Adds the offline weight quantizers and repack."""
 
@@ -185,6 +268,25 @@ class Port(_Lib):
         f.restype = C.c_int
         assert f(_ptr(out), _ptr(np.ascontiguousarray(packed)), nrow, k) == 0
         return out
+
+    def rms_norm(self, x, gamma, eps):
+        """RMSNormLayer / ReshapedRMSNormLayer: rows of gamma.size elements normalised, then times gamma."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        g = np.ascontiguousarray(gamma, dtype=np.float32)
+        y = np.empty_like(x)
+        f = self.lib.port_rms_norm
+        f.argtypes, f.restype = [_vp, _vp, _vp, C.c_size_t, C.c_size_t, C.c_float], C.c_int
+        assert f(_ptr(x), _ptr(g), _ptr(y), x.size // g.size, g.size, eps) == 0
+        return y
+
+    def topk(self, p, k):
+        """Tensor::topK on one row: std::partial_sort with the reference's comparator (float_tensor.cpp:1155-1160)."""
+        p = np.ascontiguousarray(p, dtype=np.float32)
+        idx = np.zeros(k, dtype=np.uint32)
+        f = self.lib.port_topk
+        f.argtypes, f.restype = [_vp, C.c_uint, C.c_uint, _vp], None
+        f(_ptr(p), p.size, k, _ptr(idx))
+        return idx
 
     def moe_route(self, x, router_w, top_k, router_bias=None):
         x = np.ascontiguousarray(x, dtype=np.float32)

@@ -1,0 +1,87 @@
+"""The C restatement of the helpers around the quantized matmuls (oracle/glue_port.c: SwiGLU, softmax over cache rows,
+K/V cache products, rotary embedding, RMS norm) against the reference's own x86 file
+(nntrainer/tensor/cpu_backend/x86/avx2_impl.cpp compiled unmodified into oracle/_ref): bit for bit, on seeded inputs,
+including the edges the reference code has (denormals under flush-to-zero, saturating exponent arguments, attention
+sinks, a sliding window shorter than the cache, fp16 rounding ties)."""
+import numpy as np
+import pytest
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("alpha", [None, 1.702, 0.5])
+def test_swiglu_bit_exact(port, ref, alpha):
+    rng = np.random.default_rng(0)
+    for n in (8, 16, 24, 768, 2880, 9728):
+        g = (rng.standard_normal(n) * rng.choice([0.01, 1, 10, 60], n)).astype(np.float32)
+        u = rng.standard_normal(n).astype(np.float32)
+        g[:4] = [0.0, -0.0, 1e-41, -1e-40]          # zeros and denormals (DAZ)
+        g[4:8] = [90.0, -90.0, 87.5, -200.0]         # beyond both clamps of the exponential
+        assert np.array_equal(bits(port.swiglu(g, u, alpha)), bits(ref.swiglu(g, u, alpha))), (n, alpha)
+
+
+@pytest.mark.parametrize("inplace_form", [True, False])
+@pytest.mark.parametrize("with_sink", [False, True])
+def test_softmax_rows_bit_exact(port, ref, inplace_form, with_sink):
+    rng = np.random.default_rng(1)
+    for rows, heads, lo, hi in ((1, 32, 0, 1), (7, 8, 0, 7), (300, 64, 0, 300), (130, 32, 2, 130)):
+        qk = (rng.standard_normal((rows, heads)) * 4).astype(np.float32)
+        qk[0, 0] = 100.0                              # pushes other entries past the lower clamp
+        sink = (rng.standard_normal(heads) * 2).astype(np.float32) if with_sink else None
+        a = port.softmax_rows(qk, lo, hi, sink, inplace_form)
+        b = ref.softmax_rows(qk, lo, hi, sink, inplace_form)
+        assert np.array_equal(bits(a), bits(b)), (rows, heads)
+
+
+@pytest.mark.parametrize("n_kv,gqa,hd", [(8, 4, 128), (4, 8, 128), (8, 8, 64), (1, 1, 8)])
+def test_key_and_value_cache_products_bit_exact(port, ref, n_kv, gqa, hd):
+    rng = np.random.default_rng(2)
+    rows_total = 150
+    kc = rng.standard_normal((rows_total, n_kv, hd)).astype(np.float16).view(np.uint16)
+    vc = rng.standard_normal((rows_total, n_kv, hd)).astype(np.float16).view(np.uint16)
+    q = rng.standard_normal(n_kv * gqa * hd).astype(np.float32)
+    for num_rows, window in ((1, 2 ** 31 - 1), (150, 2 ** 31 - 1), (150, 128), (100, 128), (128, 128), (129, 128)):
+        a = port.compute_kcaches(q, kc, num_rows, n_kv, hd, gqa, window)
+        b = ref.compute_kcaches(q, kc, num_rows, n_kv, hd, gqa, window)
+        assert np.array_equal(bits(a), bits(b)), ("k", num_rows, window)
+        pr = port.softmax_rows(a, 0, a.shape[0], None, True)
+        oa = port.compute_vcache(num_rows - 1, pr, vc, n_kv, gqa, hd, window)
+        ob = ref.compute_vcache(num_rows - 1, pr, vc, n_kv, gqa, hd, window)
+        assert np.array_equal(bits(oa), bits(ob)), ("v", num_rows, window)
+
+
+def test_rotary_embedding_bit_exact(port, ref):
+    rng = np.random.default_rng(3)
+    for heads, dim in ((32, 128), (8, 128), (64, 64), (3, 24)):
+        x = rng.standard_normal(heads * dim).astype(np.float32)
+        x[:2] = [1.00048828125, 65520.0]             # an fp16 rounding tie and an overflow to infinity
+        ang = rng.uniform(0, 6.28, dim // 2)
+        cos = np.concatenate([np.cos(ang), np.cos(ang)]).astype(np.float32)
+        sin = np.concatenate([np.sin(ang), np.sin(ang)]).astype(np.float32)
+        assert np.array_equal(bits(port.rotary(x, dim, cos, sin)), bits(ref.rotary(x, dim, cos, sin)))
+        assert np.array_equal(port.rotary(x, dim, cos, sin, to_fp16=True), ref.rotary(x, dim, cos, sin, to_fp16=True))
+        assert np.array_equal(port.rotary(x, dim, cos, sin, to_fp16=True, only_convert=True),
+                              ref.rotary(x, dim, cos, sin, to_fp16=True, only_convert=True))
+
+
+@pytest.mark.parametrize("width", [128, 64, 2048, 2560, 2880, 40])
+def test_rms_norm_bit_exact(port, ref, width):
+    rng = np.random.default_rng(4)
+    x = (rng.standard_normal((5, width)) * 3).astype(np.float32)
+    a = port.rms_norm_wrt_width(x, width, 1e-6)
+    b = ref.rms_norm_wrt_width(x, width, 1e-6)
+    assert np.array_equal(bits(a), bits(b))
+    gamma = rng.uniform(0.5, 1.5, width).astype(np.float32)
+    assert np.array_equal(bits(port.rms_norm(x, gamma, 1e-6)), bits(b * gamma[None, :]))
+
+
+def test_topk_is_the_library_partial_sort(port):
+    rng = np.random.default_rng(5)
+    p = rng.random(128).astype(np.float32)
+    idx = port.topk(p, 8)
+    assert list(idx) == list(np.argsort(-p, kind="stable")[:8])   # distinct values: plain descending order
+    p[[3, 40, 77]] = 2.0                                              # a three-way tie at the top
+    idx = port.topk(p, 8)
+    assert set(idx[:3]) == {3, 40, 77} and np.all(p[idx[:-1]] >= p[idx[1:]])
