@@ -73,6 +73,15 @@ uint64_t nntr_cuda_launch_count(void);
  *  limit; on expiry the kernel raises a status word and returns instead of
  *  hanging): NNTR_CUDA_OK, or NNTR_CUDA_ERR_TIMEOUT. */
 int nntr_cuda_device_status(void);
+/** Zeroes every status word of the bound device, so that a process that has seen NNTR_CUDA_ERR_TIMEOUT (or a
+ *  rejected embedding index) can go on: nntr_cuda_device_status() reports a condition once per occurrence only if
+ *  the caller clears it. Synchronizes the device. No CPU counterpart. */
+int nntr_cuda_clear_device_status(void);
+/** Upper bound on the polls of the waits on OTHER ranks' data (numbered elements and "done reading" flags of the
+ *  N-split and expert-parallel exchanges); 0 restores the default (about 2^21 polls with back-off, seconds). A
+ *  launcher that wants a dead peer noticed sooner lowers it; tests use a small value to see a wait run out. Applies to
+ *  launches made after the call on the bound device. */
+int nntr_cuda_set_exchange_poll_limit(unsigned polls);
 
 /* ---------------------------------------------- device-pointer entry points */
 
@@ -149,10 +158,13 @@ int nntr_cuda_gemm_q6_K_dev(unsigned M, unsigned N, unsigned K, const float *A, 
 /** Q4_K GEMM (device pointers, any M >= 1) for callers that cannot allocate
  *  device memory: a model whose memory was planned and handed out before
  *  inference began, a fixed device budget, or a hot path that cannot afford the
- *  device-wide stall of a cudaMalloc. Same arguments and result as
- *  nntr_cuda_gemm_q4_K_dev with M > 1, minus the workspace: the quantized
- *  activations go to an array compiled into the library
- *  (NNTR_CUDA_NOALLOC_SCRATCH_BYTES per GPU, held from load to exit).
+ *  device-wide stall of a cudaMalloc. Same arguments as
+ *  nntr_cuda_gemm_q4_K_dev minus the workspace: the quantized activations go to
+ *  an array compiled into the library (NNTR_CUDA_NOALLOC_SCRATCH_BYTES per GPU,
+ *  held from load to exit). It always runs the bit-exact CUDA-core kernels, so
+ *  its result equals that of nntr_cuda_gemm_q4_K_dev under
+ *  NNTR_CUDA_GEMM_PATH_EXACT (and the CPU result) bit for bit; from about 32
+ *  rows up the regular entry point's tensor-core paths are many times faster.
  *  Rejects M * (K/256) * 292 > NNTR_CUDA_NOALLOC_SCRATCH_BYTES with
  *  NNTR_CUDA_ERR_INVALID. The first call on a device looks up the array's
  *  address; make that call before any stream capture. All calls on a device
@@ -168,6 +180,90 @@ int nntr_cuda_gemm_q4_K_noalloc_dev(unsigned M, unsigned N, unsigned K, const fl
 /** Decode GEMV with explicit launch flags; otherwise as nntr_cuda_gemm_*_dev with M == 1. */
 int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
                        void *stream);
+
+/* ------------------------------------------- operators between the matmuls */
+
+/** RMS normalisation over rows of `width` floats, then times gamma[width] (gamma may be NULL):
+ *  RMSNormLayer::incremental_forwarding (Applications/CausalLM/layers/rms_norm.cpp:60-80) with rows = tokens, and
+ *  ReshapedRMSNormLayer (reshaped_rms_norm.cpp:84-100: the per-head q/k norm) with rows = tokens * heads and
+ *  width = head_dim. Sums in the order of rms_norm_wrt_width_fp32_intrinsic
+ *  (nntrainer/tensor/cpu_backend/x86/avx2_impl.cpp:1751-1809); width % 8 == 0. x == y is allowed. */
+int nntr_cuda_rms_norm_dev(const float *x, const float *gamma, float *y, int64_t rows, int width, float eps,
+                           unsigned flags, void *stream);
+/** out[i] = (gate[i] / (1 + exp(-gate[i]))) * up[i]: nntrainer::swiglu(N, X, Y, Z)
+ *  (cpu_backend.h swiglu -> x86/avx2_impl.cpp:906-947), same bits (table + cubic exponential, flush-to-zero). */
+int nntr_cuda_swiglu_dev(float *out, const float *gate, const float *up, int64_t n, unsigned flags, void *stream);
+/** The form with a slope, out = (gate / (1 + exp(-alpha*gate))) * up: swiglu(N, X, Y, Z, alpha)
+ *  (avx2_impl.cpp:950-996), used by the GPT-OSS experts (gpt_oss_moe_layer.cpp:423-440). */
+int nntr_cuda_swiglu_alpha_dev(float *out, const float *gate, const float *up, int64_t n, float alpha, unsigned flags,
+                               void *stream);
+/** out = a + b (Tensor::add_i of the residual connections; ele_add, avx2_impl.cpp:1042). out may alias a or b. */
+int nntr_cuda_add_dev(float *out, const float *a, const float *b, int64_t n, unsigned flags, void *stream);
+/** Greedy sampler: per row of n logits (row stride ld) the index of the greatest, the lowest index among equals --
+ *  std::max_element as Applications/CausalLM/causal_lm.cpp:530-533 calls it. idx_out (uint32) and/or idx_out_f
+ *  (the index as a float, the form in which the reference feeds the token back into its input tensor) may be NULL. */
+int nntr_cuda_argmax_dev(const float *logits, int64_t rows, int64_t n, int64_t ld, unsigned *idx_out, float *idx_out_f,
+                         unsigned flags, void *stream);
+/** Embedding lookup: y[i][0..out_dim) = row ids[i] of `table`, dequantized. The table holds in_dim PLAIN rows
+ *  (Q6_K: out_dim/256 blocks of 210 B; Q4_0: out_dim/32 blocks of 18 B; qtype 0: fp32), ids are token indices stored
+ *  as floats: EmbeddingLayer::incremental_forwarding (Applications/CausalLM/layers/embedding_layer.cpp:86-160) and
+ *  TieWordEmbedding (tie_word_embedding.cpp:183-233). An index >= in_dim makes the reference throw
+ *  std::invalid_argument; here the row is zero-filled and nntr_cuda_device_status() returns NNTR_CUDA_ERR_INVALID. */
+int nntr_cuda_embedding_dev(int qtype, const void *table, const float *ids, float *y, unsigned n_ids, unsigned in_dim,
+                            unsigned out_dim, unsigned flags, void *stream);
+
+/* --------------------------------------------------- attention (one token) */
+
+/** Shape of an attention layer: MHACoreLayer's properties (Applications/CausalLM/layers/mha_core.cpp:60-140). */
+typedef struct {
+  unsigned n_heads_q, n_heads_kv, head_dim;
+  unsigned window;   /* sliding window in cache rows (props::SlidingWindow); UINT_MAX = full attention */
+  const float *sink; /* device fp32 [n_heads_q] attention-sink logits (props::UseSink), or NULL */
+} nntr_attn_desc;
+/** cos / sin tables of MHACoreLayer::precompute_freqs with the default rope parameters (mha_core.cpp:617-688):
+ *  HOST arrays [seq_len][head_dim], filled on the host with the C library's cos/sin as the reference does. */
+int nntr_cuda_rope_table(unsigned head_dim, unsigned seq_len, float theta, float *cos_out, float *sin_out);
+/** First half of MHACoreLayer::one_batch_incremental_forwarding for one token at position pos (mha_core.cpp:489-506):
+ *  rotary embedding of q in place (fp32), of k into row pos of the fp16 key cache, and v converted into row pos of the
+ *  fp16 value cache (compute_rotary_emb_value, x86/avx2_impl.cpp:1652-1738). Caches: [row][kv head][head_dim] fp16.
+ *  cos_tab / sin_tab: DEVICE copies of the tables above. pos_dev, when not NULL, is a device word that holds the
+ *  position (so that a captured graph can be replayed for later tokens); pos is then ignored. */
+int nntr_cuda_rope_cache_append_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q,
+                                    const float *k, const float *v, void *kcache, void *vcache, const float *cos_tab,
+                                    const float *sin_tab, unsigned flags, void *stream);
+/** Scratch for the call below: scores of min(max_rows, window) cache rows x n_heads_q. */
+size_t nntr_cuda_attention_workspace_bytes(const nntr_attn_desc *a, unsigned max_rows);
+/** Second half (mha_core.cpp:521-531): scores of the query against cache rows [max(0, pos+1-window), pos]
+ *  (compute_kcaches, avx2_impl.cpp:1595), softmax over those rows per head with the optional sink
+ *  (softmax_row_inplace, :1181-1307), probabilities times the value cache (compute_fp16vcache_fp32_transposed, :1512):
+ *  out[n_heads_q][head_dim], equal to the reference's result bit for bit. With pos_dev the grids are sized for
+ *  max_rows cache rows. Three launches. n_heads_q % 8 == 0, head_dim % 8 == 0. */
+int nntr_cuda_attention_decode_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows,
+                                   const float *q, const void *kcache, const void *vcache, float *out, void *workspace,
+                                   size_t workspace_bytes, unsigned flags, void *stream);
+
+/* ------------------------------------------------------- .bin weight files */
+
+/** One tensor of a model file, in the order the model's layers request their weights. */
+#define NNTR_F32 0
+#define NNTR_F16 1
+typedef struct {
+  int dtype;     /* NNTR_F32, NNTR_F16, NNTR_Q4_0, NNTR_Q4_K or NNTR_Q6_K */
+  unsigned N, K; /* quantized: N rows of K weights (the tensor's width x height); fp: N * K elements */
+} nntr_bin_tensor;
+/** Where each tensor sits in a .bin file: NeuralNetwork::load (nntrainer/models/neuralnet.cpp:690-712) lays the
+ *  tensors out back to back in request order, each taking getMemoryBytes() bytes, plus a 2-byte quantization-scheme
+ *  word in front of the data for every type that carries one -- of the types here only Q4_K
+ *  (Uint4QTensor::read, nntrainer/tensor/uint4_tensor.cpp:370-427). data_offset[i] / bytes[i] = position and size
+ *  of tensor i's data; *total = size the file must have. Pure host arithmetic (no device needed). */
+int nntr_cuda_bin_layout(const nntr_bin_tensor *t, size_t n, size_t *data_offset, size_t *bytes, size_t *total);
+/** Reads the tensors of `path` into ONE device allocation (*arena; free with nntr_cuda_free) and returns the device
+ *  address of each (256-byte aligned) in dev_ptrs[n]; with n_ranks > 1 a rank reads only its N-split shard of every
+ *  quantized tensor whose N divides into whole 8-row groups per rank (rows [rank*N/n_ranks, (rank+1)*N/n_ranks), a
+ *  contiguous byte range) and the whole of every other tensor. The bytes go through a pinned staging buffer in
+ *  chunks; the file is the only host copy. Fails with NNTR_CUDA_ERR_INVALID if the file is shorter than the layout. */
+int nntr_cuda_bin_load(const char *path, const nntr_bin_tensor *t, size_t n, int rank, int n_ranks, void **dev_ptrs,
+                       void **arena);
 
 /* ------------------------------------------- N-split over the GPUs of a node */
 

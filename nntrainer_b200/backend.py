@@ -287,3 +287,142 @@ class MoeLayer:
         check(lib().nntr_cuda_moe_route_dev(self._C.byref(self.desc), T, x.data_ptr(), idx.data_ptr(), w.data_ptr(),
                                             ws.data_ptr(), ws.numel(), _stream()))
         return idx, w
+
+
+# ------------------------------------------------- operators between the matmuls
+def _flags(pdl: bool) -> int:
+    return capi.GEMV_PDL if pdl else 0
+
+
+def rms_norm(x, gamma, eps: float, width: int | None = None, out=None, pdl: bool = False):
+    """RMSNormLayer (rows of x.shape[-1]) or, with ``width`` = head_dim, the per-head ReshapedRMSNormLayer:
+    Applications/CausalLM/layers/rms_norm.cpp:60-80, reshaped_rms_norm.cpp:84-100. Device tensors."""
+    torch = _torch()
+    width = x.shape[-1] if width is None else width
+    out = torch.empty_like(x) if out is None else out
+    check(lib().nntr_cuda_rms_norm_dev(x.data_ptr(), gamma.data_ptr() if gamma is not None else None, out.data_ptr(),
+                                       x.numel() // width, width, eps, _flags(pdl), _stream()))
+    return out
+
+
+def swiglu(gate, up, alpha: float | None = None, out=None, pdl: bool = False):
+    """nntrainer::swiglu (cpu_backend swiglu -> x86/avx2_impl.cpp:906 / :950 with a slope). Device tensors."""
+    torch = _torch()
+    out = torch.empty_like(gate) if out is None else out
+    if alpha is None:
+        check(lib().nntr_cuda_swiglu_dev(out.data_ptr(), gate.data_ptr(), up.data_ptr(), gate.numel(), _flags(pdl), _stream()))
+    else:
+        check(lib().nntr_cuda_swiglu_alpha_dev(out.data_ptr(), gate.data_ptr(), up.data_ptr(), gate.numel(), alpha,
+                                               _flags(pdl), _stream()))
+    return out
+
+
+def add(a, b, out=None, pdl: bool = False):
+    """Residual add (Tensor::add_i). Device tensors."""
+    torch = _torch()
+    out = torch.empty_like(a) if out is None else out
+    check(lib().nntr_cuda_add_dev(out.data_ptr(), a.data_ptr(), b.data_ptr(), a.numel(), _flags(pdl), _stream()))
+    return out
+
+
+def argmax(logits, pdl: bool = False):
+    """Greedy sampler over the last dimension: std::max_element (Applications/CausalLM/causal_lm.cpp:530-533).
+    Returns (uint32 indices as an int32 tensor, the same as float32)."""
+    torch = _torch()
+    rows, n = logits.numel() // logits.shape[-1], logits.shape[-1]
+    idx = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    idx_f = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    check(lib().nntr_cuda_argmax_dev(logits.data_ptr(), rows, n, n, idx.data_ptr(), idx_f.data_ptr(), _flags(pdl), _stream()))
+    return idx, idx_f
+
+
+def embedding(qtype: str | None, table, ids_f, in_dim: int, out_dim: int, out=None, pdl: bool = False):
+    """EmbeddingLayer / TieWordEmbedding lookup: rows of a Q6_K / Q4_0 / fp32 (qtype None) table by float token ids
+    (Applications/CausalLM/layers/embedding_layer.cpp:86-160). Device tensors."""
+    torch = _torch()
+    n = ids_f.numel()
+    out = torch.empty((n, out_dim), dtype=torch.float32, device=table.device) if out is None else out
+    check(lib().nntr_cuda_embedding_dev(QTYPE[qtype] if qtype else 0, table.data_ptr(), ids_f.data_ptr(), out.data_ptr(),
+                                        n, in_dim, out_dim, _flags(pdl), _stream()))
+    return out
+
+
+# ------------------------------------------------------- attention (one token)
+def rope_table(head_dim: int, seq_len: int, theta: float):
+    """MHACoreLayer::precompute_freqs, default rope (mha_core.cpp:617-688): host numpy [seq_len, head_dim] cos, sin."""
+    cos = np.empty((seq_len, head_dim), dtype=np.float32)
+    sin = np.empty((seq_len, head_dim), dtype=np.float32)
+    check(lib().nntr_cuda_rope_table(head_dim, seq_len, theta, _np_ptr(cos), _np_ptr(sin)))
+    return cos, sin
+
+
+class Attention:
+    """One attention layer's decode step on the device (MHACoreLayer::one_batch_incremental_forwarding,
+    Applications/CausalLM/layers/mha_core.cpp:459-613): fp16 K/V caches [max_seq, n_kv, head_dim], rotary tables,
+    optional sliding window and sink logits."""
+
+    def __init__(self, n_heads_q, n_heads_kv, head_dim, max_seq, theta=1e6, window=None, sink=None, device="cuda",
+                 tables=None):
+        torch = _torch()
+        self.hq, self.hkv, self.hd, self.max_seq = n_heads_q, n_heads_kv, head_dim, max_seq
+        self.kcache = torch.zeros((max_seq, n_heads_kv, head_dim), dtype=torch.float16, device=device)
+        self.vcache = torch.zeros_like(self.kcache)
+        if tables is None:
+            cos, sin = rope_table(head_dim, max_seq, theta)
+            tables = (torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device))
+        self.cos, self.sin = tables
+        self.sink = sink
+        self.desc = capi.AttnDesc(n_heads_q, n_heads_kv, head_dim, 0xFFFFFFFF if window is None else window,
+                                  sink.data_ptr() if sink is not None else None)
+        import ctypes as C
+        self._C = C
+        need = int(lib().nntr_cuda_attention_workspace_bytes(C.byref(self.desc), max_seq))
+        self.ws = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
+
+    def step(self, q, k, v, pos: int, pos_dev=None, out=None, pdl: bool = False):
+        """q [hq*hd] (rotated in place), k, v [hkv*hd] fp32 device tensors of the token at ``pos`` -> out [hq*hd]."""
+        torch = _torch()
+        C = self._C
+        out = torch.empty(self.hq * self.hd, dtype=torch.float32, device=q.device) if out is None else out
+        pd = pos_dev.data_ptr() if pos_dev is not None else None
+        check(lib().nntr_cuda_rope_cache_append_dev(C.byref(self.desc), pos, pd, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                    self.kcache.data_ptr(), self.vcache.data_ptr(), self.cos.data_ptr(),
+                                                    self.sin.data_ptr(), _flags(pdl), _stream()))
+        check(lib().nntr_cuda_attention_decode_dev(C.byref(self.desc), pos, pd, self.max_seq, q.data_ptr(),
+                                                   self.kcache.data_ptr(), self.vcache.data_ptr(), out.data_ptr(),
+                                                   self.ws.data_ptr(), self.ws.numel(), _flags(pdl), _stream()))
+        return out
+
+
+# --------------------------------------------------------- .bin weight files
+_BIN_DTYPE = {"f32": capi.F32, "f16": capi.F16, "q4_0": capi.Q4_0, "q4_K": capi.Q4_K, "q6_K": capi.Q6_K}
+
+
+def bin_layout(tensors):
+    """Data offset and size of each tensor in a .bin file, and the file size (nntrainer/models/neuralnet.cpp:690-712).
+    ``tensors``: list of (dtype name, N, K). Pure host arithmetic."""
+    import ctypes as C
+    n = len(tensors)
+    arr = (capi.BinTensor * n)(*[capi.BinTensor(_BIN_DTYPE[d], N, K) for d, N, K in tensors])
+    off, size, total = (C.c_size_t * n)(), (C.c_size_t * n)(), C.c_size_t()
+    check(lib().nntr_cuda_bin_layout(arr, n, off, size, C.byref(total)))
+    return list(off), list(size), total.value
+
+
+class BinWeights:
+    """The tensors of a .bin file resident in device memory (one allocation). ``ptr[i]`` is tensor i's device address;
+    with ``world`` > 1 a rank holds its N-split shard of every quantized tensor that divides."""
+
+    def __init__(self, path: str, tensors, rank: int = 0, world: int = 1):
+        import ctypes as C
+        n = len(tensors)
+        arr = (capi.BinTensor * n)(*[capi.BinTensor(_BIN_DTYPE[d], N, K) for d, N, K in tensors])
+        ptrs, arena = (C.c_void_p * n)(), C.c_void_p()
+        check(lib().nntr_cuda_bin_load(path.encode(), arr, n, rank, world, ptrs, C.byref(arena)))
+        self.ptr = [p or 0 for p in ptrs]
+        self._arena = arena.value
+
+    def close(self):
+        if self._arena:
+            lib().nntr_cuda_free(self._arena)
+            self._arena = None

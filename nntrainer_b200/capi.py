@@ -36,6 +36,20 @@ SIGNATURES = {
     "nntr_cuda_sm_count": (_i, []),
     "nntr_cuda_launch_count": (C.c_uint64, []),
     "nntr_cuda_device_status": (_i, []),
+    "nntr_cuda_clear_device_status": (_i, []),
+    "nntr_cuda_set_exchange_poll_limit": (_i, [_u]),
+    "nntr_cuda_rms_norm_dev": (_i, [_vp, _vp, _vp, _i64, _i, C.c_float, _u, _vp]),
+    "nntr_cuda_swiglu_dev": (_i, [_vp, _vp, _vp, _i64, _u, _vp]),
+    "nntr_cuda_swiglu_alpha_dev": (_i, [_vp, _vp, _vp, _i64, C.c_float, _u, _vp]),
+    "nntr_cuda_add_dev": (_i, [_vp, _vp, _vp, _i64, _u, _vp]),
+    "nntr_cuda_argmax_dev": (_i, [_vp, _i64, _i64, _i64, _vp, _vp, _u, _vp]),
+    "nntr_cuda_embedding_dev": (_i, [_i, _vp, _vp, _vp, _u, _u, _u, _u, _vp]),
+    "nntr_cuda_rope_table": (_i, [_u, _u, C.c_float, _vp, _vp]),
+    "nntr_cuda_rope_cache_append_dev": (_i, [_vp, _u, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u, _vp]),
+    "nntr_cuda_attention_workspace_bytes": (_sz, [_vp, _u]),
+    "nntr_cuda_attention_decode_dev": (_i, [_vp, _u, _vp, _u, _vp, _vp, _vp, _vp, _vp, _sz, _u, _vp]),
+    "nntr_cuda_bin_layout": (_i, [_vp, _sz, _vp, _vp, _vp]),
+    "nntr_cuda_bin_load": (_i, [C.c_char_p, _vp, _sz, _i, _i, _vp, _vp]),
     "nntr_cuda_quantize_q8_K_dev": (_i, [_vp, _i64, _vp, _i64, _i64, _i, _vp]),
     "nntr_cuda_quantize_q8_0_dev": (_i, [_vp, _i64, _vp, _i64, _i64, _vp]),
     "nntr_cuda_dequantize_row_dev": (_i, [_i, _vp, _vp, _i64, _vp]),
@@ -85,6 +99,20 @@ class Exchange(C.Structure):
     """nntr_exchange of include/nntr_cuda.h."""
     _fields_ = [("n_ranks", C.c_int), ("rank", C.c_int), ("y", C.c_void_p * 8), ("flags", C.c_void_p * 8),
                 ("epoch", C.c_void_p), ("layers_per_epoch", C.c_uint), ("layer", C.c_uint), ("x_tagged", C.c_int)]
+
+
+class AttnDesc(C.Structure):
+    """nntr_attn_desc of include/nntr_cuda.h."""
+    _fields_ = [("n_heads_q", C.c_uint), ("n_heads_kv", C.c_uint), ("head_dim", C.c_uint), ("window", C.c_uint),
+                ("sink", C.c_void_p)]
+
+
+class BinTensor(C.Structure):
+    """nntr_bin_tensor of include/nntr_cuda.h."""
+    _fields_ = [("dtype", C.c_int), ("N", C.c_uint), ("K", C.c_uint)]
+
+
+F32, F16 = 0, 1
 
 
 class MoeEp(C.Structure):

@@ -1,0 +1,342 @@
+// SPDX-License-Identifier: Apache-2.0
+/**
+ * @file  attention.cu
+ * @brief Single-token attention over an fp16 key/value cache with grouped-query heads, rotary embedding, a sliding
+ *        window and attention sinks: what MHACoreLayer::one_batch_incremental_forwarding does for one decode step
+ *        (Applications/CausalLM/layers/mha_core.cpp:459-533 and :535-613 with sinks).
+ *
+ * The reference's CPU code fixes the order of every floating-point sum, and the kernels keep it, so the attention
+ * output equals the reference's bit for bit:
+ *   rotary        nntrainer/tensor/cpu_backend/x86/avx2_impl.cpp:1652-1738 -- out0 = a*cos - b*sin, out1 = a*sin + b*cos
+ *                 with separately rounded products; keys and values go to the cache as fp16 (round to nearest even);
+ *   scores        avx2_impl.cpp:1595-1650 -- per (cache row, head): eight partial sums (element i goes to lane i % 8,
+ *                 fused multiply-adds in ascending i), summed as ((l0+l4)+(l1+l5)) + ((l2+l6)+(l3+l7)), divided by
+ *                 sqrt(head_dim) in double precision;
+ *   softmax       avx2_impl.cpp:1181-1307 -- per head over the cache rows: maximum (with the sink logit), the 10th-order
+ *                 polynomial exponential (:1085-1179), the sum accumulated row by row in ascending order starting from
+ *                 the sink's term, one division per element;
+ *   values        avx2_impl.cpp:1512-1593 -- per (head, d): one fused multiply-add per cache row in ascending order.
+ * The row-ordered sums make the softmax denominator and the value product serial chains as long as the context per
+ * output; with a few thousand outputs in flight they cost a few microseconds per layer. That is the price of
+ * reproducing the reference's bits; the cache (rows x kv heads x head_dim fp16, read once for keys and once for values)
+ * is the only traffic that matters.
+ *
+ * Cache layout as the reference's: [row][kv head][head_dim] fp16, one row per position.
+ */
+#include "common.cuh"
+
+namespace nntr {
+
+/* ------------------------------------------------------------------ rotary */
+
+/* One thread per (head, pair k): q in place; k rotated and v converted into cache row `pos`. Grid covers
+ * (n_heads_q + 2 * n_heads_kv) * head_dim / 2 threads. */
+__global__ void rope_cache_append_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                         uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache,
+                                         const float *__restrict__ cos_tab, const float *__restrict__ sin_tab,
+                                         const unsigned *__restrict__ pos_dev, unsigned pos, int hq, int hkv, int hd) {
+  pdl_wait();
+  const unsigned p = pos_dev ? *pos_dev : pos;
+  const int half = hd / 2;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int total = (hq + 2 * hkv) * half;
+  if (t >= total)
+    return;
+  const int head = t / half, kk = t - head * half;
+  const float c = cos_tab[(size_t)p * hd + kk], s = sin_tab[(size_t)p * hd + kk];
+  if (head < hq) {
+    float *b = q + (size_t)head * hd;
+    const float a0 = b[kk], a1 = b[kk + half];
+    b[kk] = __fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s));
+    b[kk + half] = __fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c));
+  } else if (head < hq + hkv) {
+    const int h = head - hq;
+    const float *b = k + (size_t)h * hd;
+    uint16_t *dst = kcache + ((size_t)p * hkv + h) * hd;
+    const float a0 = b[kk], a1 = b[kk + half];
+    dst[kk] = float_to_half_bits_rn(__fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s)));
+    dst[kk + half] = float_to_half_bits_rn(__fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c)));
+  } else {
+    const int h = head - hq - hkv;
+    const float *b = v + (size_t)h * hd;
+    uint16_t *dst = vcache + ((size_t)p * hkv + h) * hd;
+    dst[kk] = float_to_half_bits_rn(b[kk]);
+    dst[kk + half] = float_to_half_bits_rn(b[kk + half]);
+  }
+}
+
+/* ------------------------------------------------------------------ scores */
+
+/* A warp takes four cache rows of one kv head; lane = (row j = lane / 8, vector lane l = lane % 8). The four key rows
+ * are staged through shared memory with 16-byte loads; every query head of the group is then dotted against them. */
+constexpr int SCORE_WARPS = 4;
+__global__ void attn_scores_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kcache,
+                                   float *__restrict__ scores, const unsigned *__restrict__ pos_dev, unsigned pos,
+                                   int hq, int hkv, int hd, unsigned window) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  pdl_wait();
+  const unsigned num_rows = (pos_dev ? *pos_dev : pos) + 1;
+  const unsigned start_row = num_rows < window ? 0u : num_rows - window;
+  const unsigned row_cnt = num_rows < window ? num_rows : window;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.y;
+  const int gqa = hq / hkv;
+  const unsigned t0 = (blockIdx.x * SCORE_WARPS + warp) * 4;
+  if (t0 >= row_cnt)
+    return;
+  uint16_t *ks = reinterpret_cast<uint16_t *>(smem_raw) + (size_t)warp * 4 * hd;
+  // stage 4 rows x hd halves (hd * 2 bytes per row, 16-byte chunks)
+  const int chunks_per_row = hd / 8;
+  for (int c = lane; c < 4 * chunks_per_row; c += 32) {
+    const int r = c / chunks_per_row, cc = c - r * chunks_per_row;
+    uint4 vv = make_uint4(0, 0, 0, 0);
+    if (t0 + r < row_cnt)
+      vv = *reinterpret_cast<const uint4 *>(kcache + ((size_t)(start_row + t0 + r) * hkv + n) * hd + cc * 8);
+    *reinterpret_cast<uint4 *>(ks + (size_t)r * hd + cc * 8) = vv;
+  }
+  __syncwarp();
+  const int j = lane >> 3, l = lane & 7;
+  const uint16_t *kr = ks + (size_t)j * hd;
+  const double norm = sqrt((double)(float)hd);
+  for (int g = 0; g < gqa; ++g) {
+    const float *qh = q + (size_t)(n * gqa + g) * hd;
+    float acc = 0.f;
+    for (int i = 0; i < hd; i += 8)
+      acc = __fmaf_rn(qh[i + l], half_bits_to_float(kr[i + l]), acc);
+    float s = __fadd_rn(acc, __shfl_down_sync(FULL, acc, 4));
+    s = __fadd_rn(s, __shfl_down_sync(FULL, s, 1));
+    s = __fadd_rn(s, __shfl_down_sync(FULL, s, 2));
+    if (l == 0 && t0 + j < row_cnt) {
+      const float sum = __fadd_rn(0.0f, s);
+      scores[(size_t)(t0 + j) * hq + n * gqa + g] = (float)((double)sum / norm);
+    }
+  }
+}
+
+/* ----------------------------------------------------------------- softmax */
+
+/** exp256_ps, avx2_impl.cpp:1085-1179 ("low-precision version III"), one lane */
+__device__ __forceinline__ float exp256_lane(float x) {
+  const float LOG2EF = 1.44269504088896341f, LN2 = 0.6931471805599453f;
+  const float max_x = 88.3762626647949f, min_x = -88.3762626647949f;
+  const float t = max_x < x ? max_x : x;
+  x = min_x > t ? min_x : t;
+  float fx = __fmul_rn(x, LOG2EF);
+  fx = floorf(__fadd_rn(fx, 0.5f));
+  const float r = __fsub_rn(x, __fmul_rn(fx, LN2));
+  float y = 1.0f / 3628800.0f;
+  y = __fmaf_rn(y, r, 1.0f / 362880.0f);
+  y = __fmaf_rn(y, r, 1.0f / 40320.0f);
+  y = __fmaf_rn(y, r, 1.0f / 5040.0f);
+  y = __fmaf_rn(y, r, 1.0f / 720.0f);
+  y = __fmaf_rn(y, r, 1.0f / 120.0f);
+  y = __fmaf_rn(y, r, 1.0f / 24.0f);
+  y = __fmaf_rn(y, r, 1.0f / 6.0f);
+  y = __fmaf_rn(y, r, 0.5f);
+  y = __fmaf_rn(y, r, 1.0f);
+  y = __fmaf_rn(y, r, 1.0f);
+  const int nn = __float2int_rn(fx);
+  return __fmul_rn(y, __uint_as_float((uint32_t)(nn + 127) << 23));
+}
+
+/* One CTA per head. Phase 1: maximum over the rows (any order: exact). Phase 2: e = exp(x - max) for every row, in
+ * parallel, written back. Phase 3: thread 0 adds the e's in ascending row order (the reference's order), starting from
+ * the sink's term. Phase 4: every element divided by the sum. */
+constexpr int SOFTMAX_THREADS = 256;
+__global__ void attn_softmax_kernel(float *__restrict__ scores, const float *__restrict__ sink,
+                                    const unsigned *__restrict__ pos_dev, unsigned pos, int hq, unsigned window) {
+  __shared__ float red[SOFTMAX_THREADS / 32];
+  __shared__ float s_bcast;
+  pdl_wait();
+  const unsigned num_rows = (pos_dev ? *pos_dev : pos) + 1;
+  const unsigned row_cnt = num_rows < window ? num_rows : window;
+  const int c = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float mx = -INFINITY;
+  for (unsigned r = threadIdx.x; r < row_cnt; r += SOFTMAX_THREADS)
+    mx = fmaxf(mx, scores[(size_t)r * hq + c]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1)
+    mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
+  if (lane == 0)
+    red[warp] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = red[0];
+    for (int w = 1; w < SOFTMAX_THREADS / 32; ++w)
+      m = fmaxf(m, red[w]);
+    if (sink)
+      m = fmaxf(m, sink[c]);
+    s_bcast = m;
+  }
+  __syncthreads();
+  mx = s_bcast;
+  for (unsigned r = threadIdx.x; r < row_cnt; r += SOFTMAX_THREADS) {
+    float *p = scores + (size_t)r * hq + c;
+    *p = exp256_lane(__fsub_rn(*p, mx));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float sum = sink ? exp256_lane(__fsub_rn(sink[c], mx)) : 0.0f;
+    unsigned r = 0;
+    for (; r + 8 <= row_cnt; r += 8) { // loads issued together, adds in order
+      float e[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        e[u] = scores[(size_t)(r + u) * hq + c];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        sum = __fadd_rn(sum, e[u]);
+    }
+    for (; r < row_cnt; ++r)
+      sum = __fadd_rn(sum, scores[(size_t)r * hq + c]);
+    s_bcast = sum;
+  }
+  __syncthreads();
+  const float sum = s_bcast;
+  for (unsigned r = threadIdx.x; r < row_cnt; r += SOFTMAX_THREADS) {
+    float *p = scores + (size_t)r * hq + c;
+    *p = __fdiv_rn(*p, sum);
+  }
+}
+
+/* ------------------------------------------------------------------ values */
+
+/* One thread per (head, d): out = chain over the window's rows of fma(p[row][head], v[row][kv head][d], out).
+ * CTA = (kv head, 32 consecutive d) x all heads of the group. */
+__global__ void attn_values_kernel(const float *__restrict__ probs, const uint16_t *__restrict__ vcache,
+                                   float *__restrict__ out, const unsigned *__restrict__ pos_dev, unsigned pos, int hq,
+                                   int hkv, int hd, unsigned window) {
+  pdl_wait();
+  const unsigned row_num = pos_dev ? *pos_dev : pos;
+  const unsigned first = row_num < window ? 0u : row_num + 1 - window;
+  const unsigned cnt = row_num + 1 - first;
+  const int gqa = hq / hkv;
+  const int n = blockIdx.y;
+  const int d = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int h = threadIdx.x >> 5; // head inside the group
+  if (h >= gqa || d >= hd)
+    return;
+  const int head = n * gqa + h;
+  const uint16_t *vp = vcache + ((size_t)first * hkv + n) * hd + d;
+  const float *pp = probs + head;
+  const size_t vstride = (size_t)hkv * hd;
+  float acc = 0.f;
+  unsigned j = 0;
+  for (; j + 8 <= cnt; j += 8) {
+    float a[8], b[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      a[u] = pp[(size_t)(j + u) * hq];
+      b[u] = half_bits_to_float(vp[(size_t)(j + u) * vstride]);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      acc = __fmaf_rn(a[u], b[u], acc);
+  }
+  for (; j < cnt; ++j)
+    acc = __fmaf_rn(pp[(size_t)j * hq], half_bits_to_float(vp[(size_t)j * vstride]), acc);
+  out[(size_t)head * hd + d] = acc;
+}
+
+/* ---------------------------------------------------------------- launchers */
+
+static int check_attn(const nntr_attn_desc *a) {
+  if (!a || a->n_heads_q == 0 || a->n_heads_kv == 0 || a->head_dim == 0)
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention: null or empty description");
+  if (a->n_heads_q % a->n_heads_kv)
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention: %u query heads are not a multiple of %u key/value heads",
+                     a->n_heads_q, a->n_heads_kv);
+  // the reference's scalar tails (libm exp for head counts that are not multiples of 8) are not reproduced
+  if (a->n_heads_q % 8 || a->head_dim % 8)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "attention: head count and head_dim must be multiples of 8 (%u, %u)",
+                     a->n_heads_q, a->head_dim);
+  if (a->n_heads_q / a->n_heads_kv > 32)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "attention: at most 32 query heads per key/value head");
+  if (a->window == 0)
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention: window of 0 rows");
+  return NNTR_CUDA_OK;
+}
+
+static void pdl_cfg(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, unsigned flags, cudaStream_t st) {
+  cfg.stream = st;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
+}
+
+int launch_rope_cache_append(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q, const float *k,
+                             const float *v, uint16_t *kcache, uint16_t *vcache, const float *cos_tab,
+                             const float *sin_tab, unsigned flags, cudaStream_t st) {
+  int rc = check_attn(a);
+  if (rc)
+    return rc;
+  if (!q || !k || !v || !kcache || !vcache || !cos_tab || !sin_tab)
+    return set_error(NNTR_CUDA_ERR_INVALID, "rope_cache_append: null pointer");
+  const int total = (int)((a->n_heads_q + 2 * a->n_heads_kv) * (a->head_dim / 2));
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  pdl_cfg(cfg, attr, flags, st);
+  cfg.gridDim = dim3((unsigned)((total + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rope_cache_append_kernel, q, k, v, kcache, vcache, cos_tab, sin_tab, pos_dev,
+                                     pos, (int)a->n_heads_q, (int)a->n_heads_kv, (int)a->head_dim);
+  count_launch();
+  return check_cuda(e, "rope_cache_append launch");
+}
+
+size_t attention_workspace_bytes(const nntr_attn_desc *a, unsigned max_rows) {
+  if (!a)
+    return 0;
+  const size_t rows = max_rows < a->window ? max_rows : a->window;
+  return rows * a->n_heads_q * sizeof(float);
+}
+
+int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows,
+                            const float *q, const uint16_t *kcache, const uint16_t *vcache, float *out, void *ws,
+                            size_t ws_bytes, unsigned flags, cudaStream_t st) {
+  int rc = check_attn(a);
+  if (rc)
+    return rc;
+  if (!q || !kcache || !vcache || !out || !ws)
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: null pointer");
+  // grids are sized for the largest row count this call can see: pos + 1 when the position comes by value, else the
+  // caller's bound
+  const unsigned bound = pos_dev ? max_rows : pos + 1;
+  if (bound == 0 || (!pos_dev && max_rows && pos + 1 > max_rows))
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: position %u beyond the %u rows allowed", pos, max_rows);
+  const unsigned rows = bound < a->window ? bound : a->window;
+  if (ws_bytes < (size_t)rows * a->n_heads_q * sizeof(float))
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: workspace of %zu bytes needed, %zu given",
+                     (size_t)rows * a->n_heads_q * sizeof(float), ws_bytes);
+  if ((reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(ws) & 15))
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: cache and workspace must be 16-byte aligned");
+  float *scores = static_cast<float *>(ws);
+  const int hq = (int)a->n_heads_q, hkv = (int)a->n_heads_kv, hd = (int)a->head_dim;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  pdl_cfg(cfg, attr, flags, st);
+  cfg.gridDim = dim3((rows + SCORE_WARPS * 4 - 1) / (SCORE_WARPS * 4), (unsigned)hkv);
+  cfg.blockDim = dim3(32 * SCORE_WARPS);
+  cfg.dynamicSmemBytes = (size_t)SCORE_WARPS * 4 * hd * sizeof(uint16_t);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_scores_kernel, q, kcache, scores, pos_dev, pos, hq, hkv, hd, a->window);
+  count_launch();
+  if ((rc = check_cuda(e, "attention scores launch")))
+    return rc;
+  cfg.gridDim = dim3((unsigned)hq);
+  cfg.blockDim = dim3(SOFTMAX_THREADS);
+  cfg.dynamicSmemBytes = 0;
+  e = cudaLaunchKernelEx(&cfg, attn_softmax_kernel, scores, a->sink, pos_dev, pos, hq, a->window);
+  count_launch();
+  if ((rc = check_cuda(e, "attention softmax launch")))
+    return rc;
+  cfg.gridDim = dim3((unsigned)((hd + 31) / 32), (unsigned)hkv);
+  cfg.blockDim = dim3(32 * (unsigned)(hq / hkv));
+  e = cudaLaunchKernelEx(&cfg, attn_values_kernel, static_cast<const float *>(scores), vcache, out, pos_dev, pos, hq, hkv,
+                         hd, a->window);
+  count_launch();
+  return check_cuda(e, "attention values launch");
+}
+
+} // namespace nntr

@@ -94,6 +94,42 @@ static size_t weight_bytes(int qtype, unsigned N, unsigned K) {
   }
 }
 
+static size_t weight_bytes(int qtype, unsigned N, unsigned K);
+
+/* Device copy for a GEMM operand B = N rows of K weights of `qtype` at host address `host`: the address must lie inside
+ * a registered tensor of the same format and row length, on a row-group boundary, with all N rows inside the range.
+ * *found = false when no registered range contains the address (the caller may then register it); a containing range
+ * that does not fit the call is an error, never a silent read of other bytes. */
+static int resolve_weight(const void *host, int qtype, unsigned N, unsigned K, const void **dev, bool *found) {
+  const uintptr_t h = reinterpret_cast<uintptr_t>(host);
+  *found = false;
+  *dev = nullptr;
+  std::lock_guard<std::mutex> lk(g_wmutex);
+  auto it = g_weights.upper_bound(h);
+  if (it == g_weights.begin())
+    return NNTR_CUDA_OK;
+  --it;
+  const WeightEntry &e = it->second;
+  if (h < it->first || h >= it->first + e.bytes)
+    return NNTR_CUDA_OK;
+  *found = true;
+  if (e.qtype != qtype || e.K != K)
+    return set_error(NNTR_CUDA_ERR_INVALID,
+                     "gemm: B lies inside a weight registered as qtype %d with K=%u, the call says qtype %d, K=%u "
+                     "(a reused host buffer must be unregistered before it is rewritten)",
+                     e.qtype, e.K, qtype, K);
+  const size_t off = h - it->first, need = weight_bytes(qtype, N, K);
+  const size_t group = weight_bytes(qtype, qtype == NNTR_Q6_K ? 1 : 8, K);
+  if (off % group)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm: B is not on a row%s boundary of its registered tensor",
+                     qtype == NNTR_Q6_K ? "" : "-group");
+  if (off + need > e.bytes)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm: N=%u rows from byte %zu run past the registered tensor (%zu bytes)", N,
+                     off, e.bytes);
+  *dev = static_cast<const uint8_t *>(e.dev) + off;
+  return NNTR_CUDA_OK;
+}
+
 static int check_weight_shape(int qtype, unsigned N, unsigned K) {
   switch (qtype) {
   case NNTR_Q4_0:
@@ -270,12 +306,20 @@ static int gemm_host(int qtype, unsigned M, unsigned N, unsigned K, const float 
     return set_error(NNTR_CUDA_ERR_INVALID, "gemm: null pointer");
   if (M > 1 && ldc < N)
     return set_error(NNTR_CUDA_ERR_INVALID, "gemm: ldc (%u) < N (%u)", ldc, N);
-  const void *dB = lookup_weight(B);
-  if (!dB) {
+  const void *dB = nullptr;
+  bool found = false;
+  if ((rc = resolve_weight(B, qtype, N, K, &dB, &found)))
+    return rc;
+  if (!found) {
+    // first use of an unregistered tensor: upload it now. The copy is keyed by address and stays until
+    // nntr_cuda_unregister_weight; a caller that rewrites the host buffer must unregister it first.
     rc = nntr_cuda_register_weight(B, weight_bytes(qtype, N, K), qtype, N, K);
     if (rc)
       return rc;
-    dB = lookup_weight(B);
+    if ((rc = resolve_weight(B, qtype, N, K, &dB, &found)))
+      return rc;
+    if (!found)
+      return set_error(NNTR_CUDA_ERR_CUDA, "gemm: weight vanished from the cache during the call");
   }
   ThreadCtx *c;
   rc = ensure_ctx(c);
@@ -370,7 +414,90 @@ int nntr_cuda_device_status(void) {
     return rc;
   if (v)
     return set_error(v, "a device kernel gave up on a bounded wait (status %d)", v);
+  if ((rc = read_embed_status(&v, false)))
+    return rc;
+  if (v)
+    return set_error(v, "an embedding lookup met a token index beyond its table");
   return NNTR_CUDA_OK;
+}
+
+} // extern "C"
+
+namespace nntr {
+int clear_device_status_words() {
+  int rc;
+  if ((rc = clear_device_status()) || (rc = clear_umma_status()) || (rc = clear_q6_status()) ||
+      (rc = clear_moe_status()) || (rc = clear_q40_status()) || (rc = clear_f16_status()))
+    return rc;
+  return NNTR_CUDA_OK;
+}
+int set_exchange_poll_limit(unsigned polls) {
+  int rc = set_exchange_poll_limit_gemv(polls);
+  return rc ? rc : set_exchange_poll_limit_moe(polls);
+}
+} // namespace nntr
+
+extern "C" {
+
+int nntr_cuda_clear_device_status(void) {
+  NNTR_CHECK_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  int rc = read_embed_status(&v, true);
+  return rc ? rc : clear_device_status_words();
+}
+
+int nntr_cuda_set_exchange_poll_limit(unsigned polls) { return set_exchange_poll_limit(polls); }
+
+int nntr_cuda_rms_norm_dev(const float *x, const float *gamma, float *y, int64_t rows, int width, float eps,
+                           unsigned flags, void *stream) {
+  return launch_rms_norm(x, gamma, y, rows, width, eps, flags, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_swiglu_dev(float *out, const float *gate, const float *up, int64_t n, unsigned flags, void *stream) {
+  return launch_swiglu(out, gate, up, n, 0, 0.f, flags, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_swiglu_alpha_dev(float *out, const float *gate, const float *up, int64_t n, float alpha, unsigned flags,
+                               void *stream) {
+  return launch_swiglu(out, gate, up, n, 1, alpha, flags, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_add_dev(float *out, const float *a, const float *b, int64_t n, unsigned flags, void *stream) {
+  return launch_add(out, a, b, n, flags, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_argmax_dev(const float *logits, int64_t rows, int64_t n, int64_t ld, unsigned *idx_out, float *idx_out_f,
+                         unsigned flags, void *stream) {
+  return launch_argmax(logits, rows, n, ld, idx_out, idx_out_f, flags, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_embedding_dev(int qtype, const void *table, const float *ids, float *y, unsigned n_ids, unsigned in_dim,
+                            unsigned out_dim, unsigned flags, void *stream) {
+  return launch_embedding(qtype, table, ids, y, n_ids, in_dim, out_dim, flags, static_cast<cudaStream_t>(stream));
+}
+
+int nntr_cuda_rope_table(unsigned head_dim, unsigned seq_len, float theta, float *cos_out, float *sin_out) {
+  return rope_table(head_dim, seq_len, theta, cos_out, sin_out);
+}
+int nntr_cuda_rope_cache_append_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q,
+                                    const float *k, const float *v, void *kcache, void *vcache, const float *cos_tab,
+                                    const float *sin_tab, unsigned flags, void *stream) {
+  return launch_rope_cache_append(a, pos, pos_dev, q, k, v, static_cast<uint16_t *>(kcache),
+                                  static_cast<uint16_t *>(vcache), cos_tab, sin_tab, flags,
+                                  static_cast<cudaStream_t>(stream));
+}
+size_t nntr_cuda_attention_workspace_bytes(const nntr_attn_desc *a, unsigned max_rows) {
+  return attention_workspace_bytes(a, max_rows);
+}
+int nntr_cuda_attention_decode_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows,
+                                   const float *q, const void *kcache, const void *vcache, float *out, void *workspace,
+                                   size_t workspace_bytes, unsigned flags, void *stream) {
+  return launch_attention_decode(a, pos, pos_dev, max_rows, q, static_cast<const uint16_t *>(kcache),
+                                 static_cast<const uint16_t *>(vcache), out, workspace, workspace_bytes, flags,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int nntr_cuda_bin_layout(const nntr_bin_tensor *t, size_t n, size_t *data_offset, size_t *bytes, size_t *total) {
+  return bin_layout(t, n, data_offset, bytes, total);
+}
+int nntr_cuda_bin_load(const char *path, const nntr_bin_tensor *t, size_t n, int rank, int n_ranks, void **dev_ptrs,
+                       void **arena) {
+  return bin_load(path, t, n, rank, n_ranks, dev_ptrs, arena);
 }
 
 int nntr_cuda_quantize_q8_K_dev(const float *x, int64_t ldx, void *y, int64_t rows, int64_t k, int rule, void *stream) {

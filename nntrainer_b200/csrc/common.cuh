@@ -66,7 +66,7 @@ int set_error(int code, const char *fmt, ...);
 int check_cuda(cudaError_t e, const char *what);
 void count_launch(unsigned n = 1);
 int sm_count();
-/** reads (and leaves) the status word device kernels raise when a bounded wait expires */
+/** reads the status word device kernels raise when a bounded wait expires (left as it is; see clear_*) */
 int read_device_status(int *out);
 
 #define NNTR_CHECK_CUDA(expr)                                                                                          \
@@ -309,5 +309,39 @@ int read_f16_status(int *out);
 int measure_int8_peak(double *tops_out, double *clk_per_mma_out);
 int launch_gemm_q6_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
                      cudaStream_t st);
+/* operators between the matmuls (glue.cu, dequantize.cu) */
+int launch_rms_norm(const float *x, const float *gamma, float *y, long long rows, int width, float eps, unsigned flags,
+                    cudaStream_t st);
+int launch_swiglu(float *out, const float *gate, const float *up, long long n, int has_alpha, float alpha,
+                  unsigned flags, cudaStream_t st);
+int launch_add(float *out, const float *a, const float *b, long long n, unsigned flags, cudaStream_t st);
+int launch_argmax(const float *x, long long rows, long long n, long long ld, unsigned *out, float *out_f, unsigned flags,
+                  cudaStream_t st);
+int launch_embedding(int qtype, const void *table, const float *ids, float *y, unsigned n_ids, unsigned in_dim,
+                     unsigned out_dim, unsigned flags, cudaStream_t st);
+int read_embed_status(int *out, bool clear);
+/* single-token attention (attention.cu) */
+int launch_rope_cache_append(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q, const float *k,
+                             const float *v, uint16_t *kcache, uint16_t *vcache, const float *cos_tab,
+                             const float *sin_tab, unsigned flags, cudaStream_t st);
+size_t attention_workspace_bytes(const nntr_attn_desc *a, unsigned max_rows);
+int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows,
+                            const float *q, const uint16_t *kcache, const uint16_t *vcache, float *out, void *ws,
+                            size_t ws_bytes, unsigned flags, cudaStream_t st);
+/* host side (model_file.cu) */
+int bin_layout(const nntr_bin_tensor *t, size_t n, size_t *data_offset, size_t *bytes, size_t *total);
+int bin_load(const char *path, const nntr_bin_tensor *t, size_t n, int rank, int n_ranks, void **dev_ptrs, void **arena);
+int rope_table(unsigned head_dim, unsigned seq_len, float theta, float *cos_out, float *sin_out);
+/* status words: clear = zero the word after reading it */
+int clear_device_status_words();
+int clear_umma_status();
+int clear_f16_status();
+int clear_q40_status();
+int clear_device_status();
+int clear_q6_status();
+int clear_moe_status();
+int set_exchange_poll_limit_gemv(unsigned polls);
+int set_exchange_poll_limit_moe(unsigned polls);
+int set_exchange_poll_limit(unsigned polls);
 
 } // namespace nntr

@@ -71,6 +71,95 @@ __global__ void dequantize_row_kernel(int qtype, const uint8_t *__restrict__ x, 
   y[i] = out;
 }
 
+/** raised when an embedding lookup meets a token index beyond the table (the reference throws
+ *  std::invalid_argument there, embedding_layer.cpp:122-124) */
+__device__ int g_embed_status = 0;
+
+/* Embedding lookup: output row i = dequantized row ids[i] of a table stored as plain rows of blocks (Q6_K or Q4_0) or
+ * as fp32 (qtype 0). Token indices arrive as floats, the way the reference's input tensor holds them
+ * (Applications/CausalLM/layers/embedding_layer.cpp:118-146, tie_word_embedding.cpp:200-233). One CTA per token. */
+__global__ void embedding_kernel(int qtype, const uint8_t *__restrict__ table, const float *__restrict__ ids,
+                                 float *__restrict__ y, unsigned in_dim, unsigned out_dim, size_t row_bytes) {
+  pdl_wait();
+  const float idf = ids[blockIdx.x];
+  float *out = y + (size_t)blockIdx.x * out_dim;
+  const size_t id = (size_t)idf;
+  if (!(idf >= 0.f) || id >= in_dim) {
+    if (threadIdx.x == 0)
+      atomicExch(&g_embed_status, NNTR_CUDA_ERR_INVALID);
+    for (unsigned i = threadIdx.x; i < out_dim; i += blockDim.x)
+      out[i] = 0.f;
+    return;
+  }
+  const uint8_t *row = table + id * row_bytes;
+  for (unsigned i = threadIdx.x; i < out_dim; i += blockDim.x) {
+    float v;
+    if (qtype == NNTR_Q6_K) {
+      v = deq_q6_K_elem(row + (size_t)(i >> 8) * sizeof(BlockQ6K), (int)(i & 255));
+    } else if (qtype == NNTR_Q4_0) {
+      const BlockQ40 *b = reinterpret_cast<const BlockQ40 *>(row) + (i >> 5);
+      const int j = (int)(i & 31);
+      const int byte = b->qs[j & 15];
+      const int q = ((j < 16) ? (byte & 0xF) : (byte >> 4)) - 8;
+      v = __fmul_rn((float)q, half_bits_to_float(b->d));
+    } else {
+      v = reinterpret_cast<const float *>(row)[i];
+    }
+    out[i] = v;
+  }
+}
+
+int launch_embedding(int qtype, const void *table, const float *ids, float *y, unsigned n_ids, unsigned in_dim,
+                     unsigned out_dim, unsigned flags, cudaStream_t st) {
+  if (!table || !ids || !y || out_dim == 0)
+    return set_error(NNTR_CUDA_ERR_INVALID, "embedding: null pointer or empty row");
+  size_t row_bytes;
+  switch (qtype) {
+  case NNTR_Q6_K:
+    // the reference rounds the block count up; a partial block cannot be decoded, so whole blocks are required
+    if (out_dim % 256)
+      return set_error(NNTR_CUDA_ERR_INVALID, "embedding q6_K: out_dim must be a multiple of 256 (got %u)", out_dim);
+    row_bytes = (size_t)(out_dim / 256) * sizeof(BlockQ6K);
+    break;
+  case NNTR_Q4_0:
+    if (out_dim % 32)
+      return set_error(NNTR_CUDA_ERR_INVALID, "embedding q4_0: out_dim must be a multiple of 32 (got %u)", out_dim);
+    row_bytes = (size_t)(out_dim / 32) * sizeof(BlockQ40);
+    break;
+  case 0:
+    row_bytes = (size_t)out_dim * sizeof(float);
+    break;
+  default:
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "embedding: tables are Q6_K, Q4_0 or fp32 (qtype 0), got %d", qtype);
+  }
+  if (n_ids == 0)
+    return NNTR_CUDA_OK;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_ids);
+  cfg.blockDim = dim3(256);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, embedding_kernel, qtype, static_cast<const uint8_t *>(table), ids, y, in_dim,
+                                     out_dim, row_bytes);
+  count_launch();
+  return check_cuda(e, "embedding launch");
+}
+
+int read_embed_status(int *out, bool clear) {
+  int v = 0;
+  NNTR_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_embed_status, sizeof(int)));
+  if (v && clear) {
+    const int zero = 0;
+    NNTR_CHECK_CUDA(cudaMemcpyToSymbol(g_embed_status, &zero, sizeof(int)));
+  }
+  *out = v;
+  return NNTR_CUDA_OK;
+}
+
 /* Whole weight tensors in the layout the tensor holds. */
 __global__ void dequantize_weight_q4_Kx8_kernel(const BlockQ4Kx8 *__restrict__ w, float *__restrict__ y, int64_t N,
                                                 int64_t K) {

@@ -441,5 +441,9 @@ int read_umma_status(int *out) {
   *out = v;
   return NNTR_CUDA_OK;
 }
+int clear_umma_status() {
+  const int zero = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_umma_status, &zero, sizeof(int)), "clear_umma_status");
+}
 
 } // namespace nntr

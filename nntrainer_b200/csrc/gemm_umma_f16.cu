@@ -621,5 +621,9 @@ int read_f16_status(int *out) {
   *out = v;
   return NNTR_CUDA_OK;
 }
+int clear_f16_status() {
+  const int zero = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_f16_status, &zero, sizeof(int)), "clear_f16_status");
+}
 
 } // namespace nntr

@@ -330,5 +330,9 @@ int read_q40_status(int *out) {
   *out = v;
   return NNTR_CUDA_OK;
 }
+int clear_q40_status() {
+  const int zero = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_q40_status, &zero, sizeof(int)), "clear_q40_status");
+}
 
 } // namespace nntr

@@ -58,6 +58,13 @@ constexpr int ACT_STRIDE = 288; // per 256 activations: 256 B q8 | 8 x int16 sum
 static_assert(NSTAGE * STAGE_BLOCKS == STEP_BLOCKS, "a consumer warp always reads the same ring slot");
 constexpr uint32_t WAIT_POLLS = 1u << 22;
 
+/** upper bound on the polls of waits on other ranks' data (0: the defaults written at each loop); set from the host */
+__device__ unsigned g_exchange_polls = 0;
+__device__ __forceinline__ uint32_t exchange_polls(uint32_t dflt) {
+  const unsigned v = *reinterpret_cast<volatile unsigned *>(&g_exchange_polls);
+  return v ? v : dflt;
+}
+
 /** Bounded wait (pipeline.cuh); raises this file's status word when it runs out. */
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
   return mbar_wait_bounded(bar, parity, abort_flag, &g_device_status, WAIT_POLLS, 1024);
@@ -268,7 +275,8 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       }
       if (seq > 1) {
         bool all_ok = false;
-        for (uint32_t it = 0; it < (1u << 21) && !all_ok; ++it) {
+        const uint32_t flag_polls = exchange_polls(1u << 21);
+        for (uint32_t it = 0; it < flag_polls && !all_ok; ++it) {
           bool mine = true;
           if (lane < ex.n_ranks) {
             const volatile unsigned long long *slot = ex.flag[ex.rank] + (size_t)lane * NSPLIT_MAX_CTAS;
@@ -339,7 +347,8 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
         {
           const volatile uint32_t *probe = reinterpret_cast<const volatile uint32_t *>(x) + 2 * (size_t)(b * QK_K + 255) + 1;
           bool seen = false;
-          for (uint32_t it = 0; it < (1u << 22) && !seen; ++it) {
+          const uint32_t probe_polls = exchange_polls(1u << 22);
+          for (uint32_t it = 0; it < probe_polls && !seen; ++it) {
             uint32_t t = 0;
             if (lane == 0)
               t = *probe;
@@ -349,7 +358,8 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
           }
         }
         bool ok = false;
-        for (uint32_t it = 0; it < (1u << 20) && !ok; ++it) {
+        const uint32_t tag_polls = exchange_polls(1u << 20);
+        for (uint32_t it = 0; it < tag_polls && !ok; ++it) {
           uint4 e[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i)
@@ -565,11 +575,19 @@ int launch_epoch_bump(unsigned long long *epoch, cudaStream_t st) {
   return check_cuda(cudaGetLastError(), "epoch_bump launch");
 }
 
+int set_exchange_poll_limit_gemv(unsigned polls) {
+  return check_cuda(cudaMemcpyToSymbol(g_exchange_polls, &polls, sizeof(unsigned)), "set_exchange_poll_limit");
+}
+
 int read_device_status(int *out) {
   int v = 0;
   NNTR_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
   *out = v;
   return NNTR_CUDA_OK;
+}
+int clear_device_status() {
+  const int zero = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)), "clear_device_status");
 }
 
 } // namespace nntr

@@ -382,5 +382,9 @@ int read_q6_status(int *out) {
   *out = v;
   return NNTR_CUDA_OK;
 }
+int clear_q6_status() {
+  const int zero = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_q6_status, &zero, sizeof(int)), "clear_q6_status");
+}
 
 } // namespace nntr

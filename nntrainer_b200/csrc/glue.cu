@@ -1,0 +1,292 @@
+// SPDX-License-Identifier: Apache-2.0
+/**
+ * @file  glue.cu
+ * @brief The small operators that sit between the quantized matmuls of a decoder layer, kept on the device so that
+ *        activations never return to the host between projections: RMS normalisation (whole row and per head),
+ *        SwiGLU, residual add, greedy arg-max.
+ *
+ * Each kernel reproduces the result of the reference's x86 code bit for bit by keeping its operation order:
+ *   RMS norm   nntrainer/tensor/cpu_backend/x86/avx2_impl.cpp:1751-1809 (rms_norm_wrt_width_fp32_intrinsic: four
+ *              vectors of eight lanes, fused multiply-adds, fixed-order horizontal sums) followed by the layers'
+ *              multiply by gamma (Applications/CausalLM/layers/rms_norm.cpp:60-80, reshaped_rms_norm.cpp:84-100);
+ *   SwiGLU     avx2_impl.cpp:906-996 with its table + cubic exponential (:228-322), evaluated with flush-to-zero
+ *              arithmetic as the reference sets DAZ|FTZ around the loop;
+ *   arg-max    std::max_element: the first of equal maxima (Applications/CausalLM/causal_lm.cpp:530-533);
+ * (The embedding-row lookup lives with the dequantizers in dequantize.cu.)
+ * All are bound by latency or by the few bytes they move; none is on the HBM roofline of a decode step.
+ */
+#include "common.cuh"
+
+namespace nntr {
+
+/* ------------------------------------------------------------------ RMS norm */
+
+/* One warp per row of `width` elements (width % 8 == 0). Lane 8a + l plays lane l of the reference's vector a. */
+__global__ void rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma, float *__restrict__ y,
+                                long long rows, int width, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows)
+    return;
+  pdl_wait();
+  const float *xr = x + row * width;
+  float *yr = y + row * width;
+  float acc = 0.f;
+  int i = 0;
+  for (; i + 32 <= width; i += 32) {
+    const float v = xr[i + lane];
+    acc = __fmaf_rn(v, v, acc);
+  }
+  for (; i + 8 <= width; i += 8) { // leftover groups of 8 go to vector 0
+    if (lane < 8) {
+      const float v = xr[i + lane];
+      acc = __fmaf_rn(v, v, acc);
+    }
+  }
+  // per vector: ((l0+l4)+(l1+l5)) + ((l2+l6)+(l3+l7))
+  float t = __fadd_rn(acc, __shfl_down_sync(FULL, acc, 4));
+  t = __fadd_rn(t, __shfl_down_sync(FULL, t, 1));
+  t = __fadd_rn(t, __shfl_down_sync(FULL, t, 2));
+  const float h0 = __shfl_sync(FULL, t, 0), h1 = __shfl_sync(FULL, t, 8), h2 = __shfl_sync(FULL, t, 16),
+              h3 = __shfl_sync(FULL, t, 24);
+  const float sumsq = __fadd_rn(__fadd_rn(__fadd_rn(h0, h1), h2), h3);
+  const float mean = __fdiv_rn(sumsq, (float)width);
+  const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+  for (i = lane; i < width; i += 32) {
+    const float n = __fmul_rn(xr[i], scale);
+    yr[i] = gamma ? __fmul_rn(n, gamma[i]) : n;
+  }
+}
+
+int launch_rms_norm(const float *x, const float *gamma, float *y, long long rows, int width, float eps, unsigned flags,
+                    cudaStream_t st) {
+  if (!x || !y || rows < 0 || width <= 0 || width % 8)
+    return set_error(NNTR_CUDA_ERR_INVALID, "rms_norm: need width %% 8 == 0 (width=%d)", width);
+  if (rows == 0)
+    return NNTR_CUDA_OK;
+  const int warps = 4;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((rows + warps - 1) / warps));
+  cfg.blockDim = dim3(32 * warps);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rms_norm_kernel, x, gamma, y, rows, width, eps);
+  count_launch();
+  return check_cuda(e, "rms_norm launch");
+}
+
+/* -------------------------------------------------------------------- SwiGLU */
+
+__device__ __forceinline__ float ftz_mul(float a, float b) {
+  float r;
+  asm("mul.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float ftz_add(float a, float b) {
+  float r;
+  asm("add.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float ftz_sub(float a, float b) {
+  float r;
+  asm("sub.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float ftz_fma(float a, float b, float c) {
+  float r;
+  asm("fma.rn.ftz.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float ftz_div(float a, float b) {
+  float r;
+  asm("div.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float ftz_max(float a, float b) {
+  float r;
+  asm("max.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float ftz_min(float a, float b) {
+  float r;
+  asm("min.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
+/** exp(x) as avx2_approx_exp_e2lookup<8> computes it (avx2_impl.cpp:228-292): clamp, scale by 8/ln2, split into an
+ *  integer (magic-number rounding) and a fraction, 2^(n/8) from an 8-entry table, cubic in the fraction. */
+__device__ __forceinline__ float approx_exp_e2lookup8(float x) {
+  const uint32_t tbl[8] = {0x3f800000u, 0x3f7b95c2u, 0x3f7837f0u, 0x3f75fed7u,
+                           0x3f7504f3u, 0x3f75672au, 0x3f7744fdu, 0x3f7ac0c7u};
+  x = ftz_max(x, -87.0f);
+  x = ftz_mul(x, (float)(1.0 / 0.693147180559945309417232121458176568 * 8));
+  x = ftz_min(x, (float)(88.3762626647949f / 0.693147180559945309417232121458176568 * 8));
+  float xi = ftz_add(x, 0x1.8p23f);
+  const uint32_t bits = __float_as_uint(xi);
+  xi = ftz_sub(xi, 0x1.8p23f);
+  const float frac = ftz_sub(x, xi);
+  const float s = __uint_as_float(tbl[bits & 7u] + (bits << 20));
+  const float C0 = 0x1.c6af84b912394p-5f / 8 / 8 / 8, C1 = 0x1.ebfce50fac4f3p-3f / 8 / 8, C2 = 0x1.62e42ff0c52d6p-1f / 8;
+  const float q0 = ftz_fma(frac, C0, C1);
+  const float f2 = ftz_mul(frac, frac);
+  const float q2 = ftz_mul(frac, C2);
+  const float p = ftz_fma(q0, f2, q2);
+  return ftz_fma(p, s, s);
+}
+
+/** (y / (exp(-[alpha*]y) + 1)) * z, avx2_impl.cpp:306-322 */
+__device__ __forceinline__ float swiglu_elem(float y, float z, bool has_alpha, float alpha) {
+  const float ax = has_alpha ? ftz_mul(alpha, y) : y;
+  const float neg = __uint_as_float(__float_as_uint(ax) ^ 0x80000000u);
+  const float inv_sig = ftz_add(approx_exp_e2lookup8(neg), 1.0f);
+  return ftz_mul(ftz_div(y, inv_sig), z);
+}
+
+/* gate and up may be two halves of one fused projection's output: separate pointers, a common row stride */
+__global__ void swiglu_kernel(float *__restrict__ out, const float *__restrict__ gate, const float *__restrict__ up,
+                              long long n, int has_alpha, float alpha, float up_add) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n)
+    return;
+  pdl_wait();
+  float z = up[i];
+  if (up_add != 0.f)
+    z = __fadd_rn(z, up_add);
+  out[i] = swiglu_elem(gate[i], z, has_alpha != 0, alpha);
+}
+
+int launch_swiglu(float *out, const float *gate, const float *up, long long n, int has_alpha, float alpha,
+                  unsigned flags, cudaStream_t st) {
+  if (!out || !gate || !up || n < 0)
+    return set_error(NNTR_CUDA_ERR_INVALID, "swiglu: null pointer");
+  if (n == 0)
+    return NNTR_CUDA_OK;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((n + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, swiglu_kernel, out, gate, up, n, has_alpha, alpha, 0.f);
+  count_launch();
+  return check_cuda(e, "swiglu launch");
+}
+
+/* -------------------------------------------------------------- residual add */
+
+__global__ void add_kernel(float *__restrict__ out, const float *__restrict__ a, const float *__restrict__ b,
+                           long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n)
+    return;
+  pdl_wait();
+  out[i] = __fadd_rn(a[i], b[i]);
+}
+
+int launch_add(float *out, const float *a, const float *b, long long n, unsigned flags, cudaStream_t st) {
+  if (!out || !a || !b || n < 0)
+    return set_error(NNTR_CUDA_ERR_INVALID, "add: null pointer");
+  if (n == 0)
+    return NNTR_CUDA_OK;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((n + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, add_kernel, out, a, b, n);
+  count_launch();
+  return check_cuda(e, "add launch");
+}
+
+/* ------------------------------------------------------------------- arg-max */
+
+/* One CTA per row of n logits; the winner is the greatest value, the lowest index among equals (what
+ * std::max_element returns). NaNs never win, as with operator<. */
+__global__ void argmax_kernel(const float *__restrict__ x, long long n, long long ld, unsigned *__restrict__ out,
+                              float *__restrict__ out_f) {
+  __shared__ float sv[32];
+  __shared__ unsigned si[32];
+  pdl_wait();
+  const float *xr = x + (long long)blockIdx.x * ld;
+  float best = -INFINITY;
+  unsigned bi = 0xffffffffu;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = xr[i];
+    if (v > best || (bi == 0xffffffffu && v == best)) {
+      best = v;
+      bi = (unsigned)i;
+    }
+  }
+  auto better = [](float v, unsigned i, float bv, unsigned bidx) {
+    return i != 0xffffffffu && (bidx == 0xffffffffu || v > bv || (v == bv && i < bidx));
+  };
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    const float ov = __shfl_xor_sync(FULL, best, o);
+    const unsigned oi = __shfl_xor_sync(FULL, bi, o);
+    if (better(ov, oi, best, bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0xffffffffu;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(FULL, best, o);
+      const unsigned oi = __shfl_xor_sync(FULL, bi, o);
+      if (better(ov, oi, best, bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      const unsigned r = bi == 0xffffffffu ? 0u : bi; // all NaN: max_element returns the first element
+      if (out)
+        out[blockIdx.x] = r;
+      if (out_f)
+        out_f[blockIdx.x] = (float)r; // the reference feeds token ids back as floats
+    }
+  }
+}
+
+int launch_argmax(const float *x, long long rows, long long n, long long ld, unsigned *out, float *out_f, unsigned flags,
+                  cudaStream_t st) {
+  if (!x || (!out && !out_f) || rows < 0 || n <= 0 || n > 0xfffffff0ll)
+    return set_error(NNTR_CUDA_ERR_INVALID, "argmax: bad arguments");
+  if (rows == 0)
+    return NNTR_CUDA_OK;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)rows);
+  cfg.blockDim = dim3(1024);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, argmax_kernel, x, n, ld, out, out_f);
+  count_launch();
+  return check_cuda(e, "argmax launch");
+}
+
+} // namespace nntr

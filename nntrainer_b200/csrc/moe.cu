@@ -267,6 +267,13 @@ __global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__re
   y[i] = acc;
 }
 
+/** upper bound on the polls of waits on other ranks' data (0: the default of 2^22); set from the host */
+__device__ unsigned g_moe_exchange_polls = 0;
+__device__ __forceinline__ uint32_t moe_exchange_polls() {
+  const unsigned v = *reinterpret_cast<volatile unsigned *>(&g_moe_exchange_polls);
+  return v ? v : (1u << 22);
+}
+
 /* Expert-parallel combine: the expert outputs arrive as (value, call number) pairs stored by the owning ranks' down
  * projections into this rank's buffer (two buffers in alternation). First the heartbeat of every rank for this call
  * (all ranks run the same calls in the same order; a rank that is a call ahead can then not overwrite a buffer still
@@ -277,10 +284,11 @@ __global__ void moe_combine_ep_kernel(const uint2 *__restrict__ eo, const int *_
   pdl_wait();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const unsigned long long seq = (*ep.epoch - 1) * ep.layers_per_epoch + ep.layer + 1;
+  const uint32_t polls = moe_exchange_polls();
   if (threadIdx.x < ep.n_ranks) {
     const volatile unsigned long long *slot = ep.hb[ep.rank] + threadIdx.x;
     bool ok = false;
-    for (uint32_t it = 0; it < (1u << 22) && !ok; ++it) {
+    for (uint32_t it = 0; it < polls && !ok; ++it) {
       ok = *slot >= seq;
       if (!ok && it > 16)
         __nanosleep(64);
@@ -312,7 +320,7 @@ __global__ void moe_combine_ep_kernel(const uint2 *__restrict__ eo, const int *_
     const volatile uint2 *src = buf + (t * topk + bj) * H + h;
     uint32_t vx = 0, vy = 0;
     bool ok = false;
-    for (uint32_t it = 0; it < (1u << 22) && !ok; ++it) {
+    for (uint32_t it = 0; it < polls && !ok; ++it) {
       asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(vx), "=r"(vy) : "l"(src) : "memory");
       ok = vy == tag;
       if (!ok && it > 16)
@@ -521,11 +529,18 @@ extern "C" int nntr_cuda_moe_forward_ep_dev(const nntr_moe_desc *d, const nntr_m
 }
 
 namespace nntr {
+int set_exchange_poll_limit_moe(unsigned polls) {
+  return check_cuda(cudaMemcpyToSymbol(g_moe_exchange_polls, &polls, sizeof(unsigned)), "set_exchange_poll_limit");
+}
 int read_moe_status(int *out) {
   int v = 0;
   NNTR_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_moe_status, sizeof(int)));
   *out = v;
   return NNTR_CUDA_OK;
+}
+int clear_moe_status() {
+  const int zero = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_moe_status, &zero, sizeof(int)), "clear_moe_status");
 }
 } // namespace nntr
 

@@ -127,6 +127,11 @@ class NSplitGroup:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if self.world > MAX_RANKS:
             raise ValueError("N-split groups span the GPUs of one node (at most 8 ranks)")
+        if layers_per_epoch % 2:
+            # the two gathered buffers alternate per launch; with an odd number of launches per pass the first launch
+            # of the next pass would write the buffer the previous pass's last launch wrote, which a slower rank (or the
+            # caller) may still be reading: the "done reading" flags cover the input of the previous launch only
+            raise ValueError("layers_per_epoch must be even (pad the sequence with one more launch)")
         self.n_local, self.layers = n_local, layers_per_epoch
         L = lib()
         self._own = []

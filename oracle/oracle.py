@@ -394,3 +394,24 @@ def random_q6_K(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
     b = rng.integers(0, 256, size=(nblk, Q6_K_BLOCK), dtype=np.uint8)
     b[:, 208:210] = _rand_f16(rng, nblk, 1e-5, 2e-4).view(np.uint8).reshape(nblk, 2)
     return b.reshape(-1)
+
+
+def modellike_q4_Kx8(rng: np.random.Generator, N: int, K: int, std: float = 0.02) -> np.ndarray:
+    """Random Q4_K blocks whose dequantized weights have roughly zero mean and the given spread (random nibbles and
+    6-bit scales/mins; d chosen for the spread, dmin = 7.5 d so that d*sc*q - dmin*m centres on zero), so that a stack
+    of layers keeps activations in the range a trained model would."""
+    nblk = (N // 8) * (K // 256)
+    b = rng.integers(0, 256, size=(nblk, Q4_KX8_BLOCK), dtype=np.uint8)
+    d = (rng.uniform(0.8, 1.2, size=nblk * 8) * (std / 150.0)).astype(np.float32)
+    b[:, 0:16] = d.astype(np.float16).view(np.uint8).reshape(nblk, 16)
+    b[:, 16:32] = (7.5 * d).astype(np.float16).view(np.uint8).reshape(nblk, 16)
+    return b.reshape(-1)
+
+
+def modellike_q6_K(rng: np.random.Generator, N: int, K: int, std: float = 0.02) -> np.ndarray:
+    """Random Q6_K blocks with zero-mean weights of roughly the given spread (6-bit values are already centred)."""
+    nblk = N * (K // 256)
+    b = rng.integers(0, 256, size=(nblk, Q6_K_BLOCK), dtype=np.uint8)
+    d = (rng.uniform(0.8, 1.2, size=nblk) * (std / (18.5 * 74.0))).astype(np.float16)  # rms of q ~18.5, of int8 scales ~74
+    b[:, 208:210] = d.view(np.uint8).reshape(nblk, 2)
+    return b.reshape(-1)

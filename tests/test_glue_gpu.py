@@ -1,0 +1,183 @@
+"""The operators between the matmuls and the single-token attention on the GPU, through the C ABI, against the C
+restatement of the reference's x86 helpers (oracle/glue_port.c, itself pinned to the reference's own file in
+tests/test_glue_oracle.py): bit for bit."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from oracle import oracle as O  # noqa: E402
+
+BIG = 2 ** 31 - 1
+
+
+@pytest.fixture(scope="module")
+def be():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from nntrainer_b200 import backend, build
+    build.build()
+    backend.init(0)
+    return backend
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def same_bits(a, b):
+    return np.array_equal(np.ascontiguousarray(a, dtype=np.float32).view(np.uint32),
+                          np.ascontiguousarray(b, dtype=np.float32).view(np.uint32))
+
+
+@pytest.mark.parametrize("rows,width", [(1, 2560), (1, 2048), (1, 2880), (40, 128), (8, 64), (3, 40), (300, 4096)])
+def test_rms_norm_bit_exact(be, port, rows, width):
+    rng = np.random.default_rng(rows * 7 + width)
+    x = (rng.standard_normal((rows, width)) * 3).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, width).astype(np.float32)
+    got = be.rms_norm(dev(x), dev(g), 1e-6, width=width).cpu().numpy()
+    assert same_bits(got, port.rms_norm(x, g, 1e-6))
+    got = be.rms_norm(dev(x), None, 1e-5, width=width).cpu().numpy()
+    assert same_bits(got, port.rms_norm_wrt_width(x, width, 1e-5))
+
+
+@pytest.mark.parametrize("alpha", [None, 1.702])
+def test_swiglu_bit_exact_incl_denormals_and_clamps(be, port, alpha):
+    rng = np.random.default_rng(5)
+    for n in (8, 768, 2880, 9728, 100003):
+        g = (rng.standard_normal(n) * rng.choice([0.01, 1, 10, 60], n)).astype(np.float32)
+        u = rng.standard_normal(n).astype(np.float32)
+        g[:8] = [0.0, -0.0, 1e-41, -1e-40, 90.0, -90.0, 87.5, -200.0]
+        u[:3] = [1e-39, 3.0, -1e-42]
+        got = be.swiglu(dev(g), dev(u), alpha).cpu().numpy()
+        assert same_bits(got, port.swiglu(g, u, alpha)), n
+
+
+def test_add_and_argmax(be):
+    rng = np.random.default_rng(6)
+    a, b = rng.standard_normal(2560).astype(np.float32), rng.standard_normal(2560).astype(np.float32)
+    assert same_bits(be.add(dev(a), dev(b)).cpu().numpy(), a + b)
+    for n in (1, 31, 1024, 151936):
+        x = rng.standard_normal((3, n)).astype(np.float32)
+        if n > 31:
+            x[1, [n - 1, 17, n // 2]] = 9.0          # equal maxima: the first index wins
+            x[2, 0] = 11.0
+        idx, idx_f = be.argmax(dev(x))
+        want = np.argmax(x, axis=1)
+        assert np.array_equal(idx.cpu().numpy(), want.astype(np.int32)), n
+        assert np.array_equal(idx_f.cpu().numpy(), want.astype(np.float32)), n
+
+
+def test_embedding_rows_q6_K_q4_0_fp32_and_bad_index(be, port):
+    rng = np.random.default_rng(7)
+    V, H = 96, 512
+    ids = np.array([0, 95, 17, 17], dtype=np.float32)
+    t6 = O.random_q6_K(rng, V, H)
+    got = be.embedding("q6_K", dev(t6), dev(ids), V, H).cpu().numpy()
+    row = 210 * (H // 256)
+    for i, t in enumerate(ids.astype(int)):
+        assert same_bits(got[i], port.dequantize_row("q6_K", t6[t * row:(t + 1) * row], H))
+    blocks = rng.integers(0, 256, size=(V * (H // 32), 18), dtype=np.uint8)
+    blocks[:, 0:2] = rng.uniform(1e-3, 1e-2, V * (H // 32)).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    t4 = blocks.reshape(-1)
+    got = be.embedding("q4_0", dev(t4), dev(ids), V, H).cpu().numpy()
+    row = 18 * (H // 32)
+    for i, t in enumerate(ids.astype(int)):
+        assert same_bits(got[i], port.dequantize_row("q4_0", t4[t * row:(t + 1) * row], H))
+    tf = rng.standard_normal((V, H)).astype(np.float32)
+    got = be.embedding(None, dev(tf), dev(ids), V, H).cpu().numpy()
+    assert same_bits(got, tf[ids.astype(int)])
+    # an index beyond the table: the reference throws std::invalid_argument; here a zero row and a status
+    be.embedding("q6_K", dev(t6), dev(np.array([96.0], dtype=np.float32)), V, H)
+    with pytest.raises(ValueError):
+        be.device_status()
+    from nntrainer_b200.capi import check, lib
+    check(lib().nntr_cuda_clear_device_status())
+    be.device_status()
+
+
+def _attention_case(be, port, hq, hkv, hd, ctx, window, with_sink, seed):
+    rng = np.random.default_rng(seed)
+    max_seq = ctx + 2
+    sink = (rng.standard_normal(hq) * 2).astype(np.float32) if with_sink else None
+    att = be.Attention(hq, hkv, hd, max_seq, theta=1e6, window=window, sink=dev(sink) if with_sink else None)
+    cos, sin = be.rope_table(hd, max_seq, 1e6)
+    kc = np.zeros((max_seq, hkv, hd), dtype=np.uint16)
+    vc = np.zeros((max_seq, hkv, hd), dtype=np.uint16)
+    w = BIG if window is None else window
+    gqa = hq // hkv
+    pos_dev = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for pos in range(ctx):
+        q = rng.standard_normal(hq * hd).astype(np.float32)
+        k = rng.standard_normal(hkv * hd).astype(np.float32)
+        v = rng.standard_normal(hkv * hd).astype(np.float32)
+        qd = dev(q)
+        if pos % 2:  # alternate between the position by value and through a device word
+            pos_dev.fill_(pos)
+            out = att.step(qd, dev(k), dev(v), 0, pos_dev=pos_dev)
+        else:
+            out = att.step(qd, dev(k), dev(v), pos)
+        qr = port.rotary(q, hd, cos[pos], sin[pos])
+        kc[pos] = port.rotary(k, hd, cos[pos], sin[pos], to_fp16=True).reshape(hkv, hd)
+        vc[pos] = port.rotary(v, hd, cos[pos], sin[pos], to_fp16=True, only_convert=True).reshape(hkv, hd)
+        if pos in (0, 1, ctx // 2, ctx - 1) or (window and pos in (window - 1, window, window + 1)):
+            assert same_bits(qd.cpu().numpy(), qr), ("rotary q", pos)
+            assert np.array_equal(att.kcache[pos].cpu().numpy().view(np.uint16), kc[pos]), ("k cache", pos)
+            assert np.array_equal(att.vcache[pos].cpu().numpy().view(np.uint16), vc[pos]), ("v cache", pos)
+            sc = port.compute_kcaches(qr, kc, pos + 1, hkv, hd, gqa, w)
+            pr = port.softmax_rows(sc, 0, sc.shape[0], sink, True)
+            want = port.compute_vcache(pos, pr, vc, hkv, gqa, hd, w).reshape(-1)
+            assert same_bits(out.cpu().numpy(), want), ("attention", pos)
+    be.device_status()
+
+
+@pytest.mark.parametrize("hq,hkv,hd,ctx,window,with_sink", [
+    (32, 8, 128, 70, None, False),     # Qwen3-4B heads
+    (32, 4, 128, 40, None, False),     # Qwen3-30B-A3B heads (8 query heads per key/value head)
+    (64, 8, 64, 150, 128, True),       # GPT-OSS: sliding window 128 and sinks
+    (64, 8, 64, 40, None, True),       # GPT-OSS full-attention layer with sinks
+    (8, 8, 8, 5, 3, False),            # smallest vector widths, window shorter than the context
+])
+def test_single_token_attention_bit_exact(be, port, hq, hkv, hd, ctx, window, with_sink):
+    _attention_case(be, port, hq, hkv, hd, ctx, window, with_sink, seed=hq + ctx)
+
+
+def test_attention_long_context_2048(be, port):
+    """BASELINE's decode context for the Qwen3-30B-A3B shape: the row-ordered sums over 2048 cache rows."""
+    rng = np.random.default_rng(11)
+    hq, hkv, hd, ctx = 32, 4, 128, 2048
+    att = be.Attention(hq, hkv, hd, ctx, theta=1e6)
+    kc = rng.standard_normal((ctx, hkv, hd)).astype(np.float16)
+    vc = rng.standard_normal((ctx, hkv, hd)).astype(np.float16)
+    att.kcache.copy_(torch.from_numpy(kc).cuda())
+    att.vcache.copy_(torch.from_numpy(vc).cuda())
+    cos, sin = be.rope_table(hd, ctx, 1e6)
+    pos = ctx - 1
+    q = rng.standard_normal(hq * hd).astype(np.float32)
+    k = rng.standard_normal(hkv * hd).astype(np.float32)
+    v = rng.standard_normal(hkv * hd).astype(np.float32)
+    qd = dev(q)
+    out = att.step(qd, dev(k), dev(v), pos).cpu().numpy()
+    kcu, vcu = kc.view(np.uint16).copy(), vc.view(np.uint16).copy()
+    kcu[pos] = port.rotary(k, hd, cos[pos], sin[pos], to_fp16=True).reshape(hkv, hd)
+    vcu[pos] = port.rotary(v, hd, cos[pos], sin[pos], to_fp16=True, only_convert=True).reshape(hkv, hd)
+    qr = port.rotary(q, hd, cos[pos], sin[pos])
+    sc = port.compute_kcaches(qr, kcu, ctx, hkv, hd, hq // hkv, BIG)
+    pr = port.softmax_rows(sc, 0, ctx, None, True)
+    want = port.compute_vcache(pos, pr, vcu, hkv, hq // hkv, hd, BIG).reshape(-1)
+    assert same_bits(out, want)
+
+
+def test_attention_argument_checks(be):
+    from nntrainer_b200 import capi
+    import ctypes as C
+    L = capi.lib()
+    d = torch.zeros(4096, device="cuda")
+    bad = capi.AttnDesc(12, 4, 128, 0xFFFFFFFF, None)   # 12 heads: the reference would take its scalar libm tail
+    rc = L.nntr_cuda_attention_decode_dev(C.byref(bad), 0, None, 1, d.data_ptr(), d.data_ptr(), d.data_ptr(), d.data_ptr(),
+                                          d.data_ptr(), 4096, 0, None)
+    assert rc == capi.ERR_UNSUPPORTED
+    ok = capi.AttnDesc(8, 3, 128, 0xFFFFFFFF, None)
+    assert L.nntr_cuda_attention_decode_dev(C.byref(ok), 0, None, 1, d.data_ptr(), d.data_ptr(), d.data_ptr(), d.data_ptr(),
+                                            d.data_ptr(), 4096, 0, None) == capi.ERR_INVALID

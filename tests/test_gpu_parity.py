@@ -355,3 +355,41 @@ def test_full_size_gemv_row_permutation(be):
     be.gemv("q4_K", N, K, x, dev(B.reshape(-1)), y1)
     be.gemv("q4_K", N, K, x, dev(B[perm].reshape(-1)), y2)
     assert torch.equal(y2.view(N // 8, 8), y1.view(N // 8, 8)[torch.from_numpy(perm).cuda()])
+
+
+def test_weight_cache_rejects_mismatched_slices_and_follows_rewrites(be, port):
+    """The host-pointer GEMMs use a device copy keyed by the weight's host address. A call whose B lies inside a
+    registered tensor must agree with it (format, K, row-group boundary, all rows inside); a host buffer that is
+    rewritten in place (the reference's cached MoE layers activate and deactivate expert tensors in the same memory,
+    gpt_oss_moe_layer_cached.cpp:315-391) gives the new result after unregister."""
+    from nntrainer_b200 import capi
+    L = capi.lib()
+    rng = np.random.default_rng(21)
+    N, K = 64, 512
+    B = O.random_q4_Kx8(rng, N, K)
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    be.register_weight("q4_K", B, N, K)
+    try:
+        y = np.zeros((1, N), dtype=np.float32)
+        # a row slice: rows 16..47 = bytes [16*row, 48*row)
+        row = K // 256 * 144
+        y2 = np.zeros((1, 32), dtype=np.float32)
+        be.gemm_q4_K(1, 32, K, x, K, B[16 * row:], 32, y2, 32)
+        assert np.array_equal(y2.view(np.uint32), port.gemm("q4_K", x, B, N)[:, 16:48].view(np.uint32))
+        # wrong K, wrong format, off a row-group boundary, past the end: all rejected, nothing read
+        for fn, n, k, sl in ((L.nntr_cuda_gemm_q4_K, N, 256, B), (L.nntr_cuda_gemm_q6_K, N, K, B),
+                             (L.nntr_cuda_gemm_q4_K, 8, K, B[row:]), (L.nntr_cuda_gemm_q4_K, N, K, B[8 * row:])):
+            xx = np.zeros((1, k), dtype=np.float32)
+            rc = fn(1, n, k, xx.ctypes.data, k, sl.ctypes.data, n, y.ctypes.data, n)
+            assert rc == capi.ERR_INVALID, L.nntr_cuda_last_error()
+    finally:
+        be.unregister_weight(B)
+    # rewrite in place after unregister: the next call uploads the new bytes
+    B2 = O.random_q4_Kx8(rng, N, K)
+    y = np.zeros((1, N), dtype=np.float32)
+    be.gemm_q4_K(1, N, K, x, K, B, N, y, N)            # implicit upload of the old bytes
+    be.unregister_weight(B)
+    B[:] = B2
+    be.gemm_q4_K(1, N, K, x, K, B, N, y, N)
+    be.unregister_weight(B)
+    assert np.array_equal(y.view(np.uint32), port.gemm("q4_K", x, B2, N).view(np.uint32))

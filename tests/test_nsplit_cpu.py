@@ -72,3 +72,15 @@ def test_two_gloo_ranks_exchange_handles_in_rank_order():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert res == [(0, True, 0, 4096), (1, True, 4096, 8192)]
+
+
+def test_odd_launch_count_per_pass_is_rejected():
+    """Two gathered buffers alternate per launch: with an odd number of launches per pass consecutive launches across a
+    pass boundary would write the same buffer. The group refuses such a sequence before touching any device."""
+    with pytest.raises(ValueError):
+        nsplit.NSplitGroup(512, 3)
+    # consecutive launch numbers alternate parity across a pass boundary exactly when the count is even
+    for L in (2, 4, 48):
+        seq = [nsplit.sequence_number(e, L, l) for e in (1, 2, 3) for l in range(L)]
+        assert all((a + 1) == b for a, b in zip(seq, seq[1:]))
+        assert all((nsplit.sequence_number(e, L, l) % 2) == ((l + 1) % 2) for e in (1, 2, 3) for l in range(L))

@@ -5,8 +5,9 @@ model's tensors were planned into one pool before inference started) or on a
 path where a cudaMalloc's device-wide stall is not acceptable. For them the
 library carries its own 4 MiB scratch array; this test drives that entry point
 straight through the C ABI and requires the same bits as the regular entry point
-(which gets a caller-owned workspace), on two calls in a row, because the second
-call finds the first call's leftovers in the shared array.
+on its exact path (which gets a caller-owned workspace) AND as the CPU checker,
+on two calls in a row, because the second call finds the first call's leftovers
+in the shared array.
 
 Collected last on purpose (file name), so a failure here cannot hide the other
 tests from a run that stops at the first failure. It must pass alone in a fresh
@@ -46,12 +47,19 @@ def _run_pair(L, M, N, K, seed):
     need = L.nntr_cuda_gemm_workspace_bytes(capi.Q4_K, M, N, K)
     ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
     want = torch.full((M, N), float("nan"), device="cuda")
-    capi.check(L.nntr_cuda_gemm_q4_K_dev(M, N, K, A.data_ptr(), K, B.data_ptr(), N, want.data_ptr(), N,
-                                         ws.data_ptr(), ws.numel(), st))
+    # the no-alloc entry point always runs the bit-exact kernels: compare with the regular one on that path
+    capi.check(L.nntr_cuda_set_gemm_path(1))
+    try:
+        capi.check(L.nntr_cuda_gemm_q4_K_dev(M, N, K, A.data_ptr(), K, B.data_ptr(), N, want.data_ptr(), N,
+                                             ws.data_ptr(), ws.numel(), st))
+    finally:
+        capi.check(L.nntr_cuda_set_gemm_path(0))
     # the entry point under test: no workspace argument, nothing allocated inside
     got = torch.full((M, N), float("nan"), device="cuda")
     capi.check(L.nntr_cuda_gemm_q4_K_noalloc_dev(M, N, K, A.data_ptr(), K, B.data_ptr(), N, got.data_ptr(), N, st))
     torch.cuda.synchronize()
+    cpu = O.port().gemm("q4_K", A.cpu().numpy(), B.cpu().numpy(), N)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), cpu.view(np.uint32)), "differs from the CPU checker"
     return got.cpu().numpy(), want.cpu().numpy()
 
 
@@ -63,6 +71,14 @@ def test_two_calls_in_a_row_match_the_regular_entry_point(L):
     # second call: different, smaller shape; the array still holds the first call's rows
     got, want = _run_pair(L, M=6, N=64, K=1024, seed=2)
     assert np.max(np.abs(got - want)) <= REL_TOL * np.max(np.abs(want))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 512), (8, 64, 512), (40, 256, 1024), (896, 8, 4096)])
+def test_more_shapes_incl_gemv_whole_groups_tensor_sized_and_the_largest_accepted(L, M, N, K):
+    """M = 1 (the decode GEMV), M % 4 == 0 (no leftover rows), a shape the regular entry point would send to the tensor
+    cores under its default setting, and the largest call the 4 MiB array takes (896 rows of 4096)."""
+    got, want = _run_pair(L, M, N, K, seed=M + N)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
