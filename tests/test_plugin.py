@@ -1,0 +1,80 @@
+"""The C++ host side of the boundary (plugin/): the run-time context plug-in loads the way the reference's Engine
+loads an external context and shows the name, allocator and factory behaviour the Engine relies on; its unresolved
+symbols are the framework's and nothing else; the cpu_backend-shaped functions give the CPU checker's results through
+the GPU and map errors to the exception types of the CPU path."""
+import os
+import struct
+import subprocess
+import tempfile
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BUILD = os.path.join(ROOT, "plugin", "_build")
+
+
+@pytest.fixture(scope="module")
+def built():
+    from nntrainer_b200 import build as nb_build
+    from oracle import oracle as O
+    nb_build.build()
+    subprocess.run(["make", "-C", os.path.join(ROOT, "plugin"), f"REF={O.reference_root()}"], check=True,
+                   stdout=subprocess.DEVNULL)
+    return BUILD
+
+
+def test_backend_library_exports_the_cpu_backend_names(built):
+    out = subprocess.run(["nm", "-DC", "--defined-only", os.path.join(built, "libcuda_backend.so")],
+                         capture_output=True, text=True, check=True).stdout
+    for fn in ("gemm_q4_0_cuda", "gemm_q4_K_cuda", "gemm_q6_K_cuda", "quantize_row_q8_K_cuda", "quantize_row_q8_0_cuda",
+               "dequantize_row_q4_K_cuda", "dequantize_row_q4_0_cuda", "dequantize_row_q6_K_cuda",
+               "dequantize_row_q8_K_cuda", "dequantize_row_q8_0_cuda", "register_weight_cuda", "unregister_weight_cuda"):
+        assert f"nntrainer::{fn}(" in out, fn
+
+
+def test_context_plugin_loads_like_an_external_context(built):
+    so, probe = os.path.join(built, "libcuda_context.so"), os.path.join(built, "context_probe")
+    if not (os.path.exists(so) and os.path.exists(probe)):
+        pytest.skip("plug-in not built (needs the reference's headers at build time)")
+    r = subprocess.run([probe, so], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr
+    kv = dict(line.split("=", 1) for line in r.stdout.split())
+    assert kv["name"] == "gpu"                       # parseComputeEngine knows cpu / gpu / qnn only
+    assert kv["mem_allocator"] != "null"             # Engine::registerContext dereferences it
+    assert kv["unknown_layer_rejected"] == "1" and kv["unknown_key_rejected"] == "1"
+    # unresolved symbols: the C ABI, the C/C++ runtime, and exactly three of the framework
+    out = subprocess.run(["nm", "-DC", "--undefined-only", so], capture_output=True, text=True, check=True).stdout
+    syms = [l.split(" U ", 1)[1].strip() for l in out.splitlines() if " U " in l]
+    fw = sorted(s for s in syms if "@" not in s and not s.startswith("nntr_cuda_"))
+    assert fw == ["__nntrainer_log_print", "nntrainer::FullyConnectedLayer::FullyConnectedLayer()",
+                  "vtable for nntrainer::MemAllocator"], fw
+    defined = subprocess.run(["nm", "-D", "--defined-only", so], capture_output=True, text=True, check=True).stdout
+    assert "ml_train_context_pluggable" in defined
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("q,M,N,K", [("q4_K", 1, 512, 1024), ("q4_K", 6, 136, 512), ("q4_0", 5, 64, 160), ("q6_K", 3, 50, 512)])
+def test_backend_functions_match_the_checker_through_the_gpu(built, port, q, M, N, K):
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from oracle import oracle as O
+    rng = np.random.default_rng(M + N)
+    gen = {"q4_K": O.random_q4_Kx8, "q4_0": O.random_q4_0x8, "q6_K": O.random_q6_K}[q]
+    B = gen(rng, N, K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    with tempfile.TemporaryDirectory() as td:
+        case, res = os.path.join(td, "case.bin"), os.path.join(td, "res.bin")
+        with open(case, "wb") as f:
+            f.write(struct.pack("<iIII", {"q4_0": 2, "q4_K": 12, "q6_K": 14}[q], M, N, K))
+            f.write(A.tobytes())
+            f.write(B.tobytes())
+        r = subprocess.run([os.path.join(built, "backend_driver"), case, res], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stdout + r.stderr
+        raw = np.fromfile(res, dtype=np.uint8)
+    C = raw[:M * N * 4].view(np.float32).reshape(M, N)
+    qa = raw[M * N * 4:]
+    assert np.array_equal(C.view(np.uint32), port.gemm(q, A, B, N).view(np.uint32))
+    want_q = port.quantize_row_q8_0(A[0]) if q == "q4_0" else port.quantize_row_q8_K(A[0])
+    assert np.array_equal(qa, want_q)
