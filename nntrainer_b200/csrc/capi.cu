@@ -412,6 +412,8 @@ int nntr_cuda_device_status(void) {
     return rc;
   if (!v && (rc = read_f16_status(&v)))
     return rc;
+  if (!v && (rc = read_resident_status(&v)))
+    return rc;
   if (v)
     return set_error(v, "a device kernel gave up on a bounded wait (status %d)", v);
   if ((rc = read_embed_status(&v, false)))
@@ -427,7 +429,7 @@ namespace nntr {
 int clear_device_status_words() {
   int rc;
   if ((rc = clear_device_status()) || (rc = clear_umma_status()) || (rc = clear_q6_status()) ||
-      (rc = clear_moe_status()) || (rc = clear_q40_status()) || (rc = clear_f16_status()))
+      (rc = clear_moe_status()) || (rc = clear_q40_status()) || (rc = clear_f16_status()) || (rc = clear_resident_status()))
     return rc;
   return NNTR_CUDA_OK;
 }

@@ -273,6 +273,12 @@ int launch_gemv_q4_K_nsplit(unsigned N, unsigned K, const float *x, const void *
 int launch_gemv_q4_K_batched_publish(unsigned N, unsigned K, const float *x, unsigned n_problems, GemvBatch batch,
                                      GemvExchange ex, cudaStream_t st);
 int read_moe_status(int *out);
+/* resident-weights variant for small per-CTA shares (gemv_q4k_resident.cu) */
+bool gemv_q4_K_resident_supported(unsigned N, unsigned K);
+int launch_gemv_q4_K_resident(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
+                              cudaStream_t st);
+int read_resident_status(int *out);
+int clear_resident_status();
 int launch_epoch_bump(unsigned long long *epoch, cudaStream_t st);
 int launch_gemv_q4_0(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
 int launch_gemv_q6_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);

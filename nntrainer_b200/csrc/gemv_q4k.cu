@@ -65,6 +65,11 @@ __device__ __forceinline__ uint32_t exchange_polls(uint32_t dflt) {
   return v ? v : dflt;
 }
 
+static int env_int(const char *name, int dflt) {
+  const char *v = getenv(name);
+  return v ? atoi(v) : dflt;
+}
+
 /** Bounded wait (pipeline.cuh); raises this file's status word when it runs out. */
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
   return mbar_wait_bounded(bar, parity, abort_flag, &g_device_status, WAIT_POLLS, 1024);
@@ -448,12 +453,12 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
   }
 }
 
-static int env_int(const char *name, int dflt) {
-  const char *v = getenv(name);
-  return v ? atoi(v) : dflt;
-}
-
 int launch_gemv_q4_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st) {
+  // launches whose per-CTA share fits in shared memory at once take the kernel that decodes its weights before the
+  // activation is available (gemv_q4k_resident.cu); NNTR_CUDA_GEMV_RESIDENT=0 keeps them on the streaming kernel
+  static const int use_resident = env_int("NNTR_CUDA_GEMV_RESIDENT", 1);
+  if (use_resident && x && y && B && gemv_q4_K_resident_supported(N, K))
+    return launch_gemv_q4_K_resident(N, K, x, B, y, flags, st);
   GemvBatch none = {};
   return launch_gemv_q4_K_batched(N, K, x, B, y, flags, 1, none, st);
 }
