@@ -308,6 +308,91 @@ def decode_step_qwen3_4b(be, torch, dev, peak, steps=10):
 
 
 # --------------------------------------------------------------------------
+# whole-model greedy decoding of a Qwen3-4B-shaped decoder: every operator of the graph, weights from a .bin file
+# --------------------------------------------------------------------------
+def model_decode_qwen3_4b(be, torch, dev, peak, context=512, new_tokens=64, cpu_tokens=3):
+    """cfg3: 36 layers, hidden 2560, 32 query / 8 key-value heads of 128, SwiGLU 9728, vocabulary 151936; Q4_K
+    projections, Q6_K embedding and lm_head, fp16 key/value cache. Random block bytes scaled like N(0, 0.02^2) weights
+    are written to a .bin file in the reference's layout and loaded through the library's loader. The first
+    `context` cache rows are filled with random fp16 values in place of a prefill (multi-token attention is not built),
+    then `new_tokens` greedy steps run from one captured CUDA graph (position and token id live on the device), every
+    operator included: embedding row, RMS norms, q/k/v/o and FFN projections, per-head q/k norms, rotary embedding,
+    attention over the cache, SwiGLU, residual adds, lm_head, arg-max. The reference's CPU pipeline (the checker's
+    functions, GEMVs from the reference's own code where it was built) decodes a few tokens of the same model beside
+    it as a reported baseline."""
+    import os
+    import tempfile
+    import time
+    from nntrainer_b200.decoder import DecoderConfig, Qwen3Decoder, tensor_list
+    from oracle import oracle as O
+    from oracle.cpu_decoder import CpuDecoder, synthetic_weights, write_bin
+    cfg = DecoderConfig(n_layers=36, hidden=2560, n_heads=32, n_kv_heads=8, head_dim=128, inter=9728, vocab=151936,
+                        max_seq=context + new_tokens + 8)
+    w = synthetic_weights(cfg, seed=5)
+    wbytes = sum(int(a.nbytes) for n, a in w.items() if a.dtype == np.uint8)
+    with tempfile.TemporaryDirectory() as td:
+        path = os.path.join(td, "qwen3_4b_shape.bin")
+        write_bin(path, cfg, w)
+        t0 = time.perf_counter()
+        dec = Qwen3Decoder(cfg, path, pdl=True)
+        load_s = time.perf_counter() - t0
+    g = torch.Generator(device=dev)
+    g.manual_seed(9)
+    kv = []
+    for a in dec.attn:
+        kc = (torch.randn((context, cfg.n_kv_heads, cfg.head_dim), device=dev, generator=g) * 0.5).to(torch.float16)
+        vc = (torch.randn((context, cfg.n_kv_heads, cfg.head_dim), device=dev, generator=g) * 0.5).to(torch.float16)
+        a.kcache[:context].copy_(kc)
+        a.vcache[:context].copy_(vc)
+        kv.append((kc, vc))
+    graph = dec.capture(context)
+    dec.tok_f.fill_(11.0)
+    stream = torch.cuda.current_stream()
+    for _ in range(3):
+        graph.replay()
+    dec.pos_dev[0] = context  # the warm-up replays advanced the position
+    dec.tok_f.fill_(11.0)
+    toks = torch.zeros(new_tokens, dtype=torch.int32, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(new_tokens):
+        graph.replay()
+        toks[i:i + 1].copy_(dec.tok, non_blocking=True)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    be.device_status()
+    ms = e0.elapsed_time(e1) / new_tokens
+    got = toks.cpu().numpy().tolist()
+    kv_bytes = 2 * cfg.n_layers * (context + new_tokens // 2) * cfg.n_kv_heads * cfg.head_dim * 2
+    # CPU pipeline on the same model and cache, a few tokens: the token stream must be the same
+    cos, sin = be.rope_table(cfg.head_dim, cfg.max_seq, cfg.rope_theta)
+    cpu = CpuDecoder(cfg, w, cos, sin, matmul=O.ref(fast=True) if O.ref_available() else None)
+    for i, (kc, vc) in enumerate(kv):
+        cpu.kc[i][:context] = kc.cpu().numpy().view(np.uint16)
+        cpu.vc[i][:context] = vc.cpu().numpy().view(np.uint16)
+    t0 = time.perf_counter()
+    want, nxt = [], 11
+    for i in range(cpu_tokens):
+        nxt = cpu.step(nxt, context + i)
+        want.append(nxt)
+    cpu_s = (time.perf_counter() - t0) / cpu_tokens
+    n_launch = 1 + cfg.n_layers * 12 + 3 + 1  # embedding, 12 per layer, final norm + lm_head + arg-max, position bump
+    out = {"shape": "Qwen3-4B-shaped decoder, whole model, batch 1, greedy, context %d" % context,
+           "tokens": new_tokens, "ms_per_token": round(ms, 4), "tok/s": round(1e3 / ms, 1),
+           "launches_per_token": n_launch, "weight_bytes_per_token": wbytes, "kv_cache_bytes_per_token": kv_bytes,
+           "GB/s": round((wbytes + kv_bytes) / (ms * 1e-3) / 1e9, 1),
+           "frac_of_hbm_peak": round((wbytes + kv_bytes) / (ms * 1e-3) / 1e9 / peak, 4),
+           "bin_load_s": round(load_s, 2),
+           "cpu_pipeline": {"tok/s": round(1.0 / cpu_s, 2), "tokens": cpu_tokens,
+                            "gemv": "oracle/_ref (reference code, its OpenMP threading)" if O.ref_available() else "C restatement, 1 thread"},
+           "first_tokens_equal_cpu": got[:cpu_tokens] == want, "distinct_tokens": len(set(got))}
+    dec.close()
+    del dec, kv, w
+    torch.cuda.empty_cache()
+    return out
+
+
+# --------------------------------------------------------------------------
 # one decode token through the MoE layers of a Qwen3-30B-A3B-shaped decoder, expert-parallel over the ranks
 # --------------------------------------------------------------------------
 QWEN3_30B_A3B = {"layers": 48, "hidden": 2048, "experts": 128, "top_k": 8, "inter": 768}
@@ -685,6 +770,7 @@ def run_ours(args):
         others = other_shapes(be, torch, dev, peak) if (world == 1 and not args.no_extra) else None
         prefill = prefill_gemm_shapes(be, torch, dev) if (world == 1 and not args.no_extra) else None
         decode = decode_step_qwen3_4b(be, torch, dev, peak) if (world == 1 and not args.no_extra) else None
+        model = model_decode_qwen3_4b(be, torch, dev, peak) if (world == 1 and not args.no_extra and not args.no_model) else None
         cpu_desc = None
         if world == 1 and not args.no_cpu:
             _, cpu_desc, _ = cpu_reference_gbps(host_ring, args.cpu_seconds)
@@ -709,7 +795,7 @@ def run_ours(args):
                             "kernel": "gemv_q4_K_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
                "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
                "other_decode_gemv_shapes": others, "prefill_gemm_sweep": prefill,
-               "decode_step": decode, "moe_decode_step": moe}
+               "decode_step": decode, "model_decode": model, "moe_decode_step": moe}
         print(json.dumps(out))
     if group is not None:
         group.close()
@@ -789,6 +875,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the other decode GEMV shapes")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer end-to-end leg (profiling runs)")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE decode step")
+    ap.add_argument("--no-model", action="store_true", help="skip the whole-model decode leg")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--ring", type=int, default=RING, help="distinct weight matrices per step (default keeps every launch out of L2)")
     ap.add_argument("--traffic", type=float, default=None,

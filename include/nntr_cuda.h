@@ -181,6 +181,15 @@ int nntr_cuda_gemm_q4_K_noalloc_dev(unsigned M, unsigned N, unsigned K, const fl
 int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
                        void *stream);
 
+/** Several decode GEMVs that share one activation in one launch: y[p][0..N) = W_p x for p < n_problems, with
+ *  w_table a DEVICE array of n_problems device pointers to Q4_K weights of N rows x K each (e.g. the q, k and v
+ *  projections of a layer cut into equal row slices, or the two halves of a gated FFN). Each output equals the
+ *  single-problem call's bit for bit. The table must be complete before the previous kernel of the stream starts
+ *  (it is read without waiting for that kernel). The reference runs these projections as separate
+ *  FullyConnectedLayer calls; one launch saves their launch and dependency latencies. */
+int nntr_cuda_gemv_batched_dev(int qtype, unsigned N, unsigned K, const float *x, const void *const *w_table,
+                               unsigned n_problems, float *y, unsigned flags, void *stream);
+
 /* ------------------------------------------- operators between the matmuls */
 
 /** RMS normalisation over rows of `width` floats, then times gamma[width] (gamma may be NULL):
@@ -190,6 +199,12 @@ int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const 
  *  (nntrainer/tensor/cpu_backend/x86/avx2_impl.cpp:1751-1809); width % 8 == 0. x == y is allowed. */
 int nntr_cuda_rms_norm_dev(const float *x, const float *gamma, float *y, int64_t rows, int width, float eps,
                            unsigned flags, void *stream);
+/** The residual connection and the norm behind it in one launch: sum = a + b (the "addition" layer between a decoder
+ *  block's halves, Applications/CausalLM/causal_lm.cpp:586-609; one rounded addition per element), y = the RMS norm of
+ *  sum times gamma as above. Same bits as nntr_cuda_add_dev followed by nntr_cuda_rms_norm_dev. sum may alias a or b.
+ *  Rows of at most 11264 elements. */
+int nntr_cuda_add_rms_norm_dev(const float *a, const float *b, float *sum, const float *gamma, float *y, int64_t rows,
+                               int width, float eps, unsigned flags, void *stream);
 /** out[i] = (gate[i] / (1 + exp(-gate[i]))) * up[i]: nntrainer::swiglu(N, X, Y, Z)
  *  (cpu_backend.h swiglu -> x86/avx2_impl.cpp:906-947), same bits (table + cubic exponential, flush-to-zero). */
 int nntr_cuda_swiglu_dev(float *out, const float *gate, const float *up, int64_t n, unsigned flags, void *stream);
@@ -201,7 +216,8 @@ int nntr_cuda_swiglu_alpha_dev(float *out, const float *gate, const float *up, i
 int nntr_cuda_add_dev(float *out, const float *a, const float *b, int64_t n, unsigned flags, void *stream);
 /** Greedy sampler: per row of n logits (row stride ld) the index of the greatest, the lowest index among equals --
  *  std::max_element as Applications/CausalLM/causal_lm.cpp:530-533 calls it. idx_out (uint32) and/or idx_out_f
- *  (the index as a float, the form in which the reference feeds the token back into its input tensor) may be NULL. */
+ *  (the index as a float, the form in which the reference feeds the token back into its input tensor) may be NULL.
+ *  At most 1024 rows per call. The first call on a device allocates a small scratch (make it before stream capture). */
 int nntr_cuda_argmax_dev(const float *logits, int64_t rows, int64_t n, int64_t ld, unsigned *idx_out, float *idx_out_f,
                          unsigned flags, void *stream);
 /** Embedding lookup: y[i][0..out_dim) = row ids[i] of `table`, dequantized. The table holds in_dim PLAIN rows
@@ -231,6 +247,14 @@ int nntr_cuda_rope_table(unsigned head_dim, unsigned seq_len, float theta, float
 int nntr_cuda_rope_cache_append_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q,
                                     const float *k, const float *v, void *kcache, void *vcache, const float *cos_tab,
                                     const float *sin_tab, unsigned flags, void *stream);
+/** The same with the per-head RMS norms of Qwen3 in front (q_norm and k_norm layers, ReshapedRMSNormLayer with
+ *  feature_size = head_dim: Applications/CausalLM/qwen3_causallm.cpp:60-93, reshaped_rms_norm.cpp:84-100): q and k are
+ *  normalised per head and multiplied by q_gamma / k_gamma [head_dim] before the rotary embedding. One launch instead
+ *  of three; same bits as nntr_cuda_rms_norm_dev on q and k followed by nntr_cuda_rope_cache_append_dev. */
+int nntr_cuda_qk_norm_rope_cache_append_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q,
+                                            const float *k, const float *v, const float *q_gamma, const float *k_gamma,
+                                            float eps, void *kcache, void *vcache, const float *cos_tab,
+                                            const float *sin_tab, unsigned flags, void *stream);
 /** Scratch for the call below: scores of min(max_rows, window) cache rows x n_heads_q. */
 size_t nntr_cuda_attention_workspace_bytes(const nntr_attn_desc *a, unsigned max_rows);
 /** Second half (mha_core.cpp:521-531): scores of the query against cache rows [max(0, pos+1-window), pos]

@@ -129,6 +129,14 @@ def gemv(qtype: str, N: int, K: int, x, B, y, pdl: bool = False):
     return y
 
 
+def gemv_batched(qtype: str, N: int, K: int, x, w_table, n_problems: int, y, pdl: bool = False):
+    """n_problems decode GEMVs sharing the activation x in one launch; w_table is a device int64 tensor of weight
+    addresses (N rows x K each), y is [n_problems, N]."""
+    check(lib().nntr_cuda_gemv_batched_dev(QTYPE[qtype], N, K, x.data_ptr(), w_table.data_ptr(), n_problems,
+                                           y.data_ptr(), capi.GEMV_PDL if pdl else 0, _stream()))
+    return y
+
+
 # ---------------------------------------------------------------- quantizers
 def quantize_row_q8_K(src, dst=None, k: int | None = None):
     """cpu_backend.h:1093. numpy in -> numpy uint8 blocks out (host entry point)."""
@@ -305,6 +313,17 @@ def rms_norm(x, gamma, eps: float, width: int | None = None, out=None, pdl: bool
     return out
 
 
+def add_rms_norm(a, b, gamma, eps: float, sum_out=None, out=None, pdl: bool = False):
+    """sum = a + b and out = RMS norm of sum times gamma, in one launch (residual connection + the norm behind it)."""
+    torch = _torch()
+    sum_out = torch.empty_like(a) if sum_out is None else sum_out
+    out = torch.empty_like(a) if out is None else out
+    width = a.shape[-1]
+    check(lib().nntr_cuda_add_rms_norm_dev(a.data_ptr(), b.data_ptr(), sum_out.data_ptr(), gamma.data_ptr(),
+                                           out.data_ptr(), a.numel() // width, width, eps, _flags(pdl), _stream()))
+    return sum_out, out
+
+
 def swiglu(gate, up, alpha: float | None = None, out=None, pdl: bool = False):
     """nntrainer::swiglu (cpu_backend swiglu -> x86/avx2_impl.cpp:906 / :950 with a slope). Device tensors."""
     torch = _torch()
@@ -325,13 +344,13 @@ def add(a, b, out=None, pdl: bool = False):
     return out
 
 
-def argmax(logits, pdl: bool = False):
+def argmax(logits, pdl: bool = False, out=(None, None)):
     """Greedy sampler over the last dimension: std::max_element (Applications/CausalLM/causal_lm.cpp:530-533).
     Returns (uint32 indices as an int32 tensor, the same as float32)."""
     torch = _torch()
     rows, n = logits.numel() // logits.shape[-1], logits.shape[-1]
-    idx = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    idx_f = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(rows, dtype=torch.int32, device=logits.device) if out[0] is None else out[0]
+    idx_f = torch.empty(rows, dtype=torch.float32, device=logits.device) if out[1] is None else out[1]
     check(lib().nntr_cuda_argmax_dev(logits.data_ptr(), rows, n, n, idx.data_ptr(), idx_f.data_ptr(), _flags(pdl), _stream()))
     return idx, idx_f
 
@@ -379,15 +398,23 @@ class Attention:
         need = int(lib().nntr_cuda_attention_workspace_bytes(C.byref(self.desc), max_seq))
         self.ws = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
 
-    def step(self, q, k, v, pos: int, pos_dev=None, out=None, pdl: bool = False):
-        """q [hq*hd] (rotated in place), k, v [hkv*hd] fp32 device tensors of the token at ``pos`` -> out [hq*hd]."""
+    def step(self, q, k, v, pos: int, pos_dev=None, out=None, pdl: bool = False, qk_norm=None):
+        """q [hq*hd] (rotated in place), k, v [hkv*hd] fp32 device tensors of the token at ``pos`` -> out [hq*hd].
+        ``qk_norm`` = (q_gamma, k_gamma, eps) applies Qwen3's per-head RMS norms to q and k in the same launch."""
         torch = _torch()
         C = self._C
         out = torch.empty(self.hq * self.hd, dtype=torch.float32, device=q.device) if out is None else out
         pd = pos_dev.data_ptr() if pos_dev is not None else None
-        check(lib().nntr_cuda_rope_cache_append_dev(C.byref(self.desc), pos, pd, q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                                    self.kcache.data_ptr(), self.vcache.data_ptr(), self.cos.data_ptr(),
-                                                    self.sin.data_ptr(), _flags(pdl), _stream()))
+        if qk_norm is None:
+            check(lib().nntr_cuda_rope_cache_append_dev(C.byref(self.desc), pos, pd, q.data_ptr(), k.data_ptr(),
+                                                        v.data_ptr(), self.kcache.data_ptr(), self.vcache.data_ptr(),
+                                                        self.cos.data_ptr(), self.sin.data_ptr(), _flags(pdl), _stream()))
+        else:
+            qg, kg, eps = qk_norm
+            check(lib().nntr_cuda_qk_norm_rope_cache_append_dev(
+                C.byref(self.desc), pos, pd, q.data_ptr(), k.data_ptr(), v.data_ptr(), qg.data_ptr(), kg.data_ptr(), eps,
+                self.kcache.data_ptr(), self.vcache.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), _flags(pdl),
+                _stream()))
         check(lib().nntr_cuda_attention_decode_dev(C.byref(self.desc), pos, pd, self.max_seq, q.data_ptr(),
                                                    self.kcache.data_ptr(), self.vcache.data_ptr(), out.data_ptr(),
                                                    self.ws.data_ptr(), self.ws.numel(), _flags(pdl), _stream()))

@@ -39,6 +39,7 @@ SIGNATURES = {
     "nntr_cuda_clear_device_status": (_i, []),
     "nntr_cuda_set_exchange_poll_limit": (_i, [_u]),
     "nntr_cuda_rms_norm_dev": (_i, [_vp, _vp, _vp, _i64, _i, C.c_float, _u, _vp]),
+    "nntr_cuda_add_rms_norm_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, C.c_float, _u, _vp]),
     "nntr_cuda_swiglu_dev": (_i, [_vp, _vp, _vp, _i64, _u, _vp]),
     "nntr_cuda_swiglu_alpha_dev": (_i, [_vp, _vp, _vp, _i64, C.c_float, _u, _vp]),
     "nntr_cuda_add_dev": (_i, [_vp, _vp, _vp, _i64, _u, _vp]),
@@ -46,6 +47,8 @@ SIGNATURES = {
     "nntr_cuda_embedding_dev": (_i, [_i, _vp, _vp, _vp, _u, _u, _u, _u, _vp]),
     "nntr_cuda_rope_table": (_i, [_u, _u, C.c_float, _vp, _vp]),
     "nntr_cuda_rope_cache_append_dev": (_i, [_vp, _u, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u, _vp]),
+    "nntr_cuda_qk_norm_rope_cache_append_dev": (_i, [_vp, _u, _vp, _vp, _vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp,
+                                                     _u, _vp]),
     "nntr_cuda_attention_workspace_bytes": (_sz, [_vp, _u]),
     "nntr_cuda_attention_decode_dev": (_i, [_vp, _u, _vp, _u, _vp, _vp, _vp, _vp, _vp, _sz, _u, _vp]),
     "nntr_cuda_bin_layout": (_i, [_vp, _sz, _vp, _vp, _vp]),
@@ -62,6 +65,7 @@ SIGNATURES = {
     "nntr_cuda_gemm_q6_K_dev": (_i, _GEMM_DEV),
     "nntr_cuda_gemm_q4_K_noalloc_dev": (_i, [_u, _u, _u, _vp, _u, _vp, _u, _vp, _u, _vp]),
     "nntr_cuda_gemv_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _u, _vp]),
+    "nntr_cuda_gemv_batched_dev": (_i, [_i, _u, _u, _vp, _vp, _u, _vp, _u, _vp]),
     "nntr_cuda_malloc": (_i, [C.POINTER(C.c_void_p), _sz]),
     "nntr_cuda_free": (_i, [_vp]),
     "nntr_cuda_memcpy": (_i, [_vp, _vp, _sz, _i]),

@@ -29,51 +29,92 @@ namespace nntr {
 
 /* ------------------------------------------------------------------ rotary */
 
-/* One thread per (head, pair k): q in place; k rotated and v converted into cache row `pos`. Grid covers
- * (n_heads_q + 2 * n_heads_kv) * head_dim / 2 threads. */
+/* One warp per head (query heads, then key heads, then value heads). Optional per-head RMS norm first
+ * (ReshapedRMSNormLayer on q and k: Applications/CausalLM/qwen3_causallm.cpp:60-93, sums in the order of
+ * rms_norm_wrt_width_fp32_intrinsic as in glue.cu), then the rotary embedding: q in place, k into cache row `pos` as
+ * fp16, v converted into cache row `pos`. The normalised head goes through shared memory so that a lane finds both
+ * elements of its (k, k + head_dim/2) pairs whatever the head size. */
+constexpr int ROPE_WARPS = 4;
 __global__ void rope_cache_append_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                         const float *__restrict__ q_gamma, const float *__restrict__ k_gamma, float eps,
                                          uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache,
                                          const float *__restrict__ cos_tab, const float *__restrict__ sin_tab,
                                          const unsigned *__restrict__ pos_dev, unsigned pos, int hq, int hkv, int hd) {
+  extern __shared__ __align__(16) float rsm[]; // [ROPE_WARPS][hd]
+  pdl_launch_dependents(); // the next kernel may start its own prologue (weight prefetch); it waits before it reads
   pdl_wait();
   const unsigned p = pos_dev ? *pos_dev : pos;
-  const int half = hd / 2;
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  const int total = (hq + 2 * hkv) * half;
-  if (t >= total)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.x * ROPE_WARPS + warp;
+  if (head >= hq + 2 * hkv)
     return;
-  const int head = t / half, kk = t - head * half;
-  const float c = cos_tab[(size_t)p * hd + kk], s = sin_tab[(size_t)p * hd + kk];
-  if (head < hq) {
-    float *b = q + (size_t)head * hd;
-    const float a0 = b[kk], a1 = b[kk + half];
-    b[kk] = __fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s));
-    b[kk + half] = __fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c));
-  } else if (head < hq + hkv) {
-    const int h = head - hq;
-    const float *b = k + (size_t)h * hd;
-    uint16_t *dst = kcache + ((size_t)p * hkv + h) * hd;
-    const float a0 = b[kk], a1 = b[kk + half];
-    dst[kk] = float_to_half_bits_rn(__fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s)));
-    dst[kk + half] = float_to_half_bits_rn(__fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c)));
-  } else {
+  const int half = hd / 2;
+  if (head >= hq + hkv) { // value head: conversion only
     const int h = head - hq - hkv;
     const float *b = v + (size_t)h * hd;
     uint16_t *dst = vcache + ((size_t)p * hkv + h) * hd;
-    dst[kk] = float_to_half_bits_rn(b[kk]);
-    dst[kk + half] = float_to_half_bits_rn(b[kk + half]);
+    for (int e = lane; e < hd; e += 32)
+      dst[e] = float_to_half_bits_rn(b[e]);
+    return;
+  }
+  const bool is_q = head < hq;
+  const float *src = is_q ? q + (size_t)head * hd : k + (size_t)(head - hq) * hd;
+  const float *gamma = is_q ? q_gamma : k_gamma;
+  float *st = rsm + (size_t)warp * hd;
+  if (gamma) {
+    float acc = 0.f;
+    int i = 0;
+    for (; i + 32 <= hd; i += 32) {
+      const float x = src[i + lane];
+      acc = __fmaf_rn(x, x, acc);
+    }
+    for (; i + 8 <= hd; i += 8)
+      if (lane < 8) {
+        const float x = src[i + lane];
+        acc = __fmaf_rn(x, x, acc);
+      }
+    float t = __fadd_rn(acc, __shfl_down_sync(FULL, acc, 4));
+    t = __fadd_rn(t, __shfl_down_sync(FULL, t, 1));
+    t = __fadd_rn(t, __shfl_down_sync(FULL, t, 2));
+    const float h0 = __shfl_sync(FULL, t, 0), h1 = __shfl_sync(FULL, t, 8), h2 = __shfl_sync(FULL, t, 16),
+                h3 = __shfl_sync(FULL, t, 24);
+    const float sumsq = __fadd_rn(__fadd_rn(__fadd_rn(h0, h1), h2), h3);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, (float)hd), eps)));
+    for (int e = lane; e < hd; e += 32)
+      st[e] = __fmul_rn(__fmul_rn(src[e], scale), gamma[e]);
+  } else {
+    for (int e = lane; e < hd; e += 32)
+      st[e] = src[e];
+  }
+  __syncwarp();
+  const float *ct = cos_tab + (size_t)p * hd, *sn = sin_tab + (size_t)p * hd;
+  for (int kk = lane; kk < half; kk += 32) {
+    const float a0 = st[kk], a1 = st[kk + half], c = ct[kk], s = sn[kk];
+    const float o0 = __fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s));
+    const float o1 = __fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c));
+    if (is_q) {
+      float *dst = q + (size_t)head * hd;
+      dst[kk] = o0;
+      dst[kk + half] = o1;
+    } else {
+      uint16_t *dst = kcache + ((size_t)p * hkv + (head - hq)) * hd;
+      dst[kk] = float_to_half_bits_rn(o0);
+      dst[kk + half] = float_to_half_bits_rn(o1);
+    }
   }
 }
 
 /* ------------------------------------------------------------------ scores */
 
-/* A warp takes four cache rows of one kv head; lane = (row j = lane / 8, vector lane l = lane % 8). The four key rows
- * are staged through shared memory with 16-byte loads; every query head of the group is then dotted against them. */
+/* A CTA takes 16 cache rows of one kv head (4 warps x 4 rows); lane = (row j = lane / 8, vector lane l = lane % 8).
+ * The group's query heads and the key rows are staged in shared memory with 16-byte loads; every query head of the
+ * group is then dotted against the rows. */
 constexpr int SCORE_WARPS = 4;
 __global__ void attn_scores_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kcache,
                                    float *__restrict__ scores, const unsigned *__restrict__ pos_dev, unsigned pos,
                                    int hq, int hkv, int hd, unsigned window) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  pdl_launch_dependents(); // the next kernel may start its own prologue; it waits before it reads
   pdl_wait();
   const unsigned num_rows = (pos_dev ? *pos_dev : pos) + 1;
   const unsigned start_row = num_rows < window ? 0u : num_rows - window;
@@ -81,11 +122,14 @@ __global__ void attn_scores_kernel(const float *__restrict__ q, const uint16_t *
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.y;
   const int gqa = hq / hkv;
-  const unsigned t0 = (blockIdx.x * SCORE_WARPS + warp) * 4;
-  if (t0 >= row_cnt)
+  if (blockIdx.x * SCORE_WARPS * 4 >= row_cnt)
     return;
-  uint16_t *ks = reinterpret_cast<uint16_t *>(smem_raw) + (size_t)warp * 4 * hd;
-  // stage 4 rows x hd halves (hd * 2 bytes per row, 16-byte chunks)
+  float *qs = reinterpret_cast<float *>(smem_raw);                           // [gqa][hd]
+  uint16_t *kall = reinterpret_cast<uint16_t *>(smem_raw + (size_t)gqa * hd * 4); // [16][hd]
+  for (int c = threadIdx.x; c < gqa * hd / 4; c += blockDim.x)
+    reinterpret_cast<float4 *>(qs)[c] = reinterpret_cast<const float4 *>(q + (size_t)n * gqa * hd)[c];
+  const unsigned t0 = (blockIdx.x * SCORE_WARPS + warp) * 4;
+  uint16_t *ks = kall + (size_t)warp * 4 * hd;
   const int chunks_per_row = hd / 8;
   for (int c = lane; c < 4 * chunks_per_row; c += 32) {
     const int r = c / chunks_per_row, cc = c - r * chunks_per_row;
@@ -94,13 +138,16 @@ __global__ void attn_scores_kernel(const float *__restrict__ q, const uint16_t *
       vv = *reinterpret_cast<const uint4 *>(kcache + ((size_t)(start_row + t0 + r) * hkv + n) * hd + cc * 8);
     *reinterpret_cast<uint4 *>(ks + (size_t)r * hd + cc * 8) = vv;
   }
-  __syncwarp();
+  __syncthreads();
+  if (t0 >= row_cnt)
+    return;
   const int j = lane >> 3, l = lane & 7;
   const uint16_t *kr = ks + (size_t)j * hd;
   const double norm = sqrt((double)(float)hd);
   for (int g = 0; g < gqa; ++g) {
-    const float *qh = q + (size_t)(n * gqa + g) * hd;
+    const float *qh = qs + (size_t)g * hd;
     float acc = 0.f;
+#pragma unroll 8
     for (int i = 0; i < hd; i += 8)
       acc = __fmaf_rn(qh[i + l], half_bits_to_float(kr[i + l]), acc);
     float s = __fadd_rn(acc, __shfl_down_sync(FULL, acc, 4));
@@ -140,21 +187,30 @@ __device__ __forceinline__ float exp256_lane(float x) {
 }
 
 /* One CTA per head. Phase 1: maximum over the rows (any order: exact). Phase 2: e = exp(x - max) for every row, in
- * parallel, written back. Phase 3: thread 0 adds the e's in ascending row order (the reference's order), starting from
- * the sink's term. Phase 4: every element divided by the sum. */
+ * parallel, kept in shared memory (cap_rows of them; rows beyond that stay in global memory). Phase 3: thread 0 adds
+ * the e's in ascending row order (the reference's order), starting from the sink's term. Phase 4: every element
+ * divided by the sum and written back. */
 constexpr int SOFTMAX_THREADS = 256;
 __global__ void attn_softmax_kernel(float *__restrict__ scores, const float *__restrict__ sink,
-                                    const unsigned *__restrict__ pos_dev, unsigned pos, int hq, unsigned window) {
+                                    const unsigned *__restrict__ pos_dev, unsigned pos, int hq, unsigned window,
+                                    unsigned cap_rows) {
+  extern __shared__ __align__(16) float es[];
   __shared__ float red[SOFTMAX_THREADS / 32];
   __shared__ float s_bcast;
+  pdl_launch_dependents();
   pdl_wait();
   const unsigned num_rows = (pos_dev ? *pos_dev : pos) + 1;
   const unsigned row_cnt = num_rows < window ? num_rows : window;
+  const unsigned in_smem = row_cnt < cap_rows ? row_cnt : cap_rows;
   const int c = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float mx = -INFINITY;
-  for (unsigned r = threadIdx.x; r < row_cnt; r += SOFTMAX_THREADS)
-    mx = fmaxf(mx, scores[(size_t)r * hq + c]);
+  for (unsigned r = threadIdx.x; r < row_cnt; r += SOFTMAX_THREADS) {
+    const float v = scores[(size_t)r * hq + c];
+    if (r < in_smem)
+      es[r] = v;
+    mx = fmaxf(mx, v);
+  }
 #pragma unroll
   for (int o = 16; o; o >>= 1)
     mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
@@ -172,14 +228,29 @@ __global__ void attn_softmax_kernel(float *__restrict__ scores, const float *__r
   __syncthreads();
   mx = s_bcast;
   for (unsigned r = threadIdx.x; r < row_cnt; r += SOFTMAX_THREADS) {
-    float *p = scores + (size_t)r * hq + c;
-    *p = exp256_lane(__fsub_rn(*p, mx));
+    if (r < in_smem) {
+      es[r] = exp256_lane(__fsub_rn(es[r], mx));
+    } else {
+      float *p = scores + (size_t)r * hq + c;
+      *p = exp256_lane(__fsub_rn(*p, mx));
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     float sum = sink ? exp256_lane(__fsub_rn(sink[c], mx)) : 0.0f;
     unsigned r = 0;
-    for (; r + 8 <= row_cnt; r += 8) { // loads issued together, adds in order
+    for (; r + 16 <= in_smem; r += 16) { // loads issued together, adds in order
+      float e[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        e[u] = es[r + u];
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        sum = __fadd_rn(sum, e[u]);
+    }
+    for (; r < in_smem; ++r)
+      sum = __fadd_rn(sum, es[r]);
+    for (; r + 8 <= row_cnt; r += 8) {
       float e[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
@@ -196,47 +267,98 @@ __global__ void attn_softmax_kernel(float *__restrict__ scores, const float *__r
   const float sum = s_bcast;
   for (unsigned r = threadIdx.x; r < row_cnt; r += SOFTMAX_THREADS) {
     float *p = scores + (size_t)r * hq + c;
-    *p = __fdiv_rn(*p, sum);
+    *p = __fdiv_rn(r < in_smem ? es[r] : *p, sum);
   }
 }
 
 /* ------------------------------------------------------------------ values */
 
-/* One thread per (head, d): out = chain over the window's rows of fma(p[row][head], v[row][kv head][d], out).
- * CTA = (kv head, 32 consecutive d) x all heads of the group. */
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+/* One thread per (head, d): out = chain over the window's rows of fma(p[row][head], v[row][kv head][d], out), rows
+ * ascending. CTA = (kv head, 32 consecutive d) x all heads of the group: warp h = head h of the group, lane = d. Tiles
+ * of VT rows (values as fp16 and the group's probabilities) are copied asynchronously into a ring of VBUF shared-memory
+ * buffers, several tiles ahead of the one being consumed, so the chain runs at the latency of its own fused
+ * multiply-adds. */
+constexpr int VT = 64;   // rows per tile
+constexpr int VBUF = 6; // buffers in the ring
 __global__ void attn_values_kernel(const float *__restrict__ probs, const uint16_t *__restrict__ vcache,
                                    float *__restrict__ out, const unsigned *__restrict__ pos_dev, unsigned pos, int hq,
                                    int hkv, int hd, unsigned window) {
+  extern __shared__ __align__(16) uint8_t vsm[];
+  pdl_launch_dependents();
   pdl_wait();
   const unsigned row_num = pos_dev ? *pos_dev : pos;
   const unsigned first = row_num < window ? 0u : row_num + 1 - window;
   const unsigned cnt = row_num + 1 - first;
   const int gqa = hq / hkv;
   const int n = blockIdx.y;
-  const int d = blockIdx.x * 32 + (threadIdx.x & 31);
-  const int h = threadIdx.x >> 5; // head inside the group
-  if (h >= gqa || d >= hd)
-    return;
-  const int head = n * gqa + h;
-  const uint16_t *vp = vcache + ((size_t)first * hkv + n) * hd + d;
-  const float *pp = probs + head;
-  const size_t vstride = (size_t)hkv * hd;
-  float acc = 0.f;
-  unsigned j = 0;
-  for (; j + 8 <= cnt; j += 8) {
-    float a[8], b[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      a[u] = pp[(size_t)(j + u) * hq];
-      b[u] = half_bits_to_float(vp[(size_t)(j + u) * vstride]);
+  const int d0 = blockIdx.x * 32;
+  const int lane = threadIdx.x & 31, h = threadIdx.x >> 5;
+  // buffers: V tile [VT][32] fp16 (64 B per row), P tile [VT][gqa] fp32
+  const size_t vbytes = (size_t)VT * 64, pbytes = (size_t)VT * gqa * 4;
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(vsm);
+  auto issue = [&](unsigned tile, int buf) {
+    const unsigned j0 = tile * VT;
+    const unsigned rows = cnt - j0 < (unsigned)VT ? cnt - j0 : (unsigned)VT;
+    const uint32_t vdst = sbase + buf * (uint32_t)(vbytes + pbytes), pdst = vdst + (uint32_t)vbytes;
+    for (unsigned c = threadIdx.x; c < rows * 4; c += blockDim.x) { // up to 4 chunks of 16 B (8 values) per row
+      const unsigned r = c >> 2, cc = c & 3;
+      if (d0 + (int)cc * 8 < hd)
+        cp_async_16(vdst + r * 64 + cc * 16, vcache + ((size_t)(first + j0 + r) * hkv + n) * hd + d0 + cc * 8);
     }
-#pragma unroll
-    for (int u = 0; u < 8; ++u)
-      acc = __fmaf_rn(a[u], b[u], acc);
+    for (unsigned c = threadIdx.x; c < rows * gqa; c += blockDim.x) {
+      const unsigned r = c / gqa, g = c - r * gqa;
+      cp_async_4(pdst + c * 4, probs + (size_t)(j0 + r) * hq + n * gqa + g);
+    }
+    cp_async_commit();
+  };
+  // ring of VBUF buffers, VBUF - 1 tiles in flight ahead of the one being consumed; one commit group per iteration
+  // (an empty one past the last tile) so that "all but the newest VBUF - 1 groups have landed" means "tile t is here"
+  const unsigned n_tiles = (cnt + VT - 1) / VT;
+  for (int t = 0; t < VBUF - 1; ++t) {
+    if ((unsigned)t < n_tiles)
+      issue(t, t);
+    else
+      cp_async_commit();
   }
-  for (; j < cnt; ++j)
-    acc = __fmaf_rn(pp[(size_t)j * hq], half_bits_to_float(vp[(size_t)j * vstride]), acc);
-  out[(size_t)head * hd + d] = acc;
+  float acc = 0.f;
+  for (unsigned t = 0; t < n_tiles; ++t) {
+    const int buf = t % VBUF;
+    if (t + VBUF - 1 < n_tiles)
+      issue(t + VBUF - 1, (t + VBUF - 1) % VBUF); // the buffer tile t - 1 used: everyone left it at the barrier below
+    else
+      cp_async_commit();
+    asm volatile("cp.async.wait_group %0;" ::"n"(VBUF - 1) : "memory");
+    __syncthreads();
+    const uint16_t *vt = reinterpret_cast<const uint16_t *>(vsm + buf * (vbytes + pbytes));
+    const float *pt = reinterpret_cast<const float *>(vsm + buf * (vbytes + pbytes) + vbytes);
+    const unsigned rows = cnt - t * VT < (unsigned)VT ? cnt - t * VT : (unsigned)VT;
+    unsigned j = 0;
+    for (; j + 8 <= rows; j += 8) {
+      float a[8], b[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        a[u] = pt[(j + u) * gqa + h];
+        b[u] = half_bits_to_float(vt[(j + u) * 32 + lane]);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        acc = __fmaf_rn(a[u], b[u], acc);
+    }
+    for (; j < rows; ++j)
+      acc = __fmaf_rn(pt[j * gqa + h], half_bits_to_float(vt[j * 32 + lane]), acc);
+    __syncthreads(); // done with this buffer before a later tile is copied into it
+  }
+  if (d0 + lane < hd)
+    out[(size_t)(n * gqa + h) * hd + d0 + lane] = acc;
 }
 
 /* ---------------------------------------------------------------- launchers */
@@ -251,8 +373,8 @@ static int check_attn(const nntr_attn_desc *a) {
   if (a->n_heads_q % 8 || a->head_dim % 8)
     return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "attention: head count and head_dim must be multiples of 8 (%u, %u)",
                      a->n_heads_q, a->head_dim);
-  if (a->n_heads_q / a->n_heads_kv > 32)
-    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "attention: at most 32 query heads per key/value head");
+  if (a->n_heads_q / a->n_heads_kv > 16)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "attention: at most 16 query heads per key/value head");
   if (a->window == 0)
     return set_error(NNTR_CUDA_ERR_INVALID, "attention: window of 0 rows");
   return NNTR_CUDA_OK;
@@ -267,21 +389,24 @@ static void pdl_cfg(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, unsigned
 }
 
 int launch_rope_cache_append(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q, const float *k,
-                             const float *v, uint16_t *kcache, uint16_t *vcache, const float *cos_tab,
-                             const float *sin_tab, unsigned flags, cudaStream_t st) {
+                             const float *v, const float *q_gamma, const float *k_gamma, float eps, uint16_t *kcache,
+                             uint16_t *vcache, const float *cos_tab, const float *sin_tab, unsigned flags,
+                             cudaStream_t st) {
   int rc = check_attn(a);
   if (rc)
     return rc;
   if (!q || !k || !v || !kcache || !vcache || !cos_tab || !sin_tab)
     return set_error(NNTR_CUDA_ERR_INVALID, "rope_cache_append: null pointer");
-  const int total = (int)((a->n_heads_q + 2 * a->n_heads_kv) * (a->head_dim / 2));
+  const int heads = (int)(a->n_heads_q + 2 * a->n_heads_kv);
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   pdl_cfg(cfg, attr, flags, st);
-  cfg.gridDim = dim3((unsigned)((total + 255) / 256));
-  cfg.blockDim = dim3(256);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, rope_cache_append_kernel, q, k, v, kcache, vcache, cos_tab, sin_tab, pos_dev,
-                                     pos, (int)a->n_heads_q, (int)a->n_heads_kv, (int)a->head_dim);
+  cfg.gridDim = dim3((unsigned)((heads + ROPE_WARPS - 1) / ROPE_WARPS));
+  cfg.blockDim = dim3(32 * ROPE_WARPS);
+  cfg.dynamicSmemBytes = (size_t)ROPE_WARPS * a->head_dim * sizeof(float);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rope_cache_append_kernel, q, k, v, q_gamma, k_gamma, eps, kcache, vcache,
+                                     cos_tab, sin_tab, pos_dev, pos, (int)a->n_heads_q, (int)a->n_heads_kv,
+                                     (int)a->head_dim);
   count_launch();
   return check_cuda(e, "rope_cache_append launch");
 }
@@ -310,8 +435,9 @@ int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigne
   if (ws_bytes < (size_t)rows * a->n_heads_q * sizeof(float))
     return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: workspace of %zu bytes needed, %zu given",
                      (size_t)rows * a->n_heads_q * sizeof(float), ws_bytes);
-  if ((reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(ws) & 15))
-    return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: cache and workspace must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(vcache) & 15) ||
+      (reinterpret_cast<uintptr_t>(ws) & 15) || (reinterpret_cast<uintptr_t>(q) & 15))
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: q, caches and workspace must be 16-byte aligned");
   float *scores = static_cast<float *>(ws);
   const int hq = (int)a->n_heads_q, hkv = (int)a->n_heads_kv, hd = (int)a->head_dim;
   cudaLaunchConfig_t cfg = {};
@@ -319,20 +445,22 @@ int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigne
   pdl_cfg(cfg, attr, flags, st);
   cfg.gridDim = dim3((rows + SCORE_WARPS * 4 - 1) / (SCORE_WARPS * 4), (unsigned)hkv);
   cfg.blockDim = dim3(32 * SCORE_WARPS);
-  cfg.dynamicSmemBytes = (size_t)SCORE_WARPS * 4 * hd * sizeof(uint16_t);
+  cfg.dynamicSmemBytes = (size_t)(hq / hkv) * hd * sizeof(float) + (size_t)SCORE_WARPS * 4 * hd * sizeof(uint16_t);
   cudaError_t e = cudaLaunchKernelEx(&cfg, attn_scores_kernel, q, kcache, scores, pos_dev, pos, hq, hkv, hd, a->window);
   count_launch();
   if ((rc = check_cuda(e, "attention scores launch")))
     return rc;
   cfg.gridDim = dim3((unsigned)hq);
   cfg.blockDim = dim3(SOFTMAX_THREADS);
-  cfg.dynamicSmemBytes = 0;
-  e = cudaLaunchKernelEx(&cfg, attn_softmax_kernel, scores, a->sink, pos_dev, pos, hq, a->window);
+  const unsigned cap_rows = rows < 11264u ? rows : 11264u; // 44 KB of shared memory at most; later rows stay in global
+  cfg.dynamicSmemBytes = (size_t)cap_rows * sizeof(float);
+  e = cudaLaunchKernelEx(&cfg, attn_softmax_kernel, scores, a->sink, pos_dev, pos, hq, a->window, cap_rows);
   count_launch();
   if ((rc = check_cuda(e, "attention softmax launch")))
     return rc;
   cfg.gridDim = dim3((unsigned)((hd + 31) / 32), (unsigned)hkv);
   cfg.blockDim = dim3(32 * (unsigned)(hq / hkv));
+  cfg.dynamicSmemBytes = VBUF * ((size_t)VT * 64 + (size_t)VT * (hq / hkv) * sizeof(float));
   e = cudaLaunchKernelEx(&cfg, attn_values_kernel, static_cast<const float *>(scores), vcache, out, pos_dev, pos, hq, hkv,
                          hd, a->window);
   count_launch();

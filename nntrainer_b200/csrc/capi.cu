@@ -452,7 +452,13 @@ int nntr_cuda_set_exchange_poll_limit(unsigned polls) { return set_exchange_poll
 
 int nntr_cuda_rms_norm_dev(const float *x, const float *gamma, float *y, int64_t rows, int width, float eps,
                            unsigned flags, void *stream) {
-  return launch_rms_norm(x, gamma, y, rows, width, eps, flags, static_cast<cudaStream_t>(stream));
+  return launch_rms_norm(x, nullptr, nullptr, gamma, y, rows, width, eps, flags, static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_add_rms_norm_dev(const float *a, const float *b, float *sum, const float *gamma, float *y, int64_t rows,
+                               int width, float eps, unsigned flags, void *stream) {
+  if (!b)
+    return set_error(NNTR_CUDA_ERR_INVALID, "add_rms_norm: null pointer");
+  return launch_rms_norm(a, b, sum, gamma, y, rows, width, eps, flags, static_cast<cudaStream_t>(stream));
 }
 int nntr_cuda_swiglu_dev(float *out, const float *gate, const float *up, int64_t n, unsigned flags, void *stream) {
   return launch_swiglu(out, gate, up, n, 0, 0.f, flags, static_cast<cudaStream_t>(stream));
@@ -479,7 +485,17 @@ int nntr_cuda_rope_table(unsigned head_dim, unsigned seq_len, float theta, float
 int nntr_cuda_rope_cache_append_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q,
                                     const float *k, const float *v, void *kcache, void *vcache, const float *cos_tab,
                                     const float *sin_tab, unsigned flags, void *stream) {
-  return launch_rope_cache_append(a, pos, pos_dev, q, k, v, static_cast<uint16_t *>(kcache),
+  return launch_rope_cache_append(a, pos, pos_dev, q, k, v, nullptr, nullptr, 0.f, static_cast<uint16_t *>(kcache),
+                                  static_cast<uint16_t *>(vcache), cos_tab, sin_tab, flags,
+                                  static_cast<cudaStream_t>(stream));
+}
+int nntr_cuda_qk_norm_rope_cache_append_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q,
+                                            const float *k, const float *v, const float *q_gamma, const float *k_gamma,
+                                            float eps, void *kcache, void *vcache, const float *cos_tab,
+                                            const float *sin_tab, unsigned flags, void *stream) {
+  if (!q_gamma || !k_gamma)
+    return set_error(NNTR_CUDA_ERR_INVALID, "qk_norm_rope_cache_append: null gamma");
+  return launch_rope_cache_append(a, pos, pos_dev, q, k, v, q_gamma, k_gamma, eps, static_cast<uint16_t *>(kcache),
                                   static_cast<uint16_t *>(vcache), cos_tab, sin_tab, flags,
                                   static_cast<cudaStream_t>(stream));
 }
@@ -562,6 +578,19 @@ int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const 
   default:
     return launch_gemv_q6_K(N, K, x, B, y, flags, st);
   }
+}
+
+int nntr_cuda_gemv_batched_dev(int qtype, unsigned N, unsigned K, const float *x, const void *const *w_table,
+                               unsigned n_problems, float *y, unsigned flags, void *stream) {
+  if (qtype != NNTR_Q4_K)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_batched: Q4_K weights only (got qtype %d)", qtype);
+  int rc = check_weight_shape(qtype, N, K);
+  if (rc)
+    return rc;
+  if (!w_table)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_batched: null weight table");
+  GemvBatch b = {w_table, 0, 1, (long long)N, 1};
+  return launch_gemv_q4_K_batched(N, K, x, nullptr, y, flags, n_problems, b, static_cast<cudaStream_t>(stream));
 }
 
 /* ---- plain device memory and CUDA IPC, for callers that do not bring a framework ---- */

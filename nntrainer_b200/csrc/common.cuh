@@ -224,6 +224,8 @@ struct GemvBatch {
   long long x_stride; // elements between consecutive activation rows
   int x_div;
   long long y_stride; // elements between the outputs of consecutive problems
+  int static_table;   // the table was complete before the previous kernel in the stream started: no need to wait for
+                      // that kernel before reading it (the weight stream may then overlap the previous kernel)
 };
 
 /** N-split of a projection over the GPUs of one node, exchange fused into the GEMV, without fences:
@@ -316,8 +318,8 @@ int measure_int8_peak(double *tops_out, double *clk_per_mma_out);
 int launch_gemm_q6_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
                      cudaStream_t st);
 /* operators between the matmuls (glue.cu, dequantize.cu) */
-int launch_rms_norm(const float *x, const float *gamma, float *y, long long rows, int width, float eps, unsigned flags,
-                    cudaStream_t st);
+int launch_rms_norm(const float *x, const float *residual, float *sum_out, const float *gamma, float *y, long long rows,
+                    int width, float eps, unsigned flags, cudaStream_t st);
 int launch_swiglu(float *out, const float *gate, const float *up, long long n, int has_alpha, float alpha,
                   unsigned flags, cudaStream_t st);
 int launch_add(float *out, const float *a, const float *b, long long n, unsigned flags, cudaStream_t st);
@@ -328,8 +330,9 @@ int launch_embedding(int qtype, const void *table, const float *ids, float *y, u
 int read_embed_status(int *out, bool clear);
 /* single-token attention (attention.cu) */
 int launch_rope_cache_append(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q, const float *k,
-                             const float *v, uint16_t *kcache, uint16_t *vcache, const float *cos_tab,
-                             const float *sin_tab, unsigned flags, cudaStream_t st);
+                             const float *v, const float *q_gamma, const float *k_gamma, float eps, uint16_t *kcache,
+                             uint16_t *vcache, const float *cos_tab, const float *sin_tab, unsigned flags,
+                             cudaStream_t st);
 size_t attention_workspace_bytes(const nntr_attn_desc *a, unsigned max_rows);
 int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows,
                             const float *q, const uint16_t *kcache, const uint16_t *vcache, float *out, void *ws,

@@ -80,6 +80,7 @@ __device__ int g_embed_status = 0;
  * (Applications/CausalLM/layers/embedding_layer.cpp:118-146, tie_word_embedding.cpp:200-233). One CTA per token. */
 __global__ void embedding_kernel(int qtype, const uint8_t *__restrict__ table, const float *__restrict__ ids,
                                  float *__restrict__ y, unsigned in_dim, unsigned out_dim, size_t row_bytes) {
+  pdl_launch_dependents(); // the next kernel may start its own prologue (weight prefetch); it waits before it reads
   pdl_wait();
   const float idf = ids[blockIdx.x];
   float *out = y + (size_t)blockIdx.x * out_dim;

@@ -164,8 +164,10 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     y += (long long)p * batch.y_stride;
   }
   if (batch.w_table) {
-    // the table is written by the kernel launched just before; a null entry marks a problem another rank owns
-    pdl_wait();
+    // unless the caller says otherwise the table is written by the kernel launched just before; a null entry marks a
+    // problem another rank owns
+    if (!batch.static_table)
+      pdl_wait();
     if (batch.w_table[blockIdx.y] == nullptr)
       return;
   }
@@ -210,7 +212,8 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
   if (warp == PRODUCER_WARP) {
     // ------------------------------------------------------------ producer
     if (batch.w_table) {
-      pdl_wait(); // the weight table is written by the kernel before this one
+      if (!batch.static_table)
+        pdl_wait(); // the weight table is written by the kernel before this one
       W = static_cast<const BlockQ4Kx8 *>(batch.w_table[blockIdx.y]);
     }
     const uint8_t *src = reinterpret_cast<const uint8_t *>(W + (size_t)g_first * nb);

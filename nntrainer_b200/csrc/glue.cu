@@ -21,60 +21,130 @@ namespace nntr {
 
 /* ------------------------------------------------------------------ RMS norm */
 
-/* One warp per row of `width` elements (width % 8 == 0). Lane 8a + l plays lane l of the reference's vector a. */
+/* Sum of squares of one row in the reference's order, by one warp: lane 8a + l plays lane l of the reference's vector
+ * a (element 32i + 8a + l is added to it in ascending i by a fused multiply-add; a leftover group of 8 goes to vector
+ * 0); each vector is summed as ((l0+l4)+(l1+l5)) + ((l2+l6)+(l3+l7)), the four results left to right. Every lane
+ * returns the sum. `row` may be shared or global memory. */
+__device__ __forceinline__ float rms_sumsq_warp(const float *row, int width, int lane) {
+  float acc = 0.f;
+  int i = 0;
+  for (; i + 256 <= width; i += 256) { // eight loads in flight, then the eight dependent multiply-adds in order
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      v[u] = row[i + 32 * u + lane];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      acc = __fmaf_rn(v[u], v[u], acc);
+  }
+  for (; i + 32 <= width; i += 32) {
+    const float v = row[i + lane];
+    acc = __fmaf_rn(v, v, acc);
+  }
+  for (; i + 8 <= width; i += 8) {
+    if (lane < 8) {
+      const float v = row[i + lane];
+      acc = __fmaf_rn(v, v, acc);
+    }
+  }
+  float t = __fadd_rn(acc, __shfl_down_sync(FULL, acc, 4));
+  t = __fadd_rn(t, __shfl_down_sync(FULL, t, 1));
+  t = __fadd_rn(t, __shfl_down_sync(FULL, t, 2));
+  const float h0 = __shfl_sync(FULL, t, 0), h1 = __shfl_sync(FULL, t, 8), h2 = __shfl_sync(FULL, t, 16),
+              h3 = __shfl_sync(FULL, t, 24);
+  return __fadd_rn(__fadd_rn(__fadd_rn(h0, h1), h2), h3);
+}
+
+/* Many rows (per-head norms, prefill): one warp per row of `width` elements (width % 8 == 0). */
 __global__ void rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma, float *__restrict__ y,
                                 long long rows, int width, float eps) {
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows)
     return;
+  pdl_launch_dependents(); // the next kernel may start its own prologue (weight prefetch); it waits before it reads
   pdl_wait();
   const float *xr = x + row * width;
   float *yr = y + row * width;
-  float acc = 0.f;
-  int i = 0;
-  for (; i + 32 <= width; i += 32) {
-    const float v = xr[i + lane];
-    acc = __fmaf_rn(v, v, acc);
-  }
-  for (; i + 8 <= width; i += 8) { // leftover groups of 8 go to vector 0
-    if (lane < 8) {
-      const float v = xr[i + lane];
-      acc = __fmaf_rn(v, v, acc);
-    }
-  }
-  // per vector: ((l0+l4)+(l1+l5)) + ((l2+l6)+(l3+l7))
-  float t = __fadd_rn(acc, __shfl_down_sync(FULL, acc, 4));
-  t = __fadd_rn(t, __shfl_down_sync(FULL, t, 1));
-  t = __fadd_rn(t, __shfl_down_sync(FULL, t, 2));
-  const float h0 = __shfl_sync(FULL, t, 0), h1 = __shfl_sync(FULL, t, 8), h2 = __shfl_sync(FULL, t, 16),
-              h3 = __shfl_sync(FULL, t, 24);
-  const float sumsq = __fadd_rn(__fadd_rn(__fadd_rn(h0, h1), h2), h3);
+  const float sumsq = rms_sumsq_warp(xr, width, lane);
   const float mean = __fdiv_rn(sumsq, (float)width);
   const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-  for (i = lane; i < width; i += 32) {
+#pragma unroll 4
+  for (int i = lane; i < width; i += 32) {
     const float n = __fmul_rn(xr[i], scale);
     yr[i] = gamma ? __fmul_rn(n, gamma[i]) : n;
   }
 }
 
-int launch_rms_norm(const float *x, const float *gamma, float *y, long long rows, int width, float eps, unsigned flags,
-                    cudaStream_t st) {
-  if (!x || !y || rows < 0 || width <= 0 || width % 8)
-    return set_error(NNTR_CUDA_ERR_INVALID, "rms_norm: need width %% 8 == 0 (width=%d)", width);
-  if (rows == 0)
-    return NNTR_CUDA_OK;
-  const int warps = 4;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)((rows + warps - 1) / warps));
-  cfg.blockDim = dim3(32 * warps);
+/* Few rows (a decode step's hidden state): one CTA per row. All threads bring the row into shared memory at once (one
+ * memory round trip instead of a dependent sequence), optionally adding a second vector on the way (the residual
+ * connection in front of the norm: sum = a + b, one rounded addition per element, written out as well); warp 0 runs
+ * the ordered sum of squares from shared memory; all threads write the normalised row. */
+constexpr int RMS_CTA_THREADS = 256;
+__global__ void rms_norm_row_kernel(const float *__restrict__ x, const float *__restrict__ residual,
+                                    float *__restrict__ sum_out, const float *__restrict__ gamma,
+                                    float *__restrict__ y, int width, float eps) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float s_scale;
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += RMS_CTA_THREADS) {
+    float v = x[base + i];
+    if (residual) {
+      v = __fadd_rn(v, residual[base + i]);
+      sum_out[base + i] = v;
+    }
+    row[i] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const float sumsq = rms_sumsq_warp(row, width, threadIdx.x);
+    if (threadIdx.x == 0)
+      s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, (float)width), eps)));
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  for (int i = threadIdx.x; i < width; i += RMS_CTA_THREADS) {
+    const float n = __fmul_rn(row[i], scale);
+    y[base + i] = gamma ? __fmul_rn(n, gamma[i]) : n;
+  }
+}
+
+static void glue_cfg(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, unsigned flags, cudaStream_t st) {
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, rms_norm_kernel, x, gamma, y, rows, width, eps);
+}
+
+/* residual != nullptr: y = norm(x + residual) * gamma and sum_out = x + residual */
+int launch_rms_norm(const float *x, const float *residual, float *sum_out, const float *gamma, float *y, long long rows,
+                    int width, float eps, unsigned flags, cudaStream_t st) {
+  if (!x || !y || rows < 0 || width <= 0 || width % 8)
+    return set_error(NNTR_CUDA_ERR_INVALID, "rms_norm: need width %% 8 == 0 (width=%d)", width);
+  if (residual && !sum_out)
+    return set_error(NNTR_CUDA_ERR_INVALID, "rms_norm: a residual input needs an output for the sum");
+  if (rows == 0)
+    return NNTR_CUDA_OK;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  glue_cfg(cfg, attr, flags, st);
+  cudaError_t e;
+  if ((rows <= 64 && width >= 512 && width <= 11264) || residual) {
+    if (width > 11264)
+      return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "rms_norm with a residual: rows of at most 11264 elements");
+    cfg.gridDim = dim3((unsigned)rows);
+    cfg.blockDim = dim3(RMS_CTA_THREADS);
+    cfg.dynamicSmemBytes = (size_t)width * sizeof(float);
+    e = cudaLaunchKernelEx(&cfg, rms_norm_row_kernel, x, residual, sum_out, gamma, y, width, eps);
+  } else {
+    const int warps = 4;
+    cfg.gridDim = dim3((unsigned)((rows + warps - 1) / warps));
+    cfg.blockDim = dim3(32 * warps);
+    e = cudaLaunchKernelEx(&cfg, rms_norm_kernel, x, gamma, y, rows, width, eps);
+  }
   count_launch();
   return check_cuda(e, "rms_norm launch");
 }
@@ -152,6 +222,7 @@ __global__ void swiglu_kernel(float *__restrict__ out, const float *__restrict__
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n)
     return;
+  pdl_launch_dependents(); // the next kernel may start its own prologue (weight prefetch); it waits before it reads
   pdl_wait();
   float z = up[i];
   if (up_add != 0.f)
@@ -186,6 +257,7 @@ __global__ void add_kernel(float *__restrict__ out, const float *__restrict__ a,
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n)
     return;
+  pdl_launch_dependents(); // the next kernel may start its own prologue (weight prefetch); it waits before it reads
   pdl_wait();
   out[i] = __fadd_rn(a[i], b[i]);
 }
@@ -211,31 +283,20 @@ int launch_add(float *out, const float *a, const float *b, long long n, unsigned
 
 /* ------------------------------------------------------------------- arg-max */
 
-/* One CTA per row of n logits; the winner is the greatest value, the lowest index among equals (what
- * std::max_element returns). NaNs never win, as with operator<. */
-__global__ void argmax_kernel(const float *__restrict__ x, long long n, long long ld, unsigned *__restrict__ out,
-                              float *__restrict__ out_f) {
-  __shared__ float sv[32];
-  __shared__ unsigned si[32];
-  pdl_wait();
-  const float *xr = x + (long long)blockIdx.x * ld;
-  float best = -INFINITY;
-  unsigned bi = 0xffffffffu;
-  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = xr[i];
-    if (v > best || (bi == 0xffffffffu && v == best)) {
-      best = v;
-      bi = (unsigned)i;
-    }
-  }
-  auto better = [](float v, unsigned i, float bv, unsigned bidx) {
-    return i != 0xffffffffu && (bidx == 0xffffffffu || v > bv || (v == bv && i < bidx));
-  };
+/* The winner of a row of n logits is the greatest value, the lowest index among equals (what std::max_element
+ * returns); NaNs never win, as with operator<. ARGMAX_SPLIT CTAs per row each reduce a contiguous slice to a
+ * (value, index) pair; the CTA that arrives last on the row's counter reduces the pairs. */
+constexpr int ARGMAX_SPLIT = 64;
+constexpr int ARGMAX_THREADS = 256;
+__device__ __forceinline__ bool argmax_better(float v, unsigned i, float bv, unsigned bidx) {
+  return i != 0xffffffffu && (bidx == 0xffffffffu || v > bv || (v == bv && i < bidx));
+}
+__device__ __forceinline__ void argmax_block_reduce(float &best, unsigned &bi, float *sv, unsigned *si) {
 #pragma unroll
   for (int o = 16; o; o >>= 1) {
     const float ov = __shfl_xor_sync(FULL, best, o);
     const unsigned oi = __shfl_xor_sync(FULL, bi, o);
-    if (better(ov, oi, best, bi)) {
+    if (argmax_better(ov, oi, best, bi)) {
       best = ov;
       bi = oi;
     }
@@ -254,37 +315,97 @@ __global__ void argmax_kernel(const float *__restrict__ x, long long n, long lon
     for (int o = 16; o; o >>= 1) {
       const float ov = __shfl_xor_sync(FULL, best, o);
       const unsigned oi = __shfl_xor_sync(FULL, bi, o);
-      if (better(ov, oi, best, bi)) {
+      if (argmax_better(ov, oi, best, bi)) {
         best = ov;
         bi = oi;
       }
     }
-    if (lane == 0) {
-      const unsigned r = bi == 0xffffffffu ? 0u : bi; // all NaN: max_element returns the first element
-      if (out)
-        out[blockIdx.x] = r;
-      if (out_f)
-        out_f[blockIdx.x] = (float)r; // the reference feeds token ids back as floats
-    }
   }
 }
+
+__global__ void argmax_kernel(const float *__restrict__ x, long long n, long long ld, unsigned *__restrict__ out,
+                              float *__restrict__ out_f, float *__restrict__ part_v, unsigned *__restrict__ part_i,
+                              unsigned *__restrict__ counters) {
+  __shared__ float sv[32];
+  __shared__ unsigned si[32];
+  __shared__ bool is_last;
+  pdl_launch_dependents(); // the next kernel may start its own prologue (weight prefetch); it waits before it reads
+  pdl_wait();
+  const int rowi = blockIdx.y, sl = blockIdx.x;
+  const float *xr = x + (long long)rowi * ld;
+  const long long lo = n * sl / ARGMAX_SPLIT, hi = n * (sl + 1) / ARGMAX_SPLIT;
+  float best = -INFINITY;
+  unsigned bi = 0xffffffffu;
+  for (long long i = lo + threadIdx.x; i < hi; i += ARGMAX_THREADS) {
+    const float v = xr[i];
+    if (v > best || (bi == 0xffffffffu && v == best)) {
+      best = v;
+      bi = (unsigned)i;
+    }
+  }
+  argmax_block_reduce(best, bi, sv, si);
+  if (threadIdx.x == 0) {
+    part_v[rowi * ARGMAX_SPLIT + sl] = best;
+    part_i[rowi * ARGMAX_SPLIT + sl] = bi;
+    __threadfence();
+    const unsigned old = atomicAdd(counters + rowi, 1u);
+    is_last = old == ARGMAX_SPLIT - 1;
+    if (is_last)
+      counters[rowi] = 0; // ready for the next call
+  }
+  __syncthreads();
+  if (!is_last)
+    return;
+  __threadfence();
+  best = -INFINITY;
+  bi = 0xffffffffu;
+  if (threadIdx.x < ARGMAX_SPLIT) {
+    best = __ldcg(part_v + rowi * ARGMAX_SPLIT + threadIdx.x);
+    bi = __ldcg(part_i + rowi * ARGMAX_SPLIT + threadIdx.x);
+  }
+  __syncthreads();
+  argmax_block_reduce(best, bi, sv, si);
+  if (threadIdx.x == 0) {
+    const unsigned r = bi == 0xffffffffu ? 0u : bi; // all NaN: max_element returns the first element
+    if (out)
+      out[rowi] = r;
+    if (out_f)
+      out_f[rowi] = (float)r; // the reference feeds token ids back as floats
+  }
+}
+
+/* scratch of the arg-max (partial winners and arrival counters), one per device, made on first use */
+constexpr int ARGMAX_MAX_ROWS = 1024;
+static void *g_argmax_scratch[64] = {};
 
 int launch_argmax(const float *x, long long rows, long long n, long long ld, unsigned *out, float *out_f, unsigned flags,
                   cudaStream_t st) {
   if (!x || (!out && !out_f) || rows < 0 || n <= 0 || n > 0xfffffff0ll)
     return set_error(NNTR_CUDA_ERR_INVALID, "argmax: bad arguments");
+  if (rows > ARGMAX_MAX_ROWS)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "argmax: at most %d rows per call", ARGMAX_MAX_ROWS);
   if (rows == 0)
     return NNTR_CUDA_OK;
+  int dev = 0;
+  NNTR_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "argmax: device ordinal %d out of range", dev);
+  const size_t pv = (size_t)ARGMAX_MAX_ROWS * ARGMAX_SPLIT * 4;
+  if (!g_argmax_scratch[dev]) {
+    // first call on this device (make it before any stream capture): partial winners + zeroed counters
+    void *p = nullptr;
+    NNTR_CHECK_CUDA(cudaMalloc(&p, 2 * pv + ARGMAX_MAX_ROWS * 4));
+    NNTR_CHECK_CUDA(cudaMemset(p, 0, 2 * pv + ARGMAX_MAX_ROWS * 4));
+    g_argmax_scratch[dev] = p;
+  }
+  uint8_t *sc = static_cast<uint8_t *>(g_argmax_scratch[dev]);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)rows);
-  cfg.blockDim = dim3(1024);
-  cfg.stream = st;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, argmax_kernel, x, n, ld, out, out_f);
+  glue_cfg(cfg, attr, flags, st);
+  cfg.gridDim = dim3(ARGMAX_SPLIT, (unsigned)rows);
+  cfg.blockDim = dim3(ARGMAX_THREADS);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, argmax_kernel, x, n, ld, out, out_f, reinterpret_cast<float *>(sc),
+                                     reinterpret_cast<unsigned *>(sc + pv), reinterpret_cast<unsigned *>(sc + 2 * pv));
   count_launch();
   return check_cuda(e, "argmax launch");
 }

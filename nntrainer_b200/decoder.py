@@ -64,21 +64,25 @@ def tensor_list(c: DecoderConfig):
 class Qwen3Decoder:
     """Greedy decoding of a Qwen3-shaped dense decoder from a .bin file, batch 1, one token per step."""
 
-    def __init__(self, cfg: DecoderConfig, bin_path: str, device: str = "cuda"):
+    def __init__(self, cfg: DecoderConfig, bin_path: str, device: str = "cuda", pdl: bool = False):
         import torch
         self.torch, self.cfg, self.dev = torch, cfg, device
         self.tensors = tensor_list(cfg)
         self.w = be.BinWeights(bin_path, [(d, n, k) for _, d, n, k in self.tensors])
         self.ptr = {name: self.w.ptr[i] for i, (name, *_r) in enumerate(self.tensors)}
+        self._shape = {name: (d, n, k) for name, d, n, k in self.tensors}
+        self.pdl = pdl
         cos, sin = be.rope_table(cfg.head_dim, cfg.max_seq, cfg.rope_theta)
         tabs = (torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device))
         self.attn = [be.Attention(cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.max_seq, window=cfg.sliding_window,
                                   device=device, tables=tabs) for _ in range(cfg.n_layers)]
         f = lambda n: torch.empty(n, dtype=torch.float32, device=device)
         q_dim, kv_dim = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
-        self.b = dict(x=f(cfg.hidden), h=f(cfg.hidden), n=f(cfg.hidden), q=f(q_dim), k=f(kv_dim), v=f(kv_dim),
-                      a=f(q_dim), o=f(cfg.hidden), up=f(cfg.inter), gate=f(cfg.inter), act=f(cfg.inter),
-                      d=f(cfg.hidden), logits=f(cfg.vocab))
+        qkv, ug = f(q_dim + 2 * kv_dim), f(2 * cfg.inter)  # q | k | v and ffn_up | ffn_gate, each from one launch
+        self.b = dict(x=f(cfg.hidden), h=f(cfg.hidden), n=f(cfg.hidden), qkv=qkv, q=qkv[:q_dim],
+                      k=qkv[q_dim:q_dim + kv_dim], v=qkv[q_dim + kv_dim:], a=f(q_dim), o=f(cfg.hidden), ug=ug,
+                      up=ug[:cfg.inter], gate=ug[cfg.inter:], act=f(cfg.inter), d=f(cfg.hidden), logits=f(cfg.vocab))
+        self._tables()
 
     class _P:  # a raw device address with the data_ptr() face the backend helpers use
         def __init__(self, p):
@@ -88,40 +92,95 @@ class Qwen3Decoder:
             return self.p
 
     def _gemv(self, name, x, y):
-        _, dtype, N, K = next(t for t in self.tensors if t[0] == name)
-        be.gemv(dtype, N, K, x, self._P(self.ptr[name]), y)
+        dtype, N, K = self._shape[name]
+        be.gemv(dtype, N, K, x, self._P(self.ptr[name]), y, pdl=self.pdl)
 
     def _norm(self, x, name, out, width=None):
-        be.rms_norm(x, self._P(self.ptr[name]), self.cfg.norm_eps, width=width, out=out)
+        be.rms_norm(x, self._P(self.ptr[name]), self.cfg.norm_eps, width=width, out=out, pdl=self.pdl)
 
-    def step(self, token_f, pos: int):
+    def _tables(self):
+        """Device tables of weight addresses for the batched launches: per layer the q, k and v projections as row
+        slices of equal height (one launch computes q | k | v into one buffer), and ffn_up | ffn_gate."""
+        torch, c = self.torch, self.cfg
+        kv_dim, q_dim = c.n_kv_heads * c.head_dim, c.n_heads * c.head_dim
+        self._qkv_ok = c.fc_dtype == "q4_K" and q_dim % kv_dim == 0 and kv_dim % 8 == 0
+        self._qkv_tab, self._ug_tab = [], []
+        row_bytes = c.hidden // 256 * 144
+        for i in range(c.n_layers):
+            p = f"layer{i}_"
+            if self._qkv_ok:
+                ptrs = [self.ptr[p + "wq"] + j * kv_dim * row_bytes for j in range(q_dim // kv_dim)]
+                ptrs += [self.ptr[p + "wk"], self.ptr[p + "wv"]]
+                self._qkv_tab.append(torch.tensor(ptrs, dtype=torch.int64, device=self.dev))
+                self._ug_tab.append(torch.tensor([self.ptr[p + "ffn_up"], self.ptr[p + "ffn_gate"]], dtype=torch.int64,
+                                                 device=self.dev))
+
+    def step(self, token_f, pos: int, pos_dev=None, out_idx=None, out_idx_f=None):
         """One decode step: ``token_f`` is a 1-element float device tensor holding the token id (the reference keeps
-        ids as floats); returns (next id as int32 tensor, as float32 tensor). Logits stay in ``self.b['logits']``."""
-        c, b = self.cfg, self.b
+        ids as floats); returns (next id as int32 tensor, as float32 tensor). Logits stay in ``self.b['logits']``.
+        With ``pos_dev`` (a device word) the position is read on the device, so the launches can be captured once into
+        a CUDA graph and replayed for every later token.
+
+        Launches per layer: (residual add +) RMS norm; q | k | v projections (one batched launch); per-head norms +
+        rotary + cache append; scores; softmax; values; attention_out; residual add + RMS norm; ffn_up | ffn_gate (one
+        batched launch); SwiGLU; ffn_down. Every fusion keeps the bits of the separate operators."""
+        c, b, pdl = self.cfg, self.b, self.pdl
+        q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
         be.embedding(c.embedding_dtype, self._P(self.ptr["embedding0"]), token_f, c.vocab, c.hidden,
-                     out=b["x"].view(1, -1))
+                     out=b["x"].view(1, -1), pdl=pdl)
         x = b["x"]
         for i in range(c.n_layers):
             p = f"layer{i}_"
-            self._norm(x, p + "attention_norm", b["n"])
-            self._gemv(p + "wv", b["n"], b["v"])
-            self._gemv(p + "wk", b["n"], b["k"])
-            self._norm(b["k"], p + "k_norm", b["k"], width=c.head_dim)
-            self._gemv(p + "wq", b["n"], b["q"])
-            self._norm(b["q"], p + "q_norm", b["q"], width=c.head_dim)
-            self.attn[i].step(b["q"], b["k"], b["v"], pos, out=b["a"])
+            if i == 0:
+                self._norm(x, p + "attention_norm", b["n"])
+            else:  # the previous block's output x = h + ffn_down, and its norm
+                be.add_rms_norm(b["h"], b["d"], self._P(self.ptr[p + "attention_norm"]), c.norm_eps, sum_out=x, out=b["n"],
+                                pdl=pdl)
+            if self._qkv_ok:
+                be.gemv_batched(c.fc_dtype, kv_dim, c.hidden, b["n"], self._qkv_tab[i], q_dim // kv_dim + 2, b["qkv"],
+                                pdl=pdl)
+            else:
+                self._gemv(p + "wv", b["n"], b["v"])
+                self._gemv(p + "wk", b["n"], b["k"])
+                self._gemv(p + "wq", b["n"], b["q"])
+            # k_norm and q_norm (per-head RMS norms) run inside the rotary / cache-append launch
+            self.attn[i].step(b["q"], b["k"], b["v"], pos, pos_dev=pos_dev, out=b["a"], pdl=pdl,
+                              qk_norm=(self._P(self.ptr[p + "q_norm"]), self._P(self.ptr[p + "k_norm"]), c.norm_eps))
             self._gemv(p + "attention_out", b["a"], b["o"])
-            be.add(x, b["o"], out=b["h"])
-            self._norm(b["h"], p + "ffn_norm", b["n"])
-            self._gemv(p + "ffn_up", b["n"], b["up"])
-            self._gemv(p + "ffn_gate", b["n"], b["gate"])
-            be.swiglu(b["up"], b["gate"], out=b["act"])
+            be.add_rms_norm(x, b["o"], self._P(self.ptr[p + "ffn_norm"]), c.norm_eps, sum_out=b["h"], out=b["n"], pdl=pdl)
+            if self._qkv_ok:
+                be.gemv_batched(c.fc_dtype, c.inter, c.hidden, b["n"], self._ug_tab[i], 2, b["ug"], pdl=pdl)
+            else:
+                self._gemv(p + "ffn_up", b["n"], b["up"])
+                self._gemv(p + "ffn_gate", b["n"], b["gate"])
+            be.swiglu(b["up"], b["gate"], out=b["act"], pdl=pdl)
             self._gemv(p + "ffn_down", b["act"], b["d"])
-            be.add(b["h"], b["d"], out=x)
-        self._norm(x, "output_norm", b["n"])
+        be.add_rms_norm(b["h"], b["d"], self._P(self.ptr["output_norm"]), c.norm_eps, sum_out=x, out=b["n"], pdl=pdl)
         head = "embedding0" if c.tie_word_embeddings else "output_of_causallm"
         self._gemv(head, b["n"], b["logits"])
-        return be.argmax(b["logits"].view(1, -1))
+        return be.argmax(b["logits"].view(1, -1), pdl=pdl, out=(out_idx, out_idx_f))
+
+    def capture(self, start_pos: int):
+        """Captures one decode step into a CUDA graph: the token id lives in ``self.tok_f`` (device float, rewritten by
+        the step's own arg-max), the position in ``self.pos_dev`` (device word, advanced by the graph). Returns the
+        graph; every ``replay()`` decodes one more token and leaves its id in ``self.tok`` / ``self.tok_f``."""
+        torch = self.torch
+        self.pos_dev = torch.full((2,), 0, dtype=torch.int32, device=self.dev)  # 8 bytes: the bump kernel adds to a u64
+        self.pos_dev[0] = start_pos
+        self.tok = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.tok_f = torch.zeros(1, dtype=torch.float32, device=self.dev)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.step(self.tok_f, 0, pos_dev=self.pos_dev, out_idx=self.tok, out_idx_f=self.tok_f)  # warm-up, eager
+            self.pos_dev[0] = start_pos
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                self.step(self.tok_f, 0, pos_dev=self.pos_dev, out_idx=self.tok, out_idx_f=self.tok_f)
+                be.check(be.lib().nntr_cuda_epoch_bump_dev(self.pos_dev.data_ptr(), be._stream()))
+        torch.cuda.current_stream().wait_stream(s)
+        return g
 
     def generate(self, prompt_ids, n_new: int):
         """Feeds the prompt one token at a time, then ``n_new`` greedy tokens; returns them as a Python list."""

@@ -1,4 +1,4 @@
-"""CPU pipeline of the Qwen3 decoder graph built from the checker's functions only (oracle/port.c GEMVs and
+"""TEST INFRASTRUCTURE ONLY. CPU pipeline of the Qwen3 decoder graph built from the checker's functions only (oracle/port.c GEMVs and
 dequantizers, oracle/glue_port.c for everything around them): the reference's arithmetic, step by step, in the order
 of Applications/CausalLM/causal_lm.cpp:174-233,566-706 and qwen3_causallm.cpp:33-110. Test infrastructure."""
 import numpy as np

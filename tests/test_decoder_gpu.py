@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 from nntrainer_b200.decoder import DecoderConfig, Qwen3Decoder  # noqa: E402
 from oracle import oracle as O  # noqa: E402
-from tests.cpu_decoder import CpuDecoder, synthetic_weights, write_bin  # noqa: E402
+from oracle.cpu_decoder import CpuDecoder, synthetic_weights, write_bin  # noqa: E402
 
 
 @pytest.fixture(scope="module")

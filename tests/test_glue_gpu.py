@@ -181,3 +181,54 @@ def test_attention_argument_checks(be):
     ok = capi.AttnDesc(8, 3, 128, 0xFFFFFFFF, None)
     assert L.nntr_cuda_attention_decode_dev(C.byref(ok), 0, None, 1, d.data_ptr(), d.data_ptr(), d.data_ptr(), d.data_ptr(),
                                             d.data_ptr(), 4096, 0, None) == capi.ERR_INVALID
+
+
+def test_fused_qk_norm_rope_equals_the_separate_launches(be):
+    """Qwen3's per-head q/k RMS norms folded into the rotary / cache-append launch: same bits as the three launches."""
+    rng = np.random.default_rng(12)
+    for hq, hkv, hd in ((32, 8, 128), (64, 8, 64), (8, 8, 24)):
+        q = rng.standard_normal(hq * hd).astype(np.float32)
+        k = rng.standard_normal(hkv * hd).astype(np.float32)
+        v = rng.standard_normal(hkv * hd).astype(np.float32)
+        qg = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+        kg = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+        a1 = be.Attention(hq, hkv, hd, 8)
+        a2 = be.Attention(hq, hkv, hd, 8)
+        q1, k1 = dev(q), dev(k)
+        be.rms_norm(q1, dev(qg), 1e-6, width=hd, out=q1)
+        be.rms_norm(k1, dev(kg), 1e-6, width=hd, out=k1)
+        o1 = a1.step(q1, k1, dev(v), 3)
+        q2 = dev(q)
+        o2 = a2.step(q2, dev(k), dev(v), 3, qk_norm=(dev(qg), dev(kg), 1e-6))
+        assert same_bits(q1.cpu().numpy(), q2.cpu().numpy())
+        assert torch.equal(a1.kcache[3].view(torch.int16), a2.kcache[3].view(torch.int16))
+        assert torch.equal(a1.vcache[3].view(torch.int16), a2.vcache[3].view(torch.int16))
+        assert same_bits(o1.cpu().numpy(), o2.cpu().numpy())
+
+
+def test_add_rms_norm_equals_add_then_norm(be, port):
+    rng = np.random.default_rng(13)
+    for rows, width in ((1, 2560), (1, 2048), (3, 2880), (2, 64)):
+        a = rng.standard_normal((rows, width)).astype(np.float32)
+        b = rng.standard_normal((rows, width)).astype(np.float32)
+        g = rng.uniform(0.5, 1.5, width).astype(np.float32)
+        s, y = be.add_rms_norm(dev(a), dev(b), dev(g), 1e-6)
+        assert same_bits(s.cpu().numpy(), a + b)
+        assert same_bits(y.cpu().numpy(), port.rms_norm(a + b, g, 1e-6))
+
+
+def test_batched_gemv_equals_single_launches(be, port):
+    rng = np.random.default_rng(14)
+    N, K, P = 1024, 2560, 6
+    Ws = [O.random_q4_Kx8(rng, N, K) for _ in range(P)]
+    Wd = [dev(w) for w in Ws]
+    tab = torch.tensor([w.data_ptr() for w in Wd], dtype=torch.int64, device="cuda")
+    x = rng.standard_normal(K).astype(np.float32)
+    y = torch.zeros((P, N), device="cuda")
+    for pdl in (False, True):
+        y.zero_()
+        be.gemv_batched("q4_K", N, K, dev(x), tab, P, y, pdl=pdl)
+        got = y.cpu().numpy()
+        for p in range(P):
+            assert same_bits(got[p], port.gemm("q4_K", x[None], Ws[p], N)[0]), (p, pdl)
+    be.device_status()
