@@ -16,6 +16,7 @@
  * All are bound by latency or by the few bytes they move; none is on the HBM roofline of a decode step.
  */
 #include "common.cuh"
+#include "swiglu.cuh"
 
 namespace nntr {
 
@@ -150,71 +151,6 @@ int launch_rms_norm(const float *x, const float *residual, float *sum_out, const
 }
 
 /* -------------------------------------------------------------------- SwiGLU */
-
-__device__ __forceinline__ float ftz_mul(float a, float b) {
-  float r;
-  asm("mul.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ float ftz_add(float a, float b) {
-  float r;
-  asm("add.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ float ftz_sub(float a, float b) {
-  float r;
-  asm("sub.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ float ftz_fma(float a, float b, float c) {
-  float r;
-  asm("fma.rn.ftz.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-  return r;
-}
-__device__ __forceinline__ float ftz_div(float a, float b) {
-  float r;
-  asm("div.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ float ftz_max(float a, float b) {
-  float r;
-  asm("max.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ float ftz_min(float a, float b) {
-  float r;
-  asm("min.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-  return r;
-}
-
-/** exp(x) as avx2_approx_exp_e2lookup<8> computes it (avx2_impl.cpp:228-292): clamp, scale by 8/ln2, split into an
- *  integer (magic-number rounding) and a fraction, 2^(n/8) from an 8-entry table, cubic in the fraction. */
-__device__ __forceinline__ float approx_exp_e2lookup8(float x) {
-  const uint32_t tbl[8] = {0x3f800000u, 0x3f7b95c2u, 0x3f7837f0u, 0x3f75fed7u,
-                           0x3f7504f3u, 0x3f75672au, 0x3f7744fdu, 0x3f7ac0c7u};
-  x = ftz_max(x, -87.0f);
-  x = ftz_mul(x, (float)(1.0 / 0.693147180559945309417232121458176568 * 8));
-  x = ftz_min(x, (float)(88.3762626647949f / 0.693147180559945309417232121458176568 * 8));
-  float xi = ftz_add(x, 0x1.8p23f);
-  const uint32_t bits = __float_as_uint(xi);
-  xi = ftz_sub(xi, 0x1.8p23f);
-  const float frac = ftz_sub(x, xi);
-  const float s = __uint_as_float(tbl[bits & 7u] + (bits << 20));
-  const float C0 = 0x1.c6af84b912394p-5f / 8 / 8 / 8, C1 = 0x1.ebfce50fac4f3p-3f / 8 / 8, C2 = 0x1.62e42ff0c52d6p-1f / 8;
-  const float q0 = ftz_fma(frac, C0, C1);
-  const float f2 = ftz_mul(frac, frac);
-  const float q2 = ftz_mul(frac, C2);
-  const float p = ftz_fma(q0, f2, q2);
-  return ftz_fma(p, s, s);
-}
-
-/** (y / (exp(-[alpha*]y) + 1)) * z, avx2_impl.cpp:306-322 */
-__device__ __forceinline__ float swiglu_elem(float y, float z, bool has_alpha, float alpha) {
-  const float ax = has_alpha ? ftz_mul(alpha, y) : y;
-  const float neg = __uint_as_float(__float_as_uint(ax) ^ 0x80000000u);
-  const float inv_sig = ftz_add(approx_exp_e2lookup8(neg), 1.0f);
-  return ftz_mul(ftz_div(y, inv_sig), z);
-}
 
 /* gate and up may be two halves of one fused projection's output: separate pointers, a common row stride */
 __global__ void swiglu_kernel(float *__restrict__ out, const float *__restrict__ gate, const float *__restrict__ up,

@@ -25,6 +25,7 @@
  * its exp through libm / a polynomial, none of which is reproduced bit for bit).
  */
 #include "common.cuh"
+#include "swiglu.cuh"
 
 namespace nntr {
 
@@ -40,6 +41,54 @@ struct MoeEp {
 constexpr int ROUTER_WARPS = 8;
 constexpr int ROUTER_SLICES = 32; // CTAs per token
 constexpr int MAX_E_PER_LANE = 8; // up to 256 experts
+
+/* std::partial_sort(idx, idx + k, idx + n, [&](a, b) { return v[a] > v[b]; }) on idx = 0..n-1, as the GNU C++ library
+ * performs it (heap selection, then heap sort): out[0..k) = the indices of the k greatest values in descending order,
+ * with the library's own order among equal values. k <= 32. Run by one thread. */
+__device__ void heap_sift(const float *v, int *h, int hole, int len, int value) {
+  const int top = hole;
+  int child = hole;
+  while (child < (len - 1) / 2) {
+    child = 2 * (child + 1);
+    if (v[h[child]] > v[h[child - 1]])
+      child--;
+    h[hole] = h[child];
+    hole = child;
+  }
+  if ((len & 1) == 0 && child == (len - 2) / 2) {
+    child = 2 * (child + 1);
+    h[hole] = h[child - 1];
+    hole = child - 1;
+  }
+  int parent = (hole - 1) / 2;
+  while (hole > top && v[h[parent]] > v[value]) {
+    h[hole] = h[parent];
+    hole = parent;
+    parent = (hole - 1) / 2;
+  }
+  h[hole] = value;
+}
+__device__ void partial_sort_desc(const float *v, int n, int k, int *out) {
+  int h[32];
+  for (int i = 0; i < k; ++i)
+    h[i] = i;
+  if (k >= 2)
+    for (int parent = (k - 2) / 2;; --parent) { // make the heap (its top is the least of the k under "greater")
+      heap_sift(v, h, parent, k, h[parent]);
+      if (parent == 0)
+        break;
+    }
+  for (int i = k; i < n; ++i)
+    if (v[i] > v[h[0]]) // strictly greater than the heap's top: it replaces the top
+      heap_sift(v, h, 0, k, i);
+  for (int last = k - 1; last > 0; --last) { // sort the heap: the top goes to the end of the shrinking range
+    const int value = h[last];
+    h[last] = h[0];
+    heap_sift(v, h, 0, last, value);
+  }
+  for (int i = 0; i < k; ++i)
+    out[i] = h[i];
+}
 
 /* ROUTER_SLICES CTAs per token: each sums its slice of the hidden dimension into partial logits (the router weight
  * is a megabyte per layer: a few CTAs alone would be bound by the latency of their own loads); the CTA that arrives last on
@@ -130,7 +179,7 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
   for (int i = 0; i < MAX_E_PER_LANE; ++i) {
     const int e = lane + 32 * i;
     if (i < per && e < E) {
-      p[i] = expf(p[i] - mx);
+      p[i] = (float)exp((double)__fsub_rn(p[i], mx)); // exp_util<float>: the double exponential, rounded to float
       sum += p[i];
     } else {
       p[i] = -1.f; // never selected: probabilities are >= 0
@@ -142,40 +191,31 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
   for (int i = 0; i < MAX_E_PER_LANE; ++i)
     if (p[i] >= 0.f)
       p[i] = __fdiv_rn(p[i], sum);
-  // k rounds of arg-max, ties to the lower expert index
-  float vsel = 0.f; // lane j keeps the j-th selected value / index
+  // top-k in the order Tensor::topK returns it: std::partial_sort over the expert indices with the comparator
+  // "probability greater" (nntrainer/tensor/float_tensor.cpp:1155-1160) -- a heap selection whose outcome among EQUAL
+  // probabilities depends on the heap's moves, so one lane runs that very procedure (heap of the first k indices,
+  // one comparison per further expert, replace the heap's least on strictly greater, then sort the heap).
+  float *pv = rsm; // the probabilities, expert-indexed (the partial sums kept here are no longer needed)
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < MAX_E_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    if (i < per && e < E)
+      pv[e] = p[i];
+  }
+  __syncwarp();
+  int *sel = reinterpret_cast<int *>(rsm + E); // [topk], room: ROUTER_WARPS * E floats with ROUTER_WARPS >= 2
+  if (lane == 0)
+    partial_sort_desc(pv, E, topk, sel);
+  __syncwarp();
+  float vsel = 0.f;
   int esel = 0;
   float ksum = 0.f;
-  for (int k = 0; k < topk; ++k) {
-    float bv = -1.f;
-    int be = 0x7fffffff;
-#pragma unroll
-    for (int i = 0; i < MAX_E_PER_LANE; ++i) {
-      const int e = lane + 32 * i;
-      if (p[i] > bv) { // ascending e within the lane: the first maximum wins
-        bv = p[i];
-        be = e;
-      }
-    }
-    for (int o = 16; o; o >>= 1) {
-      const float ov = __shfl_xor_sync(FULL, bv, o);
-      const int oe = __shfl_xor_sync(FULL, be, o);
-      if (ov > bv || (ov == bv && oe < be)) {
-        bv = ov;
-        be = oe;
-      }
-    }
-    if ((be & 31) == lane) { // the owner retires the winner
-#pragma unroll
-      for (int i = 0; i < MAX_E_PER_LANE; ++i)
-        if (i == (be >> 5))
-          p[i] = -1.f;
-    }
-    if (lane == k) {
-      vsel = bv;
-      esel = be;
-    }
-    ksum += bv; // same sequential sum in every lane
+  for (int k = 0; k < topk; ++k)
+    ksum += pv[sel[k]]; // same sequential sum in every lane
+  if (lane < topk) {
+    esel = sel[lane];
+    vsel = pv[esel];
   }
   if (lane < topk) {
     const int pr = t * topk + lane;
@@ -203,13 +243,18 @@ __global__ void moe_act_kernel(const float *__restrict__ gu, float *__restrict__
   float g = gu[(2 * p) * I + c], u = gu[(2 * p + 1) * I + c];
   float r;
   if (kind == 0) {
-    const float sig = (float)(1.0 / (1.0 + (double)expf(-g)));
+    // ActiFunc::swish (nntrainer/layers/acti_func.h:286-288,400-405): sigmoid = (float)(1.0 / (1.0 + e)) with
+    // e = exp_util<float>(-x) = the DOUBLE exponential rounded to float (nntrainer/utils/util_func.h:118 calls the C
+    // library's exp), then sigmoid * gate, then * up
+    const float e = (float)exp((double)(-g));
+    const float sig = (float)(1.0 / (1.0 + (double)e));
     r = __fmul_rn(__fmul_rn(sig, g), u);
   } else {
+    // gpt_oss_moe_layer.cpp:411-440: gate + bias; (up + bias) + 1; nntrainer::swiglu(N, X, gate, up, alpha)
     const int e = idx[p];
     g = __fadd_rn(g, gate_b[e][c]);
     u = __fadd_rn(__fadd_rn(u, up_b[e][c]), 1.f);
-    r = __fmul_rn(__fdiv_rn(g, __fadd_rn(expf(-__fmul_rn(alpha, g)), 1.f)), u);
+    r = swiglu_elem(g, u, true, alpha);
   }
   a[i] = r;
 }

@@ -10,11 +10,15 @@
  *   nntrainer/layers/acti_func.h:166-213 (softmax), :286-288 and :400-405 (sigmoid in double, swish)
  *   nntrainer/tensor/float_tensor.cpp:1108-1180 (topK = std::partial_sort with comparator '>', reproduced with the same call)
  *
- * Parity status: UNPINNED. The reference has no test for these layers and two of its steps depend on libraries that are
- * not in the checkout or differ per platform: the router product and the row sums go through BLAS (OpenBLAS, absent),
- * whose summation order is not defined here (ascending index is used), and exp() is the C library's. The GPT-OSS
- * activation uses a polynomial exp approximation in the reference (x86/avx2_impl.cpp:306-322); plain expf is used here.
- * Outputs are therefore compared within the path's tolerance (max-rel 2e-3), expert selection exactly.
+ * Parity status: PARTLY PINNED. Pinned to reference code: the expert GEMVs (port.c, bit-equal to oracle/_ref), the
+ * GPT-OSS activation (nntrainer::swiglu with a slope, restated in glue_port.c and bit-equal to the reference's
+ * x86/avx2_impl.cpp:950-996), the top-k order (the same std::partial_sort call with the same comparator, ties
+ * included). NOT pinned, because they need the Tensor class and BLAS, which do not build here: the router product and
+ * the sums over experts / over the top-k values (BLAS: OpenBLAS, absent; ascending index is used here), and the
+ * softmax / swish exponentials, which are the C library's DOUBLE exp rounded to float (exp_util<float>,
+ * nntrainer/utils/util_func.h:118 -- checked: the instantiation links against exp, not expf) and restated as such.
+ * Outputs are therefore compared within the path's tolerance (max-rel 2e-3); expert selection exactly whenever the
+ * top-k margin exceeds what the unpinned sums can move.
  */
 #include <algorithm>
 #include <cmath>
@@ -28,6 +32,7 @@ int port_gemm_q4_K(unsigned M, unsigned N, unsigned K, const float *A, unsigned 
                    float *C, unsigned ldc);
 int port_gemm_q4_0(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B, unsigned ldb,
                    float *C, unsigned ldc);
+void port_swiglu(unsigned n, float *X, const float *Y, const float *Z, int has_alpha, float alpha); /* glue_port.c */
 }
 
 static void expert_gemv(int qtype, unsigned N, unsigned K, const float *x, const void *W, float *y) {
@@ -63,7 +68,7 @@ void port_moe_route(unsigned T, unsigned H, unsigned E, unsigned topk, const flo
     }
     const float mx = *std::max_element(p.begin(), p.end()); // acti_func.h:195-199
     for (unsigned e = 0; e < E; ++e)
-      p[e] = std::exp(p[e] - mx);
+      p[e] = static_cast<float>(exp(static_cast<double>(p[e] - mx))); // exp_util<float> (util_func.h:118): double exp
     float sum = 0.f;
     for (unsigned e = 0; e < E; ++e)
       sum += p[e];
@@ -109,15 +114,16 @@ void port_moe_forward(int kind, int qtype, unsigned T, unsigned H, unsigned I, u
       expert_gemv(qtype, I, H, xt, up_w[e], up.data());
       if (kind == 0) {
         for (unsigned i = 0; i < I; ++i) {
-          const float sig = static_cast<float>(1.0 / (1.0 + std::exp(-gate[i]))); // acti_func.h:286-288
+          const float ex = static_cast<float>(exp(static_cast<double>(-gate[i]))); // exp_util<float>: double exp
+          const float sig = static_cast<float>(1.0 / (1.0 + ex));                  // acti_func.h:286-288
           act[i] = (sig * gate[i]) * up[i];                                       // :400-405, qwen_moe_layer.cpp:377
         }
       } else {
-        for (unsigned i = 0; i < I; ++i) {
-          const float g = gate[i] + gate_b[e][i];
-          const float u = (up[i] + up_b[e][i]) + 1.f;
-          act[i] = (g / (std::exp(-(alpha * g)) + 1.0f)) * u; // x86/avx2_impl.cpp:315-322
+        for (unsigned i = 0; i < I; ++i) { // gpt_oss_moe_layer.cpp:411-424
+          gate[i] = gate[i] + gate_b[e][i];
+          up[i] = (up[i] + up_b[e][i]) + 1.f;
         }
+        port_swiglu(I, act.data(), gate.data(), up.data(), 1, alpha); // nntrainer::swiglu(N, X, Y, Z, alpha), pinned
       }
       expert_gemv(qtype, H, I, act.data(), down_w[e], dn.data());
       for (unsigned h = 0; h < H; ++h) {
