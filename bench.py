@@ -455,6 +455,24 @@ def moe_decode_step(be, torch, dev, world, rank, steps=10):
            "ms_per_token": round(ms, 4), "us_per_layer": round(ms * 1e3 / Lc, 2), "layers_per_s": round(Lc * 1e3 / ms, 1),
            "weight_bytes_touched_per_token": active, "outputs_finite": bool(torch.isfinite(out).all().item()),
            "checksum": float(out.double().sum().item())}
+    if world == 1:
+        # cfg4's 256-token prefill through one layer: pairs sorted by expert, per-expert grouped GEMMs
+        T = 256
+        xp = torch.randn(T, H, device=dev)
+        with torch.cuda.stream(stream):
+            for ly in layers[:4]:
+                ly.forward(xp)
+            stream.synchronize()
+            e0.record(stream)
+            for ly in layers:
+                yp = ly.forward(xp)
+            e1.record(stream)
+            stream.synchronize()
+        be.device_status()
+        pms = e0.elapsed_time(e1) / Lc
+        res["prefill_256_tokens"] = {"ms_per_layer": round(pms, 4), "tokens_per_s_per_layer": round(T / pms * 1e3, 1),
+                                     "pairs": T * k, "path": "pairs sorted by expert, per-expert grouped GEMM (exact)",
+                                     "outputs_finite": bool(torch.isfinite(yp).all().item())}
     if world > 1:
         layers[0]._ep_buf.close()
     del layers, pool
@@ -694,6 +712,8 @@ def run_ours(args):
         if group is not None:
             finite = bool(np.isfinite(group.gathered_numpy(RING - 1)).all())
             be.device_status()
+            # the graph replays are where buffers are reused across passes: check the last pass as well
+            verified = bool(verified) and verify_nsplit()
         else:
             finite = bool(torch.isfinite(gathered[0]).all() and torch.isfinite(gathered[1]).all())
 
@@ -752,14 +772,20 @@ def run_ours(args):
         for W in registered:
             be.unregister_weight(W)
 
-    # the MoE decode step runs on every rank (expert parallel when there is more than one); a failure there must not
-    # take the headline down with it
+    # the MoE decode step runs on every rank (expert parallel when there is more than one). A failure is recorded in the
+    # line AND fails the run (exit code 3 after the line is printed)
+    failures = []
+    if e2e is not None and "error" in e2e:
+        failures.append("e2e: " + e2e["error"])
+    if group is not None and not verified:
+        failures.append("n-split verification failed")
     moe = None
     if not args.no_extra and not args.no_moe:
         try:
             moe = moe_decode_step(be, torch, dev, world, rank)
         except Exception as exc:  # noqa: BLE001
             moe = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            failures.append("moe_decode_step: " + moe["error"])
 
     if rank == 0:
         peak, which = measured_peak()
@@ -787,7 +813,15 @@ def run_ours(args):
                           f"N-split x{world}: global weight [{world * N_ROWS}, {K_COLS}], output slices stored into every "
                           f"rank's gathered vector by the GEMV epilogue as (value, launch number) pairs over NVLink, no fence and no "
                           f"collective, verified={verified}",
-                          "outputs_finite": finite},
+                          "outputs_finite": finite,
+                          # the side legs in short (the full records follow as extra keys of this line)
+                          "moe_decode": None if not moe or "error" in moe else
+                          {k: moe[k] for k in ("ranks", "ms_per_token", "us_per_layer", "checksum") if k in moe},
+                          "moe_prefill_256": None if not moe or "error" in moe else moe.get("prefill_256_tokens"),
+                          "dense_projections_tok_s": decode["tok/s"] if decode else None,
+                          "model_decode_tok_s": model["tok/s"] if model else None,
+                          "model_decode_tokens_equal_cpu": model["first_tokens_equal_cpu"] if model else None,
+                          "failures": failures},
                "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                             "frac": round(achieved / peak, 4), "peak_source": which + " (copy bandwidth)",
                             "us_per_launch": round(per_launch_us, 4),
@@ -796,11 +830,14 @@ def run_ours(args):
                "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
                "other_decode_gemv_shapes": others, "prefill_gemm_sweep": prefill,
                "decode_step": decode, "model_decode": model, "moe_decode_step": moe}
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if group is not None:
         group.close()
     if world > 1:
         dist.destroy_process_group()
+    if failures:
+        sys.stderr.write("bench: " + "; ".join(failures) + "\n")
+        sys.exit(3)
 
 
 def run_case(args):

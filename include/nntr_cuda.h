@@ -358,7 +358,8 @@ typedef struct {
   float alpha;               /* GPT-OSS activation slope */
 } nntr_moe_desc;
 
-/** Scratch bytes nntr_cuda_moe_forward_dev needs for `tokens` tokens. */
+/** Scratch bytes nntr_cuda_moe_forward_dev needs for `tokens` tokens. The scratch must be ZERO-FILLED before its
+ *  first use (nntr_cuda_malloc does that); the layer leaves it ready for the next call. */
 size_t nntr_cuda_moe_workspace_bytes(const nntr_moe_desc *d, unsigned tokens);
 /** y[tokens][H] = MoE(x[tokens][H]): MoELayer::incremental_forwarding
  *  (qwen_moe_layer.cpp:394-503) / GptOssMoELayer (gpt_oss_moe_layer.cpp:457-572)

@@ -235,7 +235,7 @@ class MoeLayer:
         torch = _torch()
         need = int(lib().nntr_cuda_moe_workspace_bytes(self._C.byref(self.desc), tokens))
         if self._ws is None or self._ws.numel() < need:
-            self._ws = torch.empty(need, dtype=torch.uint8, device=self._keep[0].device)
+            self._ws = torch.zeros(need, dtype=torch.uint8, device=self._keep[0].device)  # zero-filled before first use
         return self._ws
 
     def forward(self, x):

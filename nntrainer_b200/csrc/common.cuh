@@ -317,6 +317,10 @@ int read_f16_status(int *out);
 int measure_int8_peak(double *tops_out, double *clk_per_mma_out);
 int launch_gemm_q6_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,
                      cudaStream_t st);
+/* per-expert grouped GEMM of the MoE prefill (gemm_dp4a.cu) */
+int launch_gemm_grouped(int qtype, unsigned N, unsigned K, const void *qa, float *C, unsigned ldc,
+                        const void *const *w_table0, const void *const *w_table1, const int *off, const int *tile_off,
+                        const int *perm, int n_experts, int a_div, int c_mul, unsigned max_tiles, cudaStream_t st);
 /* operators between the matmuls (glue.cu, dequantize.cu) */
 int launch_rms_norm(const float *x, const float *residual, float *sum_out, const float *gamma, float *y, long long rows,
                     int width, float eps, unsigned flags, cudaStream_t st);

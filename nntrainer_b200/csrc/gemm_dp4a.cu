@@ -349,6 +349,226 @@ gemm_q6_K_dp4a_kernel(const float *__restrict__ x_f32, const uint8_t *__restrict
   }
 }
 
+/* ------------------------------------------------- grouped (per-expert) GEMM */
+/* Mixture-of-experts prefill: the (token, expert) pairs of a batch sorted by expert, one GEMM per expert over the
+ * rows routed to it, all experts in one launch through a device-side problem table (the shape of
+ * Applications/CausalLM/layers/qwen_moe_layer_cached.cpp:190-262: one [num_tokens, H] product per expert). An expert's
+ * weights are then fetched once per tile of MT rows and stay in L2 between tiles, instead of once per pair. Every row
+ * runs the GEMV float chain (one fused multiply-add per super-block / per 32-block), because the reference computes
+ * each (token, expert) pair with M = 1 (qwen_moe_layer.cpp:358-381), so results equal the per-pair GEMVs bit for bit.
+ *   blockIdx.y = tile index over all experts (tile_off[e] .. tile_off[e+1] are expert e's tiles of MT rows)
+ *   blockIdx.z = which weight table (gate / up), 0 for the down projection
+ *   row m of expert e = pair p = perm[off[e] + m]; activation row p / a_div; output row p * c_mul + blockIdx.z */
+struct GroupedGemm {
+  const void *const *w_table[2]; // per expert weight pointers, one table per blockIdx.z
+  const int *off;                // [E + 1] first pair of every expert in perm
+  const int *tile_off;           // [E + 1] first tile of every expert
+  const int *perm;               // [pairs] pair indices sorted by expert
+  int n_experts, a_div, c_mul;
+};
+
+__device__ __forceinline__ bool grouped_tile(const GroupedGemm &gg, int &e, int &m0, int &rows) {
+  const int ty = blockIdx.y;
+  if (ty >= gg.tile_off[gg.n_experts])
+    return false;
+  int lo = 0, hi = gg.n_experts; // the expert whose tile range holds ty
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (gg.tile_off[mid] <= ty)
+      lo = mid;
+    else
+      hi = mid;
+  }
+  e = lo;
+  m0 = (ty - gg.tile_off[e]) * MT;
+  rows = gg.off[e + 1] - gg.off[e] - m0;
+  return rows > 0;
+}
+
+__global__ void __launch_bounds__(DP_WARPS * 32)
+gemm_q4_K_grouped_kernel(const uint8_t *__restrict__ qa, float *__restrict__ C, int ldc, int n_groups, int nb,
+                         GroupedGemm gg) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = lane & 7, c = lane >> 3;
+  int e, m0, rows;
+  if (!grouped_tile(gg, e, m0, rows))
+    return;
+  const int g = blockIdx.x * DP_WARPS + warp;
+  if (g >= n_groups)
+    return;
+  const BlockQ4Kx8 *W = static_cast<const BlockQ4Kx8 *>(gg.w_table[blockIdx.z][e]);
+  if (!W)
+    return; // expert owned by another rank
+  int pair[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+    pair[i] = i < rows ? gg.perm[gg.off[e] + m0 + i] : 0;
+  float acc[MT], accm[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+    acc[i] = accm[i] = 0.f;
+  for (int b = 0; b < nb; ++b) {
+    const BlockQ4Kx8 *blk = W + (size_t)g * nb + b;
+    uint2 q[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      q[k] = *reinterpret_cast<const uint2 *>(blk->qs + ((4 * c + k) * 8 + r) * 8);
+    int sc_lo, m_lo, sc_hi, m_hi;
+    scale_min_k4(r, blk->scales + 12 * (2 * c), sc_lo, m_lo);
+    scale_min_k4(r, blk->scales + 12 * (2 * c + 1), sc_hi, m_hi);
+    const float dw = half_bits_to_float(blk->d[r]), dmw = half_bits_to_float(blk->dmin[r]);
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      if (i >= rows)
+        break; // uniform across the warp
+      const uint8_t *a = qa + ((size_t)(pair[i] / gg.a_div) * nb + b) * sizeof(BlockQ8K);
+      const uint32_t *aw = reinterpret_cast<const uint32_t *>(a + 4 + 64 * c);
+      int dlo = 0, dhi = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        dlo = __dp4a((int)(q[k].x & 0x0f0f0f0fu), (int)aw[2 * k], dlo);
+        dlo = __dp4a((int)(q[k].y & 0x0f0f0f0fu), (int)aw[2 * k + 1], dlo);
+        dhi = __dp4a((int)((q[k].x >> 4) & 0x0f0f0f0fu), (int)aw[8 + 2 * k], dhi);
+        dhi = __dp4a((int)((q[k].y >> 4) & 0x0f0f0f0fu), (int)aw[8 + 2 * k + 1], dhi);
+      }
+      const int16_t *bs = reinterpret_cast<const int16_t *>(a + 260) + 4 * c;
+      int Ic = sc_lo * dlo + sc_hi * dhi;
+      int Jc = m_lo * ((int)bs[0] + (int)bs[1]) + m_hi * ((int)bs[2] + (int)bs[3]);
+      Ic += __shfl_down_sync(FULL, Ic, 8) + __shfl_down_sync(FULL, Ic, 16) + __shfl_down_sync(FULL, Ic, 24);
+      Jc += __shfl_down_sync(FULL, Jc, 8) + __shfl_down_sync(FULL, Jc, 16) + __shfl_down_sync(FULL, Jc, 24);
+      if (lane < 8) { // GEMV chain: one fused multiply-add pair per super-block (integer sums are exact in any order)
+        const float da = *reinterpret_cast<const float *>(a);
+        acc[i] = __fmaf_rn((float)Ic, __fmul_rn(dw, da), acc[i]);
+        accm[i] = __fmaf_rn((float)Jc, __fmul_rn(dmw, da), accm[i]);
+      }
+    }
+  }
+  if (lane < 8) {
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+      if (i < rows)
+        C[(size_t)(pair[i] * gg.c_mul + blockIdx.z) * ldc + g * 8 + r] = __fsub_rn(acc[i], accm[i]);
+  }
+}
+
+__global__ void __launch_bounds__(DP_WARPS * 32)
+gemm_q4_0_grouped_kernel(const uint8_t *__restrict__ qa, float *__restrict__ C, int ldc, int n_groups, int nb32,
+                         GroupedGemm gg) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = lane & 7, c = lane >> 3;
+  int e, m0, rows;
+  if (!grouped_tile(gg, e, m0, rows))
+    return;
+  const int g = blockIdx.x * DP_WARPS + warp;
+  if (g >= n_groups)
+    return;
+  const BlockQ40x8 *W = static_cast<const BlockQ40x8 *>(gg.w_table[blockIdx.z][e]);
+  if (!W)
+    return;
+  int pair[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+    pair[i] = i < rows ? gg.perm[gg.off[e] + m0 + i] : 0;
+  float acc[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+    acc[i] = 0.f;
+  const int nu = (nb32 + 7) / 8;
+  for (int u = 0; u < nu; ++u) {
+    uint2 q0[2], q1[2];
+    float dw[2];
+    bool have[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int b = u * 8 + 2 * c + s;
+      have[s] = b < nb32;
+      const BlockQ40x8 *blk = W + (size_t)g * nb32 + (have[s] ? b : 0);
+      q0[s] = *reinterpret_cast<const uint2 *>(blk->qs + r * 8);
+      q1[s] = *reinterpret_cast<const uint2 *>(blk->qs + 64 + r * 8);
+      dw[s] = half_bits_to_float(blk->d[r]);
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      if (i >= rows)
+        break;
+      int Is[2];
+      float sd[2];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const int b = u * 8 + 2 * c + s;
+        const uint8_t *a = qa + ((size_t)(pair[i] / gg.a_div) * nb32 + (have[s] ? b : 0)) * sizeof(BlockQ80);
+        uint32_t aw[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          aw[k] = ld_u32_a2(a + 2 + 4 * k);
+        const uint32_t w0 = q0[s].x ^ 0x88888888u, w1 = q0[s].y ^ 0x88888888u, w2 = q1[s].x ^ 0x88888888u,
+                       w3 = q1[s].y ^ 0x88888888u;
+        int dot = 0, asum = 0;
+        dot = __dp4a((int)(w0 & 0x0f0f0f0fu), (int)aw[0], dot);
+        dot = __dp4a((int)(w1 & 0x0f0f0f0fu), (int)aw[1], dot);
+        dot = __dp4a((int)(w2 & 0x0f0f0f0fu), (int)aw[2], dot);
+        dot = __dp4a((int)(w3 & 0x0f0f0f0fu), (int)aw[3], dot);
+        dot = __dp4a((int)((w0 >> 4) & 0x0f0f0f0fu), (int)aw[4], dot);
+        dot = __dp4a((int)((w1 >> 4) & 0x0f0f0f0fu), (int)aw[5], dot);
+        dot = __dp4a((int)((w2 >> 4) & 0x0f0f0f0fu), (int)aw[6], dot);
+        dot = __dp4a((int)((w3 >> 4) & 0x0f0f0f0fu), (int)aw[7], dot);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          asum = __dp4a(0x01010101, (int)aw[k], asum);
+        Is[s] = dot - 8 * asum;
+        sd[s] = __fmul_rn(dw[s], half_bits_to_float(*reinterpret_cast<const uint16_t *>(a)));
+      }
+      int Iall[8];
+      float sall[8];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          Iall[2 * cc + s] = __shfl_sync(FULL, Is[s], r + 8 * cc);
+          sall[2 * cc + s] = __shfl_sync(FULL, sd[s], r + 8 * cc);
+        }
+      }
+      if (lane < 8) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (u * 8 + k < nb32)
+            acc[i] = __fmaf_rn((float)Iall[k], sall[k], acc[i]);
+      }
+    }
+  }
+  if (lane < 8) {
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+      if (i < rows)
+        C[(size_t)(pair[i] * gg.c_mul + blockIdx.z) * ldc + g * 8 + r] = acc[i];
+  }
+}
+
+/* qa: quantized activation rows (Q8_K for Q4_K experts, Q8_0 for Q4_0); max_tiles bounds the tile index */
+int launch_gemm_grouped(int qtype, unsigned N, unsigned K, const void *qa, float *C, unsigned ldc,
+                        const void *const *w_table0, const void *const *w_table1, const int *off, const int *tile_off,
+                        const int *perm, int n_experts, int a_div, int c_mul, unsigned max_tiles, cudaStream_t st) {
+  if (!qa || !C || !w_table0 || !off || !tile_off || !perm)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemm_grouped: null pointer");
+  if (max_tiles == 0 || N == 0)
+    return NNTR_CUDA_OK;
+  GroupedGemm gg = {{w_table0, w_table1 ? w_table1 : w_table0}, off, tile_off, perm, n_experts, a_div, c_mul};
+  const int n_groups = (int)(N / 8);
+  const dim3 grid((unsigned)((n_groups + DP_WARPS - 1) / DP_WARPS), max_tiles, w_table1 ? 2u : 1u);
+  if (max_tiles > 65535)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemm_grouped: %u row tiles exceed the grid limit", max_tiles);
+  if (qtype == NNTR_Q4_K)
+    gemm_q4_K_grouped_kernel<<<grid, DP_WARPS * 32, 0, st>>>(static_cast<const uint8_t *>(qa), C, (int)ldc, n_groups,
+                                                            (int)(K / QK_K), gg);
+  else if (qtype == NNTR_Q4_0)
+    gemm_q4_0_grouped_kernel<<<grid, DP_WARPS * 32, 0, st>>>(static_cast<const uint8_t *>(qa), C, (int)ldc, n_groups,
+                                                            (int)(K / 32), gg);
+  else
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemm_grouped: expert weights must be Q4_K or Q4_0");
+  count_launch();
+  return check_cuda(cudaGetLastError(), "gemm_grouped launch");
+}
+
 /* ---------------------------------------------------------------- launchers */
 static unsigned grid_for(long tasks) { return (unsigned)((tasks + DP_WARPS - 1) / DP_WARPS); }
 

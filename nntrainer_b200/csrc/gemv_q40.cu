@@ -102,10 +102,12 @@ __global__ void __launch_bounds__(Q40_THREADS, 1)
 gemv_q4_0_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, float *__restrict__ y, int n_groups, int K,
                  int n_ring, GemvBatch batch) {
   extern __shared__ __align__(128) uint8_t smem[];
-  if (batch.w_table) { // batched launch: blockIdx.y picks the problem; the table is written by the kernel before
-    pdl_wait();
+  if (batch.w_table) { // batched launch: blockIdx.y picks the problem; unless the caller says the table is older, it
+    // was written by the kernel launched just before
+    if (!batch.static_table)
+      pdl_wait();
     const int p = blockIdx.y;
-    W = static_cast<const uint8_t *>(batch.w_table[p]);
+    W = reinterpret_cast<const uint8_t *>(__ldcg(reinterpret_cast<const unsigned long long *>(batch.w_table) + p));
     if (W == nullptr)
       return; // a problem another rank owns
     x += (long long)(p / batch.x_div) * batch.x_stride;

@@ -168,7 +168,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     // problem another rank owns
     if (!batch.static_table)
       pdl_wait();
-    if (batch.w_table[blockIdx.y] == nullptr)
+    if (__ldcg(reinterpret_cast<const unsigned long long *>(batch.w_table) + blockIdx.y) == 0ull)
       return;
   }
   const SmemLayout L = smem_layout(nb, ngslot);
@@ -214,7 +214,8 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     if (batch.w_table) {
       if (!batch.static_table)
         pdl_wait(); // the weight table is written by the kernel before this one
-      W = static_cast<const BlockQ4Kx8 *>(batch.w_table[blockIdx.y]);
+      W = reinterpret_cast<const BlockQ4Kx8 *>(
+        __ldcg(reinterpret_cast<const unsigned long long *>(batch.w_table) + blockIdx.y));
     }
     const uint8_t *src = reinterpret_cast<const uint8_t *>(W + (size_t)g_first * nb);
     // one bulk copy per block, so that blocks land BLK_STRIDE apart

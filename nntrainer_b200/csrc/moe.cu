@@ -24,6 +24,8 @@
  * tolerance (the reference's router product and row sums go through BLAS and
  * its exp through libm / a polynomial, none of which is reproduced bit for bit).
  */
+#include <algorithm>
+
 #include "common.cuh"
 #include "swiglu.cuh"
 
@@ -38,6 +40,9 @@ struct MoeEp {
   unsigned long long parity_stride; // elements between the two alternating expert-output buffers
 };
 
+constexpr unsigned GROUPED_MIN_TOKENS = 8; // from here on the pairs are sorted by expert and run as per-expert GEMMs
+constexpr int GROUPED_MT = 4;              // rows per tile of the grouped GEMM (MT of gemm_dp4a.cu)
+constexpr int MOE_COUNTER_TOKENS = 4096;   // arrival counters kept at the start of the scratch for up to this many tokens
 constexpr int ROUTER_WARPS = 8;
 constexpr int ROUTER_SLICES = 32; // CTAs per token
 constexpr int MAX_E_PER_LANE = 8; // up to 256 experts
@@ -102,6 +107,8 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
   extern __shared__ float rsm[]; // [ROUTER_WARPS][E]
   __shared__ bool is_last;
   const int t = blockIdx.x, sl = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_launch_dependents(); // the expert GEMVs may be scheduled now; they wait for this grid before reading its tables
+  pdl_wait();              // x comes from the kernel before (no-op without the launch attribute)
   if (ep.n_ranks && t == 0 && sl == 0 && threadIdx.x < ep.n_ranks) {
     // heartbeat: "this rank has started layer call seq", i.e. it has finished combining seq - 1 (stream order)
     const unsigned long long seq = (*ep.epoch - 1) * ep.layers_per_epoch + ep.layer + 1;
@@ -192,9 +199,10 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
     if (p[i] >= 0.f)
       p[i] = __fdiv_rn(p[i], sum);
   // top-k in the order Tensor::topK returns it: std::partial_sort over the expert indices with the comparator
-  // "probability greater" (nntrainer/tensor/float_tensor.cpp:1155-1160) -- a heap selection whose outcome among EQUAL
-  // probabilities depends on the heap's moves, so one lane runs that very procedure (heap of the first k indices,
-  // one comparison per further expert, replace the heap's least on strictly greater, then sort the heap).
+  // "probability greater" (nntrainer/tensor/float_tensor.cpp:1155-1160). With distinct values that is plain descending
+  // order: k (+1) rounds of a warp arg-max. Among EQUAL probabilities the library's order comes from its heap moves,
+  // so when a tie touches the selection (two equal values among the k + 1 greatest) one lane reruns the selection
+  // with the library's own procedure.
   float *pv = rsm; // the probabilities, expert-indexed (the partial sums kept here are no longer needed)
   __syncwarp();
 #pragma unroll
@@ -203,9 +211,42 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
     if (i < per && e < E)
       pv[e] = p[i];
   }
-  __syncwarp();
   int *sel = reinterpret_cast<int *>(rsm + E); // [topk], room: ROUTER_WARPS * E floats with ROUTER_WARPS >= 2
-  if (lane == 0)
+  float prev = -1.f;
+  bool tie = false;
+  const int rounds = topk < E ? topk + 1 : topk;
+  for (int k = 0; k < rounds; ++k) {
+    float bv = -1.f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (p[i] > bv) { // ascending e within the lane: the first maximum wins
+        bv = p[i];
+        be = e;
+      }
+    }
+    for (int o = 16; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(FULL, bv, o);
+      const int oe = __shfl_xor_sync(FULL, be, o);
+      if (ov > bv || (ov == bv && oe < be)) {
+        bv = ov;
+        be = oe;
+      }
+    }
+    if ((be & 31) == lane) { // the owner retires the winner
+#pragma unroll
+      for (int i = 0; i < MAX_E_PER_LANE; ++i)
+        if (i == (be >> 5))
+          p[i] = -1.f;
+    }
+    tie = tie || (k > 0 && bv == prev);
+    prev = bv;
+    if (k < topk && lane == 0)
+      sel[k] = be;
+  }
+  __syncwarp();
+  if (tie && lane == 0)
     partial_sort_desc(pv, E, topk, sel);
   __syncwarp();
   float vsel = 0.f;
@@ -225,6 +266,37 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
     gu_table[2 * pr + 1] = up_w[esel];
     dn_table[pr] = down_w[esel];
   }
+}
+
+/* Sorts the (token, expert) pairs of a batch by expert: off[e] = first position of expert e's pairs in perm, tile_off[e]
+ * = first tile of GROUPED_MT rows of expert e, perm = pair indices grouped by expert (order inside an expert is
+ * arbitrary: every row of the grouped GEMM is computed on its own). One CTA; the pair list of a prefill is a few
+ * thousand entries. */
+__global__ void moe_permute_kernel(const int *__restrict__ idx, int P, int E, int *__restrict__ off,
+                                   int *__restrict__ tile_off, int *__restrict__ perm) {
+  __shared__ int cnt[256], cur[256];
+  pdl_wait(); // idx comes from the router launched just before
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x)
+    atomicAdd(&cnt[idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, t = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = o;
+      tile_off[e] = t;
+      cur[e] = o;
+      o += cnt[e];
+      t += (cnt[e] + GROUPED_MT - 1) / GROUPED_MT;
+    }
+    off[E] = o;
+    tile_off[E] = t;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x)
+    perm[atomicAdd(&cur[idx[p]], 1)] = p;
 }
 
 /* a[p][i] from the gate / up GEMV outputs gu[2p][i], gu[2p+1][i] */
@@ -263,6 +335,7 @@ __global__ void moe_act_kernel(const float *__restrict__ gu, float *__restrict__
 __global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__restrict__ idx, const float *__restrict__ w,
                                    const float *const *__restrict__ down_b, float *__restrict__ y, int H, int topk,
                                    long total) {
+  pdl_launch_dependents();
   pdl_wait();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total)
@@ -404,12 +477,16 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned 
 }
 
 struct MoeWs {
-  size_t idx, w, gu_tab, dn_tab, rpart, rcount, gu, act, dn, total;
+  size_t idx, w, gu_tab, dn_tab, rpart, rcount, gu, act, dn, off, tile_off, perm, qx, qact, total;
 };
+
 static MoeWs moe_ws(unsigned T, unsigned H, unsigned I, unsigned topk, unsigned E = 256) {
   MoeWs s;
   const size_t P = (size_t)T * topk;
-  size_t o = 0;
+  // the routers' arrival counters sit at a fixed place whatever the token count, so that a scratch reused for calls of
+  // different sizes keeps them zero (every call leaves them zero); beyond MOE_COUNTER_TOKENS tokens they follow the
+  // other fields and are cleared by the call itself
+  size_t o = (size_t)MOE_COUNTER_TOKENS * 4;
   s.idx = o;
   o = align_up(o + P * 4, 256);
   s.w = o;
@@ -420,14 +497,27 @@ static MoeWs moe_ws(unsigned T, unsigned H, unsigned I, unsigned topk, unsigned 
   o = align_up(o + P * 8, 256);
   s.rpart = o; // sized for the largest expert count so that the layout does not depend on it
   o = align_up(o + (size_t)T * ROUTER_SLICES * E * 4, 256);
-  s.rcount = o;
-  o = align_up(o + (size_t)T * 4, 256);
+  s.rcount = T <= (unsigned)MOE_COUNTER_TOKENS ? 0 : o;
+  o = align_up(o + (T <= (unsigned)MOE_COUNTER_TOKENS ? 0 : (size_t)T * 4), 256);
   s.gu = o;
   o = align_up(o + 2 * P * I * 4, 256);
   s.act = o;
   o = align_up(o + P * I * 4, 256);
   s.dn = o;
   o = align_up(o + P * H * 4, 256);
+  // grouped path: per-expert offsets into the sorted pair list, the list, and the quantized activation rows
+  s.off = o;
+  o = align_up(o + (E + 1) * 4, 256);
+  s.tile_off = o;
+  o = align_up(o + (E + 1) * 4, 256);
+  s.perm = o;
+  o = align_up(o + P * 4, 256);
+  const size_t rowH = std::max((size_t)(H / 32) * 34, (size_t)((H + 255) / 256) * 292);
+  const size_t rowI = std::max((size_t)(I / 32) * 34, (size_t)((I + 255) / 256) * 292);
+  s.qx = o;
+  o = align_up(o + (T >= GROUPED_MIN_TOKENS ? (size_t)T * rowH : 0), 256);
+  s.qact = o;
+  o = align_up(o + (T >= GROUPED_MIN_TOKENS ? P * rowI : 0), 256);
   s.total = o;
   return s;
 }
@@ -497,13 +587,60 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
   float *dn = reinterpret_cast<float *>(ws + s.dn);
   const unsigned P = tokens * K;
 
-  NNTR_CHECK_CUDA(cudaMemsetAsync(ws + s.rcount, 0, (size_t)tokens * 4, st));
-  moe_router_kernel<<<dim3(tokens, ROUTER_SLICES), ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float), st>>>(
-    x, d->router_w, d->router_bias, (int)H, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx, w, gu_tab, dn_tab,
-    reinterpret_cast<float *>(ws + s.rpart), reinterpret_cast<unsigned *>(ws + s.rcount), ep);
-  count_launch();
-  NNTR_CHECK_CUDA(cudaGetLastError());
+  // the arrival counters start at zero (the workspace is zero-filled before its first use) and the last arriver of
+  // every token puts its counter back, so no clearing launch is needed
+  if (tokens > (unsigned)MOE_COUNTER_TOKENS)
+    NNTR_CHECK_CUDA(cudaMemsetAsync(ws + s.rcount, 0, (size_t)tokens * 4, st));
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tokens, ROUTER_SLICES);
+    cfg.blockDim = dim3(ROUTER_WARPS * 32);
+    cfg.dynamicSmemBytes = ROUTER_WARPS * E * sizeof(float);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NNTR_CHECK_CUDA(cudaLaunchKernelEx(&cfg, moe_router_kernel, x, d->router_w, d->router_bias, (int)H, (int)E, (int)K,
+                                       d->gate_w, d->up_w, d->down_w, idx, w, gu_tab, dn_tab,
+                                       reinterpret_cast<float *>(ws + s.rpart),
+                                       reinterpret_cast<unsigned *>(ws + s.rcount), ep));
+    count_launch();
+  }
 
+  if (!epd && tokens >= GROUPED_MIN_TOKENS) {
+    /* prefill: sort the pairs by expert, quantize every token's activation once, one grouped GEMM for gate and up,
+     * activation, quantize the activations, one grouped GEMM for down, combine. Same bits as the per-pair GEMVs. */
+    int *off = reinterpret_cast<int *>(ws + s.off), *tile_off = reinterpret_cast<int *>(ws + s.tile_off),
+        *perm = reinterpret_cast<int *>(ws + s.perm);
+    NNTR_CHECK_CUDA(launch_pdl(moe_permute_kernel, 1u, 1024u, st, idx, (int)P, (int)E, off, tile_off, perm));
+    count_launch();
+    const unsigned max_tiles = P / GROUPED_MT + E; // sum over experts of ceil(count / MT) <= P / MT + E
+    int rc2 = d->qtype == NNTR_Q4_K ? launch_quantize_q8_K(x, H, ws + s.qx, tokens, H, 0, st)
+                                    : launch_quantize_q8_0(x, H, ws + s.qx, tokens, H, st);
+    if (rc2)
+      return rc2;
+    if ((rc2 = launch_gemm_grouped(d->qtype, I, H, ws + s.qx, gu, I, d->gate_w, d->up_w, off, tile_off, perm, (int)E,
+                                   (int)K, 2, max_tiles, st)))
+      return rc2;
+    const long n_act2 = (long)P * I;
+    NNTR_CHECK_CUDA(launch_pdl(moe_act_kernel, (unsigned)((n_act2 + 255) / 256), 256, st, gu, act, idx, d->gate_b,
+                               d->up_b, d->kind, d->alpha, (int)I, n_act2, 0, (int)E));
+    count_launch();
+    rc2 = d->qtype == NNTR_Q4_K ? launch_quantize_q8_K(act, I, ws + s.qact, P, I, 0, st)
+                                : launch_quantize_q8_0(act, I, ws + s.qact, P, I, st);
+    if (rc2)
+      return rc2;
+    if ((rc2 = launch_gemm_grouped(d->qtype, H, I, ws + s.qact, dn, H, d->down_w, nullptr, off, tile_off, perm, (int)E,
+                                   1, 1, max_tiles, st)))
+      return rc2;
+    const long n_out2 = (long)tokens * H;
+    const cudaError_t e2 = launch_pdl(moe_combine_kernel, (unsigned)((n_out2 + 255) / 256), 256, st, dn, idx, w,
+                                      d->kind == 1 ? d->down_b : nullptr, y, (int)H, (int)K, n_out2);
+    count_launch();
+    return check_cuda(e2, "moe_combine launch");
+  }
   GemvBatch b1 = {gu_tab, (long long)H, (int)(2 * K), (long long)I};
   // programmatic dependent launch: the batched kernels wait for the grid before them as their first action, so only
   // their launch latency overlaps the previous kernel
@@ -518,7 +655,10 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
                              d->kind, d->alpha, (int)I, n_act, e_lo, e_hi));
   count_launch();
 
-  GemvBatch b2 = {dn_tab, (long long)I, 1, (long long)H};
+  // the down table was written by the router, three launches back; the activation kernel in between releases its
+  // dependents only after the gate/up grid (hence the router) has completed, so the down launch may read its table and
+  // stream its weights while the activation kernel runs
+  GemvBatch b2 = {dn_tab, (long long)I, 1, (long long)H, 1};
   const long n_out = (long)tokens * H;
   if (!epd) {
     rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched(H, I, act, nullptr, dn, pdl, P, b2, st)

@@ -206,3 +206,54 @@ def test_selection_margin_is_far_above_what_the_unpinned_sums_can_move(be, port)
     safe = gap > 1e-5
     assert safe.all()
     assert np.array_equal(idx.cpu().numpy().astype(np.uint32)[safe], ridx[safe])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,H,I,E,k", [(8, 512, 256, 16, 4), (37, 512, 256, 16, 4), (256, 2048, 768, 128, 8)])
+def test_grouped_prefill_equals_the_per_pair_path_bit_for_bit(be, port, T, H, I, E, k):
+    """From 8 tokens on the layer sorts the (token, expert) pairs by expert and runs per-expert grouped GEMMs with a
+    device-side problem table. Every row keeps the GEMV float chain of the reference (which computes each pair with
+    M = 1), so the result must equal that of the same tokens sent through the decode path in chunks of fewer than 8 --
+    bit for bit -- and the checker's within tolerance. The last case is the benchmark's 256-token prefill of the
+    Qwen3-30B-A3B layer shape."""
+    import torch
+    rng = np.random.default_rng(T + E)
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    router, gate, up, down = make_layer(rng, H, I, E, distinct=min(E, 8))
+    layer = device_layer(be, router, gate, up, down, k)
+    xd = torch.from_numpy(x).cuda()
+    got = layer.forward(xd).cpu().numpy()
+    be.device_status()
+    chunks = [layer.forward(xd[i:i + 5].contiguous()).cpu().numpy() for i in range(0, T, 5)]
+    per_pair = np.concatenate(chunks, axis=0)
+    assert np.array_equal(got.view(np.uint32), per_pair.view(np.uint32))
+    if T <= 64:
+        want = port.moe_forward(x, router, gate, up, down, k)
+        assert np.max(np.abs(got - want)) <= REL_TOL * np.max(np.abs(want))
+
+
+@pytest.mark.gpu
+def test_grouped_prefill_gpt_oss_form_q4_0(be, port):
+    import torch
+    rng = np.random.default_rng(50)
+    T, H, I, E, k, alpha = 24, 352, 352, 8, 4, 1.702
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    router = (rng.standard_normal((H, E)) * 0.02).astype(np.float32)
+    rbias = (rng.standard_normal(E) * 0.01).astype(np.float32)
+    gate = [O.random_q4_0x8(rng, I, H) for _ in range(E)]
+    up = [O.random_q4_0x8(rng, I, H) for _ in range(E)]
+    down = [O.random_q4_0x8(rng, H, I) for _ in range(E)]
+    gb = [(rng.standard_normal(I) * 0.1).astype(np.float32) for _ in range(E)]
+    ub = [(rng.standard_normal(I) * 0.1).astype(np.float32) for _ in range(E)]
+    db = [(rng.standard_normal(H) * 0.1).astype(np.float32) for _ in range(E)]
+    cu = lambda arrs: [torch.from_numpy(a).cuda() for a in arrs]
+    layer = be.MoeLayer(torch.from_numpy(router).cuda(), cu(gate), cu(up), cu(down), k, qtype="q4_0", kind=1,
+                        router_bias=torch.from_numpy(rbias).cuda(), gate_b=cu(gb), up_b=cu(ub), down_b=cu(db), alpha=alpha)
+    xd = torch.from_numpy(x).cuda()
+    got = layer.forward(xd).cpu().numpy()
+    per_pair = np.concatenate([layer.forward(xd[i:i + 6].contiguous()).cpu().numpy() for i in range(0, T, 6)], axis=0)
+    assert np.array_equal(got.view(np.uint32), per_pair.view(np.uint32))
+    want = port.moe_forward(x, router, gate, up, down, k, qtype="q4_0", kind=1, router_bias=rbias, gate_b=gb, up_b=ub,
+                            down_b=db, alpha=alpha)
+    assert np.max(np.abs(got - want)) <= 2e-5 * np.max(np.abs(want))
+    be.device_status()
