@@ -620,7 +620,7 @@ def run_ours(args):
     group = None
     if nsplit:
         from nntrainer_b200.nsplit import NSplitGroup
-        group = NSplitGroup(N_ROWS, RING)
+        group = NSplitGroup(N_ROWS, RING, ring=args.gather_ring)
 
     def step_body():
         sp = int(torch.cuda.current_stream().cuda_stream)
@@ -913,6 +913,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer end-to-end leg (profiling runs)")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE decode step")
     ap.add_argument("--no-model", action="store_true", help="skip the whole-model decode leg")
+    ap.add_argument("--gather-ring", type=int, default=4, help="gathered buffers in rotation on the N-split path (2: exchange in "
+                    "the streaming kernel; 4: in the resident-weights kernel)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--ring", type=int, default=RING, help="distinct weight matrices per step (default keeps every launch out of L2)")
     ap.add_argument("--traffic", type=float, default=None,

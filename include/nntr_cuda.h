@@ -329,6 +329,12 @@ typedef struct {
   const unsigned long long *epoch;  /* this rank's epoch word */
   unsigned layers_per_epoch, layer;
   int x_tagged;                     /* the activation of this launch is a (value, number) vector */
+  unsigned ring;                    /* gathered buffers in rotation: 0 or 2 = two; up to 16. The caller alternates y[] (and
+                                       the next launch's x) over that many buffers, launch by launch; with four or more
+                                       the "done reading" round trip is three launches old when it is needed, i.e. off
+                                       the critical path. More than two needs a per-CTA share of at most 64 super-blocks
+                                       (N_local * K / 2048 / SMs), else NNTR_CUDA_ERR_UNSUPPORTED. layers_per_epoch
+                                       must be a multiple of the ring. */
 } nntr_exchange;
 int nntr_cuda_gemv_nsplit_dev(int qtype, unsigned N_local, unsigned K, const float *x, const void *B,
                               const nntr_exchange *ex, unsigned flags, void *stream);

@@ -102,7 +102,8 @@ class MoeDesc(C.Structure):
 class Exchange(C.Structure):
     """nntr_exchange of include/nntr_cuda.h."""
     _fields_ = [("n_ranks", C.c_int), ("rank", C.c_int), ("y", C.c_void_p * 8), ("flags", C.c_void_p * 8),
-                ("epoch", C.c_void_p), ("layers_per_epoch", C.c_uint), ("layer", C.c_uint), ("x_tagged", C.c_int)]
+                ("epoch", C.c_void_p), ("layers_per_epoch", C.c_uint), ("layer", C.c_uint), ("x_tagged", C.c_int),
+                ("ring", C.c_uint)]
 
 
 class AttnDesc(C.Structure):

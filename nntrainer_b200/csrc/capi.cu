@@ -435,6 +435,8 @@ int clear_device_status_words() {
 }
 int set_exchange_poll_limit(unsigned polls) {
   int rc = set_exchange_poll_limit_gemv(polls);
+  if (!rc)
+    rc = set_exchange_poll_limit_resident(polls);
   return rc ? rc : set_exchange_poll_limit_moe(polls);
 }
 } // namespace nntr
@@ -645,6 +647,9 @@ int nntr_cuda_gemv_nsplit_dev(int qtype, unsigned N_local, unsigned K, const flo
   g.layers_per_epoch = ex->layers_per_epoch;
   g.layer = ex->layer;
   g.x_tagged = ex->x_tagged;
+  g.ring = (int)ex->ring;
+  if (ex->ring == 1 || ex->ring > 16)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_nsplit: ring must be 0 (two buffers) or 2..16");
   return launch_gemv_q4_K_nsplit(N_local, K, x, B, g, flags, static_cast<cudaStream_t>(stream));
 }
 

@@ -253,6 +253,10 @@ struct GemvExchange {
    * reading" flags -- the ranks stay in step through the heartbeat words of the MoE kernels (moe.cu). */
   int no_flags;
   unsigned long long parity_stride;
+  /* number of gathered buffers in rotation (0 = 2). The host picks the buffer of a launch (y[d], and x for the next
+   * launch); the kernel only needs the count to know which "done reading" flag guards a buffer's reuse. More than two
+   * is served by the resident-weights kernel only. */
+  int ring;
 };
 
 /* Activation tiles of the tensor-core GEMM: per (128 activation rows, super-block) the Q8_K values in the MMA operand
@@ -276,9 +280,11 @@ int launch_gemv_q4_K_batched_publish(unsigned N, unsigned K, const float *x, uns
                                      GemvExchange ex, cudaStream_t st);
 int read_moe_status(int *out);
 /* resident-weights variant for small per-CTA shares (gemv_q4k_resident.cu) */
-bool gemv_q4_K_resident_supported(unsigned N, unsigned K);
+bool gemv_q4_K_resident_supported(unsigned N, unsigned K, bool exchange = false);
+struct GemvExchange;
 int launch_gemv_q4_K_resident(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
-                              cudaStream_t st);
+                              cudaStream_t st, const GemvExchange *exchange = nullptr);
+int set_exchange_poll_limit_resident(unsigned polls);
 int read_resident_status(int *out);
 int clear_resident_status();
 int launch_epoch_bump(unsigned long long *epoch, cudaStream_t st);

@@ -500,6 +500,23 @@ int launch_gemv_q4_K_nsplit(unsigned N, unsigned K, const float *x, const void *
       return set_error(NNTR_CUDA_ERR_INVALID, "gemv_nsplit: null peer pointer for rank %d", d);
   GemvBatch none = {};
   ex.slice_offset = (unsigned long long)ex.rank * N;
+  if (ex.ring > 2) {
+    // a ring of three or more gathered buffers is the protocol of the resident-weights kernel (one "done reading" slot
+    // per CTA, checked three launches late); every launch of such a group must fit that kernel
+    if (!gemv_q4_K_resident_supported(N, K, true))
+      return set_error(NNTR_CUDA_ERR_UNSUPPORTED,
+                       "gemv_nsplit: a ring of %d gathered buffers needs the resident-weights kernel (per-CTA share of "
+                       "at most 64 super-blocks; N_local=%u K=%u)", ex.ring, N, K);
+    if ((unsigned)sm_count() > (unsigned)NSPLIT_MAX_CTAS)
+      return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_nsplit: more CTAs than flag slots");
+    GemvExchange rex = ex;
+    // launches after the first of a pass could be ordered by the numbered elements alone; measured on one GPU that is
+    // slower than waiting for the previous grid (the spinning launch competes with the one it waits for), so the wait
+    // stays unless NNTR_NSPLIT_GRID_WAIT=0
+    if (env_int("NNTR_NSPLIT_GRID_WAIT", 1))
+      rex.x_tagged |= 2;
+    return launch_gemv_q4_K_resident(N, K, x, B, nullptr, flags, st, &rex);
+  }
   // arrivals per layer at every rank = CTAs per launch (same on all ranks) x ranks; filled in by the launcher below
   static thread_local GemvExchange tl_ex;
   tl_ex = ex;

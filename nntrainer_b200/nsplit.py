@@ -115,10 +115,10 @@ class PeerBuffers:
 
 
 class NSplitGroup:
-    """Per-process state of an N-split group: two alternating gathered vectors, a flag array and an epoch
+    """Per-process state of an N-split group: ``ring`` gathered vectors in rotation, a flag array and an epoch
     word in this rank's memory, and the peers' copies mapped through CUDA IPC."""
 
-    def __init__(self, n_local: int, layers_per_epoch: int, group=None):
+    def __init__(self, n_local: int, layers_per_epoch: int, group=None, ring: int = 2):
         import torch
         import torch.distributed as dist
 
@@ -127,12 +127,13 @@ class NSplitGroup:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if self.world > MAX_RANKS:
             raise ValueError("N-split groups span the GPUs of one node (at most 8 ranks)")
-        if layers_per_epoch % 2:
-            # the two gathered buffers alternate per launch; with an odd number of launches per pass the first launch
-            # of the next pass would write the buffer the previous pass's last launch wrote, which a slower rank (or the
-            # caller) may still be reading: the "done reading" flags cover the input of the previous launch only
-            raise ValueError("layers_per_epoch must be even (pad the sequence with one more launch)")
-        self.n_local, self.layers = n_local, layers_per_epoch
+        if ring < 2 or ring > 16 or layers_per_epoch % ring:
+            # the gathered buffers rotate per launch; if the launches of a pass were not a multiple of the ring, the first
+            # launch of the next pass would not continue the rotation, and a buffer could be overwritten while a slower
+            # rank (or the caller) still reads it: the "done reading" flags assume the rotation
+            raise ValueError(f"layers_per_epoch must be a multiple of the ring of {ring} gathered buffers "
+                             "(pad the sequence with more launches)")
+        self.n_local, self.layers, self.ring = n_local, layers_per_epoch, ring
         L = lib()
         self._own = []
         nbytes = self.world * n_local * 8  # (fp32 value, launch number) per element
@@ -143,12 +144,12 @@ class NSplitGroup:
             self._own.append(p.value)
             return p.value
 
-        self.buf = [alloc(nbytes), alloc(nbytes)]  # gathered vectors (ping-pong)
+        self.buf = [alloc(nbytes) for _ in range(ring)]  # gathered vectors in rotation
         self.counter = alloc(8 * 512 * 8)  # flag array: [source rank][source CTA] sequence numbers
         self.epoch = alloc(8)
         # exchange IPC handles of buf[0], buf[1], counter
         mine = []
-        for p in (self.buf[0], self.buf[1], self.counter):
+        for p in (*self.buf, self.counter):
             h = (C.c_ubyte * 64)()
             check(L.nntr_cuda_ipc_export(p, h))
             mine.append(bytes(h))
@@ -161,7 +162,7 @@ class NSplitGroup:
         self.peer = []  # per rank: (buf0, buf1, counter) device pointers valid in THIS process
         for r in range(self.world):
             if r == self.rank:
-                self.peer.append((self.buf[0], self.buf[1], self.counter))
+                self.peer.append((*self.buf, self.counter))
                 continue
             ptrs = []
             for hb in allh[r]:
@@ -174,12 +175,13 @@ class NSplitGroup:
             dist.barrier(group=group)
 
     def exchange(self, layer: int, x_tagged: bool = True) -> capi.Exchange:
-        """Description of launch ``layer`` of the sequence: it writes gathered buffer layer % 2."""
+        """Description of launch ``layer`` of the sequence: it writes gathered buffer layer % ring."""
         ex = capi.Exchange()
         ex.n_ranks, ex.rank = self.world, self.rank
+        ex.ring = self.ring
         for r in range(self.world):
-            ex.y[r] = self.peer[r][layer % 2]
-            ex.flags[r] = self.peer[r][2]
+            ex.y[r] = self.peer[r][layer % self.ring]
+            ex.flags[r] = self.peer[r][self.ring]
         ex.epoch = self.epoch
         ex.layers_per_epoch, ex.layer = self.layers, layer
         ex.x_tagged = 1 if x_tagged else 0
@@ -189,10 +191,10 @@ class NSplitGroup:
         """Where launch ``layer`` (>= 1) finds its activation: the slice rank ``src_rank`` (default: this rank)
         contributed to the previous gathered vector."""
         r = self.rank if src_rank is None else src_rank
-        return self.buf[(layer - 1) % 2] + r * self.n_local * 8
+        return self.buf[(layer - 1) % self.ring] + r * self.n_local * 8
 
     def gathered_ptr(self, layer: int) -> int:
-        return self.buf[layer % 2]
+        return self.buf[layer % self.ring]
 
     def bump_epoch(self, stream: int) -> None:
         check(lib().nntr_cuda_epoch_bump_dev(self.epoch, stream))

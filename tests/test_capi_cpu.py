@@ -71,3 +71,27 @@ def test_workspace_sizes(L):
     assert L.nntr_cuda_gemm_workspace_bytes(capi.Q4_0, 64, 4104, 4096) == 64 * 128 * 34
     assert L.nntr_cuda_gemm_workspace_bytes(capi.Q6_K, 3, 8, 2560) == 128 * 2560 * 2  # fp16 tiles (any N)
     assert L.nntr_cuda_set_gemm_path(7) == capi.ERR_INVALID and L.nntr_cuda_set_gemm_path(0) == 0
+
+
+def test_ctypes_structures_have_the_sizes_the_header_gives_them(tmp_path):
+    """The structs of the C ABI are mirrored by hand in capi.py; a field added on one side only shifts every later
+    field. Compile the header with the C compiler and compare sizes and the offsets of the last fields."""
+    import os
+    import subprocess
+    src = tmp_path / "sz.c"
+    hdr = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "nntr_cuda.h")
+    src.write_text(f'''#include <stdio.h>
+#include <stddef.h>
+#include "{hdr}"
+int main(void) {{
+  printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(nntr_exchange), offsetof(nntr_exchange, ring), sizeof(nntr_moe_desc),
+         offsetof(nntr_moe_desc, alpha), sizeof(nntr_moe_ep), offsetof(nntr_moe_ep, layer), sizeof(nntr_attn_desc),
+         sizeof(nntr_bin_tensor));
+  return 0;
+}}''')
+    exe = tmp_path / "sz"
+    subprocess.run(["gcc", "-std=c11", str(src), "-o", str(exe)], check=True)
+    got = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    want = [ctypes.sizeof(capi.Exchange), capi.Exchange.ring.offset, ctypes.sizeof(capi.MoeDesc), capi.MoeDesc.alpha.offset,
+            ctypes.sizeof(capi.MoeEp), capi.MoeEp.layer.offset, ctypes.sizeof(capi.AttnDesc), ctypes.sizeof(capi.BinTensor)]
+    assert got == want

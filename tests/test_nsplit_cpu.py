@@ -79,6 +79,8 @@ def test_odd_launch_count_per_pass_is_rejected():
     pass boundary would write the same buffer. The group refuses such a sequence before touching any device."""
     with pytest.raises(ValueError):
         nsplit.NSplitGroup(512, 3)
+    with pytest.raises(ValueError):
+        nsplit.NSplitGroup(512, 6, ring=4)  # six launches per pass do not continue a rotation of four buffers
     # consecutive launch numbers alternate parity across a pass boundary exactly when the count is even
     for L in (2, 4, 48):
         seq = [nsplit.sequence_number(e, L, l) for e in (1, 2, 3) for l in range(L)]
