@@ -43,8 +43,8 @@ RING = 48
 WEIGHT_BYTES = N_ROWS * K_COLS // 256 * 144          # 9 437 184
 ALG_BYTES = WEIGHT_BYTES + 4 * K_COLS + 4 * N_ROWS   # 9 469 952 per GEMV
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q4_K_kernel launch on this workload, from the ncu
-# capture summarised in profiles/gemv_q4_K_cfg1_4096x4096.md
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q4_K_resident_kernel launch on this workload (one ncu
+# capture of three launches of the chained ring; the figure is per launch)
 NCU_TRAFFIC_BYTES = 9_489_152
 
 
@@ -460,7 +460,7 @@ def moe_decode_step(be, torch, dev, world, rank, steps=10):
         T = 256
         xp = torch.randn(T, H, device=dev)
         with torch.cuda.stream(stream):
-            for ly in layers[:4]:
+            for ly in layers:  # every layer grows its scratch to 256 tokens here, outside the timed region
                 ly.forward(xp)
             stream.synchronize()
             e0.record(stream)
@@ -729,16 +729,18 @@ def run_ours(args):
 
         err, registered = None, []
         try:
-            xh = torch.empty((1, K_COLS), dtype=torch.float32).pin_memory()
-            yh = torch.empty((1, N_ROWS), dtype=torch.float32).pin_memory()
-            xh.copy_(x0.cpu()[None])
-            xn, yn = xh.numpy(), yh.numpy()
+            # activation and result live where the plug-in's allocator puts the framework's tensors: page-locked memory
+            xn = be.host_alloc((1, K_COLS), np.float32)
+            yn = be.host_alloc((1, N_ROWS), np.float32)
+            xn[...] = x0.cpu().numpy()[None]
+            yn[...] = 0.0
             for W in host_ring:
                 be.register_weight("q4_K", W, N_ROWS, K_COLS)
                 registered.append(W)
+            calls = [be.bind_gemm("q4_K", 1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS) for W in host_ring]
             for _ in range(2):
-                for W in host_ring:
-                    be.gemm_q4_K(1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS)
+                for call in calls:
+                    call()
             torch.cuda.synchronize()
         except Exception as exc:  # noqa: BLE001
             err = f"{type(exc).__name__}: {exc}"[:300]
@@ -750,8 +752,8 @@ def run_ours(args):
             try:
                 tt0 = time.perf_counter()
                 for _ in range(e2e_steps):
-                    for W in host_ring:
-                        be.gemm_q4_K(1, N_ROWS, K_COLS, xn, K_COLS, W, N_ROWS, yn, N_ROWS)
+                    for call in calls:
+                        call()  # synchronous: the result is in yn when it returns
                         np.multiply(yn, 0.78, out=xn)  # chain on the host (one cheap pass; 0.78 keeps the magnitude level)
                 torch.cuda.synchronize()
                 dt = time.perf_counter() - tt0
@@ -826,7 +828,7 @@ def run_ours(args):
                             "frac": round(achieved / peak, 4), "peak_source": which + " (copy bandwidth)",
                             "us_per_launch": round(per_launch_us, 4),
                             "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_BYTES,
-                            "kernel": "gemv_q4_K_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
+                            "kernel": "gemv_q4_K_resident_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
                "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
                "other_decode_gemv_shapes": others, "prefill_gemm_sweep": prefill,
                "decode_step": decode, "model_decode": model, "moe_decode_step": moe}

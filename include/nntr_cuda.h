@@ -416,6 +416,18 @@ int nntr_cuda_unregister_weight(const void *host_ptr);
 /** Device address of a registered weight (NULL if unknown). */
 const void *nntr_cuda_weight_device_ptr(const void *host_ptr);
 
+/** Page-locked, device-mapped host memory for activations and results -- what a Context's MemAllocator hands the
+ *  framework's memory pool (nntrainer/mem_allocator.h:29-37 alloc/free; the pool takes every tensor's bytes from it,
+ *  nntrainer/tensor/memory_pool.cpp:170-188). nntr_cuda_host_alloc returns such memory (free it with
+ *  nntr_cuda_host_free); nntr_cuda_host_register page-locks bytes the caller already owns, in place (4096-byte
+ *  granularity is the caller's business; undo with nntr_cuda_host_unregister before freeing them). A decode call
+ *  (M == 1) whose A and C both lie in such memory runs without a copy engine transfer and without a stream
+ *  synchronisation; any other host memory still works, through staged copies. */
+int nntr_cuda_host_alloc(void **p, size_t bytes);
+int nntr_cuda_host_free(void *p);
+int nntr_cuda_host_register(void *p, size_t bytes);
+int nntr_cuda_host_unregister(void *p);
+
 /** Drop-ins for cpu_backend.h:937-977: A, C host fp32; B the host address of the
  *  weight blocks (uploaded on first use if not registered). Synchronous. */
 int nntr_cuda_gemm_q4_0(unsigned M, unsigned N, unsigned K, const float *A, unsigned lda, const void *B, unsigned ldb,

@@ -84,6 +84,76 @@ def _gemm(qtype: str, M: int, N: int, K: int, A, lda: int, B, ldb: int, C, ldc: 
     return C
 
 
+class _HostBlock:
+    """Owner of one nntr_cuda_host_alloc block: frees it when the last numpy view goes away."""
+
+    def __init__(self, nbytes: int):
+        import ctypes as C
+        p = C.c_void_p()
+        check(lib().nntr_cuda_host_alloc(C.byref(p), nbytes))
+        self.ptr, self.nbytes = p.value, nbytes
+        self.buffer = (C.c_uint8 * nbytes).from_address(self.ptr)
+
+    def __del__(self):
+        try:
+            lib().nntr_cuda_host_free(self.ptr)
+        except Exception:  # noqa: BLE001  (interpreter shutdown)
+            pass
+
+
+def host_alloc(shape, dtype=np.float32) -> np.ndarray:
+    """A numpy array in page-locked, device-mapped host memory (nntr_cuda_host_alloc): activations and results kept in
+    such arrays take the short decode path of the host-pointer GEMM entry points."""
+    dt = np.dtype(dtype)
+    n = int(np.prod(shape)) * dt.itemsize
+    block = _HostBlock(max(n, 1))
+    arr = np.frombuffer(block.buffer, dtype=dt, count=int(np.prod(shape))).reshape(shape)
+    _HOST_BLOCKS[block.ptr] = block  # numpy keeps block.buffer alive, not the block: tie their lifetimes here
+    return arr
+
+
+def host_free(arr: np.ndarray) -> None:
+    """Release an array made by host_alloc (also happens at interpreter exit)."""
+    _HOST_BLOCKS.pop(arr.ctypes.data, None)
+
+
+_HOST_BLOCKS: dict = {}
+
+
+def host_register(arr: np.ndarray) -> None:
+    """Page-lock a caller-owned array in place (nntr_cuda_host_register)."""
+    check(lib().nntr_cuda_host_register(arr.ctypes.data, arr.nbytes))
+
+
+def host_unregister(arr: np.ndarray) -> None:
+    check(lib().nntr_cuda_host_unregister(arr.ctypes.data))
+
+
+def lib_check(name: str, *args) -> None:
+    """Call an int-returning entry point by name and raise on a non-zero code (tests of the error paths)."""
+    check(getattr(lib(), name)(*args))
+
+
+def bind_gemm(qtype: str, M: int, N: int, K: int, A: np.ndarray, lda: int, B: np.ndarray, ldb: int, C: np.ndarray,
+              ldc: int):
+    """The host-pointer GEMM of `qtype` on fixed buffers as a zero-argument callable: argument conversion happens once,
+    a call costs one foreign-function call (a decode loop calls the same projection on the same buffers every token).
+    The arrays must stay alive and in place while the callable is used."""
+    import ctypes as C_
+    fn = getattr(lib(), f"nntr_cuda_gemm_{qtype}")
+    args = (C_.c_uint(M), C_.c_uint(N), C_.c_uint(K), C_.c_void_p(_np_ptr(A)), C_.c_uint(lda), C_.c_void_p(_np_ptr(B)),
+            C_.c_uint(ldb), C_.c_void_p(_np_ptr(C)), C_.c_uint(ldc))
+    keep = (A, B, C)
+
+    def call():
+        rc = fn(*args)
+        if rc:
+            check(rc)
+        return keep[2]
+
+    return call
+
+
 def gemm_workspace_bytes(qtype: str, M: int, N: int, K: int) -> int:
     """Scratch a device-pointer GEMM call needs for its quantized activations."""
     return int(lib().nntr_cuda_gemm_workspace_bytes(QTYPE[qtype], M, N, K))

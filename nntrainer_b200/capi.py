@@ -82,6 +82,10 @@ SIGNATURES = {
     "nntr_cuda_register_weight": (_i, [_vp, _sz, _i, _u, _u]),
     "nntr_cuda_unregister_weight": (_i, [_vp]),
     "nntr_cuda_weight_device_ptr": (_vp, [_vp]),
+    "nntr_cuda_host_alloc": (_i, [C.POINTER(C.c_void_p), _sz]),
+    "nntr_cuda_host_free": (_i, [_vp]),
+    "nntr_cuda_host_register": (_i, [_vp, _sz]),
+    "nntr_cuda_host_unregister": (_i, [_vp]),
     "nntr_cuda_gemm_q4_0": (_i, _GEMM_HOST),
     "nntr_cuda_gemm_q4_K": (_i, _GEMM_HOST),
     "nntr_cuda_gemm_q6_K": (_i, _GEMM_HOST),

@@ -19,6 +19,8 @@
 #include <atomic>
 #include <map>
 #include <mutex>
+#include <shared_mutex>
+#include <immintrin.h>
 
 #include "common.cuh"
 
@@ -155,7 +157,11 @@ struct ThreadCtx {
   void *dA = nullptr, *dC = nullptr, *dQ = nullptr; // device staging: activations, outputs, quantized rows
   size_t capA = 0, capC = 0, capQ = 0;
   int device = -1;
+  unsigned long long *done_host = nullptr, *done_dev = nullptr; // completion word in page-locked, device-mapped memory
+  unsigned long long done_seq = 0;
   ~ThreadCtx() {
+    if (done_host)
+      cudaFreeHost(done_host);
     // best effort; the context may already be gone at thread exit
     if (dA)
       cudaFree(dA);
@@ -174,6 +180,9 @@ static int ensure_ctx(ThreadCtx *&out) {
   if (!c.stream) {
     NNTR_CHECK_CUDA(cudaGetDevice(&c.device));
     NNTR_CHECK_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    NNTR_CHECK_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&c.done_host), 64, cudaHostAllocMapped | cudaHostAllocPortable));
+    *c.done_host = 0;
+    NNTR_CHECK_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&c.done_dev), c.done_host, 0));
   }
   out = &c;
   return NNTR_CUDA_OK;
@@ -191,6 +200,71 @@ static int grow(void *&p, size_t &cap, size_t need) {
   NNTR_CHECK_CUDA(cudaMalloc(&p, want));
   cap = want;
   return NNTR_CUDA_OK;
+}
+
+
+/* ------------------------------------------- page-locked host ranges known to the library */
+/* Activation and output buffers that the caller obtained from nntr_cuda_host_alloc or passed to nntr_cuda_host_register:
+ * [start, start + bytes) -> the address the device uses for the same bytes. A decode call whose A and C lie in such
+ * ranges takes the short path of gemm_host without asking the driver about the pointers. */
+struct HostRange {
+  size_t bytes;
+  uintptr_t dev;
+  bool owned; // allocated by nntr_cuda_host_alloc (freed by nntr_cuda_host_free), else registered in place
+};
+static std::shared_mutex g_hmutex;
+static std::map<uintptr_t, HostRange> g_host_ranges;
+static std::atomic<uint64_t> g_host_gen{1}; // bumped by every change of the table: invalidates the per-thread cache
+
+struct HostHit {
+  uint64_t gen = 0;
+  uintptr_t lo = 0, hi = 0, dev = 0;
+};
+static thread_local HostHit tl_hit[2];
+
+/** device alias of host bytes [p, p + bytes), or nullptr when the range is not wholly inside a known page-locked range.
+ * `slot` picks one of the thread's two cached hits (A and C of a call usually come from two different buffers). */
+static void *host_alias(const void *p, size_t bytes, int slot) {
+  const uintptr_t h = reinterpret_cast<uintptr_t>(p);
+  HostHit &c = tl_hit[slot & 1];
+  const uint64_t gen = g_host_gen.load(std::memory_order_acquire);
+  if (c.gen == gen && h >= c.lo && h + bytes <= c.hi)
+    return reinterpret_cast<void *>(c.dev + (h - c.lo));
+  std::shared_lock<std::shared_mutex> lk(g_hmutex);
+  auto it = g_host_ranges.upper_bound(h);
+  if (it == g_host_ranges.begin())
+    return nullptr;
+  --it;
+  if (h + bytes > it->first + it->second.bytes)
+    return nullptr;
+  c.gen = g_host_gen.load(std::memory_order_acquire);
+  c.lo = it->first;
+  c.hi = it->first + it->second.bytes;
+  c.dev = it->second.dev;
+  return reinterpret_cast<void *>(c.dev + (h - c.lo));
+}
+
+/** the same for memory page-locked by someone else (the driver knows; one query per pointer and call) */
+static void *driver_alias(const void *p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
+    return attr.devicePointer;
+  (void)cudaGetLastError();
+  return nullptr;
+}
+
+/* One CTA copies the activation from the caller's page-locked buffer into device memory (every CTA of the GEMV reads
+ * all of it, which must not cross the host link 148 times); the GEMV behind it starts fetching weights meanwhile. */
+__global__ void host_gather_kernel(const float4 *__restrict__ src, float4 *__restrict__ dst, int n4) {
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < n4; i += blockDim.x)
+    dst[i] = src[i];
+}
+/* Completion word: runs when the GEMV's grid has completed (its result, written straight into the caller's buffer, is
+ * then on its way ahead of this store: posted writes of one device arrive in order). */
+__global__ void host_done_kernel(unsigned long long *word, unsigned long long value) {
+  pdl_wait();
+  *reinterpret_cast<volatile unsigned long long *>(word) = value;
 }
 
 /* --------------------------------------------------------- GEMM dispatch */
@@ -332,18 +406,69 @@ static int gemm_host(int qtype, unsigned M, unsigned N, unsigned K, const float 
   if ((rc = grow(c->dA, c->capA, bytesA)) || (rc = grow(c->dC, c->capC, bytesC)) ||
       (rc = grow(c->dQ, c->capQ, workspace_bytes(qtype, M, N, K))))
     return rc;
-  NNTR_CHECK_CUDA(cudaMemcpyAsync(c->dA, A, bytesA, cudaMemcpyHostToDevice, c->stream));
-  /* Decode (M == 1) with C in page-locked, device-mapped host memory: the kernel's epilogue writes the result straight
-   * into the caller's buffer (16 KB of posted writes) instead of a device buffer plus a copy back. The activation
-   * still travels by copy: every CTA reads all of x, which must not cross the host link 148 times. */
+  /* Decode (M == 1) with A and C in page-locked, device-mapped host memory -- the short path. Three launches chained
+   * by programmatic dependent launch and no stream synchronisation: a one-CTA kernel brings the activation into device
+   * memory, the GEMV (already fetching its weights) writes the result straight into the caller's buffer (N floats of
+   * posted writes), a last one-thread kernel stores this call's number into a completion word in page-locked memory,
+   * and the calling thread spins on that word. Waking a thread through the driver's stream synchronisation costs more
+   * than the GEMV itself. */
   float *c_direct = nullptr;
   if (M == 1) {
-    cudaPointerAttributes attr;
-    if (cudaPointerGetAttributes(&attr, C) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
-      c_direct = static_cast<float *>(attr.devicePointer);
-    else
-      (void)cudaGetLastError();
+    void *a_dev = host_alias(A, bytesA, 0), *c_dev = host_alias(C, bytesC, 1);
+    if (!c_dev)
+      c_dev = driver_alias(C);
+    if (c_dev && !a_dev)
+      a_dev = driver_alias(A);
+    c_direct = static_cast<float *>(c_dev);
+    if (a_dev && c_dev && !(reinterpret_cast<uintptr_t>(a_dev) & 15)) {
+      host_gather_kernel<<<1, 1024, 0, c->stream>>>(static_cast<const float4 *>(a_dev), static_cast<float4 *>(c->dA),
+                                                    (int)(K / 4));
+      count_launch();
+      switch (qtype) {
+      case NNTR_Q4_K:
+        rc = launch_gemv_q4_K(N, K, static_cast<const float *>(c->dA), dB, c_direct, NNTR_CUDA_GEMV_PDL, c->stream);
+        break;
+      case NNTR_Q4_0:
+        rc = launch_gemv_q4_0(N, K, static_cast<const float *>(c->dA), dB, c_direct, NNTR_CUDA_GEMV_PDL, c->stream);
+        break;
+      default:
+        rc = launch_gemv_q6_K(N, K, static_cast<const float *>(c->dA), dB, c_direct, NNTR_CUDA_GEMV_PDL, c->stream);
+      }
+      if (rc)
+        return rc;
+      const unsigned long long want = ++c->done_seq;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(1);
+      cfg.blockDim = dim3(1);
+      cfg.stream = c->stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      NNTR_CHECK_CUDA(cudaLaunchKernelEx(&cfg, host_done_kernel, c->done_dev, want));
+      count_launch();
+      volatile unsigned long long *word = c->done_host;
+      for (unsigned spins = 1;; ++spins) {
+        if (*word == want)
+          break;
+        _mm_pause();
+        if ((spins & 0x3fff) == 0) { // now and then ask the driver whether the stream failed or finished without us
+          const cudaError_t q = cudaStreamQuery(c->stream);
+          if (q == cudaSuccess) {
+            if (*word == want)
+              break;
+            return set_error(NNTR_CUDA_ERR_CUDA, "gemm: the stream finished without the completion word");
+          }
+          if (q != cudaErrorNotReady)
+            return check_cuda(q, "gemm (host, decode)");
+        }
+      }
+      std::atomic_thread_fence(std::memory_order_acquire);
+      return NNTR_CUDA_OK;
+    }
   }
+  NNTR_CHECK_CUDA(cudaMemcpyAsync(c->dA, A, bytesA, cudaMemcpyHostToDevice, c->stream));
   rc = gemm_dev(qtype, M, N, K, static_cast<const float *>(c->dA), dB, c_direct ? c_direct : static_cast<float *>(c->dC),
                 N, c->dQ, c->capQ, c->stream);
   if (rc)
@@ -603,6 +728,61 @@ int nntr_cuda_malloc(void **p, size_t bytes) {
   return check_cuda(cudaMemset(*p, 0, bytes ? bytes : 16), "malloc: clear");
 }
 int nntr_cuda_free(void *p) { return check_cuda(cudaFree(p), "free"); }
+
+static int host_range_add(void *p, size_t bytes, bool owned) {
+  void *dev = nullptr;
+  NNTR_CHECK_CUDA(cudaHostGetDevicePointer(&dev, p, 0));
+  std::unique_lock<std::shared_mutex> lk(g_hmutex);
+  g_host_ranges[reinterpret_cast<uintptr_t>(p)] = HostRange{bytes, reinterpret_cast<uintptr_t>(dev), owned};
+  g_host_gen.fetch_add(1, std::memory_order_release);
+  return NNTR_CUDA_OK;
+}
+static int host_range_remove(void *p, bool owned) {
+  std::unique_lock<std::shared_mutex> lk(g_hmutex);
+  auto it = g_host_ranges.find(reinterpret_cast<uintptr_t>(p));
+  if (it == g_host_ranges.end() || it->second.owned != owned)
+    return set_error(NNTR_CUDA_ERR_INVALID, owned ? "host_free: not a pointer from nntr_cuda_host_alloc"
+                                                  : "host_unregister: not a pointer given to nntr_cuda_host_register");
+  g_host_ranges.erase(it);
+  g_host_gen.fetch_add(1, std::memory_order_release);
+  return NNTR_CUDA_OK;
+}
+int nntr_cuda_host_alloc(void **p, size_t bytes) {
+  if (!p || bytes == 0)
+    return set_error(NNTR_CUDA_ERR_INVALID, "host_alloc: null pointer or zero size");
+  NNTR_CHECK_CUDA(cudaHostAlloc(p, bytes, cudaHostAllocMapped | cudaHostAllocPortable));
+  const int rc = host_range_add(*p, bytes, true);
+  if (rc) {
+    cudaFreeHost(*p);
+    *p = nullptr;
+  }
+  return rc;
+}
+int nntr_cuda_host_free(void *p) {
+  if (!p)
+    return NNTR_CUDA_OK;
+  const int rc = host_range_remove(p, true);
+  if (rc)
+    return rc;
+  return check_cuda(cudaFreeHost(p), "host_free");
+}
+int nntr_cuda_host_register(void *p, size_t bytes) {
+  if (!p || bytes == 0)
+    return set_error(NNTR_CUDA_ERR_INVALID, "host_register: null pointer or zero size");
+  NNTR_CHECK_CUDA(cudaHostRegister(p, bytes, cudaHostRegisterMapped | cudaHostRegisterPortable));
+  const int rc = host_range_add(p, bytes, false);
+  if (rc)
+    cudaHostUnregister(p);
+  return rc;
+}
+int nntr_cuda_host_unregister(void *p) {
+  if (!p)
+    return NNTR_CUDA_OK;
+  const int rc = host_range_remove(p, false);
+  if (rc)
+    return rc;
+  return check_cuda(cudaHostUnregister(p), "host_unregister");
+}
 int nntr_cuda_memcpy(void *dst, const void *src, size_t bytes, int kind) {
   if (kind < 1 || kind > 3)
     return set_error(NNTR_CUDA_ERR_INVALID, "memcpy: kind must be 1 (host to device), 2 (device to host) or 3 (device to device)");

@@ -7,6 +7,7 @@
 #include "cuda_context.h"
 
 #include <algorithm>
+#include <new>
 #include <stdexcept>
 
 #include <fc_layer.h>
@@ -18,10 +19,25 @@
 
 namespace nntrainer {
 
+void CudaHostAllocator::alloc(void **ptr, size_t size, size_t alignment) {
+  // page-locked memory starts on a page boundary, which satisfies every alignment the framework asks for
+  if (!ptr || (alignment & (alignment - 1)) || alignment > 4096)
+    throw std::invalid_argument("cuda_context: unsupported allocation request");
+  if (nntr_cuda_host_alloc(ptr, size ? size : 1) != NNTR_CUDA_OK) {
+    ml_loge("cuda_context: %s", nntr_cuda_last_error());
+    throw std::bad_alloc();
+  }
+}
+
+void CudaHostAllocator::free(void *ptr) {
+  if (nntr_cuda_host_free(ptr) != NNTR_CUDA_OK)
+    ml_loge("cuda_context: %s", nntr_cuda_last_error());
+}
+
 CudaContext::CudaContext() : Context(std::make_shared<ContextData>()) {
   // host-side allocator for whatever the framework plans on this context's behalf; device memory is managed inside
   // libnntr_cuda.so (weights are mirrored into HBM when they are registered)
-  getContextData()->setMemAllocator(std::make_shared<MemAllocator>());
+  getContextData()->setMemAllocator(std::make_shared<CudaHostAllocator>());
 }
 
 int CudaContext::init() {

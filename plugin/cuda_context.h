@@ -11,8 +11,10 @@
  * of the reference changes. It keeps its own factory map like ClContext does (nntrainer/cl_context.h:96-205) and
  * overrides BOTH createLayerObject overloads (nntrainer/context.h:116-140; the base versions return nullptr). The
  * layers it hands out are the stock ones: a fully connected layer created here forwards through
- * Tensor::dot -> FloatTensor::dotQnK, where the ENABLE_CUDA branch calls cuda_backend (INTEGRATION.md section 2).
- * Engine::registerContext dereferences getMemAllocator() (nntrainer/engine.h:82-84), so the constructor installs one.
+ * Tensor::dot -> FloatTensor::dotQnK, where the ENABLE_CUDA branch calls cuda_backend.
+ * Engine::registerContext dereferences getMemAllocator() (nntrainer/engine.h:82-84) and keeps it under the context's
+ * name, so the constructor installs one: CudaHostAllocator, whose memory is page-locked and device-mapped, so that a
+ * decode call on tensors planned into it needs no copy-engine transfer and no stream synchronisation.
  */
 #ifndef NNTR_CUDA_CONTEXT_H_
 #define NNTR_CUDA_CONTEXT_H_
@@ -27,6 +29,15 @@
 #include <mem_allocator.h>
 
 namespace nntrainer {
+
+/** MemAllocator (nntrainer/mem_allocator.h:25-32) over nntr_cuda_host_alloc / nntr_cuda_host_free */
+class CudaHostAllocator : public MemAllocator {
+public:
+  /** @throws std::bad_alloc when the driver refuses (no device bound yet, or out of page-locked memory) */
+  void alloc(void **ptr, size_t size, size_t alignment) override;
+  void free(void *ptr) override;
+  std::string getName() override { return "gpu"; }
+};
 
 class CudaContext : public Context {
 public:

@@ -251,6 +251,63 @@ def test_host_pointer_gemv_into_page_locked_output(be, port, q, gen):
     be.unregister_weight(B)
 
 
+@pytest.mark.parametrize("q,gen", [("q4_K", O.random_q4_Kx8), ("q4_0", O.random_q4_0x8), ("q6_K", O.random_q6_K)])
+def test_host_pointer_decode_short_path_in_library_memory(be, port, q, gen):
+    """Activation and result in memory from nntr_cuda_host_alloc (what the plug-in's allocator gives the framework):
+    gather kernel + GEMV + completion word, no copy-engine transfer and no stream synchronisation. Repeated calls on
+    the same buffers, chained on the host, stay bit-equal to the checker (each call's completion is really waited
+    for)."""
+    rng = np.random.default_rng(29)
+    N, K = 1024, 1024
+    B = gen(rng, N, K)
+    xn = be.host_alloc((1, K), np.float32)
+    yn = be.host_alloc((1, N), np.float32)
+    xn[...] = acts(rng, 1, K)
+    ref = xn.copy()
+    launches0 = be.launch_count()
+    for step in range(6):
+        yn[...] = np.nan
+        getattr(be, f"gemm_{q}")(1, N, K, xn, K, B, N, yn, N)
+        want = port.gemm(q, ref, B, N)
+        assert np.array_equal(bits(yn), bits(want)), step
+        ref = (want * 0.5).astype(np.float32)
+        xn[...] = ref
+    assert be.launch_count() - launches0 == 18  # three launches per call
+    # an offset inside the block is found too (a tensor planned at an offset of the pool)
+    big = be.host_alloc((4, K), np.float32)
+    big[...] = 0
+    big[2] = ref[0]
+    getattr(be, f"gemm_{q}")(1, N, K, big[2:3], K, B, N, yn, N)
+    assert np.array_equal(bits(yn), bits(port.gemm(q, ref, B, N)))
+    be.unregister_weight(B)
+    for a in (xn, yn, big):
+        be.host_free(a)
+
+
+def test_host_register_in_place_and_errors(be, port):
+    rng = np.random.default_rng(31)
+    N, K = 512, 1024
+    B = O.random_q4_Kx8(rng, N, K)
+    raw = np.zeros(3 * 4096 + 4 * (K + N), dtype=np.uint8)
+    off = (-raw.ctypes.data) % 4096
+    buf = raw[off:off + 2 * 4096 + 0].view(np.float32)          # two whole pages, page aligned
+    x, y = buf[:K][None], buf[K:K + N][None]
+    x[...] = acts(rng, 1, K)
+    want = port.gemm("q4_K", x.copy(), B, N)
+    be.host_register(buf)
+    be.gemm_q4_K(1, N, K, x, K, B, N, y, N)
+    assert np.array_equal(bits(y), bits(want))
+    with pytest.raises(ValueError):
+        be.lib_check("nntr_cuda_host_free", buf.ctypes.data)      # registered in place, not allocated by the library
+    be.host_unregister(buf)
+    with pytest.raises(ValueError):
+        be.host_unregister(buf)
+    y[...] = 0
+    be.gemm_q4_K(1, N, K, x, K, B, N, y, N)                       # ordinary memory again: staged copies, same bits
+    assert np.array_equal(bits(y), bits(want))
+    be.unregister_weight(B)
+
+
 # ------------------------------------------------------------------- GEMM
 @pytest.mark.parametrize("q,gen", [("q4_K", O.random_q4_Kx8), ("q4_0", O.random_q4_0x8), ("q6_K", O.random_q6_K)])
 @pytest.mark.parametrize("M", [2, 3, 4, 5, 8, 13, 64, 67])
