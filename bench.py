@@ -45,7 +45,7 @@ ALG_BYTES = WEIGHT_BYTES + 4 * K_COLS + 4 * N_ROWS   # 9 469 952 per GEMV
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q4_K_resident_kernel launch on this workload (one ncu
 # capture of three launches of the chained ring; the figure is per launch)
-NCU_TRAFFIC_BYTES = 9_489_152
+NCU_TRAFFIC_BYTES = 9_478_912
 
 
 def measured_peak():
@@ -881,6 +881,33 @@ def run_case(args):
         x = torch.randn(1, H, device=dev)
         call = lambda: layer.forward(x)
         work = {"case": "moe_layer", "hidden": H, "inter": I, "experts": E, "top_k": k, "tokens": 1}
+    elif args.case == "decoder":
+        # four layers of the Qwen3-4B shape with the full vocabulary, 512 cache rows in place of a prefill; steps run
+        # eagerly so that a profiler sees every launch of a token
+        import os
+        import tempfile
+        from nntrainer_b200.decoder import DecoderConfig, Qwen3Decoder
+        from oracle.cpu_decoder import synthetic_weights, write_bin
+        context = 512
+        cfg = DecoderConfig(n_layers=4, hidden=2560, n_heads=32, n_kv_heads=8, head_dim=128, inter=9728, vocab=151936,
+                            max_seq=context + 64)
+        w = synthetic_weights(cfg, seed=5)
+        with tempfile.TemporaryDirectory() as td:
+            path = os.path.join(td, "decoder_case.bin")
+            write_bin(path, cfg, w)
+            dec = Qwen3Decoder(cfg, path, pdl=True)
+        for a in dec.attn:
+            a.kcache[:context].copy_((torch.randn((context, cfg.n_kv_heads, cfg.head_dim), device=dev) * 0.5).half())
+            a.vcache[:context].copy_((torch.randn((context, cfg.n_kv_heads, cfg.head_dim), device=dev) * 0.5).half())
+        tok = torch.full((1,), 11.0, device=dev)
+        state = {"pos": context}
+
+        def call():
+            nxt, nxt_f = dec.step(tok, state["pos"])
+            tok.copy_(nxt_f)
+            state["pos"] += 1
+        work = {"case": "decoder", "layers": cfg.n_layers, "hidden": cfg.hidden, "vocab": cfg.vocab, "context": context,
+                "launches_per_token": 1 + cfg.n_layers * 12 + 3}
     else:  # lm_head
         N, K = 151936, 2560
         W = torch.from_numpy(O.random_q6_K(rng, N, K)).to(dev)
@@ -921,7 +948,7 @@ def main():
     ap.add_argument("--ring", type=int, default=RING, help="distinct weight matrices per step (default keeps every launch out of L2)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the GEMV kernel from an ncu capture (reported as roofline.traffic)")
-    ap.add_argument("--case", default=None, choices=["prefill", "prefill_f16", "lm_head", "lm_head_prefill", "moe_layer"],
+    ap.add_argument("--case", default=None, choices=["prefill", "prefill_f16", "lm_head", "lm_head_prefill", "moe_layer", "decoder"],
                     help="run one small single-kernel case (profiler captures) instead of the benchmark")
     args = ap.parse_args()
     globals()["RING"] = args.ring
