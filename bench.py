@@ -798,7 +798,7 @@ def run_ours(args):
         others = other_shapes(be, torch, dev, peak) if (world == 1 and not args.no_extra) else None
         prefill = prefill_gemm_shapes(be, torch, dev) if (world == 1 and not args.no_extra) else None
         decode = decode_step_qwen3_4b(be, torch, dev, peak) if (world == 1 and not args.no_extra) else None
-        model = model_decode_qwen3_4b(be, torch, dev, peak) if (world == 1 and not args.no_extra and not args.no_model) else None
+        model = model_decode_qwen3_4b(be, torch, dev, peak) if (world == 1 and not args.no_model) else None
         cpu_desc = None
         if world == 1 and not args.no_cpu:
             _, cpu_desc, _ = cpu_reference_gbps(host_ring, args.cpu_seconds)

@@ -82,12 +82,21 @@ __global__ void rms_norm_kernel(const float *__restrict__ x, const float *__rest
  * connection in front of the norm: sum = a + b, one rounded addition per element, written out as well); warp 0 runs
  * the ordered sum of squares from shared memory; all threads write the normalised row. */
 constexpr int RMS_CTA_THREADS = 256;
+constexpr int RMS_GAMMA_PRE = 12; // covers rows of up to 3072 elements
 __global__ void rms_norm_row_kernel(const float *__restrict__ x, const float *__restrict__ residual,
                                     float *__restrict__ sum_out, const float *__restrict__ gamma,
                                     float *__restrict__ y, int width, float eps) {
   extern __shared__ __align__(16) float row[];
   __shared__ float s_scale;
   pdl_launch_dependents();
+  // gamma is a weight: its first RMS_GAMMA_PRE * 256 elements are fetched before the wait for the previous kernel, which
+  // takes one memory round trip off the dependent part
+  float gpre[RMS_GAMMA_PRE];
+#pragma unroll
+  for (int u = 0; u < RMS_GAMMA_PRE; ++u) {
+    const int i = threadIdx.x + u * RMS_CTA_THREADS;
+    gpre[u] = (gamma && i < width) ? gamma[i] : 1.0f;
+  }
   pdl_wait();
   const size_t base = (size_t)blockIdx.x * width;
   for (int i = threadIdx.x; i < width; i += RMS_CTA_THREADS) {
@@ -106,7 +115,15 @@ __global__ void rms_norm_row_kernel(const float *__restrict__ x, const float *__
   }
   __syncthreads();
   const float scale = s_scale;
-  for (int i = threadIdx.x; i < width; i += RMS_CTA_THREADS) {
+#pragma unroll
+  for (int u = 0; u < RMS_GAMMA_PRE; ++u) {
+    const int i = threadIdx.x + u * RMS_CTA_THREADS;
+    if (i < width) {
+      const float n = __fmul_rn(row[i], scale);
+      y[base + i] = gamma ? __fmul_rn(n, gpre[u]) : n;
+    }
+  }
+  for (int i = threadIdx.x + RMS_GAMMA_PRE * RMS_CTA_THREADS; i < width; i += RMS_CTA_THREADS) {
     const float n = __fmul_rn(row[i], scale);
     y[base + i] = gamma ? __fmul_rn(n, gamma[i]) : n;
   }
