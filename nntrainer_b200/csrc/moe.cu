@@ -14,15 +14,17 @@
  *        d = a.Wd[e] (+ bd[e])
  *   y[token] = sum over the token's experts in ASCENDING expert index of d * w
  *
- * Five launches per layer: router (one CTA per token), batched gate+up GEMV
- * (2 * pairs problems in one grid; the expert picked per problem through a
- * device-side pointer table the router writes), activation, batched down GEMV,
- * combine. The reference runs every expert GEMV with M = 1 even in prefill, so
- * the batched GEMV reproduces its numerics; top-k ties (measure zero) resolve
- * to the lower expert index here, unspecified in the reference (heap order of
- * std::partial_sort). Parity: expert selection exact, outputs within the path's
- * tolerance (the reference's router product and row sums go through BLAS and
- * its exp through libm / a polynomial, none of which is reproduced bit for bit).
+ * Decode (fewer than 8 tokens), five launches per layer and no clearing launch: router (32 CTAs per token, the last
+ * to arrive reduces, selects and writes the device-side weight-pointer tables), batched gate+up GEMV (2 * pairs
+ * problems in one grid, the expert picked per problem through those tables), activation, batched down GEMV, combine.
+ * The reference runs every expert GEMV with M = 1 even in prefill, so the batched GEMV reproduces its numerics.
+ * Prefill (8 tokens or more): the pairs are sorted by expert and each projection stage is ONE grouped GEMM launch over
+ * a device-side problem table; every row keeps the M = 1 float chain, so both paths give the same bits.
+ * Top-k follows std::partial_sort of the GNU library, ties included (heap order emulated when two of the k + 1 greatest
+ * probabilities are equal). The exponentials are the reference's (double exp for softmax and sigmoid, its table +
+ * cubic form inside swiglu). Not reproduced bit for bit: the router product and the row sums, which the reference
+ * computes through BLAS in an order that is not defined; expert selection is exact wherever the top-k margin exceeds
+ * the difference between two summation orders (tests log the margin).
  */
 #include <algorithm>
 
