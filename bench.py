@@ -782,7 +782,7 @@ def run_ours(args):
     if group is not None and not verified:
         failures.append("n-split verification failed")
     moe = None
-    if not args.no_extra and not args.no_moe:
+    if not args.no_moe:
         try:
             moe = moe_decode_step(be, torch, dev, world, rank)
         except Exception as exc:  # noqa: BLE001

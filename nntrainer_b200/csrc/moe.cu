@@ -48,6 +48,7 @@ constexpr int MOE_COUNTER_TOKENS = 4096;   // arrival counters kept at the start
 constexpr int ROUTER_WARPS = 8;
 constexpr int ROUTER_SLICES = 32; // CTAs per token
 constexpr int MAX_E_PER_LANE = 8; // up to 256 experts
+constexpr int ROUTER_PRE = 8;     // rows of a warp's slice fetched before the dependency wait
 
 /* std::partial_sort(idx, idx + k, idx + n, [&](a, b) { return v[a] > v[b]; }) on idx = 0..n-1, as the GNU C++ library
  * performs it (heap selection, then heap sort): out[0..k) = the indices of the k greatest values in descending order,
@@ -110,7 +111,22 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
   __shared__ bool is_last;
   const int t = blockIdx.x, sl = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_launch_dependents(); // the expert GEMVs may be scheduled now; they wait for this grid before reading its tables
-  pdl_wait();              // x comes from the kernel before (no-op without the launch attribute)
+  // The router weight does not depend on the previous kernel: the first ROUTER_PRE rows of this warp's slice are
+  // fetched into registers before the wait (for H = 2048 that is the whole slice), so that only the activation's
+  // round trip is left behind it.
+  const int per = (E + 31) / 32;
+  const int nw = ROUTER_SLICES * ROUTER_WARPS, wi = sl * ROUTER_WARPS + warp;
+  const int h0 = (int)(((long long)wi * H) / nw), h1 = (int)(((long long)(wi + 1) * H) / nw);
+  float wpre[ROUTER_PRE][MAX_E_PER_LANE];
+#pragma unroll
+  for (int u = 0; u < ROUTER_PRE; ++u) {
+    const int hh = h0 + u < h1 ? h0 + u : h1 - 1;
+    const float *row = wr + (size_t)hh * E;
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; ++i)
+      wpre[u][i] = (i < per && lane + 32 * i < E && h1 > h0) ? row[lane + 32 * i] : 0.f;
+  }
+  pdl_wait(); // x comes from the kernel before (no-op without the launch attribute)
   if (ep.n_ranks && t == 0 && sl == 0 && threadIdx.x < ep.n_ranks) {
     // heartbeat: "this rank has started layer call seq", i.e. it has finished combining seq - 1 (stream order)
     const unsigned long long seq = (*ep.epoch - 1) * ep.layers_per_epoch + ep.layer + 1;
@@ -118,14 +134,22 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
     *slot = seq;
   }
   const float *xt = x + (size_t)t * H;
-  const int per = (E + 31) / 32;
   float acc[MAX_E_PER_LANE];
 #pragma unroll
   for (int i = 0; i < MAX_E_PER_LANE; ++i)
     acc[i] = 0.f;
-  const int nw = ROUTER_SLICES * ROUTER_WARPS, wi = sl * ROUTER_WARPS + warp;
-  const int h0 = (int)(((long long)wi * H) / nw), h1 = (int)(((long long)(wi + 1) * H) / nw);
-  for (int h = h0; h < h1; h += 4) { // four rows in flight per lane
+  {
+    float xv[ROUTER_PRE];
+#pragma unroll
+    for (int u = 0; u < ROUTER_PRE; ++u)
+      xv[u] = h0 + u < h1 ? xt[h0 + u] : 0.f;
+#pragma unroll
+    for (int u = 0; u < ROUTER_PRE; ++u)
+#pragma unroll
+      for (int i = 0; i < MAX_E_PER_LANE; ++i)
+        acc[i] = fmaf(xv[u], wpre[u][i], acc[i]); // rows past the slice: x = 0, as in the tail of the loop below
+  }
+  for (int h = h0 + ROUTER_PRE; h < h1; h += 4) { // four rows in flight per lane
     float xv[4], wv[4][MAX_E_PER_LANE];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
