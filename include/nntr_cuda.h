@@ -190,6 +190,16 @@ int nntr_cuda_gemv_dev(int qtype, unsigned N, unsigned K, const float *x, const 
 int nntr_cuda_gemv_batched_dev(int qtype, unsigned N, unsigned K, const float *x, const void *const *w_table,
                                unsigned n_problems, float *y, unsigned flags, void *stream);
 
+/** The same with the residual add and RMS norm that precede the projections folded into the launch: every problem's
+ *  activation is rms_norm(x + residual) * gamma (Applications/CausalLM/layers/rms_norm.cpp:60-80 after the addition
+ *  layer), computed by each CTA for itself in the GEMV's prologue, and sum_out[K] receives x + residual (the next
+ *  residual; written by one CTA; a buffer of its own). residual may be NULL: no addition, sum_out unused. Same bits as
+ *  nntr_cuda_add_rms_norm_dev followed by nntr_cuda_gemv_batched_dev; one launch instead of two. Q4_K only. */
+int nntr_cuda_gemv_batched_add_norm_dev(int qtype, unsigned N, unsigned K, const float *x, const float *residual,
+                                        float *sum_out, const float *gamma, float eps, const void *const *w_table,
+                                        unsigned n_problems, float *y, unsigned flags, void *stream);
+
+
 /* ------------------------------------------- operators between the matmuls */
 
 /** RMS normalisation over rows of `width` floats, then times gamma[width] (gamma may be NULL):

@@ -207,6 +207,17 @@ def gemv_batched(qtype: str, N: int, K: int, x, w_table, n_problems: int, y, pdl
     return y
 
 
+def gemv_batched_add_norm(qtype: str, N: int, K: int, x, residual, sum_out, gamma, eps: float, w_table,
+                          n_problems: int, y, pdl: bool = False):
+    """gemv_batched on rms_norm(x + residual) * gamma, the add and the norm computed in the GEMV's prologue; sum_out
+    receives x + residual. residual=None: plain norm."""
+    check(lib().nntr_cuda_gemv_batched_add_norm_dev(
+        QTYPE[qtype], N, K, x.data_ptr(), residual.data_ptr() if residual is not None else None,
+        sum_out.data_ptr() if sum_out is not None else None, gamma.data_ptr(), eps, w_table.data_ptr(), n_problems,
+        y.data_ptr(), capi.GEMV_PDL if pdl else 0, _stream()))
+    return y
+
+
 # ---------------------------------------------------------------- quantizers
 def quantize_row_q8_K(src, dst=None, k: int | None = None):
     """cpu_backend.h:1093. numpy in -> numpy uint8 blocks out (host entry point)."""

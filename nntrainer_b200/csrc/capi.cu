@@ -720,6 +720,23 @@ int nntr_cuda_gemv_batched_dev(int qtype, unsigned N, unsigned K, const float *x
   return launch_gemv_q4_K_batched(N, K, x, nullptr, y, flags, n_problems, b, static_cast<cudaStream_t>(stream));
 }
 
+int nntr_cuda_gemv_batched_add_norm_dev(int qtype, unsigned N, unsigned K, const float *x, const float *residual,
+                                        float *sum_out, const float *gamma, float eps, const void *const *w_table,
+                                        unsigned n_problems, float *y, unsigned flags, void *stream) {
+  if (qtype != NNTR_Q4_K)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_batched_add_norm: Q4_K weights only (got qtype %d)", qtype);
+  int rc = check_weight_shape(qtype, N, K);
+  if (rc)
+    return rc;
+  if (!w_table || !x || !gamma || !y)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_batched_add_norm: null pointer");
+  if (residual && (!sum_out || sum_out == x || sum_out == residual))
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_batched_add_norm: the sum needs a buffer of its own (every CTA reads "
+                                            "both addends while one CTA writes the sum)");
+  GemvBatch b = {w_table, 0, 1, (long long)N, 1, GEMV_ACT_ADD_NORM, residual, gamma, sum_out, eps};
+  return launch_gemv_q4_K_batched(N, K, x, nullptr, y, flags, n_problems, b, static_cast<cudaStream_t>(stream));
+}
+
 /* ---- plain device memory and CUDA IPC, for callers that do not bring a framework ---- */
 int nntr_cuda_malloc(void **p, size_t bytes) {
   if (!p)

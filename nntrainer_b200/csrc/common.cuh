@@ -226,7 +226,18 @@ struct GemvBatch {
   long long y_stride; // elements between the outputs of consecutive problems
   int static_table;   // the table was complete before the previous kernel in the stream started: no need to wait for
                       // that kernel before reading it (the weight stream may then overlap the previous kernel)
+  // what the activation is computed from, in the kernel's prologue, before it is quantized (every problem shares ONE
+  // activation row then):
+  //   GEMV_ACT_PLAIN    x as it is
+  //   GEMV_ACT_ADD_NORM rms_norm(x + x2) * gamma, the sum also stored to sum_out by one CTA (x2 may be null: no
+  //                     addition, no sum_out) -- the residual add and RMS norm in front of a projection
+  int act;
+  const float *x2;
+  const float *gamma;
+  float *sum_out;
+  float eps;
 };
+enum { GEMV_ACT_PLAIN = 0, GEMV_ACT_ADD_NORM = 2 };
 
 /** N-split of a projection over the GPUs of one node, exchange fused into the GEMV, without fences:
  *   data   every rank computes the output rows of its weight shard and its epilogue stores each as an 8-byte

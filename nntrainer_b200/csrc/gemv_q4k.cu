@@ -37,6 +37,7 @@
  */
 #include "common.cuh"
 #include "pipeline.cuh"
+#include "rms.cuh"
 
 namespace nntr {
 
@@ -154,13 +155,15 @@ __device__ __forceinline__ void row_block_sums(const uint8_t *blk, const uint8_t
   J = j_acc;
 }
 
+template <int ACT>
 __global__ void __launch_bounds__(GEMV_THREADS, 2)
 gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, float *__restrict__ y, int n_groups,
                  int nb, int ngslot, GemvBatch batch, GemvExchange ex) {
   extern __shared__ __align__(128) uint8_t smem[];
   if (batch.w_table) { // batched launch: blockIdx.y picks the problem
     const int p = blockIdx.y;
-    x += (long long)(p / batch.x_div) * batch.x_stride;
+    if (ACT == GEMV_ACT_PLAIN)
+      x += (long long)(p / batch.x_div) * batch.x_stride;
     y += (long long)p * batch.y_stride;
   }
   if (batch.w_table) {
@@ -341,13 +344,57 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     unsigned long long epoch_early = 0;
     if (ex.n_ranks && ex.layer > 0)
       epoch_early = *reinterpret_cast<const volatile unsigned long long *>(ex.epoch);
+    // gamma is a weight: the part for this warp's first block is fetched before the wait for the previous kernel
+    float4 gpre0 = make_float4(1.f, 1.f, 1.f, 1.f), gpre1 = gpre0;
+    if (ACT == GEMV_ACT_ADD_NORM && warp < nb) {
+      const float *gm = batch.gamma + warp * QK_K + lane * 8;
+      gpre0 = *reinterpret_cast<const float4 *>(gm);
+      gpre1 = *reinterpret_cast<const float4 *>(gm + 4);
+    }
     if (!chained_by_tags)
       pdl_wait();
     const uint32_t in_tag =
       ex.n_ranks ? (uint32_t)(((ex.layer > 0 ? epoch_early : *ex.epoch) - 1) * ex.layers_per_epoch + ex.layer) : 0u;
+    // ---- activation prologues (see GemvBatch::act): the operators in front of the projection, computed by every CTA
+    // for itself (a few thousand elements: cheaper than a launch of their own and the round trip through memory)
+    float act_scale = 1.0f;
+    if (ACT == GEMV_ACT_ADD_NORM) {
+      // the row (x + x2) goes to shared memory -- the part[] area, free until the first dot product, which comes after
+      // the barrier at the end of the quantization -- one CTA also stores it; warp 0 runs the ordered sum of squares
+      float *row = reinterpret_cast<float *>(part);
+      float *scale_slot = row + (size_t)nb * QK_K;
+      const int K = nb * QK_K, ct = threadIdx.x; // consumer warps are warps 0..15
+      for (int i = ct; i < K; i += CONSUMER_WARPS * 32) {
+        float v = x[i];
+        if (batch.x2) {
+          v = __fadd_rn(v, batch.x2[i]);
+          if (blockIdx.x == 0 && blockIdx.y == 0)
+            batch.sum_out[i] = v;
+        }
+        row[i] = v;
+      }
+      consumer_bar_sync();
+      if (warp == 0) {
+        const float sumsq = rms_sumsq_warp(row, K, lane);
+        if (lane == 0)
+          *scale_slot = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, (float)K), batch.eps)));
+      }
+      consumer_bar_sync();
+      act_scale = *scale_slot;
+    }
     for (int b = warp; b < nb && !*abort_flag; b += CONSUMER_WARPS) {
       float4 v0, v1;
-      if (ex.x_tagged & 1) {
+      if (ACT == GEMV_ACT_ADD_NORM) {
+        const float *rs = reinterpret_cast<const float *>(part) + b * QK_K + lane * 8;
+        const float *gm = batch.gamma + b * QK_K + lane * 8;
+        const float4 r0 = *reinterpret_cast<const float4 *>(rs), r1 = *reinterpret_cast<const float4 *>(rs + 4);
+        const float4 m0 = b == warp ? gpre0 : *reinterpret_cast<const float4 *>(gm);
+        const float4 m1 = b == warp ? gpre1 : *reinterpret_cast<const float4 *>(gm + 4);
+        v0 = make_float4(__fmul_rn(__fmul_rn(r0.x, act_scale), m0.x), __fmul_rn(__fmul_rn(r0.y, act_scale), m0.y),
+                         __fmul_rn(__fmul_rn(r0.z, act_scale), m0.z), __fmul_rn(__fmul_rn(r0.w, act_scale), m0.w));
+        v1 = make_float4(__fmul_rn(__fmul_rn(r1.x, act_scale), m1.x), __fmul_rn(__fmul_rn(r1.y, act_scale), m1.y),
+                         __fmul_rn(__fmul_rn(r1.z, act_scale), m1.z), __fmul_rn(__fmul_rn(r1.w, act_scale), m1.w));
+      } else if (ex.x_tagged & 1) {
         // the activation arrives as (value, launch number) pairs stored by the previous launch of every rank:
         // poll (bounded) until all eight elements of the lane carry that launch's number
         const uint4 *xs = reinterpret_cast<const uint4 *>(x) + (size_t)(b * QK_K + lane * 8) / 2;
@@ -547,7 +594,18 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
   if (N == 0)
     return NNTR_CUDA_OK;
   const int n_groups = (int)(N / 8), nb = (int)(K / QK_K), sms = sm_count();
-  const int ngslot = pick_ngslot(nb);
+  int ngslot = pick_ngslot(nb);
+  if (batch.act != GEMV_ACT_PLAIN) {
+    if (g_next_exchange)
+      return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_q4_K: an activation prologue cannot be combined with the exchange");
+    if (batch.act == GEMV_ACT_ADD_NORM) {
+      if (!batch.gamma || (reinterpret_cast<uintptr_t>(batch.gamma) & 15) || (batch.x2 && !batch.sum_out))
+        return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: norm prologue needs gamma (16-byte aligned) and, with a "
+                                                "second addend, an output for the sum");
+      if (ngslot < 16)
+        ngslot = 16; // the row (K floats) and the scale live in the area of the partial results until the dots start
+    }
+  }
   const SmemLayout L = smem_layout(nb, ngslot);
   if (L.total > 200 * 1024)
     return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_q4_K: K=%u needs %u B of shared memory", K, L.total);
@@ -555,7 +613,8 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
   int dev = 0;
   NNTR_CHECK_CUDA(cudaGetDevice(&dev));
   if (!attr_done[dev & 63]) {
-    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<GEMV_ACT_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<GEMV_ACT_ADD_NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_done[dev & 63] = true;
   }
   // A share that fits the ring (one step per warp) runs one CTA per SM and leaves
@@ -586,7 +645,9 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
     if (grid > (unsigned)NSPLIT_MAX_CTAS)
       return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_nsplit: %u CTAs exceed the %d flag slots per rank", grid, NSPLIT_MAX_CTAS);
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel, x, Wp, y, n_groups, nb, ngslot, batch, ex);
+  cudaError_t e =
+    batch.act == GEMV_ACT_ADD_NORM ? cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_ADD_NORM>, x, Wp, y, n_groups, nb, ngslot, batch, ex)
+                                   : cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_PLAIN>, x, Wp, y, n_groups, nb, ngslot, batch, ex);
   count_launch();
   return check_cuda(e, "gemv_q4_K launch");
 }

@@ -51,8 +51,6 @@ __device__ __forceinline__ float ftz_min(float a, float b) {
 /** exp(x) as avx2_approx_exp_e2lookup<8> computes it (avx2_impl.cpp:228-292): clamp, scale by 8/ln2, split into an
  *  integer (magic-number rounding) and a fraction, 2^(n/8) from an 8-entry table, cubic in the fraction. */
 __device__ __forceinline__ float approx_exp_e2lookup8(float x) {
-  const uint32_t tbl[8] = {0x3f800000u, 0x3f7b95c2u, 0x3f7837f0u, 0x3f75fed7u,
-                           0x3f7504f3u, 0x3f75672au, 0x3f7744fdu, 0x3f7ac0c7u};
   x = ftz_max(x, -87.0f);
   x = ftz_mul(x, (float)(1.0 / 0.693147180559945309417232121458176568 * 8));
   x = ftz_min(x, (float)(88.3762626647949f / 0.693147180559945309417232121458176568 * 8));
@@ -60,7 +58,13 @@ __device__ __forceinline__ float approx_exp_e2lookup8(float x) {
   const uint32_t bits = __float_as_uint(xi);
   xi = ftz_sub(xi, 0x1.8p23f);
   const float frac = ftz_sub(x, xi);
-  const float s = __uint_as_float(tbl[bits & 7u] + (bits << 20));
+  // the 8-entry table as a tree of selects: an indexed local array would live in local memory (eight stores and a load
+  // per call)
+  const bool b0 = bits & 1u, b1 = bits & 2u, b2 = bits & 4u;
+  const uint32_t l0 = b0 ? 0x3f7b95c2u : 0x3f800000u, l1 = b0 ? 0x3f75fed7u : 0x3f7837f0u;
+  const uint32_t l2 = b0 ? 0x3f75672au : 0x3f7504f3u, l3 = b0 ? 0x3f7ac0c7u : 0x3f7744fdu;
+  const uint32_t m0 = b1 ? l1 : l0, m1 = b1 ? l3 : l2;
+  const float s = __uint_as_float((b2 ? m1 : m0) + (bits << 20));
   const float C0 = 0x1.c6af84b912394p-5f / 8 / 8 / 8, C1 = 0x1.ebfce50fac4f3p-3f / 8 / 8, C2 = 0x1.62e42ff0c52d6p-1f / 8;
   const float q0 = ftz_fma(frac, C0, C1);
   const float f2 = ftz_mul(frac, frac);

@@ -64,9 +64,10 @@ def tensor_list(c: DecoderConfig):
 class Qwen3Decoder:
     """Greedy decoding of a Qwen3-shaped dense decoder from a .bin file, batch 1, one token per step."""
 
-    def __init__(self, cfg: DecoderConfig, bin_path: str, device: str = "cuda", pdl: bool = False):
+    def __init__(self, cfg: DecoderConfig, bin_path: str, device: str = "cuda", pdl: bool = False, fuse: bool = True):
         import torch
         self.torch, self.cfg, self.dev = torch, cfg, device
+        self.fuse = fuse  # fold the residual adds and RMS norms into the prologues of the projections behind them
         self.tensors = tensor_list(cfg)
         self.w = be.BinWeights(bin_path, [(d, n, k) for _, d, n, k in self.tensors])
         self.ptr = {name: self.w.ptr[i] for i, (name, *_r) in enumerate(self.tensors)}
@@ -121,16 +122,37 @@ class Qwen3Decoder:
         With ``pos_dev`` (a device word) the position is read on the device, so the launches can be captured once into
         a CUDA graph and replayed for every later token.
 
-        Launches per layer: (residual add +) RMS norm; q | k | v projections (one batched launch); per-head norms +
-        rotary + cache append; scores; softmax; values; attention_out; residual add + RMS norm; ffn_up | ffn_gate (one
-        batched launch); SwiGLU; ffn_down. Every fusion keeps the bits of the separate operators."""
+        Launches per layer without ``fuse``: (residual add +) RMS norm; q | k | v projections (one batched launch);
+        per-head norms + rotary + cache append; scores; softmax; values; attention_out; residual add + RMS norm;
+        ffn_up | ffn_gate (one batched launch); SwiGLU; ffn_down -- twelve. With ``fuse`` the two norms run in the
+        prologues of the projections behind them -- ten. (The SwiGLU in the prologue of ffn_down was measured slower
+        than its own launch: every CTA would recompute all 9728 activations.) Every fusion keeps the bits of the
+        separate operators."""
         c, b, pdl = self.cfg, self.b, self.pdl
         q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
         be.embedding(c.embedding_dtype, self._P(self.ptr["embedding0"]), token_f, c.vocab, c.hidden,
                      out=b["x"].view(1, -1), pdl=pdl)
         x = b["x"]
+        fuse = self.fuse and self._qkv_ok
         for i in range(c.n_layers):
             p = f"layer{i}_"
+            qk_norm = (self._P(self.ptr[p + "q_norm"]), self._P(self.ptr[p + "k_norm"]), c.norm_eps)
+            if fuse:
+                # 10 launches: (add +) norm + q|k|v; rotary; scores; softmax; values; o; add + norm + up|gate; SwiGLU; down
+                g_att, g_ffn = self._P(self.ptr[p + "attention_norm"]), self._P(self.ptr[p + "ffn_norm"])
+                if i == 0:
+                    be.gemv_batched_add_norm(c.fc_dtype, kv_dim, c.hidden, x, None, None, g_att, c.norm_eps,
+                                             self._qkv_tab[i], q_dim // kv_dim + 2, b["qkv"], pdl=pdl)
+                else:  # the previous block's output x = h + ffn_down, and its norm
+                    be.gemv_batched_add_norm(c.fc_dtype, kv_dim, c.hidden, b["h"], b["d"], x, g_att, c.norm_eps,
+                                             self._qkv_tab[i], q_dim // kv_dim + 2, b["qkv"], pdl=pdl)
+                self.attn[i].step(b["q"], b["k"], b["v"], pos, pos_dev=pos_dev, out=b["a"], pdl=pdl, qk_norm=qk_norm)
+                self._gemv(p + "attention_out", b["a"], b["o"])
+                be.gemv_batched_add_norm(c.fc_dtype, c.inter, c.hidden, x, b["o"], b["h"], g_ffn, c.norm_eps,
+                                         self._ug_tab[i], 2, b["ug"], pdl=pdl)
+                be.swiglu(b["up"], b["gate"], out=b["act"], pdl=pdl)
+                self._gemv(p + "ffn_down", b["act"], b["d"])
+                continue
             if i == 0:
                 self._norm(x, p + "attention_norm", b["n"])
             else:  # the previous block's output x = h + ffn_down, and its norm
@@ -144,8 +166,7 @@ class Qwen3Decoder:
                 self._gemv(p + "wk", b["n"], b["k"])
                 self._gemv(p + "wq", b["n"], b["q"])
             # k_norm and q_norm (per-head RMS norms) run inside the rotary / cache-append launch
-            self.attn[i].step(b["q"], b["k"], b["v"], pos, pos_dev=pos_dev, out=b["a"], pdl=pdl,
-                              qk_norm=(self._P(self.ptr[p + "q_norm"]), self._P(self.ptr[p + "k_norm"]), c.norm_eps))
+            self.attn[i].step(b["q"], b["k"], b["v"], pos, pos_dev=pos_dev, out=b["a"], pdl=pdl, qk_norm=qk_norm)
             self._gemv(p + "attention_out", b["a"], b["o"])
             be.add_rms_norm(x, b["o"], self._P(self.ptr[p + "ffn_norm"]), c.norm_eps, sum_out=b["h"], out=b["n"], pdl=pdl)
             if self._qkv_ok:

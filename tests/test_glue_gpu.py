@@ -232,3 +232,38 @@ def test_batched_gemv_equals_single_launches(be, port):
         for p in range(P):
             assert same_bits(got[p], port.gemm("q4_K", x[None], Ws[p], N)[0]), (p, pdl)
     be.device_status()
+
+
+@pytest.mark.parametrize("N,K,n_problems", [(1024, 2560, 6), (9728, 2560, 2), (64, 256, 3), (512, 4096, 1)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_projections_with_the_add_and_norm_in_their_prologue(be, port, N, K, n_problems, with_residual):
+    """nntr_cuda_gemv_batched_add_norm_dev against the separate launches (residual add + RMS norm, then the batched
+    GEMV) and against the checker: same bits, and the sum written out."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(N + K + n_problems)
+    Ws = [O.random_q4_Kx8(rng, N, K) for _ in range(n_problems)]
+    dW = [dev(w) for w in Ws]
+    table = torch.tensor([w.data_ptr() for w in dW], dtype=torch.int64, device="cuda")
+    x = rng.standard_normal(K).astype(np.float32)
+    r = rng.standard_normal(K).astype(np.float32) if with_residual else None
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    eps = 1e-6
+    s = (x + r).astype(np.float32) if with_residual else x
+    n = port.rms_norm(s[None], gamma, eps)[0]
+    want = np.stack([port.gemm("q4_K", n[None], w, N)[0] for w in Ws])
+    y = torch.full((n_problems, N), float("nan"), device="cuda")
+    sum_out = torch.full((K,), float("nan"), device="cuda") if with_residual else None
+    be.gemv_batched_add_norm("q4_K", N, K, dev(x), dev(r) if with_residual else None, sum_out, dev(gamma), eps, table,
+                             n_problems, y)
+    assert same_bits(y.cpu().numpy(), want)
+    if with_residual:
+        assert same_bits(sum_out.cpu().numpy(), s)
+    # chained behind another kernel with programmatic dependent launch
+    y2 = torch.full((n_problems, N), float("nan"), device="cuda")
+    xd = dev(x)
+    xd.mul_(1.0)
+    so2 = torch.empty(K, device="cuda") if with_residual else None
+    be.gemv_batched_add_norm("q4_K", N, K, xd, dev(r) if with_residual else None, so2, dev(gamma), eps, table,
+                             n_problems, y2, pdl=True)
+    assert same_bits(y2.cpu().numpy(), want)
+    be.device_status()
