@@ -271,7 +271,9 @@ size_t nntr_cuda_attention_workspace_bytes(const nntr_attn_desc *a, unsigned max
  *  (compute_kcaches, avx2_impl.cpp:1595), softmax over those rows per head with the optional sink
  *  (softmax_row_inplace, :1181-1307), probabilities times the value cache (compute_fp16vcache_fp32_transposed, :1512):
  *  out[n_heads_q][head_dim], equal to the reference's result bit for bit. With pos_dev the grids are sized for
- *  max_rows cache rows. Three launches. n_heads_q % 8 == 0, head_dim % 8 == 0. */
+ *  max_rows cache rows. Two launches (scores; softmax + values) for windows of up to 2048 rows, else -- or with
+ *  NNTR_CUDA_ATTN_SEPARATE in flags -- three; same bits either way. n_heads_q % 8 == 0, head_dim % 8 == 0. */
+#define NNTR_CUDA_ATTN_SEPARATE 2u
 int nntr_cuda_attention_decode_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows,
                                    const float *q, const void *kcache, const void *vcache, float *out, void *workspace,
                                    size_t workspace_bytes, unsigned flags, void *stream);

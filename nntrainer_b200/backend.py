@@ -479,7 +479,7 @@ class Attention:
         need = int(lib().nntr_cuda_attention_workspace_bytes(C.byref(self.desc), max_seq))
         self.ws = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
 
-    def step(self, q, k, v, pos: int, pos_dev=None, out=None, pdl: bool = False, qk_norm=None):
+    def step(self, q, k, v, pos: int, pos_dev=None, out=None, pdl: bool = False, qk_norm=None, separate: bool = False):
         """q [hq*hd] (rotated in place), k, v [hkv*hd] fp32 device tensors of the token at ``pos`` -> out [hq*hd].
         ``qk_norm`` = (q_gamma, k_gamma, eps) applies Qwen3's per-head RMS norms to q and k in the same launch."""
         torch = _torch()
@@ -498,7 +498,8 @@ class Attention:
                 _stream()))
         check(lib().nntr_cuda_attention_decode_dev(C.byref(self.desc), pos, pd, self.max_seq, q.data_ptr(),
                                                    self.kcache.data_ptr(), self.vcache.data_ptr(), out.data_ptr(),
-                                                   self.ws.data_ptr(), self.ws.numel(), _flags(pdl), _stream()))
+                                                   self.ws.data_ptr(), self.ws.numel(),
+                                                   _flags(pdl) | (capi.ATTN_SEPARATE if separate else 0), _stream()))
         return out
 
 

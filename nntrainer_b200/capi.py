@@ -20,6 +20,7 @@ HEADER = os.path.join(HERE, "..", "include", "nntr_cuda.h")
 Q4_0, Q8_0, Q4_K, Q6_K, Q8_K = 2, 8, 12, 14, 15
 QTYPE = {"q4_0": Q4_0, "q8_0": Q8_0, "q4_K": Q4_K, "q6_K": Q6_K, "q8_K": Q8_K}
 GEMV_PDL = 1
+ATTN_SEPARATE = 2
 
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOMEM, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5
 _EXC = {ERR_INVALID: ValueError, ERR_CUDA: RuntimeError, ERR_UNSUPPORTED: NotImplementedError,

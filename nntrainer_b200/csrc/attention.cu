@@ -361,6 +361,126 @@ __global__ void attn_values_kernel(const float *__restrict__ probs, const uint16
     out[(size_t)(n * gqa + h) * hd + d0 + lane] = acc;
 }
 
+/* Softmax and values in one launch, for windows of at most SV_MAX_ROWS rows: the CTA layout of attn_values_kernel
+ * (kv head, 32 consecutive d; warp h = head h of the group), with the softmax of the group's heads computed by every
+ * CTA for itself in front -- warp h: maximum, exponentials into shared memory, lane 0 adds them in ascending row
+ * order, all lanes divide -- while the first value tiles are already on their way. Same arithmetic and order as
+ * attn_softmax_kernel + attn_values_kernel; one launch, one dependency wait and no trip of the probabilities through
+ * global memory less. */
+constexpr unsigned SV_MAX_ROWS = 2048;
+__global__ void attn_softmax_values_kernel(const float *__restrict__ scores, const uint16_t *__restrict__ vcache,
+                                           float *__restrict__ out, const float *__restrict__ sink,
+                                           const unsigned *__restrict__ pos_dev, unsigned pos, int hq, int hkv, int hd,
+                                           unsigned window, unsigned cap_rows) {
+  extern __shared__ __align__(16) uint8_t vsm[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned row_num = pos_dev ? *pos_dev : pos;
+  const unsigned first = row_num < window ? 0u : row_num + 1 - window;
+  unsigned cnt = row_num + 1 - first;
+  if (cnt > cap_rows)
+    cnt = cap_rows; // the launch was sized for cap_rows (the scores kernel before it computed no more either)
+  const int gqa = hq / hkv;
+  const int n = blockIdx.y;
+  const int d0 = blockIdx.x * 32;
+  const int lane = threadIdx.x & 31, h = threadIdx.x >> 5;
+  // shared memory: probabilities [gqa][stride] f32 | ring of VBUF value tiles [VT][32] f16
+  const unsigned p_stride = (cap_rows + 3u) & ~3u;
+  float *probs = reinterpret_cast<float *>(vsm);
+  uint8_t *vring = vsm + (size_t)gqa * p_stride * 4;
+  const size_t vbytes = (size_t)VT * 64;
+  const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(vring);
+  auto issue = [&](unsigned tile, int buf) {
+    const unsigned j0 = tile * VT;
+    const unsigned rows = cnt - j0 < (unsigned)VT ? cnt - j0 : (unsigned)VT;
+    const uint32_t vdst = vbase + buf * (uint32_t)vbytes;
+    for (unsigned c = threadIdx.x; c < rows * 4; c += blockDim.x) { // up to 4 chunks of 16 B (8 values) per row
+      const unsigned r = c >> 2, cc = c & 3;
+      if (d0 + (int)cc * 8 < hd)
+        cp_async_16(vdst + r * 64 + cc * 16, vcache + ((size_t)(first + j0 + r) * hkv + n) * hd + d0 + cc * 8);
+    }
+    cp_async_commit();
+  };
+  const unsigned n_tiles = (cnt + VT - 1) / VT;
+  for (int t = 0; t < VBUF - 1; ++t) {
+    if ((unsigned)t < n_tiles)
+      issue(t, t);
+    else
+      cp_async_commit();
+  }
+  // ---- softmax of head n * gqa + h by warp h (attn_softmax_kernel's steps)
+  {
+    float *e = probs + (size_t)h * p_stride;
+    const int c = n * gqa + h;
+    float mx = -INFINITY;
+    for (unsigned r = lane; r < cnt; r += 32) {
+      const float v = scores[(size_t)r * hq + c];
+      e[r] = v;
+      mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1)
+      mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
+    if (sink)
+      mx = fmaxf(mx, sink[c]);
+    for (unsigned r = lane; r < cnt; r += 32)
+      e[r] = exp256_lane(__fsub_rn(e[r], mx));
+    __syncwarp();
+    float sum = 0.f;
+    if (lane == 0) {
+      sum = sink ? exp256_lane(__fsub_rn(sink[c], mx)) : 0.0f;
+      unsigned r = 0;
+      for (; r + 16 <= cnt; r += 16) { // loads issued together, adds in order
+        float ev[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          ev[u] = e[r + u];
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          sum = __fadd_rn(sum, ev[u]);
+      }
+      for (; r < cnt; ++r)
+        sum = __fadd_rn(sum, e[r]);
+    }
+    sum = __shfl_sync(FULL, sum, 0);
+    for (unsigned r = lane; r < cnt; r += 32)
+      e[r] = __fdiv_rn(e[r], sum);
+    __syncwarp(); // warp h reads only its own head's probabilities below
+  }
+  // ---- values
+  const float *pr = probs + (size_t)h * p_stride;
+  float acc = 0.f;
+  for (unsigned t = 0; t < n_tiles; ++t) {
+    const int buf = t % VBUF;
+    if (t + VBUF - 1 < n_tiles)
+      issue(t + VBUF - 1, (t + VBUF - 1) % VBUF); // the buffer tile t - 1 used: everyone left it at the barrier below
+    else
+      cp_async_commit();
+    asm volatile("cp.async.wait_group %0;" ::"n"(VBUF - 1) : "memory");
+    __syncthreads();
+    const uint16_t *vt = reinterpret_cast<const uint16_t *>(vring + buf * vbytes);
+    const float *pt = pr + t * VT;
+    const unsigned rows = cnt - t * VT < (unsigned)VT ? cnt - t * VT : (unsigned)VT;
+    unsigned j = 0;
+    for (; j + 8 <= rows; j += 8) {
+      float a[8], b[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        a[u] = pt[j + u];
+        b[u] = half_bits_to_float(vt[(j + u) * 32 + lane]);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        acc = __fmaf_rn(a[u], b[u], acc);
+    }
+    for (; j < rows; ++j)
+      acc = __fmaf_rn(pt[j], half_bits_to_float(vt[j * 32 + lane]), acc);
+    __syncthreads(); // done with this buffer before a later tile is copied into it
+  }
+  if (d0 + lane < hd)
+    out[(size_t)(n * gqa + h) * hd + d0 + lane] = acc;
+}
+
 /* ---------------------------------------------------------------- launchers */
 
 static int check_attn(const nntr_attn_desc *a) {
@@ -450,6 +570,24 @@ int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigne
   count_launch();
   if ((rc = check_cuda(e, "attention scores launch")))
     return rc;
+  // short windows: the softmax runs in front of the values, in the same launch (NNTR_CUDA_ATTN_SEPARATE keeps them apart)
+  const size_t sv_smem = (size_t)(hq / hkv) * ((rows + 3u) & ~3u) * sizeof(float) + (size_t)VBUF * VT * 64;
+  if (!(flags & NNTR_CUDA_ATTN_SEPARATE) && rows <= SV_MAX_ROWS && sv_smem <= 160u * 1024u) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    NNTR_CHECK_CUDA(cudaGetDevice(&dev));
+    if (!attr_done[dev & 63]) {
+      NNTR_CHECK_CUDA(cudaFuncSetAttribute(attn_softmax_values_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      attr_done[dev & 63] = true;
+    }
+    cfg.gridDim = dim3((unsigned)((hd + 31) / 32), (unsigned)hkv);
+    cfg.blockDim = dim3(32 * (unsigned)(hq / hkv));
+    cfg.dynamicSmemBytes = sv_smem;
+    e = cudaLaunchKernelEx(&cfg, attn_softmax_values_kernel, static_cast<const float *>(scores), vcache, out, a->sink,
+                           pos_dev, pos, hq, hkv, hd, a->window, rows);
+    count_launch();
+    return check_cuda(e, "attention softmax + values launch");
+  }
   cfg.gridDim = dim3((unsigned)hq);
   cfg.blockDim = dim3(SOFTMAX_THREADS);
   const unsigned cap_rows = rows < 11264u ? rows : 11264u; // 44 KB of shared memory at most; later rows stay in global

@@ -97,7 +97,7 @@ def test_embedding_rows_q6_K_q4_0_fp32_and_bad_index(be, port):
     be.device_status()
 
 
-def _attention_case(be, port, hq, hkv, hd, ctx, window, with_sink, seed):
+def _attention_case(be, port, hq, hkv, hd, ctx, window, with_sink, seed, separate=False):
     rng = np.random.default_rng(seed)
     max_seq = ctx + 2
     sink = (rng.standard_normal(hq) * 2).astype(np.float32) if with_sink else None
@@ -115,9 +115,9 @@ def _attention_case(be, port, hq, hkv, hd, ctx, window, with_sink, seed):
         qd = dev(q)
         if pos % 2:  # alternate between the position by value and through a device word
             pos_dev.fill_(pos)
-            out = att.step(qd, dev(k), dev(v), 0, pos_dev=pos_dev)
+            out = att.step(qd, dev(k), dev(v), 0, pos_dev=pos_dev, separate=separate)
         else:
-            out = att.step(qd, dev(k), dev(v), pos)
+            out = att.step(qd, dev(k), dev(v), pos, separate=separate)
         qr = port.rotary(q, hd, cos[pos], sin[pos])
         kc[pos] = port.rotary(k, hd, cos[pos], sin[pos], to_fp16=True).reshape(hkv, hd)
         vc[pos] = port.rotary(v, hd, cos[pos], sin[pos], to_fp16=True, only_convert=True).reshape(hkv, hd)
@@ -139,12 +139,14 @@ def _attention_case(be, port, hq, hkv, hd, ctx, window, with_sink, seed):
     (64, 8, 64, 40, None, True),       # GPT-OSS full-attention layer with sinks
     (8, 8, 8, 5, 3, False),            # smallest vector widths, window shorter than the context
 ])
-def test_single_token_attention_bit_exact(be, port, hq, hkv, hd, ctx, window, with_sink):
-    _attention_case(be, port, hq, hkv, hd, ctx, window, with_sink, seed=hq + ctx)
+@pytest.mark.parametrize("separate", [False, True], ids=["two_launches", "three_launches"])
+def test_single_token_attention_bit_exact(be, port, hq, hkv, hd, ctx, window, with_sink, separate):
+    _attention_case(be, port, hq, hkv, hd, ctx, window, with_sink, seed=hq + ctx, separate=separate)
 
 
-def test_attention_long_context_2048(be, port):
-    """BASELINE's decode context for the Qwen3-30B-A3B shape: the row-ordered sums over 2048 cache rows."""
+@pytest.mark.parametrize("separate", [False, True], ids=["two_launches", "three_launches"])
+def test_attention_long_context_2048(be, port, separate):
+    """The decode context of the Qwen3-30B-A3B configuration: the row-ordered sums over 2048 cache rows."""
     rng = np.random.default_rng(11)
     hq, hkv, hd, ctx = 32, 4, 128, 2048
     att = be.Attention(hq, hkv, hd, ctx, theta=1e6)
@@ -158,7 +160,7 @@ def test_attention_long_context_2048(be, port):
     k = rng.standard_normal(hkv * hd).astype(np.float32)
     v = rng.standard_normal(hkv * hd).astype(np.float32)
     qd = dev(q)
-    out = att.step(qd, dev(k), dev(v), pos).cpu().numpy()
+    out = att.step(qd, dev(k), dev(v), pos, separate=separate).cpu().numpy()
     kcu, vcu = kc.view(np.uint16).copy(), vc.view(np.uint16).copy()
     kcu[pos] = port.rotary(k, hd, cos[pos], sin[pos], to_fp16=True).reshape(hkv, hd)
     vcu[pos] = port.rotary(v, hd, cos[pos], sin[pos], to_fp16=True, only_convert=True).reshape(hkv, hd)
