@@ -265,7 +265,7 @@ int nntr_cuda_qk_norm_rope_cache_append_dev(const nntr_attn_desc *a, unsigned po
                                             const float *k, const float *v, const float *q_gamma, const float *k_gamma,
                                             float eps, void *kcache, void *vcache, const float *cos_tab,
                                             const float *sin_tab, unsigned flags, void *stream);
-/** Scratch for the call below: scores of min(max_rows, window) cache rows x n_heads_q. */
+/** Scratch for the call below: scores of min(max_rows, window) cache rows (rounded up to four) x n_heads_q. */
 size_t nntr_cuda_attention_workspace_bytes(const nntr_attn_desc *a, unsigned max_rows);
 /** Second half (mha_core.cpp:521-531): scores of the query against cache rows [max(0, pos+1-window), pos]
  *  (compute_kcaches, avx2_impl.cpp:1595), softmax over those rows per head with the optional sink

@@ -112,7 +112,7 @@ __global__ void rope_cache_append_kernel(float *__restrict__ q, const float *__r
 constexpr int SCORE_WARPS = 4;
 __global__ void attn_scores_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kcache,
                                    float *__restrict__ scores, const unsigned *__restrict__ pos_dev, unsigned pos,
-                                   int hq, int hkv, int hd, unsigned window) {
+                                   int hq, int hkv, int hd, unsigned window, unsigned head_stride) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   pdl_launch_dependents(); // the next kernel may start its own prologue; it waits before it reads
   pdl_wait();
@@ -155,7 +155,10 @@ __global__ void attn_scores_kernel(const float *__restrict__ q, const uint16_t *
     s = __fadd_rn(s, __shfl_down_sync(FULL, s, 2));
     if (l == 0 && t0 + j < row_cnt) {
       const float sum = __fadd_rn(0.0f, s);
-      scores[(size_t)(t0 + j) * hq + n * gqa + g] = (float)((double)sum / norm);
+      // head_stride != 0: head-major [head][head_stride] (what the fused softmax + values kernel reads, one head per
+      // CTA, contiguously); else the reference's [row][head]
+      const size_t at = head_stride ? (size_t)(n * gqa + g) * head_stride + t0 + j : (size_t)(t0 + j) * hq + n * gqa + g;
+      scores[at] = (float)((double)sum / norm);
     }
   }
 }
@@ -361,18 +364,22 @@ __global__ void attn_values_kernel(const float *__restrict__ probs, const uint16
     out[(size_t)(n * gqa + h) * hd + d0 + lane] = acc;
 }
 
-/* Softmax and values in one launch, for windows of at most SV_MAX_ROWS rows: the CTA layout of attn_values_kernel
- * (kv head, 32 consecutive d; warp h = head h of the group), with the softmax of the group's heads computed by every
- * CTA for itself in front -- warp h: maximum, exponentials into shared memory, lane 0 adds them in ascending row
- * order, all lanes divide -- while the first value tiles are already on their way. Same arithmetic and order as
- * attn_softmax_kernel + attn_values_kernel; one launch, one dependency wait and no trip of the probabilities through
- * global memory less. */
+/* Softmax and values in one launch, for windows of at most SV_MAX_ROWS rows. One CTA per query head, warp w = head
+ * dimensions 32 w .. 32 w + 31. The scores arrive head-major, so the CTA reads its head's row contiguously. All warps
+ * share the softmax (maximum, exponentials, the division), thread 0 adds the exponentials in ascending row order (the
+ * reference's order), and meanwhile the first value tiles are on their way; then every thread runs its row-ordered
+ * multiply-add chain over tiles of SVT rows of the kv head's values (the heads of a group read the same tiles from
+ * L2). Same arithmetic and order as attn_softmax_kernel + attn_values_kernel. */
 constexpr unsigned SV_MAX_ROWS = 2048;
+constexpr int SVT = 128;  // rows per value tile
+constexpr int SVBUF = 3;  // tiles in the ring
 __global__ void attn_softmax_values_kernel(const float *__restrict__ scores, const uint16_t *__restrict__ vcache,
                                            float *__restrict__ out, const float *__restrict__ sink,
                                            const unsigned *__restrict__ pos_dev, unsigned pos, int hq, int hkv, int hd,
                                            unsigned window, unsigned cap_rows) {
   extern __shared__ __align__(16) uint8_t vsm[];
+  __shared__ float red[8];
+  __shared__ float s_bcast;
   pdl_launch_dependents();
   pdl_wait();
   const unsigned row_num = pos_dev ? *pos_dev : pos;
@@ -381,54 +388,58 @@ __global__ void attn_softmax_values_kernel(const float *__restrict__ scores, con
   if (cnt > cap_rows)
     cnt = cap_rows; // the launch was sized for cap_rows (the scores kernel before it computed no more either)
   const int gqa = hq / hkv;
-  const int n = blockIdx.y;
-  const int d0 = blockIdx.x * 32;
-  const int lane = threadIdx.x & 31, h = threadIdx.x >> 5;
-  // shared memory: probabilities [gqa][stride] f32 | ring of VBUF value tiles [VT][32] f16
+  const int c = blockIdx.x, n = c / gqa;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nthreads = blockDim.x, nwarps = nthreads >> 5;
+  const int d = threadIdx.x;
+  // shared memory: probabilities [stride] f32 | ring of SVBUF value tiles [SVT][hd] f16
   const unsigned p_stride = (cap_rows + 3u) & ~3u;
-  float *probs = reinterpret_cast<float *>(vsm);
-  uint8_t *vring = vsm + (size_t)gqa * p_stride * 4;
-  const size_t vbytes = (size_t)VT * 64;
+  float *e = reinterpret_cast<float *>(vsm);
+  uint8_t *vring = vsm + (size_t)p_stride * 4;
+  const size_t vbytes = (size_t)SVT * hd * 2;
   const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(vring);
+  const int chunks_per_row = hd / 8;
   auto issue = [&](unsigned tile, int buf) {
-    const unsigned j0 = tile * VT;
-    const unsigned rows = cnt - j0 < (unsigned)VT ? cnt - j0 : (unsigned)VT;
+    const unsigned j0 = tile * SVT;
+    const unsigned rows = cnt - j0 < (unsigned)SVT ? cnt - j0 : (unsigned)SVT;
     const uint32_t vdst = vbase + buf * (uint32_t)vbytes;
-    for (unsigned c = threadIdx.x; c < rows * 4; c += blockDim.x) { // up to 4 chunks of 16 B (8 values) per row
-      const unsigned r = c >> 2, cc = c & 3;
-      if (d0 + (int)cc * 8 < hd)
-        cp_async_16(vdst + r * 64 + cc * 16, vcache + ((size_t)(first + j0 + r) * hkv + n) * hd + d0 + cc * 8);
+    for (unsigned k = threadIdx.x; k < rows * chunks_per_row; k += nthreads) {
+      const unsigned r = k / chunks_per_row, cc = k - r * chunks_per_row;
+      cp_async_16(vdst + (r * hd + cc * 8) * 2, vcache + ((size_t)(first + j0 + r) * hkv + n) * hd + cc * 8);
     }
     cp_async_commit();
   };
-  const unsigned n_tiles = (cnt + VT - 1) / VT;
-  for (int t = 0; t < VBUF - 1; ++t) {
+  const unsigned n_tiles = (cnt + SVT - 1) / SVT;
+  for (int t = 0; t < SVBUF - 1; ++t) {
     if ((unsigned)t < n_tiles)
       issue(t, t);
     else
       cp_async_commit();
   }
-  // ---- softmax of head n * gqa + h by warp h (attn_softmax_kernel's steps)
+  // ---- softmax of head c by the whole CTA (attn_softmax_kernel's steps)
   {
-    float *e = probs + (size_t)h * p_stride;
-    const int c = n * gqa + h;
+    const float *sr = scores + (size_t)c * p_stride; // head-major, stride = the launch's row bound rounded up to 4
     float mx = -INFINITY;
-    for (unsigned r = lane; r < cnt; r += 32) {
-      const float v = scores[(size_t)r * hq + c];
+    for (unsigned r = threadIdx.x; r < cnt; r += nthreads) {
+      const float v = sr[r];
       e[r] = v;
       mx = fmaxf(mx, v);
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1)
       mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
+    if (lane == 0)
+      red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < nwarps; ++w)
+      mx = fmaxf(mx, red[w]);
     if (sink)
       mx = fmaxf(mx, sink[c]);
-    for (unsigned r = lane; r < cnt; r += 32)
-      e[r] = exp256_lane(__fsub_rn(e[r], mx));
-    __syncwarp();
-    float sum = 0.f;
-    if (lane == 0) {
-      sum = sink ? exp256_lane(__fsub_rn(sink[c], mx)) : 0.0f;
+    for (unsigned r = threadIdx.x; r < cnt; r += nthreads)
+      e[r] = exp256_lane(__fsub_rn(e[r], mx)); // each thread rewrites the elements it stored itself
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float sum = sink ? exp256_lane(__fsub_rn(sink[c], mx)) : 0.0f;
       unsigned r = 0;
       for (; r + 16 <= cnt; r += 16) { // loads issued together, adds in order
         float ev[16];
@@ -441,44 +452,47 @@ __global__ void attn_softmax_values_kernel(const float *__restrict__ scores, con
       }
       for (; r < cnt; ++r)
         sum = __fadd_rn(sum, e[r]);
+      s_bcast = sum;
     }
-    sum = __shfl_sync(FULL, sum, 0);
-    for (unsigned r = lane; r < cnt; r += 32)
+    __syncthreads();
+    const float sum = s_bcast;
+    for (unsigned r = threadIdx.x; r < cnt; r += nthreads)
       e[r] = __fdiv_rn(e[r], sum);
-    __syncwarp(); // warp h reads only its own head's probabilities below
+    // the barrier inside the first tile's wait below orders these writes before the chain reads them
   }
   // ---- values
-  const float *pr = probs + (size_t)h * p_stride;
   float acc = 0.f;
   for (unsigned t = 0; t < n_tiles; ++t) {
-    const int buf = t % VBUF;
-    if (t + VBUF - 1 < n_tiles)
-      issue(t + VBUF - 1, (t + VBUF - 1) % VBUF); // the buffer tile t - 1 used: everyone left it at the barrier below
+    const int buf = t % SVBUF;
+    if (t + SVBUF - 1 < n_tiles)
+      issue(t + SVBUF - 1, (t + SVBUF - 1) % SVBUF); // the buffer tile t - 1 used: everyone left it at the barrier below
     else
       cp_async_commit();
-    asm volatile("cp.async.wait_group %0;" ::"n"(VBUF - 1) : "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(SVBUF - 1) : "memory");
     __syncthreads();
     const uint16_t *vt = reinterpret_cast<const uint16_t *>(vring + buf * vbytes);
-    const float *pt = pr + t * VT;
-    const unsigned rows = cnt - t * VT < (unsigned)VT ? cnt - t * VT : (unsigned)VT;
-    unsigned j = 0;
-    for (; j + 8 <= rows; j += 8) {
-      float a[8], b[8];
+    const float *pt = e + t * SVT;
+    const unsigned rows = cnt - t * SVT < (unsigned)SVT ? cnt - t * SVT : (unsigned)SVT;
+    if (d < hd) {
+      unsigned j = 0;
+      for (; j + 8 <= rows; j += 8) {
+        const float4 pa = *reinterpret_cast<const float4 *>(pt + j), pb = *reinterpret_cast<const float4 *>(pt + j + 4);
+        const float a[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+        float b[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        a[u] = pt[j + u];
-        b[u] = half_bits_to_float(vt[(j + u) * 32 + lane]);
+        for (int u = 0; u < 8; ++u)
+          b[u] = half_bits_to_float(vt[(j + u) * hd + d]);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          acc = __fmaf_rn(a[u], b[u], acc);
       }
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        acc = __fmaf_rn(a[u], b[u], acc);
+      for (; j < rows; ++j)
+        acc = __fmaf_rn(pt[j], half_bits_to_float(vt[j * hd + d]), acc);
     }
-    for (; j < rows; ++j)
-      acc = __fmaf_rn(pt[j], half_bits_to_float(vt[j * 32 + lane]), acc);
     __syncthreads(); // done with this buffer before a later tile is copied into it
   }
-  if (d0 + lane < hd)
-    out[(size_t)(n * gqa + h) * hd + d0 + lane] = acc;
+  if (d < hd)
+    out[(size_t)c * hd + d] = acc;
 }
 
 /* ---------------------------------------------------------------- launchers */
@@ -535,7 +549,7 @@ size_t attention_workspace_bytes(const nntr_attn_desc *a, unsigned max_rows) {
   if (!a)
     return 0;
   const size_t rows = max_rows < a->window ? max_rows : a->window;
-  return rows * a->n_heads_q * sizeof(float);
+  return ((rows + 3) & ~(size_t)3) * a->n_heads_q * sizeof(float); // head-major rows are padded to four elements
 }
 
 int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows,
@@ -552,9 +566,9 @@ int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigne
   if (bound == 0 || (!pos_dev && max_rows && pos + 1 > max_rows))
     return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: position %u beyond the %u rows allowed", pos, max_rows);
   const unsigned rows = bound < a->window ? bound : a->window;
-  if (ws_bytes < (size_t)rows * a->n_heads_q * sizeof(float))
-    return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: workspace of %zu bytes needed, %zu given",
-                     (size_t)rows * a->n_heads_q * sizeof(float), ws_bytes);
+  const size_t ws_need = (((size_t)rows + 3) & ~(size_t)3) * a->n_heads_q * sizeof(float);
+  if (ws_bytes < ws_need)
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: workspace of %zu bytes needed, %zu given", ws_need, ws_bytes);
   if ((reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(vcache) & 15) ||
       (reinterpret_cast<uintptr_t>(ws) & 15) || (reinterpret_cast<uintptr_t>(q) & 15))
     return set_error(NNTR_CUDA_ERR_INVALID, "attention_decode: q, caches and workspace must be 16-byte aligned");
@@ -566,22 +580,27 @@ int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigne
   cfg.gridDim = dim3((rows + SCORE_WARPS * 4 - 1) / (SCORE_WARPS * 4), (unsigned)hkv);
   cfg.blockDim = dim3(32 * SCORE_WARPS);
   cfg.dynamicSmemBytes = (size_t)(hq / hkv) * hd * sizeof(float) + (size_t)SCORE_WARPS * 4 * hd * sizeof(uint16_t);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_scores_kernel, q, kcache, scores, pos_dev, pos, hq, hkv, hd, a->window);
+  // short windows: the softmax runs in front of the values, in the same launch, on scores stored head-major
+  // (NNTR_CUDA_ATTN_SEPARATE keeps the three kernels)
+  const unsigned sv_stride = (rows + 3u) & ~3u;
+  const int sv_threads = 32 * ((hd + 31) / 32);
+  const size_t sv_smem = (size_t)sv_stride * sizeof(float) + (size_t)SVBUF * SVT * hd * 2;
+  const bool fused = !(flags & NNTR_CUDA_ATTN_SEPARATE) && rows <= SV_MAX_ROWS && sv_threads <= 256 && sv_smem <= 200u * 1024u;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_scores_kernel, q, kcache, scores, pos_dev, pos, hq, hkv, hd, a->window,
+                                     fused ? sv_stride : 0u);
   count_launch();
   if ((rc = check_cuda(e, "attention scores launch")))
     return rc;
-  // short windows: the softmax runs in front of the values, in the same launch (NNTR_CUDA_ATTN_SEPARATE keeps them apart)
-  const size_t sv_smem = (size_t)(hq / hkv) * ((rows + 3u) & ~3u) * sizeof(float) + (size_t)VBUF * VT * 64;
-  if (!(flags & NNTR_CUDA_ATTN_SEPARATE) && rows <= SV_MAX_ROWS && sv_smem <= 160u * 1024u) {
+  if (fused) {
     static bool attr_done[64] = {};
     int dev = 0;
     NNTR_CHECK_CUDA(cudaGetDevice(&dev));
     if (!attr_done[dev & 63]) {
-      NNTR_CHECK_CUDA(cudaFuncSetAttribute(attn_softmax_values_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      NNTR_CHECK_CUDA(cudaFuncSetAttribute(attn_softmax_values_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
       attr_done[dev & 63] = true;
     }
-    cfg.gridDim = dim3((unsigned)((hd + 31) / 32), (unsigned)hkv);
-    cfg.blockDim = dim3(32 * (unsigned)(hq / hkv));
+    cfg.gridDim = dim3((unsigned)hq);
+    cfg.blockDim = dim3((unsigned)sv_threads);
     cfg.dynamicSmemBytes = sv_smem;
     e = cudaLaunchKernelEx(&cfg, attn_softmax_values_kernel, static_cast<const float *>(scores), vcache, out, a->sink,
                            pos_dev, pos, hq, hkv, hd, a->window, rows);
