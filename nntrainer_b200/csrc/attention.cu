@@ -23,7 +23,10 @@
  *
  * Cache layout as the reference's: [row][kv head][head_dim] fp16, one row per position.
  */
+#include <cuda.h>
+
 #include "common.cuh"
+#include "pipeline.cuh"
 
 namespace nntr {
 
@@ -373,13 +376,24 @@ __global__ void attn_values_kernel(const float *__restrict__ probs, const uint16
 constexpr unsigned SV_MAX_ROWS = 2048;
 constexpr int SVT = 128;  // rows per value tile
 constexpr int SVBUF = 3;  // tiles in the ring
-__global__ void attn_softmax_values_kernel(const float *__restrict__ scores, const uint16_t *__restrict__ vcache,
+__device__ int g_attn_status = 0; // raised when a bounded wait for a value tile runs out
+__global__ void attn_softmax_values_kernel(const __grid_constant__ CUtensorMap vmap, const float *__restrict__ scores,
                                            float *__restrict__ out, const float *__restrict__ sink,
                                            const unsigned *__restrict__ pos_dev, unsigned pos, int hq, int hkv, int hd,
                                            unsigned window, unsigned cap_rows) {
-  extern __shared__ __align__(16) uint8_t vsm[];
+  extern __shared__ __align__(128) uint8_t svsm[]; // the value tiles are TMA destinations: 128-byte aligned
   __shared__ float red[8];
   __shared__ float s_bcast;
+  __shared__ __align__(8) unsigned long long tile_bar[SVBUF];
+  __shared__ int abort_word;
+  volatile int *abort_flag = &abort_word;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int i = 0; i < SVBUF; ++i)
+      mbar_init(smem_u32(&tile_bar[i]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
   pdl_launch_dependents();
   pdl_wait();
   const unsigned row_num = pos_dev ? *pos_dev : pos;
@@ -393,28 +407,27 @@ __global__ void attn_softmax_values_kernel(const float *__restrict__ scores, con
   const int d = threadIdx.x;
   // shared memory: probabilities [stride] f32 | ring of SVBUF value tiles [SVT][hd] f16
   const unsigned p_stride = (cap_rows + 3u) & ~3u;
-  float *e = reinterpret_cast<float *>(vsm);
-  uint8_t *vring = vsm + (size_t)p_stride * 4;
+  float *e = reinterpret_cast<float *>(svsm);
+  uint8_t *vring = svsm + (((size_t)p_stride * 4 + 127) & ~(size_t)127); // TMA destination: 128-byte aligned
   const size_t vbytes = (size_t)SVT * hd * 2;
   const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(vring);
-  const int chunks_per_row = hd / 8;
+  // One tiled TMA copy per tile: a box of SVT cache rows x head_dim values of kv head n out of the [row][kv head x
+  // head_dim] cache (rows of a head are 2 x hkv x head_dim bytes apart, so plain bulk copies would be one per row, and
+  // an SM accepts those far too slowly: measured 16 GB/s). The box's first coordinate, n * head_dim elements, is a
+  // multiple of 8 elements = 16 bytes. Rows of the box past the end of the cache arrive as zeros and are not used.
   auto issue = [&](unsigned tile, int buf) {
-    const unsigned j0 = tile * SVT;
-    const unsigned rows = cnt - j0 < (unsigned)SVT ? cnt - j0 : (unsigned)SVT;
-    const uint32_t vdst = vbase + buf * (uint32_t)vbytes;
-    for (unsigned k = threadIdx.x; k < rows * chunks_per_row; k += nthreads) {
-      const unsigned r = k / chunks_per_row, cc = k - r * chunks_per_row;
-      cp_async_16(vdst + (r * hd + cc * 8) * 2, vcache + ((size_t)(first + j0 + r) * hkv + n) * hd + cc * 8);
+    if (threadIdx.x == 0) {
+      const uint32_t vdst = vbase + buf * (uint32_t)vbytes, bar = smem_u32(&tile_bar[buf]);
+      mbar_expect_tx(bar, (uint32_t)vbytes);
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                   ::"r"(vdst), "l"(reinterpret_cast<uint64_t>(&vmap)), "r"(n * hd), "r"((int)(first + tile * SVT)), "r"(bar)
+                   : "memory");
     }
-    cp_async_commit();
   };
   const unsigned n_tiles = (cnt + SVT - 1) / SVT;
-  for (int t = 0; t < SVBUF - 1; ++t) {
+  for (int t = 0; t < SVBUF - 1; ++t)
     if ((unsigned)t < n_tiles)
       issue(t, t);
-    else
-      cp_async_commit();
-  }
   // ---- softmax of head c by the whole CTA (attn_softmax_kernel's steps)
   {
     const float *sr = scores + (size_t)c * p_stride; // head-major, stride = the launch's row bound rounded up to 4
@@ -458,7 +471,7 @@ __global__ void attn_softmax_values_kernel(const float *__restrict__ scores, con
     const float sum = s_bcast;
     for (unsigned r = threadIdx.x; r < cnt; r += nthreads)
       e[r] = __fdiv_rn(e[r], sum);
-    // the barrier inside the first tile's wait below orders these writes before the chain reads them
+    __syncthreads(); // the chain below reads every thread's probabilities
   }
   // ---- values
   float acc = 0.f;
@@ -466,10 +479,8 @@ __global__ void attn_softmax_values_kernel(const float *__restrict__ scores, con
     const int buf = t % SVBUF;
     if (t + SVBUF - 1 < n_tiles)
       issue(t + SVBUF - 1, (t + SVBUF - 1) % SVBUF); // the buffer tile t - 1 used: everyone left it at the barrier below
-    else
-      cp_async_commit();
-    asm volatile("cp.async.wait_group %0;" ::"n"(SVBUF - 1) : "memory");
-    __syncthreads();
+    if (!mbar_wait_bounded(smem_u32(&tile_bar[buf]), (t / SVBUF) & 1, abort_flag, &g_attn_status, 1u << 22, 1024))
+      break;
     const uint16_t *vt = reinterpret_cast<const uint16_t *>(vring + buf * vbytes);
     const float *pt = e + t * SVT;
     const unsigned rows = cnt - t * SVT < (unsigned)SVT ? cnt - t * SVT : (unsigned)SVT;
@@ -491,11 +502,50 @@ __global__ void attn_softmax_values_kernel(const float *__restrict__ scores, con
     }
     __syncthreads(); // done with this buffer before a later tile is copied into it
   }
-  if (d < hd)
+  if (d < hd && !*abort_flag)
     out[(size_t)c * hd + d] = acc;
 }
 
+int read_attn_status(int *out) {
+  int v = 0;
+  NNTR_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)));
+  *out = v;
+  return NNTR_CUDA_OK;
+}
+int clear_attn_status() {
+  const int zero = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int)), "clear_attn_status");
+}
+
 /* ---------------------------------------------------------------- launchers */
+
+/* The driver's tensor-map encoder, looked up through the runtime (the library does not link against the driver). */
+static int encode_value_map(CUtensorMap *map, const uint16_t *vcache, unsigned rows, unsigned hkv, unsigned hd) {
+  typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeTiled encode = nullptr;
+  if (!encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult found;
+    NNTR_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found));
+    if (!fn || found != cudaDriverEntryPointSuccess)
+      return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "attention: the driver has no cuTensorMapEncodeTiled");
+    encode = reinterpret_cast<EncodeTiled>(fn);
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)hkv * hd, rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)hkv * hd * 2}; // bytes between rows: a multiple of 16 (head_dim % 8 == 0)
+  const cuuint32_t box[2] = {hd, (cuuint32_t)SVT};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<uint16_t *>(vcache), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(NNTR_CUDA_ERR_CUDA, "attention: cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return NNTR_CUDA_OK;
+}
+
+
 
 static int check_attn(const nntr_attn_desc *a) {
   if (!a || a->n_heads_q == 0 || a->n_heads_kv == 0 || a->head_dim == 0)
@@ -584,7 +634,7 @@ int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigne
   // (NNTR_CUDA_ATTN_SEPARATE keeps the three kernels)
   const unsigned sv_stride = (rows + 3u) & ~3u;
   const int sv_threads = 32 * ((hd + 31) / 32);
-  const size_t sv_smem = (size_t)sv_stride * sizeof(float) + (size_t)SVBUF * SVT * hd * 2;
+  const size_t sv_smem = (((size_t)sv_stride * sizeof(float) + 127) & ~(size_t)127) + (size_t)SVBUF * SVT * hd * 2;
   const bool fused = !(flags & NNTR_CUDA_ATTN_SEPARATE) && rows <= SV_MAX_ROWS && sv_threads <= 256 && sv_smem <= 200u * 1024u;
   cudaError_t e = cudaLaunchKernelEx(&cfg, attn_scores_kernel, q, kcache, scores, pos_dev, pos, hq, hkv, hd, a->window,
                                      fused ? sv_stride : 0u);
@@ -599,10 +649,14 @@ int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigne
       NNTR_CHECK_CUDA(cudaFuncSetAttribute(attn_softmax_values_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
       attr_done[dev & 63] = true;
     }
+    // tensor map of the value cache as seen by this call: [bound rows][hkv * hd] fp16, boxes of SVT rows x hd values
+    CUtensorMap vmap;
+    if ((rc = encode_value_map(&vmap, vcache, bound, (unsigned)hkv, (unsigned)hd)))
+      return rc;
     cfg.gridDim = dim3((unsigned)hq);
     cfg.blockDim = dim3((unsigned)sv_threads);
     cfg.dynamicSmemBytes = sv_smem;
-    e = cudaLaunchKernelEx(&cfg, attn_softmax_values_kernel, static_cast<const float *>(scores), vcache, out, a->sink,
+    e = cudaLaunchKernelEx(&cfg, attn_softmax_values_kernel, vmap, static_cast<const float *>(scores), out, a->sink,
                            pos_dev, pos, hq, hkv, hd, a->window, rows);
     count_launch();
     return check_cuda(e, "attention softmax + values launch");

@@ -539,6 +539,8 @@ int nntr_cuda_device_status(void) {
     return rc;
   if (!v && (rc = read_resident_status(&v)))
     return rc;
+  if (!v && (rc = read_attn_status(&v)))
+    return rc;
   if (v)
     return set_error(v, "a device kernel gave up on a bounded wait (status %d)", v);
   if ((rc = read_embed_status(&v, false)))
@@ -554,7 +556,8 @@ namespace nntr {
 int clear_device_status_words() {
   int rc;
   if ((rc = clear_device_status()) || (rc = clear_umma_status()) || (rc = clear_q6_status()) ||
-      (rc = clear_moe_status()) || (rc = clear_q40_status()) || (rc = clear_f16_status()) || (rc = clear_resident_status()))
+      (rc = clear_moe_status()) || (rc = clear_q40_status()) || (rc = clear_f16_status()) || (rc = clear_resident_status()) ||
+      (rc = clear_attn_status()))
     return rc;
   return NNTR_CUDA_OK;
 }

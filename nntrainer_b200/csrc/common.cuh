@@ -298,6 +298,8 @@ int launch_gemv_q4_K_resident(unsigned N, unsigned K, const float *x, const void
 int set_exchange_poll_limit_resident(unsigned polls);
 int read_resident_status(int *out);
 int clear_resident_status();
+int read_attn_status(int *out);
+int clear_attn_status();
 int launch_epoch_bump(unsigned long long *epoch, cudaStream_t st);
 int launch_gemv_q4_0(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
 int launch_gemv_q6_K(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags, cudaStream_t st);
