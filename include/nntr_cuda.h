@@ -277,6 +277,17 @@ size_t nntr_cuda_attention_workspace_bytes(const nntr_attn_desc *a, unsigned max
 int nntr_cuda_attention_decode_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows,
                                    const float *q, const void *kcache, const void *vcache, float *out, void *workspace,
                                    size_t workspace_bytes, unsigned flags, void *stream);
+/** Both halves in one call (MHACoreLayer::one_batch_incremental_forwarding, mha_core.cpp:459-613): per-head RMS norms
+ *  of q and k when q_gamma / k_gamma are given (both or neither), rotary embedding, append of the token's key and
+ *  value rows to the fp16 caches, scores, softmax, values. For windows of up to 2048 rows that is two launches (the
+ *  rotary work runs in the prologue of the scores launch: every CTA rotates its group's query heads for itself, the
+ *  CTA that owns the token's cache row appends it); q is then left untouched and q_rot, when not NULL, receives the
+ *  rotated query heads. Otherwise -- or with NNTR_CUDA_ATTN_SEPARATE -- it is nntr_cuda_(qk_norm_)rope_cache_append_dev
+ *  followed by nntr_cuda_attention_decode_dev (q rotated in place, copied to q_rot). Same bits either way. */
+int nntr_cuda_attention_step_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows, float *q,
+                                 const float *k, const float *v, const float *q_gamma, const float *k_gamma, float eps,
+                                 void *kcache, void *vcache, const float *cos_tab, const float *sin_tab, float *q_rot,
+                                 float *out, void *workspace, size_t workspace_bytes, unsigned flags, void *stream);
 
 /* ------------------------------------------------------- .bin weight files */
 

@@ -479,27 +479,23 @@ class Attention:
         need = int(lib().nntr_cuda_attention_workspace_bytes(C.byref(self.desc), max_seq))
         self.ws = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
 
-    def step(self, q, k, v, pos: int, pos_dev=None, out=None, pdl: bool = False, qk_norm=None, separate: bool = False):
-        """q [hq*hd] (rotated in place), k, v [hkv*hd] fp32 device tensors of the token at ``pos`` -> out [hq*hd].
-        ``qk_norm`` = (q_gamma, k_gamma, eps) applies Qwen3's per-head RMS norms to q and k in the same launch."""
+    def step(self, q, k, v, pos: int, pos_dev=None, out=None, pdl: bool = False, qk_norm=None, separate: bool = False,
+             q_rot=None):
+        """q [hq*hd], k, v [hkv*hd] fp32 device tensors of the token at ``pos`` -> out [hq*hd]. ``qk_norm`` = (q_gamma,
+        k_gamma, eps) applies Qwen3's per-head RMS norms to q and k. Two launches for windows of up to 2048 rows (q is
+        left as it is; ``q_rot`` receives the rotated heads if given), else -- or with ``separate`` -- the rotary
+        launch (q rotated in place) and three attention launches."""
         torch = _torch()
         C = self._C
         out = torch.empty(self.hq * self.hd, dtype=torch.float32, device=q.device) if out is None else out
         pd = pos_dev.data_ptr() if pos_dev is not None else None
-        if qk_norm is None:
-            check(lib().nntr_cuda_rope_cache_append_dev(C.byref(self.desc), pos, pd, q.data_ptr(), k.data_ptr(),
-                                                        v.data_ptr(), self.kcache.data_ptr(), self.vcache.data_ptr(),
-                                                        self.cos.data_ptr(), self.sin.data_ptr(), _flags(pdl), _stream()))
-        else:
-            qg, kg, eps = qk_norm
-            check(lib().nntr_cuda_qk_norm_rope_cache_append_dev(
-                C.byref(self.desc), pos, pd, q.data_ptr(), k.data_ptr(), v.data_ptr(), qg.data_ptr(), kg.data_ptr(), eps,
-                self.kcache.data_ptr(), self.vcache.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), _flags(pdl),
-                _stream()))
-        check(lib().nntr_cuda_attention_decode_dev(C.byref(self.desc), pos, pd, self.max_seq, q.data_ptr(),
-                                                   self.kcache.data_ptr(), self.vcache.data_ptr(), out.data_ptr(),
-                                                   self.ws.data_ptr(), self.ws.numel(),
-                                                   _flags(pdl) | (capi.ATTN_SEPARATE if separate else 0), _stream()))
+        qg, kg, eps = qk_norm if qk_norm is not None else (None, None, 0.0)
+        check(lib().nntr_cuda_attention_step_dev(
+            C.byref(self.desc), pos, pd, self.max_seq, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+            qg.data_ptr() if qg is not None else None, kg.data_ptr() if kg is not None else None, eps,
+            self.kcache.data_ptr(), self.vcache.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+            q_rot.data_ptr() if q_rot is not None else None, out.data_ptr(), self.ws.data_ptr(), self.ws.numel(),
+            _flags(pdl) | (capi.ATTN_SEPARATE if separate else 0), _stream()))
         return out
 
 

@@ -52,6 +52,8 @@ SIGNATURES = {
                                                      _u, _vp]),
     "nntr_cuda_attention_workspace_bytes": (_sz, [_vp, _u]),
     "nntr_cuda_attention_decode_dev": (_i, [_vp, _u, _vp, _u, _vp, _vp, _vp, _vp, _vp, _sz, _u, _vp]),
+    "nntr_cuda_attention_step_dev": (_i, [_vp, _u, _vp, _u, _vp, _vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp,
+                                          _vp, _sz, _u, _vp]),
     "nntr_cuda_bin_layout": (_i, [_vp, _sz, _vp, _vp, _vp]),
     "nntr_cuda_bin_load": (_i, [C.c_char_p, _vp, _sz, _i, _i, _vp, _vp]),
     "nntr_cuda_quantize_q8_K_dev": (_i, [_vp, _i64, _vp, _i64, _i64, _i, _vp]),

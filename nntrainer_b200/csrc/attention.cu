@@ -32,38 +32,13 @@ namespace nntr {
 
 /* ------------------------------------------------------------------ rotary */
 
-/* One warp per head (query heads, then key heads, then value heads). Optional per-head RMS norm first
- * (ReshapedRMSNormLayer on q and k: Applications/CausalLM/qwen3_causallm.cpp:60-93, sums in the order of
- * rms_norm_wrt_width_fp32_intrinsic as in glue.cu), then the rotary embedding: q in place, k into cache row `pos` as
- * fp16, v converted into cache row `pos`. The normalised head goes through shared memory so that a lane finds both
- * elements of its (k, k + head_dim/2) pairs whatever the head size. */
-constexpr int ROPE_WARPS = 4;
-__global__ void rope_cache_append_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
-                                         const float *__restrict__ q_gamma, const float *__restrict__ k_gamma, float eps,
-                                         uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache,
-                                         const float *__restrict__ cos_tab, const float *__restrict__ sin_tab,
-                                         const unsigned *__restrict__ pos_dev, unsigned pos, int hq, int hkv, int hd) {
-  extern __shared__ __align__(16) float rsm[]; // [ROPE_WARPS][hd]
-  pdl_launch_dependents(); // the next kernel may start its own prologue (weight prefetch); it waits before it reads
-  pdl_wait();
-  const unsigned p = pos_dev ? *pos_dev : pos;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int head = blockIdx.x * ROPE_WARPS + warp;
-  if (head >= hq + 2 * hkv)
-    return;
-  const int half = hd / 2;
-  if (head >= hq + hkv) { // value head: conversion only
-    const int h = head - hq - hkv;
-    const float *b = v + (size_t)h * hd;
-    uint16_t *dst = vcache + ((size_t)p * hkv + h) * hd;
-    for (int e = lane; e < hd; e += 32)
-      dst[e] = float_to_half_bits_rn(b[e]);
-    return;
-  }
-  const bool is_q = head < hq;
-  const float *src = is_q ? q + (size_t)head * hd : k + (size_t)(head - hq) * hd;
-  const float *gamma = is_q ? q_gamma : k_gamma;
-  float *st = rsm + (size_t)warp * hd;
+/* One head by one warp: optional RMS norm over the head (sums in the order of rms_norm_wrt_width_fp32_intrinsic, as in
+ * glue.cu) times gamma, then the rotary embedding of the pairs (k, k + head_dim/2) with the position's cos / sin rows;
+ * the result is left in st[head_dim] (shared memory, this warp's). A lane owns both elements of its pairs, so the
+ * rotation is done in place. */
+__device__ __forceinline__ void rope_head(const float *__restrict__ src, const float *__restrict__ gamma, float eps,
+                                          const float *__restrict__ ct, const float *__restrict__ sn, int hd, int lane,
+                                          float *st) {
   if (gamma) {
     float acc = 0.f;
     int i = 0;
@@ -90,20 +65,54 @@ __global__ void rope_cache_append_kernel(float *__restrict__ q, const float *__r
       st[e] = src[e];
   }
   __syncwarp();
-  const float *ct = cos_tab + (size_t)p * hd, *sn = sin_tab + (size_t)p * hd;
+  const int half = hd / 2;
   for (int kk = lane; kk < half; kk += 32) {
     const float a0 = st[kk], a1 = st[kk + half], c = ct[kk], s = sn[kk];
-    const float o0 = __fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s));
-    const float o1 = __fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c));
-    if (is_q) {
-      float *dst = q + (size_t)head * hd;
-      dst[kk] = o0;
-      dst[kk + half] = o1;
-    } else {
-      uint16_t *dst = kcache + ((size_t)p * hkv + (head - hq)) * hd;
-      dst[kk] = float_to_half_bits_rn(o0);
-      dst[kk + half] = float_to_half_bits_rn(o1);
-    }
+    st[kk] = __fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s));
+    st[kk + half] = __fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c));
+  }
+  __syncwarp();
+}
+
+/* One warp per head (query heads, then key heads, then value heads). Optional per-head RMS norm first
+ * (ReshapedRMSNormLayer on q and k: Applications/CausalLM/qwen3_causallm.cpp:60-93, sums in the order of
+ * rms_norm_wrt_width_fp32_intrinsic as in glue.cu), then the rotary embedding: q in place, k into cache row `pos` as
+ * fp16, v converted into cache row `pos`. The normalised head goes through shared memory so that a lane finds both
+ * elements of its (k, k + head_dim/2) pairs whatever the head size. */
+constexpr int ROPE_WARPS = 4;
+__global__ void rope_cache_append_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                         const float *__restrict__ q_gamma, const float *__restrict__ k_gamma, float eps,
+                                         uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache,
+                                         const float *__restrict__ cos_tab, const float *__restrict__ sin_tab,
+                                         const unsigned *__restrict__ pos_dev, unsigned pos, int hq, int hkv, int hd) {
+  extern __shared__ __align__(16) float rsm[]; // [ROPE_WARPS][hd]
+  pdl_launch_dependents(); // the next kernel may start its own prologue (weight prefetch); it waits before it reads
+  pdl_wait();
+  const unsigned p = pos_dev ? *pos_dev : pos;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.x * ROPE_WARPS + warp;
+  if (head >= hq + 2 * hkv)
+    return;
+  if (head >= hq + hkv) { // value head: conversion only
+    const int h = head - hq - hkv;
+    const float *b = v + (size_t)h * hd;
+    uint16_t *dst = vcache + ((size_t)p * hkv + h) * hd;
+    for (int e = lane; e < hd; e += 32)
+      dst[e] = float_to_half_bits_rn(b[e]);
+    return;
+  }
+  const bool is_q = head < hq;
+  const float *src = is_q ? q + (size_t)head * hd : k + (size_t)(head - hq) * hd;
+  float *st = rsm + (size_t)warp * hd;
+  rope_head(src, is_q ? q_gamma : k_gamma, eps, cos_tab + (size_t)p * hd, sin_tab + (size_t)p * hd, hd, lane, st);
+  if (is_q) {
+    float *dst = q + (size_t)head * hd;
+    for (int e = lane; e < hd; e += 32)
+      dst[e] = st[e];
+  } else {
+    uint16_t *dst = kcache + ((size_t)p * hkv + (head - hq)) * hd;
+    for (int e = lane; e < hd; e += 32)
+      dst[e] = float_to_half_bits_rn(st[e]);
   }
 }
 
@@ -160,6 +169,87 @@ __global__ void attn_scores_kernel(const float *__restrict__ q, const uint16_t *
       const float sum = __fadd_rn(0.0f, s);
       // head_stride != 0: head-major [head][head_stride] (what the fused softmax + values kernel reads, one head per
       // CTA, contiguously); else the reference's [row][head]
+      const size_t at = head_stride ? (size_t)(n * gqa + g) * head_stride + t0 + j : (size_t)(t0 + j) * hq + n * gqa + g;
+      scores[at] = (float)((double)sum / norm);
+    }
+  }
+}
+
+/* The rotary launch folded into the scores launch (short windows, head-major scores for attn_softmax_values_kernel):
+ * every CTA normalises and rotates the raw query heads of its group for itself (four warps, a few hundred operations:
+ * far cheaper than a launch and a trip through memory); the one warp whose four cache rows include the token's own row
+ * computes the new key row, stores it to the cache AND uses it, and converts the token's value row into the cache.
+ * q_rot, when not null, receives the rotated query heads (written by the CTAs of the first row tile). Same bits as
+ * rope_cache_append_kernel + attn_scores_kernel. */
+__global__ void attn_rope_scores_kernel(const float *__restrict__ q, const float *__restrict__ k,
+                                        const float *__restrict__ v, const float *__restrict__ q_gamma,
+                                        const float *__restrict__ k_gamma, float eps, uint16_t *__restrict__ kcache,
+                                        uint16_t *__restrict__ vcache, const float *__restrict__ cos_tab,
+                                        const float *__restrict__ sin_tab, float *__restrict__ q_rot,
+                                        float *__restrict__ scores, const unsigned *__restrict__ pos_dev, unsigned pos,
+                                        int hq, int hkv, int hd, unsigned window, unsigned head_stride) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned p = pos_dev ? *pos_dev : pos;
+  const unsigned num_rows = p + 1;
+  const unsigned start_row = num_rows < window ? 0u : num_rows - window;
+  const unsigned row_cnt = num_rows < window ? num_rows : window;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.y;
+  const int gqa = hq / hkv;
+  if (blockIdx.x * SCORE_WARPS * 4 >= row_cnt)
+    return;
+  float *qs = reinterpret_cast<float *>(smem_raw);                                    // [gqa][hd]
+  uint16_t *kall = reinterpret_cast<uint16_t *>(smem_raw + (size_t)gqa * hd * 4);     // [16][hd]
+  float *ktmp = reinterpret_cast<float *>(smem_raw + (size_t)gqa * hd * 4 + (size_t)SCORE_WARPS * 4 * hd * 2) +
+                (size_t)warp * hd;                                                     // [SCORE_WARPS][hd]
+  const float *ct = cos_tab + (size_t)p * hd, *sn = sin_tab + (size_t)p * hd;
+  for (int g = warp; g < gqa; g += SCORE_WARPS) {
+    rope_head(q + (size_t)(n * gqa + g) * hd, q_gamma, eps, ct, sn, hd, lane, qs + (size_t)g * hd);
+    if (q_rot && blockIdx.x == 0)
+      for (int e = lane; e < hd; e += 32)
+        q_rot[(size_t)(n * gqa + g) * hd + e] = qs[(size_t)g * hd + e];
+  }
+  const unsigned t0 = (blockIdx.x * SCORE_WARPS + warp) * 4;
+  uint16_t *ks = kall + (size_t)warp * 4 * hd;
+  const int chunks_per_row = hd / 8;
+  const unsigned own = p - start_row; // the token's own row, window-relative (the last one)
+  for (int c = lane; c < 4 * chunks_per_row; c += 32) {
+    const int r = c / chunks_per_row, cc = c - r * chunks_per_row;
+    uint4 vv = make_uint4(0, 0, 0, 0);
+    if (t0 + r < row_cnt && t0 + r != own)
+      vv = *reinterpret_cast<const uint4 *>(kcache + ((size_t)(start_row + t0 + r) * hkv + n) * hd + cc * 8);
+    *reinterpret_cast<uint4 *>(ks + (size_t)r * hd + cc * 8) = vv;
+  }
+  if (own >= t0 && own < t0 + 4) { // this warp appends the token's key and value rows of kv head n
+    __syncwarp();
+    rope_head(k + (size_t)n * hd, k_gamma, eps, ct, sn, hd, lane, ktmp);
+    uint16_t *krow = kcache + ((size_t)p * hkv + n) * hd, *vrow = vcache + ((size_t)p * hkv + n) * hd;
+    for (int e = lane; e < hd; e += 32) {
+      const uint16_t kb = float_to_half_bits_rn(ktmp[e]);
+      krow[e] = kb;
+      ks[(size_t)(own - t0) * hd + e] = kb;
+      vrow[e] = float_to_half_bits_rn(v[(size_t)n * hd + e]);
+    }
+  }
+  __syncthreads();
+  if (t0 >= row_cnt)
+    return;
+  const int j = lane >> 3, l = lane & 7;
+  const uint16_t *kr = ks + (size_t)j * hd;
+  const double norm = sqrt((double)(float)hd);
+  for (int g = 0; g < gqa; ++g) {
+    const float *qh = qs + (size_t)g * hd;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < hd; i += 8)
+      acc = __fmaf_rn(qh[i + l], half_bits_to_float(kr[i + l]), acc);
+    float s = __fadd_rn(acc, __shfl_down_sync(FULL, acc, 4));
+    s = __fadd_rn(s, __shfl_down_sync(FULL, s, 1));
+    s = __fadd_rn(s, __shfl_down_sync(FULL, s, 2));
+    if (l == 0 && t0 + j < row_cnt) {
+      const float sum = __fadd_rn(0.0f, s);
       const size_t at = head_stride ? (size_t)(n * gqa + g) * head_stride + t0 + j : (size_t)(t0 + j) * hq + n * gqa + g;
       scores[at] = (float)((double)sum / norm);
     }
@@ -676,6 +766,76 @@ int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigne
                          hd, a->window);
   count_launch();
   return check_cuda(e, "attention values launch");
+}
+
+/* One token's whole attention step: per-head norms (gammas may be null) + rotary + cache append + scores, then
+ * softmax + values -- two launches for windows of up to SV_MAX_ROWS rows; otherwise (or with NNTR_CUDA_ATTN_SEPARATE)
+ * the rotary launch followed by launch_attention_decode, which rotates q in place. */
+int launch_attention_step(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows, float *q,
+                          const float *k, const float *v, const float *q_gamma, const float *k_gamma, float eps,
+                          uint16_t *kcache, uint16_t *vcache, const float *cos_tab, const float *sin_tab, float *q_rot,
+                          float *out, void *ws, size_t ws_bytes, unsigned flags, cudaStream_t st) {
+  int rc = check_attn(a);
+  if (rc)
+    return rc;
+  if (!q || !k || !v || !kcache || !vcache || !cos_tab || !sin_tab || !out || !ws)
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_step: null pointer");
+  if ((q_gamma == nullptr) != (k_gamma == nullptr))
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_step: q_gamma and k_gamma come together or not at all");
+  const unsigned bound = pos_dev ? max_rows : pos + 1;
+  if (bound == 0 || (!pos_dev && max_rows && pos + 1 > max_rows))
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_step: position %u beyond the %u rows allowed", pos, max_rows);
+  const unsigned rows = bound < a->window ? bound : a->window;
+  const int hq = (int)a->n_heads_q, hkv = (int)a->n_heads_kv, hd = (int)a->head_dim;
+  const unsigned sv_stride = (rows + 3u) & ~3u;
+  const int sv_threads = 32 * ((hd + 31) / 32);
+  const size_t sv_smem = (((size_t)sv_stride * sizeof(float) + 127) & ~(size_t)127) + (size_t)SVBUF * SVT * hd * 2;
+  const bool fused = !(flags & NNTR_CUDA_ATTN_SEPARATE) && rows <= SV_MAX_ROWS && sv_threads <= 256 && sv_smem <= 200u * 1024u;
+  if (!fused) {
+    if ((rc = launch_rope_cache_append(a, pos, pos_dev, q, k, v, q_gamma, k_gamma, eps, kcache, vcache, cos_tab, sin_tab, flags,
+                                       st)))
+      return rc;
+    if (q_rot)
+      NNTR_CHECK_CUDA(cudaMemcpyAsync(q_rot, q, (size_t)hq * hd * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    return launch_attention_decode(a, pos, pos_dev, max_rows, q, kcache, vcache, out, ws, ws_bytes, flags, st);
+  }
+  const size_t ws_need = (size_t)sv_stride * a->n_heads_q * sizeof(float);
+  if (ws_bytes < ws_need)
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_step: workspace of %zu bytes needed, %zu given", ws_need, ws_bytes);
+  if ((reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(vcache) & 15) ||
+      (reinterpret_cast<uintptr_t>(ws) & 15))
+    return set_error(NNTR_CUDA_ERR_INVALID, "attention_step: caches and workspace must be 16-byte aligned");
+  float *scores = static_cast<float *>(ws);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  pdl_cfg(cfg, attr, flags, st);
+  cfg.gridDim = dim3((rows + SCORE_WARPS * 4 - 1) / (SCORE_WARPS * 4), (unsigned)hkv);
+  cfg.blockDim = dim3(32 * SCORE_WARPS);
+  cfg.dynamicSmemBytes = (size_t)(hq / hkv) * hd * sizeof(float) + (size_t)SCORE_WARPS * 4 * hd * sizeof(uint16_t) +
+                         (size_t)SCORE_WARPS * hd * sizeof(float);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_rope_scores_kernel, static_cast<const float *>(q), k, v, q_gamma, k_gamma, eps,
+                                     kcache, vcache, cos_tab, sin_tab, q_rot, scores, pos_dev, pos, hq, hkv, hd, a->window,
+                                     sv_stride);
+  count_launch();
+  if ((rc = check_cuda(e, "attention rotary + scores launch")))
+    return rc;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  NNTR_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_done[dev & 63]) {
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(attn_softmax_values_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_done[dev & 63] = true;
+  }
+  CUtensorMap vmap;
+  if ((rc = encode_value_map(&vmap, vcache, bound, (unsigned)hkv, (unsigned)hd)))
+    return rc;
+  cfg.gridDim = dim3((unsigned)hq);
+  cfg.blockDim = dim3((unsigned)sv_threads);
+  cfg.dynamicSmemBytes = sv_smem;
+  e = cudaLaunchKernelEx(&cfg, attn_softmax_values_kernel, vmap, static_cast<const float *>(scores), out, a->sink, pos_dev, pos,
+                         hq, hkv, hd, a->window, rows);
+  count_launch();
+  return check_cuda(e, "attention softmax + values launch");
 }
 
 } // namespace nntr

@@ -640,6 +640,15 @@ int nntr_cuda_attention_decode_dev(const nntr_attn_desc *a, unsigned pos, const 
                                  static_cast<cudaStream_t>(stream));
 }
 
+int nntr_cuda_attention_step_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows, float *q,
+                                 const float *k, const float *v, const float *q_gamma, const float *k_gamma, float eps,
+                                 void *kcache, void *vcache, const float *cos_tab, const float *sin_tab, float *q_rot,
+                                 float *out, void *workspace, size_t workspace_bytes, unsigned flags, void *stream) {
+  return launch_attention_step(a, pos, pos_dev, max_rows, q, k, v, q_gamma, k_gamma, eps, static_cast<uint16_t *>(kcache),
+                               static_cast<uint16_t *>(vcache), cos_tab, sin_tab, q_rot, out, workspace, workspace_bytes, flags,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int nntr_cuda_bin_layout(const nntr_bin_tensor *t, size_t n, size_t *data_offset, size_t *bytes, size_t *total) {
   return bin_layout(t, n, data_offset, bytes, total);
 }

@@ -360,6 +360,10 @@ size_t attention_workspace_bytes(const nntr_attn_desc *a, unsigned max_rows);
 int launch_attention_decode(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows,
                             const float *q, const uint16_t *kcache, const uint16_t *vcache, float *out, void *ws,
                             size_t ws_bytes, unsigned flags, cudaStream_t st);
+int launch_attention_step(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, unsigned max_rows, float *q,
+                          const float *k, const float *v, const float *q_gamma, const float *k_gamma, float eps,
+                          uint16_t *kcache, uint16_t *vcache, const float *cos_tab, const float *sin_tab, float *q_rot,
+                          float *out, void *ws, size_t ws_bytes, unsigned flags, cudaStream_t st);
 /* host side (model_file.cu) */
 int bin_layout(const nntr_bin_tensor *t, size_t n, size_t *data_offset, size_t *bytes, size_t *total);
 int bin_load(const char *path, const nntr_bin_tensor *t, size_t n, int rank, int n_ranks, void **dev_ptrs, void **arena);

@@ -123,9 +123,9 @@ class Qwen3Decoder:
         a CUDA graph and replayed for every later token.
 
         Launches per layer without ``fuse``: (residual add +) RMS norm; q | k | v projections (one batched launch);
-        per-head norms + rotary + cache append; scores; softmax + values; attention_out; residual add + RMS norm;
-        ffn_up | ffn_gate (one batched launch); SwiGLU; ffn_down -- eleven. With ``fuse`` the two norms run in the
-        prologues of the projections behind them -- nine. (The SwiGLU in the prologue of ffn_down was measured slower
+        per-head norms + rotary + cache append + scores; softmax + values; attention_out; residual add + RMS norm;
+        ffn_up | ffn_gate (one batched launch); SwiGLU; ffn_down -- ten. With ``fuse`` the two norms run in the
+        prologues of the projections behind them -- eight. (The SwiGLU in the prologue of ffn_down was measured slower
         than its own launch: every CTA would recompute all 9728 activations.) Every fusion keeps the bits of the
         separate operators."""
         c, b, pdl = self.cfg, self.b, self.pdl
@@ -138,7 +138,7 @@ class Qwen3Decoder:
             p = f"layer{i}_"
             qk_norm = (self._P(self.ptr[p + "q_norm"]), self._P(self.ptr[p + "k_norm"]), c.norm_eps)
             if fuse:
-                # 9 launches: (add +) norm + q|k|v; rotary; scores; softmax + values; o; add + norm + up|gate; SwiGLU; down
+                # 8 launches: (add +) norm + q|k|v; rotary + scores; softmax + values; o; add + norm + up|gate; SwiGLU; down
                 g_att, g_ffn = self._P(self.ptr[p + "attention_norm"]), self._P(self.ptr[p + "ffn_norm"])
                 if i == 0:
                     be.gemv_batched_add_norm(c.fc_dtype, kv_dim, c.hidden, x, None, None, g_att, c.norm_eps,

@@ -113,11 +113,13 @@ def _attention_case(be, port, hq, hkv, hd, ctx, window, with_sink, seed, separat
         k = rng.standard_normal(hkv * hd).astype(np.float32)
         v = rng.standard_normal(hkv * hd).astype(np.float32)
         qd = dev(q)
+        q_rot = torch.empty_like(qd)
         if pos % 2:  # alternate between the position by value and through a device word
             pos_dev.fill_(pos)
-            out = att.step(qd, dev(k), dev(v), 0, pos_dev=pos_dev, separate=separate)
+            out = att.step(qd, dev(k), dev(v), 0, pos_dev=pos_dev, separate=separate, q_rot=q_rot)
         else:
-            out = att.step(qd, dev(k), dev(v), pos, separate=separate)
+            out = att.step(qd, dev(k), dev(v), pos, separate=separate, q_rot=q_rot)
+        qd = q_rot  # the rotated query heads, whichever launch sequence produced them
         qr = port.rotary(q, hd, cos[pos], sin[pos])
         kc[pos] = port.rotary(k, hd, cos[pos], sin[pos], to_fp16=True).reshape(hkv, hd)
         vc[pos] = port.rotary(v, hd, cos[pos], sin[pos], to_fp16=True, only_convert=True).reshape(hkv, hd)
@@ -186,7 +188,8 @@ def test_attention_argument_checks(be):
 
 
 def test_fused_qk_norm_rope_equals_the_separate_launches(be):
-    """Qwen3's per-head q/k RMS norms folded into the rotary / cache-append launch: same bits as the three launches."""
+    """Qwen3's per-head q/k RMS norms folded into the rotary work (itself in the prologue of the scores launch, or in
+    a launch of its own): same bits as separate norm launches in front."""
     rng = np.random.default_rng(12)
     for hq, hkv, hd in ((32, 8, 128), (64, 8, 64), (8, 8, 24)):
         q = rng.standard_normal(hq * hd).astype(np.float32)
@@ -199,10 +202,19 @@ def test_fused_qk_norm_rope_equals_the_separate_launches(be):
         q1, k1 = dev(q), dev(k)
         be.rms_norm(q1, dev(qg), 1e-6, width=hd, out=q1)
         be.rms_norm(k1, dev(kg), 1e-6, width=hd, out=k1)
-        o1 = a1.step(q1, k1, dev(v), 3)
+        r1, r2, r3 = torch.empty_like(q1), torch.empty_like(q1), torch.empty_like(q1)
+        o1 = a1.step(q1, k1, dev(v), 3, q_rot=r1)
         q2 = dev(q)
-        o2 = a2.step(q2, dev(k), dev(v), 3, qk_norm=(dev(qg), dev(kg), 1e-6))
-        assert same_bits(q1.cpu().numpy(), q2.cpu().numpy())
+        o2 = a2.step(q2, dev(k), dev(v), 3, qk_norm=(dev(qg), dev(kg), 1e-6), q_rot=r2)
+        assert same_bits(q2.cpu().numpy(), q), "the two-launch sequence leaves the query untouched"
+        assert same_bits(r1.cpu().numpy(), r2.cpu().numpy())
+        # the rotary launch of its own rotates the query in place and gives the same heads
+        a3 = be.Attention(hq, hkv, hd, 8)
+        q3 = dev(q)
+        o3 = a3.step(q3, dev(k), dev(v), 3, qk_norm=(dev(qg), dev(kg), 1e-6), q_rot=r3, separate=True)
+        assert same_bits(q3.cpu().numpy(), r2.cpu().numpy()) and same_bits(r3.cpu().numpy(), r2.cpu().numpy())
+        assert torch.equal(a3.kcache[3].view(torch.int16), a2.kcache[3].view(torch.int16))
+        assert same_bits(o3.cpu().numpy(), o2.cpu().numpy())
         assert torch.equal(a1.kcache[3].view(torch.int16), a2.kcache[3].view(torch.int16))
         assert torch.equal(a1.vcache[3].view(torch.int16), a2.vcache[3].view(torch.int16))
         assert same_bits(o1.cpu().numpy(), o2.cpu().numpy())
