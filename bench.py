@@ -377,7 +377,7 @@ def model_decode_qwen3_4b(be, torch, dev, peak, context=512, new_tokens=64, cpu_
         nxt = cpu.step(nxt, context + i)
         want.append(nxt)
     cpu_s = (time.perf_counter() - t0) / cpu_tokens
-    n_launch = 1 + cfg.n_layers * 8 + 3 + 1  # embedding, 8 per layer, final norm + lm_head + arg-max, position bump
+    n_launch = 1 + cfg.n_layers * 7 + 3 + 1  # embedding, 7 per layer, final norm + lm_head + arg-max, position bump
     out = {"shape": "Qwen3-4B-shaped decoder, whole model, batch 1, greedy, context %d" % context,
            "tokens": new_tokens, "ms_per_token": round(ms, 4), "tok/s": round(1e3 / ms, 1),
            "launches_per_token": n_launch, "weight_bytes_per_token": wbytes, "kv_cache_bytes_per_token": kv_bytes,
@@ -908,7 +908,7 @@ def run_case(args):
             tok.copy_(nxt_f)
             state["pos"] += 1
         work = {"case": "decoder", "layers": cfg.n_layers, "hidden": cfg.hidden, "vocab": cfg.vocab, "context": context,
-                "launches_per_token": 1 + cfg.n_layers * 8 + 3}
+                "launches_per_token": 1 + cfg.n_layers * 7 + 3}
     else:  # lm_head
         N, K = 151936, 2560
         W = torch.from_numpy(O.random_q6_K(rng, N, K)).to(dev)

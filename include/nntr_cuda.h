@@ -198,6 +198,15 @@ int nntr_cuda_gemv_batched_dev(int qtype, unsigned N, unsigned K, const float *x
 int nntr_cuda_gemv_batched_add_norm_dev(int qtype, unsigned N, unsigned K, const float *x, const float *residual,
                                         float *sum_out, const float *gamma, float eps, const void *const *w_table,
                                         unsigned n_problems, float *y, unsigned flags, void *stream);
+/** The input half of a gated FFN in one launch: n = rms_norm(x + residual) * gamma as above, then
+ *  y[N] = swiglu(W_first n, W_second n) -- the two projections of N rows x K and the SwiGLU layer behind them
+ *  (Applications/CausalLM/layers/swiglu.cpp:40-57 -> swiglu, x86/avx2_impl.cpp:906; the sigmoid branch takes the first
+ *  projection, which in the CausalLM graphs is ffn_up). A CTA computes the same output rows of both matrices and its
+ *  epilogue applies the activation, so neither projection's output goes through memory. Same bits as
+ *  nntr_cuda_add_rms_norm_dev, two GEMVs and nntr_cuda_swiglu_dev; one launch instead of four. Q4_K only. */
+int nntr_cuda_gated_ffn_in_dev(int qtype, unsigned N, unsigned K, const float *x, const float *residual, float *sum_out,
+                               const float *gamma, float eps, const void *W_first, const void *W_second, float *y,
+                               unsigned flags, void *stream);
 
 
 /* ------------------------------------------- operators between the matmuls */

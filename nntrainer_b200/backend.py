@@ -218,6 +218,17 @@ def gemv_batched_add_norm(qtype: str, N: int, K: int, x, residual, sum_out, gamm
     return y
 
 
+def gated_ffn_in(qtype: str, N: int, K: int, x, residual, sum_out, gamma, eps: float, W_first, W_second, y,
+                 pdl: bool = False):
+    """y = swiglu(W_first n, W_second n) with n = rms_norm(x + residual) * gamma: residual add, norm, both projections
+    of a gated FFN and its SwiGLU in one launch; sum_out receives x + residual."""
+    check(lib().nntr_cuda_gated_ffn_in_dev(
+        QTYPE[qtype], N, K, x.data_ptr(), residual.data_ptr() if residual is not None else None,
+        sum_out.data_ptr() if sum_out is not None else None, gamma.data_ptr(), eps, W_first.data_ptr(),
+        W_second.data_ptr(), y.data_ptr(), capi.GEMV_PDL if pdl else 0, _stream()))
+    return y
+
+
 # ---------------------------------------------------------------- quantizers
 def quantize_row_q8_K(src, dst=None, k: int | None = None):
     """cpu_backend.h:1093. numpy in -> numpy uint8 blocks out (host entry point)."""

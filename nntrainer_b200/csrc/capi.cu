@@ -749,6 +749,29 @@ int nntr_cuda_gemv_batched_add_norm_dev(int qtype, unsigned N, unsigned K, const
   return launch_gemv_q4_K_batched(N, K, x, nullptr, y, flags, n_problems, b, static_cast<cudaStream_t>(stream));
 }
 
+int nntr_cuda_gated_ffn_in_dev(int qtype, unsigned N, unsigned K, const float *x, const float *residual, float *sum_out,
+                               const float *gamma, float eps, const void *W_first, const void *W_second, float *y,
+                               unsigned flags, void *stream) {
+  if (qtype != NNTR_Q4_K)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gated_ffn_in: Q4_K weights only (got qtype %d)", qtype);
+  int rc = check_weight_shape(qtype, N, K);
+  if (rc)
+    return rc;
+  if (!x || !gamma || !W_first || !W_second || !y)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gated_ffn_in: null pointer");
+  if (residual && (!sum_out || sum_out == x || sum_out == residual))
+    return set_error(NNTR_CUDA_ERR_INVALID, "gated_ffn_in: the sum needs a buffer of its own (every CTA reads both "
+                                            "addends while one CTA writes the sum)");
+  GemvBatch b = {};
+  b.act = GEMV_ACT_ADD_NORM_PAIR;
+  b.x2 = residual;
+  b.gamma = gamma;
+  b.sum_out = sum_out;
+  b.eps = eps;
+  b.w2 = W_second;
+  return launch_gemv_q4_K_batched(N, K, x, W_first, y, flags, 1, b, static_cast<cudaStream_t>(stream));
+}
+
 /* ---- plain device memory and CUDA IPC, for callers that do not bring a framework ---- */
 int nntr_cuda_malloc(void **p, size_t bytes) {
   if (!p)

@@ -231,13 +231,17 @@ struct GemvBatch {
   //   GEMV_ACT_PLAIN    x as it is
   //   GEMV_ACT_ADD_NORM rms_norm(x + x2) * gamma, the sum also stored to sum_out by one CTA (x2 may be null: no
   //                     addition, no sum_out) -- the residual add and RMS norm in front of a projection
+  //   GEMV_ACT_ADD_NORM_PAIR  the same prologue, ONE problem over two weight tensors (B and w2, same shape): a CTA
+  //                     computes the same output rows of both and its epilogue stores swiglu(first, second) -- the gated
+  //                     FFN's two projections and the SwiGLU layer behind them in one launch
   int act;
   const float *x2;
   const float *gamma;
   float *sum_out;
   float eps;
+  const void *w2;
 };
-enum { GEMV_ACT_PLAIN = 0, GEMV_ACT_ADD_NORM = 2 };
+enum { GEMV_ACT_PLAIN = 0, GEMV_ACT_ADD_NORM = 2, GEMV_ACT_ADD_NORM_PAIR = 3 };
 
 /** N-split of a projection over the GPUs of one node, exchange fused into the GEMV, without fences:
  *   data   every rank computes the output rows of its weight shard and its epilogue stores each as an 8-byte

@@ -38,6 +38,7 @@
 #include "common.cuh"
 #include "pipeline.cuh"
 #include "rms.cuh"
+#include "swiglu.cuh"
 
 namespace nntr {
 
@@ -78,10 +79,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 
 
 struct SmemLayout {
-  uint32_t ring, act, part, bars, abort_flag, total;
+  uint32_t ring, act, part, bars, abort_flag, stash, total;
 };
-/* ngslot: row groups whose partial results may be pending at once (power of two) */
-__host__ __device__ inline SmemLayout smem_layout(int nb, int ngslot) {
+/* ngslot: row groups whose partial results may be pending at once (power of two); stash_groups: row groups whose
+ * outputs the epilogue keeps back (paired launches: the first matrix's outputs wait for the second's) */
+__host__ __device__ inline SmemLayout smem_layout(int nb, int ngslot, int stash_groups = 0) {
   SmemLayout L;
   uint32_t o = 0;
   L.ring = o;
@@ -94,6 +96,8 @@ __host__ __device__ inline SmemLayout smem_layout(int nb, int ngslot) {
   o += (2 * NSTAGE + 2 * ngslot) * 8;
   L.abort_flag = o;
   o += 16;
+  L.stash = o;
+  o += stash_groups * 8 * 4;
   L.total = o;
   return L;
 }
@@ -160,9 +164,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2)
 gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, float *__restrict__ y, int n_groups,
                  int nb, int ngslot, GemvBatch batch, GemvExchange ex) {
   extern __shared__ __align__(128) uint8_t smem[];
+  constexpr bool NORM = ACT == GEMV_ACT_ADD_NORM || ACT == GEMV_ACT_ADD_NORM_PAIR;
+  constexpr bool PAIR = ACT == GEMV_ACT_ADD_NORM_PAIR;
   if (batch.w_table) { // batched launch: blockIdx.y picks the problem
     const int p = blockIdx.y;
-    if (ACT == GEMV_ACT_PLAIN)
+    if (!NORM)
       x += (long long)(p / batch.x_div) * batch.x_stride;
     y += (long long)p * batch.y_stride;
   }
@@ -192,7 +198,8 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
   // the CTA's share: a contiguous run of whole row groups
   const int g_first = (int)(((long long)blockIdx.x * n_groups) / gridDim.x);
   const int g_end = (int)(((long long)(blockIdx.x + 1) * n_groups) / gridDim.x);
-  const int ng = g_end - g_first;
+  const int ng_rows = g_end - g_first;       // row groups of the output this CTA owns
+  const int ng = PAIR ? 2 * ng_rows : ng_rows; // paired launch: the same row groups of a second matrix follow
   const int total_blocks = ng * nb;
   const int total_stages = (total_blocks + STAGE_BLOCKS - 1) / STAGE_BLOCKS;
 
@@ -237,9 +244,14 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       if (lane == 0)
         mbar_expect_tx(full0 + 8 * st, nblk * BLK_BYTES);
       __syncwarp();
-      if (lane < nblk)
-        bulk_g2s(smem_u32(ring + st * STAGE_BYTES + lane * BLK_STRIDE),
-                 src + ((size_t)q * STAGE_BLOCKS + lane) * BLK_BYTES, BLK_BYTES, full0 + 8 * st);
+      if (lane < nblk) {
+        const size_t i = (size_t)q * STAGE_BLOCKS + lane, first_part = (size_t)ng_rows * nb;
+        const uint8_t *from = (PAIR && i >= first_part)
+                                ? reinterpret_cast<const uint8_t *>(static_cast<const BlockQ4Kx8 *>(batch.w2) +
+                                                                    (size_t)g_first * nb) + (i - first_part) * BLK_BYTES
+                                : src + i * BLK_BYTES;
+        bulk_g2s(smem_u32(ring + st * STAGE_BYTES + lane * BLK_STRIDE), from, BLK_BYTES, full0 + 8 * st);
+      }
     }
     if (!ok && lane == 0) {
       // leave only after the copies already issued have landed (bounded)
@@ -306,6 +318,9 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     }
     for (int gl0 = 0; gl0 < ng; gl0 += 4) {
       const int gl = gl0 + j;
+      float v = 0.f;
+      bool have = false;
+      const size_t o = (size_t)(g_first + (PAIR && gl >= ng_rows ? gl - ng_rows : gl)) * 8 + r;
       if (gl < ng) {
         const int slot = gl & slot_mask;
         if (mbar_wait(done0 + 8 * slot, (gl >> slot_shift) & 1, abort_flag)) {
@@ -313,13 +328,17 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
           float a0 = 0.f, a1 = 0.f;
 #pragma unroll 8
           for (int b = 0; b < nb; ++b) {
-            const float4 v = p[b * 8];
-            a0 = __fmaf_rn(v.x, v.y, a0);
-            a1 = __fmaf_rn(v.z, v.w, a1);
+            const float4 pv = p[b * 8];
+            a0 = __fmaf_rn(pv.x, pv.y, a0);
+            a1 = __fmaf_rn(pv.z, pv.w, a1);
           }
-          const float v = __fsub_rn(a0, a1);
-          const size_t o = (size_t)(g_first + gl) * 8 + r;
-          if (ex.n_ranks == 0) {
+          v = __fsub_rn(a0, a1);
+          have = true;
+          if (PAIR) {
+            // first matrix: the value waits in shared memory for its partner of the second matrix
+            if (gl < ng_rows)
+              reinterpret_cast<float *>(smem + L.stash)[gl * 8 + r] = v;
+          } else if (ex.n_ranks == 0) {
             y[o] = v;
           } else {
             // (value, launch number) in one 8-byte store straight into every rank's gathered vector: the reader checks
@@ -331,6 +350,13 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
             }
           }
         }
+      }
+      if (PAIR) {
+        // second matrix: y = swiglu(first, second), the SwiGLU layer behind a gated FFN's two projections (its sigmoid
+        // branch takes the first). The partner was stored in this round or an earlier one.
+        __syncwarp();
+        if (have && gl >= ng_rows)
+          y[o] = swiglu_elem(reinterpret_cast<const float *>(smem + L.stash)[(gl - ng_rows) * 8 + r], v, false, 0.f);
       }
       __syncwarp();
       if (r == 0 && gl < ng)
@@ -346,7 +372,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       epoch_early = *reinterpret_cast<const volatile unsigned long long *>(ex.epoch);
     // gamma is a weight: the part for this warp's first block is fetched before the wait for the previous kernel
     float4 gpre0 = make_float4(1.f, 1.f, 1.f, 1.f), gpre1 = gpre0;
-    if (ACT == GEMV_ACT_ADD_NORM && warp < nb) {
+    if (NORM && warp < nb) {
       const float *gm = batch.gamma + warp * QK_K + lane * 8;
       gpre0 = *reinterpret_cast<const float4 *>(gm);
       gpre1 = *reinterpret_cast<const float4 *>(gm + 4);
@@ -358,7 +384,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     // ---- activation prologues (see GemvBatch::act): the operators in front of the projection, computed by every CTA
     // for itself (a few thousand elements: cheaper than a launch of their own and the round trip through memory)
     float act_scale = 1.0f;
-    if (ACT == GEMV_ACT_ADD_NORM) {
+    if (NORM) {
       // the row (x + x2) goes to shared memory -- the part[] area, free until the first dot product, which comes after
       // the barrier at the end of the quantization -- one CTA also stores it; warp 0 runs the ordered sum of squares
       float *row = reinterpret_cast<float *>(part);
@@ -384,7 +410,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     }
     for (int b = warp; b < nb && !*abort_flag; b += CONSUMER_WARPS) {
       float4 v0, v1;
-      if (ACT == GEMV_ACT_ADD_NORM) {
+      if (NORM) {
         const float *rs = reinterpret_cast<const float *>(part) + b * QK_K + lane * 8;
         const float *gm = batch.gamma + b * QK_K + lane * 8;
         const float4 r0 = *reinterpret_cast<const float4 *>(rs), r1 = *reinterpret_cast<const float4 *>(rs + 4);
@@ -598,7 +624,10 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
   if (batch.act != GEMV_ACT_PLAIN) {
     if (g_next_exchange)
       return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_q4_K: an activation prologue cannot be combined with the exchange");
-    if (batch.act == GEMV_ACT_ADD_NORM) {
+    if (batch.act == GEMV_ACT_ADD_NORM_PAIR && (batch.w_table || !batch.w2 || n_problems != 1 ||
+                                                (reinterpret_cast<uintptr_t>(batch.w2) & 15)))
+      return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: a paired launch takes two weight tensors (16-byte aligned), no table");
+    if (batch.act == GEMV_ACT_ADD_NORM || batch.act == GEMV_ACT_ADD_NORM_PAIR) {
       if (!batch.gamma || (reinterpret_cast<uintptr_t>(batch.gamma) & 15) || (batch.x2 && !batch.sum_out))
         return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: norm prologue needs gamma (16-byte aligned) and, with a "
                                                 "second addend, an output for the sum");
@@ -606,7 +635,19 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
         ngslot = 16; // the row (K floats) and the scale live in the area of the partial results until the dots start
     }
   }
-  const SmemLayout L = smem_layout(nb, ngslot);
+  const bool pair = batch.act == GEMV_ACT_ADD_NORM_PAIR;
+  // A share that fits the ring (one step per warp) runs one CTA per SM and leaves
+  // room for the next kernel's CTAs under programmatic dependent launch; longer
+  // streams run two CTAs per SM: 32 consumer warps and 16 stages in flight per SM.
+  const long blocks_per_sm = ((long)n_groups * nb * n_problems * (pair ? 2 : 1) + sms - 1) / sms;
+  const bool two_fit = 2u * smem_layout(nb, ngslot, pair ? 64 : 0).total <= 220u * 1024u;
+  const int per_sm = env_int("NNTR_CUDA_GEMV_CTAS_PER_SM", (blocks_per_sm > STEP_BLOCKS && two_fit) ? 2 : 1);
+  int max_ctas = (sms * per_sm + (int)n_problems - 1) / (int)n_problems; // CTAs per problem
+  if (max_ctas < 1)
+    max_ctas = 1;
+  const unsigned grid = (unsigned)(n_groups < max_ctas ? n_groups : max_ctas);
+  const int stash_groups = pair ? (n_groups + (int)grid - 1) / (int)grid : 0;
+  const SmemLayout L = smem_layout(nb, ngslot, stash_groups);
   if (L.total > 200 * 1024)
     return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_q4_K: K=%u needs %u B of shared memory", K, L.total);
   static bool attr_done[64] = {};
@@ -615,19 +656,9 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
   if (!attr_done[dev & 63]) {
     NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<GEMV_ACT_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<GEMV_ACT_ADD_NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<GEMV_ACT_ADD_NORM_PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_done[dev & 63] = true;
   }
-  // A share that fits the ring (one step per warp) runs one CTA per SM and leaves
-  // room for the next kernel's CTAs under programmatic dependent launch; longer
-  // streams run two CTAs per SM: 32 consumer warps and 16 stages in flight per SM.
-  const long blocks_per_sm = ((long)n_groups * nb * n_problems + sms - 1) / sms;
-  const bool two_fit = 2u * L.total <= 220u * 1024u;
-  const int per_sm = env_int("NNTR_CUDA_GEMV_CTAS_PER_SM", (blocks_per_sm > STEP_BLOCKS && two_fit) ? 2 : 1);
-  int max_ctas = (sms * per_sm + (int)n_problems - 1) / (int)n_problems; // CTAs per problem
-  if (max_ctas < 1)
-    max_ctas = 1;
-  const unsigned grid = (unsigned)(n_groups < max_ctas ? n_groups : max_ctas);
-
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, n_problems);
   cfg.blockDim = dim3(GEMV_THREADS);
@@ -646,7 +677,8 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
       return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_nsplit: %u CTAs exceed the %d flag slots per rank", grid, NSPLIT_MAX_CTAS);
   }
   cudaError_t e =
-    batch.act == GEMV_ACT_ADD_NORM ? cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_ADD_NORM>, x, Wp, y, n_groups, nb, ngslot, batch, ex)
+    batch.act == GEMV_ACT_ADD_NORM_PAIR ? cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_ADD_NORM_PAIR>, x, Wp, y, n_groups, nb, ngslot, batch, ex)
+    : batch.act == GEMV_ACT_ADD_NORM    ? cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_ADD_NORM>, x, Wp, y, n_groups, nb, ngslot, batch, ex)
                                    : cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_PLAIN>, x, Wp, y, n_groups, nb, ngslot, batch, ex);
   count_launch();
   return check_cuda(e, "gemv_q4_K launch");

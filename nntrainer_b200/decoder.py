@@ -125,8 +125,7 @@ class Qwen3Decoder:
         Launches per layer without ``fuse``: (residual add +) RMS norm; q | k | v projections (one batched launch);
         per-head norms + rotary + cache append + scores; softmax + values; attention_out; residual add + RMS norm;
         ffn_up | ffn_gate (one batched launch); SwiGLU; ffn_down -- ten. With ``fuse`` the two norms run in the
-        prologues of the projections behind them -- eight. (The SwiGLU in the prologue of ffn_down was measured slower
-        than its own launch: every CTA would recompute all 9728 activations.) Every fusion keeps the bits of the
+        prologues of the projections behind them and the SwiGLU in the epilogue of the up | gate launch -- seven. Every fusion keeps the bits of the
         separate operators."""
         c, b, pdl = self.cfg, self.b, self.pdl
         q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
@@ -138,7 +137,7 @@ class Qwen3Decoder:
             p = f"layer{i}_"
             qk_norm = (self._P(self.ptr[p + "q_norm"]), self._P(self.ptr[p + "k_norm"]), c.norm_eps)
             if fuse:
-                # 8 launches: (add +) norm + q|k|v; rotary + scores; softmax + values; o; add + norm + up|gate; SwiGLU; down
+                # 7 launches: (add +) norm + q|k|v; rotary + scores; softmax + values; o; add + norm + up|gate + SwiGLU; down
                 g_att, g_ffn = self._P(self.ptr[p + "attention_norm"]), self._P(self.ptr[p + "ffn_norm"])
                 if i == 0:
                     be.gemv_batched_add_norm(c.fc_dtype, kv_dim, c.hidden, x, None, None, g_att, c.norm_eps,
@@ -148,9 +147,8 @@ class Qwen3Decoder:
                                              self._qkv_tab[i], q_dim // kv_dim + 2, b["qkv"], pdl=pdl)
                 self.attn[i].step(b["q"], b["k"], b["v"], pos, pos_dev=pos_dev, out=b["a"], pdl=pdl, qk_norm=qk_norm)
                 self._gemv(p + "attention_out", b["a"], b["o"])
-                be.gemv_batched_add_norm(c.fc_dtype, c.inter, c.hidden, x, b["o"], b["h"], g_ffn, c.norm_eps,
-                                         self._ug_tab[i], 2, b["ug"], pdl=pdl)
-                be.swiglu(b["up"], b["gate"], out=b["act"], pdl=pdl)
+                be.gated_ffn_in(c.fc_dtype, c.inter, c.hidden, x, b["o"], b["h"], g_ffn, c.norm_eps,
+                                self._P(self.ptr[p + "ffn_up"]), self._P(self.ptr[p + "ffn_gate"]), b["act"], pdl=pdl)
                 self._gemv(p + "ffn_down", b["act"], b["d"])
                 continue
             if i == 0:

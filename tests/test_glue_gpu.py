@@ -281,3 +281,33 @@ def test_projections_with_the_add_and_norm_in_their_prologue(be, port, N, K, n_p
                              n_problems, y2, pdl=True)
     assert same_bits(y2.cpu().numpy(), want)
     be.device_status()
+
+
+@pytest.mark.parametrize("N,K", [(9728, 2560), (64, 256), (768, 2048), (1184, 512), (8, 256)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_gated_ffn_input_half_in_one_launch(be, port, N, K, with_residual):
+    """nntr_cuda_gated_ffn_in_dev (residual add, norm, both projections, SwiGLU) against the checker's separate steps."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(3 * N + K)
+    W1, W2 = O.random_q4_Kx8(rng, N, K), O.random_q4_Kx8(rng, N, K)
+    x = rng.standard_normal(K).astype(np.float32)
+    r = rng.standard_normal(K).astype(np.float32) if with_residual else None
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    eps = 1e-6
+    s = (x + r).astype(np.float32) if with_residual else x
+    n = port.rms_norm(s[None], gamma, eps)[0]
+    first = port.gemm("q4_K", n[None], W1, N)[0]
+    second = port.gemm("q4_K", n[None], W2, N)[0]
+    want = port.swiglu(first, second)
+    for pdl in (False, True):
+        y = torch.full((N,), float("nan"), device="cuda")
+        sum_out = torch.full((K,), float("nan"), device="cuda") if with_residual else None
+        xd = dev(x)
+        if pdl:
+            xd.mul_(1.0)
+        be.gated_ffn_in("q4_K", N, K, xd, dev(r) if with_residual else None, sum_out, dev(gamma), eps, dev(W1), dev(W2), y,
+                        pdl=pdl)
+        assert same_bits(y.cpu().numpy(), want), pdl
+        if with_residual:
+            assert same_bits(sum_out.cpu().numpy(), s)
+    be.device_status()
