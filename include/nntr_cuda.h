@@ -198,6 +198,11 @@ int nntr_cuda_gemv_batched_dev(int qtype, unsigned N, unsigned K, const float *x
 int nntr_cuda_gemv_batched_add_norm_dev(int qtype, unsigned N, unsigned K, const float *x, const float *residual,
                                         float *sum_out, const float *gamma, float eps, const void *const *w_table,
                                         unsigned n_problems, float *y, unsigned flags, void *stream);
+/** One projection with the same prologue: y[N] = W q8K(rms_norm(x + residual) * gamma). Shapes whose per-SM share fits
+ *  in shared memory run in the resident-weights kernel (e.g. the q, k and v projections of a layer stored as one
+ *  6144 x 2560 tensor). */
+int nntr_cuda_gemv_add_norm_dev(int qtype, unsigned N, unsigned K, const float *x, const float *residual, float *sum_out,
+                                const float *gamma, float eps, const void *B, float *y, unsigned flags, void *stream);
 /** The input half of a gated FFN in one launch: n = rms_norm(x + residual) * gamma as above, then
  *  y[N] = swiglu(W_first n, W_second n) -- the two projections of N rows x K and the SwiGLU layer behind them
  *  (Applications/CausalLM/layers/swiglu.cpp:40-57 -> swiglu, x86/avx2_impl.cpp:906; the sigmoid branch takes the first

@@ -218,6 +218,15 @@ def gemv_batched_add_norm(qtype: str, N: int, K: int, x, residual, sum_out, gamm
     return y
 
 
+def gemv_add_norm(qtype: str, N: int, K: int, x, residual, sum_out, gamma, eps: float, B, y, pdl: bool = False):
+    """y = W . (rms_norm(x + residual) * gamma), the add and the norm computed in the GEMV's prologue."""
+    check(lib().nntr_cuda_gemv_add_norm_dev(
+        QTYPE[qtype], N, K, x.data_ptr(), residual.data_ptr() if residual is not None else None,
+        sum_out.data_ptr() if sum_out is not None else None, gamma.data_ptr(), eps, B.data_ptr(), y.data_ptr(),
+        capi.GEMV_PDL if pdl else 0, _stream()))
+    return y
+
+
 def gated_ffn_in(qtype: str, N: int, K: int, x, residual, sum_out, gamma, eps: float, W_first, W_second, y,
                  pdl: bool = False):
     """y = swiglu(W_first n, W_second n) with n = rms_norm(x + residual) * gamma: residual add, norm, both projections

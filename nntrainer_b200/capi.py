@@ -69,6 +69,7 @@ SIGNATURES = {
     "nntr_cuda_gemm_q4_K_noalloc_dev": (_i, [_u, _u, _u, _vp, _u, _vp, _u, _vp, _u, _vp]),
     "nntr_cuda_gemv_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _u, _vp]),
     "nntr_cuda_gemv_batched_dev": (_i, [_i, _u, _u, _vp, _vp, _u, _vp, _u, _vp]),
+    "nntr_cuda_gemv_add_norm_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _u, _vp]),
     "nntr_cuda_gated_ffn_in_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _vp, _u, _vp]),
     "nntr_cuda_gemv_batched_add_norm_dev": (_i, [_i, _u, _u, _vp, _vp, _vp, _vp, C.c_float, _vp, _u, _vp, _u, _vp]),
     "nntr_cuda_malloc": (_i, [C.POINTER(C.c_void_p), _sz]),

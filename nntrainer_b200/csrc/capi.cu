@@ -749,6 +749,27 @@ int nntr_cuda_gemv_batched_add_norm_dev(int qtype, unsigned N, unsigned K, const
   return launch_gemv_q4_K_batched(N, K, x, nullptr, y, flags, n_problems, b, static_cast<cudaStream_t>(stream));
 }
 
+int nntr_cuda_gemv_add_norm_dev(int qtype, unsigned N, unsigned K, const float *x, const float *residual, float *sum_out,
+                                const float *gamma, float eps, const void *B, float *y, unsigned flags, void *stream) {
+  if (qtype != NNTR_Q4_K)
+    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_add_norm: Q4_K weights only (got qtype %d)", qtype);
+  int rc = check_weight_shape(qtype, N, K);
+  if (rc)
+    return rc;
+  if (!x || !gamma || !B || !y)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_add_norm: null pointer");
+  if (residual && (!sum_out || sum_out == x || sum_out == residual))
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_add_norm: the sum needs a buffer of its own (every CTA reads both "
+                                            "addends while one CTA writes the sum)");
+  GemvBatch b = {};
+  b.act = GEMV_ACT_ADD_NORM;
+  b.x2 = residual;
+  b.gamma = gamma;
+  b.sum_out = sum_out;
+  b.eps = eps;
+  return launch_gemv_q4_K_batched(N, K, x, B, y, flags, 1, b, static_cast<cudaStream_t>(stream));
+}
+
 int nntr_cuda_gated_ffn_in_dev(int qtype, unsigned N, unsigned K, const float *x, const float *residual, float *sum_out,
                                const float *gamma, float eps, const void *W_first, const void *W_second, float *y,
                                unsigned flags, void *stream) {

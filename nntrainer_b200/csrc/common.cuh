@@ -295,10 +295,10 @@ int launch_gemv_q4_K_batched_publish(unsigned N, unsigned K, const float *x, uns
                                      GemvExchange ex, cudaStream_t st);
 int read_moe_status(int *out);
 /* resident-weights variant for small per-CTA shares (gemv_q4k_resident.cu) */
-bool gemv_q4_K_resident_supported(unsigned N, unsigned K, bool exchange = false);
+bool gemv_q4_K_resident_supported(unsigned N, unsigned K, bool exchange = false, bool norm = false);
 struct GemvExchange;
 int launch_gemv_q4_K_resident(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
-                              cudaStream_t st, const GemvExchange *exchange = nullptr);
+                              cudaStream_t st, const GemvExchange *exchange = nullptr, const GemvBatch *norm = nullptr);
 int set_exchange_poll_limit_resident(unsigned polls);
 int read_resident_status(int *out);
 int clear_resident_status();

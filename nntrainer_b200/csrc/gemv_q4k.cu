@@ -619,6 +619,11 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
     return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: x and B must be 16-byte aligned");
   if (N == 0)
     return NNTR_CUDA_OK;
+  // one problem with the norm prologue whose per-CTA share fits in shared memory: the resident-weights kernel
+  static const int use_resident = env_int("NNTR_CUDA_GEMV_RESIDENT", 1);
+  if (use_resident && batch.act == GEMV_ACT_ADD_NORM && n_problems == 1 && !batch.w_table && B && !g_next_exchange &&
+      gemv_q4_K_resident_supported(N, K, false, true))
+    return launch_gemv_q4_K_resident(N, K, x, B, y, flags, st, nullptr, &batch);
   const int n_groups = (int)(N / 8), nb = (int)(K / QK_K), sms = sm_count();
   int ngslot = pick_ngslot(nb);
   if (batch.act != GEMV_ACT_PLAIN) {

@@ -25,6 +25,7 @@
  */
 #include "common.cuh"
 #include "pipeline.cuh"
+#include "rms.cuh"
 
 namespace nntr {
 
@@ -63,7 +64,7 @@ struct RLayout {
 };
 /** `exchange`: the part[] region doubles as the per-warp staging area of the numbered activation (1 KB per warp, used
  * before the first barrier; part[] is written after it), so it is 16 KB instead of 8 */
-__host__ __device__ inline RLayout r_layout(int nb, bool exchange) {
+__host__ __device__ inline RLayout r_layout(int nb, bool exchange, bool norm = false) {
   RLayout L;
   uint32_t o = 0;
   L.ring = o;
@@ -72,7 +73,10 @@ __host__ __device__ inline RLayout r_layout(int nb, bool exchange) {
   o += nb * R_ACT_STRIDE;
   o = (o + 15) & ~15u;
   L.part = o;
-  o += exchange ? R_WARPS * 1024 : R_MAX_BLOCKS * 8 * 16;
+  // (with the norm prologue the area first holds the K floats of the activation row and the scale)
+  const uint32_t part_bytes = exchange ? R_WARPS * 1024 : R_MAX_BLOCKS * 8 * 16, row_bytes = norm ? nb * QK_K * 4 + 16 : 0;
+  o += part_bytes > row_bytes ? part_bytes : row_bytes;
+  o = (o + 15) & ~15u;
   L.bars = o;
   o += R_NBAR * 8;
   L.abort_flag = o;
@@ -83,16 +87,18 @@ __host__ __device__ inline RLayout r_layout(int nb, bool exchange) {
 
 } // namespace
 
-template <bool EXCHANGE>
+/* NORM: the activation is rms_norm(x + nm.x2) * nm.gamma, computed by every CTA for itself after the wait (the residual
+ * add and RMS norm in front of a projection; one CTA stores the sum to nm.sum_out); see GemvBatch::act. */
+template <bool EXCHANGE, bool NORM>
 __global__ void __maxnreg__(EXCHANGE ? 64 : 56)
 gemv_q4_K_resident_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, float *__restrict__ y,
-                          int n_groups, int nb, const GemvExchange ex) {
+                          int n_groups, int nb, const GemvExchange ex, const GemvBatch nm) {
   // Every use of `ex` is guarded by the compile-time EXCHANGE, so the plain instantiation carries none of that code.
   // Its pointer arrays are only ever indexed through pick8() with constant indices: a run-time index into a kernel
   // parameter would make the compiler copy the whole description into every thread's local memory (measured: 15 MB
   // of local-memory stores per launch, more than the weights).
   extern __shared__ __align__(128) uint8_t smem[];
-  const RLayout L = r_layout(nb, EXCHANGE);
+  const RLayout L = r_layout(nb, EXCHANGE, NORM);
   uint8_t *ring = smem + L.ring;
   uint8_t *act = smem + L.act;
   float4 *part = reinterpret_cast<float4 *>(smem + L.part);
@@ -218,6 +224,31 @@ gemv_q4_K_resident_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restr
   // ---- everything below depends on the previous kernel's output
   if (!chained_by_tags)
     pdl_wait();
+  float act_scale = 1.0f;
+  if (NORM) {
+    // the row (x + x2) goes to shared memory -- the part[] area, free until the dot products, which come after the
+    // barrier at the end of the quantization; warp 0 runs the ordered sum of squares
+    float *row = reinterpret_cast<float *>(part);
+    float *scale_slot = row + (size_t)nb * QK_K;
+    const int K = nb * QK_K;
+    for (int i = threadIdx.x; i < K; i += R_THREADS) {
+      float v = x[i];
+      if (nm.x2) {
+        v = __fadd_rn(v, nm.x2[i]);
+        if (blockIdx.x == 0)
+          nm.sum_out[i] = v;
+      }
+      row[i] = v;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const float sumsq = rms_sumsq_warp(row, K, lane);
+      if (lane == 0)
+        *scale_slot = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, (float)K), nm.eps)));
+    }
+    __syncthreads();
+    act_scale = *scale_slot;
+  }
   if (EXCHANGE && ex.n_ranks && ex.layer == 0)
     seq = (*reinterpret_cast<const volatile unsigned long long *>(ex.epoch) - 1) * ex.layers_per_epoch + ex.layer + 1;
   if (EXCHANGE && ex.n_ranks && !early_flags && warp == 0 && seq >= (unsigned long long)n_ring)
@@ -282,9 +313,20 @@ gemv_q4_K_resident_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restr
         v0 = v1 = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     } else {
-      const float *xs = x + bb * QK_K + lane * 8;
-      v0 = *reinterpret_cast<const float4 *>(xs);
-      v1 = *reinterpret_cast<const float4 *>(xs + 4);
+      if (NORM) {
+        const float *rs = reinterpret_cast<const float *>(part) + bb * QK_K + lane * 8;
+        const float *gm = nm.gamma + bb * QK_K + lane * 8;
+        const float4 r0 = *reinterpret_cast<const float4 *>(rs), r1 = *reinterpret_cast<const float4 *>(rs + 4);
+        const float4 m0 = *reinterpret_cast<const float4 *>(gm), m1 = *reinterpret_cast<const float4 *>(gm + 4);
+        v0 = make_float4(__fmul_rn(__fmul_rn(r0.x, act_scale), m0.x), __fmul_rn(__fmul_rn(r0.y, act_scale), m0.y),
+                         __fmul_rn(__fmul_rn(r0.z, act_scale), m0.z), __fmul_rn(__fmul_rn(r0.w, act_scale), m0.w));
+        v1 = make_float4(__fmul_rn(__fmul_rn(r1.x, act_scale), m1.x), __fmul_rn(__fmul_rn(r1.y, act_scale), m1.y),
+                         __fmul_rn(__fmul_rn(r1.z, act_scale), m1.z), __fmul_rn(__fmul_rn(r1.w, act_scale), m1.w));
+      } else {
+        const float *xs = x + bb * QK_K + lane * 8;
+        v0 = *reinterpret_cast<const float4 *>(xs);
+        v1 = *reinterpret_cast<const float4 *>(xs + 4);
+      }
     }
     const Q8KLane qv = q8K_quantize_warp(v0, v1, lane, 0);
     uint8_t *dst = act + bb * R_ACT_STRIDE;
@@ -382,7 +424,7 @@ gemv_q4_K_resident_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restr
 }
 
 /** true when the launch fits: one problem, K blocks and row groups such that every CTA's share is at most 64 blocks */
-bool gemv_q4_K_resident_supported(unsigned N, unsigned K, bool exchange) {
+bool gemv_q4_K_resident_supported(unsigned N, unsigned K, bool exchange, bool norm) {
   if (K == 0 || K % QK_K || N % 8 || N == 0)
     return false;
   const int n_groups = (int)(N / 8), nb = (int)(K / QK_K), sms = sm_count();
@@ -390,12 +432,18 @@ bool gemv_q4_K_resident_supported(unsigned N, unsigned K, bool exchange) {
     return false;
   const int grid = n_groups < sms ? n_groups : sms;
   const int max_groups = (n_groups + grid - 1) / grid;
-  return max_groups * nb <= R_MAX_BLOCKS && r_layout(nb, exchange).total <= 112u * 1024u;
+  return max_groups * nb <= R_MAX_BLOCKS && r_layout(nb, exchange, norm).total <= 112u * 1024u && !(exchange && norm);
 }
 
 int launch_gemv_q4_K_resident(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
-                              cudaStream_t st, const GemvExchange *exchange) {
+                              cudaStream_t st, const GemvExchange *exchange, const GemvBatch *norm) {
   GemvExchange ex = {};
+  GemvBatch nm = {};
+  if (norm) {
+    nm = *norm;
+    if (exchange || !nm.gamma || (reinterpret_cast<uintptr_t>(nm.gamma) & 15) || (nm.x2 && !nm.sum_out))
+      return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K (resident): bad norm prologue description");
+  }
   if (exchange) {
     ex = *exchange;
     y = reinterpret_cast<float *>(ex.y[ex.rank]);
@@ -405,21 +453,20 @@ int launch_gemv_q4_K_resident(unsigned N, unsigned K, const float *x, const void
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: x and B must be 16-byte aligned");
   const int n_groups = (int)(N / 8), nb = (int)(K / QK_K), sms = sm_count();
-  const RLayout L = r_layout(nb, exchange != nullptr);
+  const RLayout L = r_layout(nb, exchange != nullptr, norm != nullptr);
   static bool attr_done[64] = {};
   int dev = 0;
   NNTR_CHECK_CUDA(cudaGetDevice(&dev));
   if (!attr_done[dev & 63]) {
-    NNTR_CHECK_CUDA(
-      cudaFuncSetAttribute(gemv_q4_K_resident_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    NNTR_CHECK_CUDA(
-      cudaFuncSetAttribute(gemv_q4_K_resident_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_resident_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                         cudaSharedmemCarveoutMaxShared));
     // two CTAs per SM must fit (this launch's and the next one's, which prefetches its weights meanwhile): ask for the
     // largest shared-memory carve-out instead of the one the driver would derive from a single CTA's need
-    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_resident_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                         cudaSharedmemCarveoutMaxShared));
+#define NNTR_RESIDENT_ATTRS(KERNEL)                                                                                          \
+  NNTR_CHECK_CUDA(cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));                   \
+  NNTR_CHECK_CUDA(cudaFuncSetAttribute(KERNEL, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    NNTR_RESIDENT_ATTRS((gemv_q4_K_resident_kernel<false, false>))
+    NNTR_RESIDENT_ATTRS((gemv_q4_K_resident_kernel<true, false>))
+    NNTR_RESIDENT_ATTRS((gemv_q4_K_resident_kernel<false, true>))
+#undef NNTR_RESIDENT_ATTRS
     attr_done[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -433,8 +480,9 @@ int launch_gemv_q4_K_resident(unsigned N, unsigned K, const float *x, const void
   cfg.attrs = attr;
   cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
   const BlockQ4Kx8 *Wp = static_cast<const BlockQ4Kx8 *>(B);
-  cudaError_t e = exchange ? cudaLaunchKernelEx(&cfg, gemv_q4_K_resident_kernel<true>, x, Wp, y, n_groups, nb, ex)
-                           : cudaLaunchKernelEx(&cfg, gemv_q4_K_resident_kernel<false>, x, Wp, y, n_groups, nb, ex);
+  cudaError_t e = exchange ? cudaLaunchKernelEx(&cfg, gemv_q4_K_resident_kernel<true, false>, x, Wp, y, n_groups, nb, ex, nm)
+                  : norm   ? cudaLaunchKernelEx(&cfg, gemv_q4_K_resident_kernel<false, true>, x, Wp, y, n_groups, nb, ex, nm)
+                           : cudaLaunchKernelEx(&cfg, gemv_q4_K_resident_kernel<false, false>, x, Wp, y, n_groups, nb, ex, nm);
   count_launch();
   return check_cuda(e, "gemv_q4_K (resident) launch");
 }

@@ -115,6 +115,19 @@ class Qwen3Decoder:
                 self._qkv_tab.append(torch.tensor(ptrs, dtype=torch.int64, device=self.dev))
                 self._ug_tab.append(torch.tensor([self.ptr[p + "ffn_up"], self.ptr[p + "ffn_gate"]], dtype=torch.int64,
                                                  device=self.dev))
+        # With ``fuse`` the q, k and v projections run as ONE 6144-row problem (its per-SM share fits in shared memory, so
+        # it takes the resident-weights kernel): the file stores wv, wk, k_norm, wq, so the three tensors are packed
+        # once into q | k | v order (8.8 MB per layer beside the loaded copy).
+        self._qkv_packed = []
+        if self.fuse and self._qkv_ok:
+            for i in range(c.n_layers):
+                p = f"layer{i}_"
+                packed = torch.empty((q_dim + 2 * kv_dim) * row_bytes, dtype=torch.uint8, device=self.dev)
+                off = 0
+                for name, rows in ((p + "wq", q_dim), (p + "wk", kv_dim), (p + "wv", kv_dim)):
+                    be.check(be.lib().nntr_cuda_memcpy(packed.data_ptr() + off, self.ptr[name], rows * row_bytes, 3))
+                    off += rows * row_bytes
+                self._qkv_packed.append(packed)
 
     def step(self, token_f, pos: int, pos_dev=None, out_idx=None, out_idx_f=None):
         """One decode step: ``token_f`` is a 1-element float device tensor holding the token id (the reference keeps
@@ -140,11 +153,11 @@ class Qwen3Decoder:
                 # 7 launches: (add +) norm + q|k|v; rotary + scores; softmax + values; o; add + norm + up|gate + SwiGLU; down
                 g_att, g_ffn = self._P(self.ptr[p + "attention_norm"]), self._P(self.ptr[p + "ffn_norm"])
                 if i == 0:
-                    be.gemv_batched_add_norm(c.fc_dtype, kv_dim, c.hidden, x, None, None, g_att, c.norm_eps,
-                                             self._qkv_tab[i], q_dim // kv_dim + 2, b["qkv"], pdl=pdl)
+                    be.gemv_add_norm(c.fc_dtype, q_dim + 2 * kv_dim, c.hidden, x, None, None, g_att, c.norm_eps,
+                                     self._qkv_packed[i], b["qkv"], pdl=pdl)
                 else:  # the previous block's output x = h + ffn_down, and its norm
-                    be.gemv_batched_add_norm(c.fc_dtype, kv_dim, c.hidden, b["h"], b["d"], x, g_att, c.norm_eps,
-                                             self._qkv_tab[i], q_dim // kv_dim + 2, b["qkv"], pdl=pdl)
+                    be.gemv_add_norm(c.fc_dtype, q_dim + 2 * kv_dim, c.hidden, b["h"], b["d"], x, g_att, c.norm_eps,
+                                     self._qkv_packed[i], b["qkv"], pdl=pdl)
                 self.attn[i].step(b["q"], b["k"], b["v"], pos, pos_dev=pos_dev, out=b["a"], pdl=pdl, qk_norm=qk_norm)
                 self._gemv(p + "attention_out", b["a"], b["o"])
                 be.gated_ffn_in(c.fc_dtype, c.inter, c.hidden, x, b["o"], b["h"], g_ffn, c.norm_eps,

@@ -311,3 +311,31 @@ def test_gated_ffn_input_half_in_one_launch(be, port, N, K, with_residual):
         if with_residual:
             assert same_bits(sum_out.cpu().numpy(), s)
     be.device_status()
+
+
+@pytest.mark.parametrize("N,K", [(6144, 2560), (4096, 4096), (64, 256), (2560, 9728)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_single_projection_with_the_add_and_norm_in_its_prologue(be, port, N, K, with_residual):
+    """nntr_cuda_gemv_add_norm_dev: the resident-weights kernel where the shape fits (the first three), the streaming
+    kernel otherwise; same bits as the checker's separate steps."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(5 * N + K)
+    W = O.random_q4_Kx8(rng, N, K)
+    x = rng.standard_normal(K).astype(np.float32)
+    r = rng.standard_normal(K).astype(np.float32) if with_residual else None
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    eps = 1e-6
+    s = (x + r).astype(np.float32) if with_residual else x
+    n = port.rms_norm(s[None], gamma, eps)[0]
+    want = port.gemm("q4_K", n[None], W, N)[0]
+    for pdl in (False, True):
+        y = torch.full((N,), float("nan"), device="cuda")
+        sum_out = torch.full((K,), float("nan"), device="cuda") if with_residual else None
+        xd = dev(x)
+        if pdl:
+            xd.mul_(1.0)
+        be.gemv_add_norm("q4_K", N, K, xd, dev(r) if with_residual else None, sum_out, dev(gamma), eps, dev(W), y, pdl=pdl)
+        assert same_bits(y.cpu().numpy(), want), pdl
+        if with_residual:
+            assert same_bits(sum_out.cpu().numpy(), s)
+    be.device_status()
