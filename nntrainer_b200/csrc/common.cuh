@@ -234,6 +234,8 @@ struct GemvBatch {
   //   GEMV_ACT_ADD_NORM_PAIR  the same prologue, ONE problem over two weight tensors (B and w2, same shape): a CTA
   //                     computes the same output rows of both and its epilogue stores swiglu(first, second) -- the gated
   //                     FFN's two projections and the SwiGLU layer behind them in one launch
+  //   GEMV_ACT_PAIR_SWISH  batched pairs (MoE experts, Qwen form): problem p takes w_table[2p] (gate) and w_table[2p+1]
+  //                     (up) against activation row p / x_div and stores swish(gate) * up to y + p * y_stride
   int act;
   const float *x2;
   const float *gamma;
@@ -241,7 +243,7 @@ struct GemvBatch {
   float eps;
   const void *w2;
 };
-enum { GEMV_ACT_PLAIN = 0, GEMV_ACT_ADD_NORM = 2, GEMV_ACT_ADD_NORM_PAIR = 3 };
+enum { GEMV_ACT_PLAIN = 0, GEMV_ACT_ADD_NORM = 2, GEMV_ACT_ADD_NORM_PAIR = 3, GEMV_ACT_PAIR_SWISH = 4 };
 
 /** N-split of a projection over the GPUs of one node, exchange fused into the GEMV, without fences:
  *   data   every rank computes the output rows of its weight shard and its epilogue stores each as an 8-byte

@@ -165,7 +165,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
                  int nb, int ngslot, GemvBatch batch, GemvExchange ex) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr bool NORM = ACT == GEMV_ACT_ADD_NORM || ACT == GEMV_ACT_ADD_NORM_PAIR;
-  constexpr bool PAIR = ACT == GEMV_ACT_ADD_NORM_PAIR;
+  constexpr bool PAIR = ACT == GEMV_ACT_ADD_NORM_PAIR || ACT == GEMV_ACT_PAIR_SWISH;
   if (batch.w_table) { // batched launch: blockIdx.y picks the problem
     const int p = blockIdx.y;
     if (!NORM)
@@ -177,7 +177,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
     // problem another rank owns
     if (!batch.static_table)
       pdl_wait();
-    if (__ldcg(reinterpret_cast<const unsigned long long *>(batch.w_table) + blockIdx.y) == 0ull)
+    if (__ldcg(reinterpret_cast<const unsigned long long *>(batch.w_table) + (PAIR ? 2 : 1) * blockIdx.y) == 0ull)
       return;
   }
   const SmemLayout L = smem_layout(nb, ngslot);
@@ -225,8 +225,13 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       if (!batch.static_table)
         pdl_wait(); // the weight table is written by the kernel before this one
       W = reinterpret_cast<const BlockQ4Kx8 *>(
-        __ldcg(reinterpret_cast<const unsigned long long *>(batch.w_table) + blockIdx.y));
+        __ldcg(reinterpret_cast<const unsigned long long *>(batch.w_table) + (PAIR ? 2 : 1) * blockIdx.y));
     }
+    // the second matrix of a paired launch: given directly, or the odd entry of the pair in the table
+    const BlockQ4Kx8 *W2 = static_cast<const BlockQ4Kx8 *>(batch.w2);
+    if (PAIR && batch.w_table)
+      W2 = reinterpret_cast<const BlockQ4Kx8 *>(
+        __ldcg(reinterpret_cast<const unsigned long long *>(batch.w_table) + 2 * blockIdx.y + 1));
     const uint8_t *src = reinterpret_cast<const uint8_t *>(W + (size_t)g_first * nb);
     // one bulk copy per block, so that blocks land BLK_STRIDE apart
     int q = 0;
@@ -247,8 +252,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       if (lane < nblk) {
         const size_t i = (size_t)q * STAGE_BLOCKS + lane, first_part = (size_t)ng_rows * nb;
         const uint8_t *from = (PAIR && i >= first_part)
-                                ? reinterpret_cast<const uint8_t *>(static_cast<const BlockQ4Kx8 *>(batch.w2) +
-                                                                    (size_t)g_first * nb) + (i - first_part) * BLK_BYTES
+                                ? reinterpret_cast<const uint8_t *>(W2 + (size_t)g_first * nb) + (i - first_part) * BLK_BYTES
                                 : src + i * BLK_BYTES;
         bulk_g2s(smem_u32(ring + st * STAGE_BYTES + lane * BLK_STRIDE), from, BLK_BYTES, full0 + 8 * st);
       }
@@ -355,8 +359,10 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
         // second matrix: y = swiglu(first, second), the SwiGLU layer behind a gated FFN's two projections (its sigmoid
         // branch takes the first). The partner was stored in this round or an earlier one.
         __syncwarp();
-        if (have && gl >= ng_rows)
-          y[o] = swiglu_elem(reinterpret_cast<const float *>(smem + L.stash)[(gl - ng_rows) * 8 + r], v, false, 0.f);
+        if (have && gl >= ng_rows) {
+          const float first = reinterpret_cast<const float *>(smem + L.stash)[(gl - ng_rows) * 8 + r];
+          y[o] = ACT == GEMV_ACT_PAIR_SWISH ? swish_mul_elem(first, v) : swiglu_elem(first, v, false, 0.f);
+        }
       }
       __syncwarp();
       if (r == 0 && gl < ng)
@@ -629,6 +635,8 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
   if (batch.act != GEMV_ACT_PLAIN) {
     if (g_next_exchange)
       return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_q4_K: an activation prologue cannot be combined with the exchange");
+    if (batch.act == GEMV_ACT_PAIR_SWISH && (!batch.w_table || batch.w2))
+      return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: batched pairs take a table of 2 x n_problems weight tensors");
     if (batch.act == GEMV_ACT_ADD_NORM_PAIR && (batch.w_table || !batch.w2 || n_problems != 1 ||
                                                 (reinterpret_cast<uintptr_t>(batch.w2) & 15)))
       return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_K: a paired launch takes two weight tensors (16-byte aligned), no table");
@@ -640,7 +648,7 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
         ngslot = 16; // the row (K floats) and the scale live in the area of the partial results until the dots start
     }
   }
-  const bool pair = batch.act == GEMV_ACT_ADD_NORM_PAIR;
+  const bool pair = batch.act == GEMV_ACT_ADD_NORM_PAIR || batch.act == GEMV_ACT_PAIR_SWISH;
   // A share that fits the ring (one step per warp) runs one CTA per SM and leaves
   // room for the next kernel's CTAs under programmatic dependent launch; longer
   // streams run two CTAs per SM: 32 consumer warps and 16 stages in flight per SM.
@@ -662,6 +670,7 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
     NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<GEMV_ACT_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<GEMV_ACT_ADD_NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<GEMV_ACT_ADD_NORM_PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<GEMV_ACT_PAIR_SWISH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_done[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -682,7 +691,8 @@ int launch_gemv_q4_K_batched(unsigned N, unsigned K, const float *x, const void 
       return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "gemv_nsplit: %u CTAs exceed the %d flag slots per rank", grid, NSPLIT_MAX_CTAS);
   }
   cudaError_t e =
-    batch.act == GEMV_ACT_ADD_NORM_PAIR ? cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_ADD_NORM_PAIR>, x, Wp, y, n_groups, nb, ngslot, batch, ex)
+    batch.act == GEMV_ACT_PAIR_SWISH      ? cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_PAIR_SWISH>, x, Wp, y, n_groups, nb, ngslot, batch, ex)
+    : batch.act == GEMV_ACT_ADD_NORM_PAIR ? cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_ADD_NORM_PAIR>, x, Wp, y, n_groups, nb, ngslot, batch, ex)
     : batch.act == GEMV_ACT_ADD_NORM    ? cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_ADD_NORM>, x, Wp, y, n_groups, nb, ngslot, batch, ex)
                                    : cudaLaunchKernelEx(&cfg, gemv_q4_K_kernel<GEMV_ACT_PLAIN>, x, Wp, y, n_groups, nb, ngslot, batch, ex);
   count_launch();

@@ -14,9 +14,11 @@
  *        d = a.Wd[e] (+ bd[e])
  *   y[token] = sum over the token's experts in ASCENDING expert index of d * w
  *
- * Decode (fewer than 8 tokens), five launches per layer and no clearing launch: router (32 CTAs per token, the last
- * to arrive reduces, selects and writes the device-side weight-pointer tables), batched gate+up GEMV (2 * pairs
- * problems in one grid, the expert picked per problem through those tables), activation, batched down GEMV, combine.
+ * Decode (fewer than 8 tokens), no clearing launch: router (32 CTAs per token, the last to arrive reduces, selects and
+ * writes the device-side weight-pointer tables), batched gate+up GEMV (the expert picked per problem through those
+ * tables; Qwen form with Q4_K experts on one GPU: one problem per pair over both matrices with the activation in the
+ * epilogue -- four launches per layer; otherwise 2 * pairs problems and an activation launch -- five), batched down
+ * GEMV, combine.
  * The reference runs every expert GEMV with M = 1 even in prefill, so the batched GEMV reproduces its numerics.
  * Prefill (8 tokens or more): the pairs are sorted by expert and each projection stage is ONE grouped GEMM launch over
  * a device-side problem table; every row keeps the M = 1 float chain, so both paths give the same bits.
@@ -29,6 +31,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "moe_combine.cuh"
 #include "swiglu.cuh"
 
 namespace nntr {
@@ -104,7 +107,8 @@ __device__ void partial_sort_desc(const float *v, int n, int k, int *out) {
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, const float *__restrict__ bias, int H, int E,
                   int topk, const void *const *__restrict__ gate_w, const void *const *__restrict__ up_w,
-                  const void *const *__restrict__ down_w, int *__restrict__ idx_out, float *__restrict__ w_out,
+                  const void *const *__restrict__ down_w, int *__restrict__ idx_out, int *__restrict__ ord_out,
+                  float *__restrict__ w_out,
                   const void **__restrict__ gu_table, const void **__restrict__ dn_table, float *__restrict__ rpart,
                   unsigned *__restrict__ rcount, MoeEp ep) {
   extern __shared__ float rsm[]; // [ROUTER_WARPS][E]
@@ -291,6 +295,11 @@ moe_router_kernel(const float *__restrict__ x, const float *__restrict__ wr, con
     gu_table[2 * pr] = gate_w[esel];
     gu_table[2 * pr + 1] = up_w[esel];
     dn_table[pr] = down_w[esel];
+    // the combine adds a token's experts in ascending index: slot of the k-th smallest, for its use
+    int rank = 0;
+    for (int j = 0; j < topk; ++j)
+      rank += sel[j] < esel;
+    ord_out[t * topk + rank] = lane;
   }
 }
 
@@ -341,12 +350,7 @@ __global__ void moe_act_kernel(const float *__restrict__ gu, float *__restrict__
   float g = gu[(2 * p) * I + c], u = gu[(2 * p + 1) * I + c];
   float r;
   if (kind == 0) {
-    // ActiFunc::swish (nntrainer/layers/acti_func.h:286-288,400-405): sigmoid = (float)(1.0 / (1.0 + e)) with
-    // e = exp_util<float>(-x) = the DOUBLE exponential rounded to float (nntrainer/utils/util_func.h:118 calls the C
-    // library's exp), then sigmoid * gate, then * up
-    const float e = (float)exp((double)(-g));
-    const float sig = (float)(1.0 / (1.0 + (double)e));
-    r = __fmul_rn(__fmul_rn(sig, g), u);
+    r = swish_mul_elem(g, u);
   } else {
     // gpt_oss_moe_layer.cpp:411-440: gate + bias; (up + bias) + 1; nntrainer::swiglu(N, X, gate, up, alpha)
     const int e = idx[p];
@@ -358,7 +362,8 @@ __global__ void moe_act_kernel(const float *__restrict__ gu, float *__restrict__
 }
 
 /* y[t][h] = sum over the token's experts, ascending expert index, of (d (+ bias)) * w */
-__global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__restrict__ idx, const float *__restrict__ w,
+__global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__restrict__ idx, const int *__restrict__ ord,
+                                   const float *__restrict__ w,
                                    const float *const *__restrict__ down_b, float *__restrict__ y, int H, int topk,
                                    long total) {
   pdl_launch_dependents();
@@ -368,47 +373,7 @@ __global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__re
     return;
   const long t = i / H;
   const int h = (int)(i - t * H);
-  // the token's experts in ascending order (top_k <= 32: a bitmask of taken slots), then eight values in flight at a
-  // time, added in that order
-  int ids[32];
-  for (int j = 0; j < topk; ++j)
-    ids[j] = idx[t * topk + j];
-  float acc = 0.f;
-  unsigned taken = 0;
-  for (int k0 = 0; k0 < topk; k0 += 8) {
-    int sel[8], se[8];
-    float v[8], ww[8];
-    const int n = topk - k0 < 8 ? topk - k0 : 8;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      sel[k] = -1;
-      se[k] = 0;
-      if (k < n) {
-        int best = 0x7fffffff, bj = -1;
-        for (int j = 0; j < topk; ++j)
-          if (!((taken >> j) & 1u) && ids[j] < best) {
-            best = ids[j];
-            bj = j;
-          }
-        taken |= 1u << bj;
-        sel[k] = bj;
-        se[k] = best;
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (sel[k] >= 0) {
-        v[k] = dn[(t * topk + sel[k]) * H + h];
-        ww[k] = w[t * topk + sel[k]];
-        if (down_b)
-          v[k] = __fadd_rn(v[k], down_b[se[k]][h]);
-      }
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (sel[k] >= 0)
-        acc = __fadd_rn(acc, __fmul_rn(v[k], ww[k]));
-  }
-  y[i] = acc;
+  y[i] = moe_combine_elem(dn, idx, ord, w, down_b, t, h, H, topk);
 }
 
 /** upper bound on the polls of waits on other ranks' data (0: the default of 2^22); set from the host */
@@ -503,7 +468,7 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned 
 }
 
 struct MoeWs {
-  size_t idx, w, gu_tab, dn_tab, rpart, rcount, gu, act, dn, off, tile_off, perm, qx, qact, total;
+  size_t idx, ord, w, gu_tab, dn_tab, rpart, rcount, gu, act, dn, off, tile_off, perm, qx, qact, total;
 };
 
 static MoeWs moe_ws(unsigned T, unsigned H, unsigned I, unsigned topk, unsigned E = 256) {
@@ -514,6 +479,8 @@ static MoeWs moe_ws(unsigned T, unsigned H, unsigned I, unsigned topk, unsigned 
   // other fields and are cleared by the call itself
   size_t o = (size_t)MOE_COUNTER_TOKENS * 4;
   s.idx = o;
+  o = align_up(o + P * 4, 256);
+  s.ord = o;
   o = align_up(o + P * 4, 256);
   s.w = o;
   o = align_up(o + P * 4, 256);
@@ -605,6 +572,7 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: workspace of %zu bytes (256-byte aligned) needed", s.total);
   uint8_t *ws = static_cast<uint8_t *>(workspace);
   int *idx = reinterpret_cast<int *>(ws + s.idx);
+  int *ord = reinterpret_cast<int *>(ws + s.ord);
   float *w = reinterpret_cast<float *>(ws + s.w);
   const void **gu_tab = reinterpret_cast<const void **>(ws + s.gu_tab);
   const void **dn_tab = reinterpret_cast<const void **>(ws + s.dn_tab);
@@ -629,7 +597,7 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     NNTR_CHECK_CUDA(cudaLaunchKernelEx(&cfg, moe_router_kernel, x, d->router_w, d->router_bias, (int)H, (int)E, (int)K,
-                                       d->gate_w, d->up_w, d->down_w, idx, w, gu_tab, dn_tab,
+                                       d->gate_w, d->up_w, d->down_w, idx, ord, w, gu_tab, dn_tab,
                                        reinterpret_cast<float *>(ws + s.rpart),
                                        reinterpret_cast<unsigned *>(ws + s.rcount), ep));
     count_launch();
@@ -662,7 +630,7 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
                                    1, 1, max_tiles, st)))
       return rc2;
     const long n_out2 = (long)tokens * H;
-    const cudaError_t e2 = launch_pdl(moe_combine_kernel, (unsigned)((n_out2 + 255) / 256), 256, st, dn, idx, w,
+    const cudaError_t e2 = launch_pdl(moe_combine_kernel, (unsigned)((n_out2 + 255) / 256), 256, st, dn, idx, ord, w,
                                       d->kind == 1 ? d->down_b : nullptr, y, (int)H, (int)K, n_out2);
     count_launch();
     return check_cuda(e2, "moe_combine launch");
@@ -671,19 +639,30 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
   // programmatic dependent launch: the batched kernels wait for the grid before them as their first action, so only
   // their launch latency overlaps the previous kernel
   const unsigned pdl = NNTR_CUDA_GEMV_PDL;
-  int rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched(I, H, x, nullptr, gu, pdl, 2 * P, b1, st)
-                                 : launch_gemv_q4_0_batched(I, H, x, nullptr, gu, pdl, 2 * P, b1, st);
-  if (rc)
-    return rc;
+  int rc;
+  if (d->kind == 0 && d->qtype == NNTR_Q4_K && !epd) {
+    // Qwen form on one GPU: one problem per (token, expert) pair over the expert's gate AND up matrices; a CTA owns the
+    // same rows of both and its epilogue stores swish(gate) * up -- no activation launch, no trip of the two
+    // projections through memory. (The kernel releases its dependents only after its own wait for the router, so the
+    // down launch behind it still finds its table complete.)
+    GemvBatch bp = {gu_tab, (long long)H, (int)K, (long long)I};
+    bp.act = GEMV_ACT_PAIR_SWISH;
+    if ((rc = launch_gemv_q4_K_batched(I, H, x, nullptr, act, pdl, P, bp, st)))
+      return rc;
+  } else {
+    rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched(I, H, x, nullptr, gu, pdl, 2 * P, b1, st)
+                               : launch_gemv_q4_0_batched(I, H, x, nullptr, gu, pdl, 2 * P, b1, st);
+    if (rc)
+      return rc;
+    const long n_act = (long)P * I;
+    NNTR_CHECK_CUDA(launch_pdl(moe_act_kernel, (unsigned)((n_act + 255) / 256), 256, st, gu, act, idx, d->gate_b, d->up_b,
+                               d->kind, d->alpha, (int)I, n_act, e_lo, e_hi));
+    count_launch();
+  }
 
-  const long n_act = (long)P * I;
-  NNTR_CHECK_CUDA(launch_pdl(moe_act_kernel, (unsigned)((n_act + 255) / 256), 256, st, gu, act, idx, d->gate_b, d->up_b,
-                             d->kind, d->alpha, (int)I, n_act, e_lo, e_hi));
-  count_launch();
-
-  // the down table was written by the router, three launches back; the activation kernel in between releases its
-  // dependents only after the gate/up grid (hence the router) has completed, so the down launch may read its table and
-  // stream its weights while the activation kernel runs
+  // the down table was written by the router; the launch in between (the activation kernel, or the paired gate/up
+  // launch) releases its dependents only after its own wait, i.e. after the router has completed, so the down launch may
+  // read its table at once and stream its weights while that launch runs
   GemvBatch b2 = {dn_tab, (long long)I, 1, (long long)H, 1};
   const long n_out = (long)tokens * H;
   if (!epd) {
@@ -691,7 +670,7 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
                                : launch_gemv_q4_0_batched(H, I, act, nullptr, dn, pdl, P, b2, st);
     if (rc)
       return rc;
-    const cudaError_t e = launch_pdl(moe_combine_kernel, (unsigned)((n_out + 255) / 256), 256, st, dn, idx, w,
+    const cudaError_t e = launch_pdl(moe_combine_kernel, (unsigned)((n_out + 255) / 256), 256, st, dn, idx, ord, w,
                                      d->kind == 1 ? d->down_b : nullptr, y, (int)H, (int)K, n_out);
     count_launch();
     return check_cuda(e, "moe_combine launch");
@@ -771,7 +750,7 @@ extern "C" int nntr_cuda_moe_route_dev(const nntr_moe_desc *d, unsigned tokens, 
   NNTR_CHECK_CUDA(cudaMemsetAsync(ws + s.rcount, 0, (size_t)tokens * 4, static_cast<cudaStream_t>(stream)));
   moe_router_kernel<<<dim3(tokens, ROUTER_SLICES), ROUTER_WARPS * 32, ROUTER_WARPS * E * sizeof(float),
                       static_cast<cudaStream_t>(stream)>>>(
-    x, d->router_w, d->router_bias, (int)d->hidden, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx_out, w_out,
+    x, d->router_w, d->router_bias, (int)d->hidden, (int)E, (int)K, d->gate_w, d->up_w, d->down_w, idx_out, reinterpret_cast<int *>(ws + s.ord), w_out,
     reinterpret_cast<const void **>(ws + s.gu_tab), reinterpret_cast<const void **>(ws + s.dn_tab),
     reinterpret_cast<float *>(ws + s.rpart), reinterpret_cast<unsigned *>(ws + s.rcount), MoeEp{});
   count_launch();

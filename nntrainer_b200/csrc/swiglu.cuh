@@ -81,4 +81,13 @@ __device__ __forceinline__ float swiglu_elem(float y, float z, bool has_alpha, f
   return ftz_mul(ftz_div(y, inv_sig), z);
 }
 
+/** ActiFunc::swish times the up projection, as the Qwen MoE layer computes it (nntrainer/layers/acti_func.h:286-288,
+ *  400-405): sigmoid = (float)(1.0 / (1.0 + e)) with e = exp_util<float>(-g) = the DOUBLE exponential rounded to float
+ *  (nntrainer/utils/util_func.h:118 calls the C library's exp), then sigmoid * gate, then * up. */
+__device__ __forceinline__ float swish_mul_elem(float g, float u) {
+  const float e = (float)exp((double)(-g));
+  const float sig = (float)(1.0 / (1.0 + (double)e));
+  return __fmul_rn(__fmul_rn(sig, g), u);
+}
+
 } // namespace nntr
