@@ -16,7 +16,7 @@
  *
  * Decode (fewer than 8 tokens), no clearing launch: router (32 CTAs per token, the last to arrive reduces, selects and
  * writes the device-side weight-pointer tables), batched gate+up GEMV (the expert picked per problem through those
- * tables; Qwen form with Q4_K experts on one GPU: one problem per pair over both matrices with the activation in the
+ * tables; Qwen form with Q4_K experts: one problem per pair over both matrices with the activation in the
  * epilogue -- four launches per layer; otherwise 2 * pairs problems and an activation launch -- five), batched down
  * GEMV, combine.
  * The reference runs every expert GEMV with M = 1 even in prefill, so the batched GEMV reproduces its numerics.
@@ -640,11 +640,12 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
   // their launch latency overlaps the previous kernel
   const unsigned pdl = NNTR_CUDA_GEMV_PDL;
   int rc;
-  if (d->kind == 0 && d->qtype == NNTR_Q4_K && !epd) {
-    // Qwen form on one GPU: one problem per (token, expert) pair over the expert's gate AND up matrices; a CTA owns the
+  if (d->kind == 0 && d->qtype == NNTR_Q4_K) {
+    // Qwen form: one problem per (token, expert) pair over the expert's gate AND up matrices; a CTA owns the
     // same rows of both and its epilogue stores swish(gate) * up -- no activation launch, no trip of the two
     // projections through memory. (The kernel releases its dependents only after its own wait for the router, so the
-    // down launch behind it still finds its table complete.)
+    // down launch behind it still finds its table complete. Under expert parallelism the pairs of experts another rank
+    // owns have null table entries and are skipped.)
     GemvBatch bp = {gu_tab, (long long)H, (int)K, (long long)I};
     bp.act = GEMV_ACT_PAIR_SWISH;
     if ((rc = launch_gemv_q4_K_batched(I, H, x, nullptr, act, pdl, P, bp, st)))
