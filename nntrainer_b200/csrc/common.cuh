@@ -320,6 +320,8 @@ int launch_gemv_q4_0_stream(unsigned N, unsigned K, const float *x, const void *
                             cudaStream_t st);
 int launch_gemv_q4_0_batched(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
                              unsigned n_problems, GemvBatch batch, cudaStream_t st);
+int launch_gemv_q4_0_batched_publish(unsigned N, unsigned K, const float *x, unsigned n_problems, GemvBatch batch,
+                                     GemvExchange ex, cudaStream_t st);
 int read_q40_status(int *out);
 /* M > 1 with activations already quantized to plain Q8 rows in `qa` */
 int launch_gemm_q4_K(unsigned M, unsigned N, unsigned K, const void *qa, const void *B, float *C, unsigned ldc,

@@ -98,9 +98,12 @@ __device__ __forceinline__ int dot8(uint32_t w, uint32_t a_lo, uint32_t a_hi, in
   return __dp4a((int)(w & 0xf0f0f0f0u), (int)a_hi, acc);
 }
 
+/* PUBLISH (expert-parallel MoE, see GemvExchange with no_flags): the outputs go as (value, call number) pairs straight
+ * into every rank's buffer instead of y. */
+template <bool PUBLISH>
 __global__ void __launch_bounds__(Q40_THREADS, 1)
 gemv_q4_0_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, float *__restrict__ y, int n_groups, int K,
-                 int n_ring, GemvBatch batch) {
+                 int n_ring, GemvBatch batch, const GemvExchange ex) {
   extern __shared__ __align__(128) uint8_t smem[];
   if (batch.w_table) { // batched launch: blockIdx.y picks the problem; unless the caller says the table is older, it
     // was written by the kernel launched just before
@@ -166,6 +169,13 @@ gemv_q4_0_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, flo
   } else {
     /* ---- consumers: quantize x (256 elements per warp pass, masked beyond K), then whole row groups ---- */
     pdl_wait();
+    uint32_t tag = 0;
+    unsigned long long ex_off = 0;
+    if (PUBLISH) {
+      const unsigned long long seq = (*ex.epoch - 1) * ex.layers_per_epoch + ex.layer + 1;
+      tag = (uint32_t)seq;
+      ex_off = (unsigned long long)blockIdx.y * (unsigned long long)batch.y_stride + (seq & 1) * ex.parity_stride;
+    }
     for (int u8 = warp; u8 * 256 < K; u8 += Q40_CONSUMER_WARPS) {
       const int e0 = u8 * 256 + lane * 8;
       const bool valid = e0 < K;
@@ -243,8 +253,23 @@ gemv_q4_0_kernel(const float *__restrict__ x, const uint8_t *__restrict__ W, flo
         if (lane == 0)
           mbar_arrive(FREE_BAR(s));
       }
-      if (ok && lane < 8)
-        y[(size_t)(g_lo + i) * 8 + lane] = acc;
+      if (ok && lane < 8) {
+        const size_t o = (size_t)(g_lo + i) * 8 + lane;
+        if (!PUBLISH) {
+          y[o] = acc;
+        } else {
+          // (value, call number) in one 8-byte store into every rank's buffer: the reader checks the number of every
+          // element it uses, so no fence orders these stores against anything. The pointer array is indexed with
+          // constants only (a run-time index into a kernel parameter would put the whole description on the stack).
+#pragma unroll
+          for (int d = 0; d < 8; ++d)
+            if (d < ex.n_ranks) {
+              volatile uint2 *dst = ex.y[d] + ex_off + o;
+              asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(acc)), "r"(tag)
+                           : "memory");
+            }
+        }
+      }
       if (!ok)
         break;
     }
@@ -280,6 +305,23 @@ bool gemv_q4_0_stream_supported(unsigned N, unsigned K) {
   return q40_plan(N, K, ring, smem);
 }
 
+static thread_local const GemvExchange *g_q40_publish = nullptr; // set by the publishing launcher around its launch
+
+/* Batched launch whose epilogue publishes each problem's outputs, numbered, into every rank's buffer (expert-parallel
+ * MoE). ex.no_flags must be set; problems with a null table entry are skipped. */
+int launch_gemv_q4_0_batched_publish(unsigned N, unsigned K, const float *x, unsigned n_problems, GemvBatch batch,
+                                     GemvExchange ex, cudaStream_t st) {
+  if (ex.n_ranks < 1 || ex.n_ranks > 8 || ex.rank < 0 || ex.rank >= ex.n_ranks || !ex.epoch || !ex.no_flags)
+    return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_0_batched_publish: bad exchange description");
+  for (int d = 0; d < ex.n_ranks; ++d)
+    if (!ex.y[d])
+      return set_error(NNTR_CUDA_ERR_INVALID, "gemv_q4_0_batched_publish: null peer pointer for rank %d", d);
+  g_q40_publish = &ex;
+  const int rc = launch_gemv_q4_0_batched(N, K, x, nullptr, reinterpret_cast<float *>(ex.y[ex.rank]), 0, n_problems, batch, st);
+  g_q40_publish = nullptr;
+  return rc;
+}
+
 /* n_problems > 1: `batch.w_table` (device memory) holds one weight pointer per problem, B is ignored. */
 int launch_gemv_q4_0_batched(unsigned N, unsigned K, const float *x, const void *B, float *y, unsigned flags,
                              unsigned n_problems, GemvBatch batch, cudaStream_t st) {
@@ -297,7 +339,8 @@ int launch_gemv_q4_0_batched(unsigned N, unsigned K, const float *x, const void 
   int dev = 0;
   NNTR_CHECK_CUDA(cudaGetDevice(&dev));
   if (!attr_done[dev & 63]) {
-    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q40_SMEM_BUDGET));
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_0_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q40_SMEM_BUDGET));
+    NNTR_CHECK_CUDA(cudaFuncSetAttribute(gemv_q4_0_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q40_SMEM_BUDGET));
     attr_done[dev & 63] = true;
   }
   const int n_groups = (int)(N / 8), sms = sm_count();
@@ -314,8 +357,11 @@ int launch_gemv_q4_0_batched(unsigned N, unsigned K, const float *x, const void 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = (flags & NNTR_CUDA_GEMV_PDL) ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel, x, static_cast<const uint8_t *>(B), y, n_groups, (int)K, ring,
-                                     batch);
+  const GemvExchange ex = g_q40_publish ? *g_q40_publish : GemvExchange{};
+  cudaError_t e = g_q40_publish ? cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<true>, x, static_cast<const uint8_t *>(B), y,
+                                                     n_groups, (int)K, ring, batch, ex)
+                                : cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<false>, x, static_cast<const uint8_t *>(B), y,
+                                                     n_groups, (int)K, ring, batch, ex);
   count_launch();
   return check_cuda(e, "gemv_q4_0 launch");
 }

@@ -531,8 +531,6 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: null pointer");
   if (d->qtype != NNTR_Q4_K && d->qtype != NNTR_Q4_0)
     return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "moe_forward: expert weights must be Q4_K or Q4_0 (got qtype %d)", d->qtype);
-  if (d->qtype == NNTR_Q4_0 && epd)
-    return set_error(NNTR_CUDA_ERR_UNSUPPORTED, "moe_forward_ep: expert parallelism is built for Q4_K experts only");
   if (d->kind != 0 && d->kind != 1)
     return set_error(NNTR_CUDA_ERR_INVALID, "moe_forward: kind must be 0 (Qwen) or 1 (GPT-OSS)");
   if (d->kind == 1 && (!d->gate_b || !d->up_b || !d->down_b))
@@ -688,7 +686,8 @@ static int moe_forward(const nntr_moe_desc *d, const nntr_moe_ep *epd, unsigned 
   ex.layer = epd->layer;
   ex.no_flags = 1;
   ex.parity_stride = ep.parity_stride;
-  rc = launch_gemv_q4_K_batched_publish(H, I, act, P, b2, ex, st);
+  rc = d->qtype == NNTR_Q4_K ? launch_gemv_q4_K_batched_publish(H, I, act, P, b2, ex, st)
+                             : launch_gemv_q4_0_batched_publish(H, I, act, P, b2, ex, st);
   if (rc)
     return rc;
   int *status = nullptr;
