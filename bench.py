@@ -314,6 +314,118 @@ def decode_step_qwen3_4b(be, torch, dev, peak, steps=10):
     return out
 
 
+def decode_step_sharded(be, torch, dev, dist, world, rank, peak, steps=10):
+    """The same four projections per layer, every one sharded by rows over the ranks (N-split, strong scaling: the model
+    is fixed, a rank holds 1/world of every matrix) and chained for real: a launch reads the WHOLE gathered vector of
+    the launch before it (the first K elements where the graph would have attention or the activation in between) and
+    stores its row slice into every rank's gathered vector. 144 launches per token, no lm_head. Weights: N(0, 1/K)
+    through the reference's quantizer where it was built (magnitudes stay level along the chain), rolled per layer.
+    The last gathered vector is compared bit for bit with the same chain run on one GPU over the whole matrices."""
+    from nntrainer_b200.nsplit import NSplitGroup
+    from oracle import oracle as O
+    c = QWEN3_4B
+    shapes = [(c["q_dim"] + 2 * c["kv_dim"], c["hidden"]), (c["hidden"], c["q_dim"]), (2 * c["inter"], c["hidden"]),
+              (c["hidden"], c["inter"])]
+    if any((N // 8) % world for N, _ in shapes):
+        return {"error": f"row groups do not divide over {world} ranks"}
+    rng = np.random.default_rng(33)
+    bases = []
+    for N, K in shapes:
+        if O.ref_available():
+            R = O.ref()
+            W = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+            bases.append(torch.from_numpy(R.repack("q4_K", R.quantize_weight("q4_K", W), N, K)).to(dev))
+        else:
+            bases.append(torch.from_numpy(O.modellike_q4_Kx8(rng, N, K)).to(dev))
+    rolled = lambda l, j: torch.roll(bases[j], 1152 * (7 * l + 3)) if l else bases[j]
+    nl = [N // world for N, _ in shapes]
+    shard_bytes = [n * K // 256 * 144 for n, (_, K) in zip(nl, shapes)]
+    shards = [[rolled(l, j)[rank * shard_bytes[j]:(rank + 1) * shard_bytes[j]].clone() for j in range(4)]
+              for l in range(c["layers"])]
+    n_launch = 4 * c["layers"]
+
+    def resident_fits(n_local, K, sms=148):  # per-CTA share of at most 64 super-blocks: the ring-of-four protocol
+        groups, nb = n_local // 8, K // 256
+        grid = min(groups, sms)
+        return -(-groups // grid) * nb <= 64 and nb <= 64
+
+    ring = 4 if all(resident_fits(n, K) for n, (_, K) in zip(nl, shapes)) else 2
+    group = NSplitGroup(max(nl), n_launch, ring=ring)
+    x0 = torch.randn(c["hidden"], device=dev, generator=torch.Generator(device=dev).manual_seed(7))
+    stream = torch.cuda.Stream(device=dev)
+
+    def one_token():
+        group.bump_epoch(stream.cuda_stream)
+        for l in range(c["layers"]):
+            for j, (N, K) in enumerate(shapes):
+                i = 4 * l + j
+                group.gemv("q4_K", K, x0.data_ptr() if i == 0 else group.gathered_ptr(i - 1), shards[l][j].data_ptr(), i,
+                           stream.cuda_stream, pdl=True, x_tagged=i > 0, n_local=nl[j])
+
+    barrier = dist.barrier if world > 1 else (lambda: None)
+
+    def timed(fn):
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                fn()
+            for _ in range(3):
+                g.replay()
+            stream.synchronize()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        be.device_status()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms = timed(one_token)
+    plain_ms = None
+    if world == 1:  # the same chain without the exchange: plain launches, outputs in ordinary vectors
+        ys = [torch.empty(N, device=dev) for N, _ in shapes]
+
+        def plain_token():
+            x = x0
+            for l in range(c["layers"]):
+                for j, (N, K) in enumerate(shapes):
+                    be.gemv("q4_K", N, K, x, shards[l][j], ys[j], pdl=True)
+                    x = ys[j]
+        plain_ms = timed(plain_token)
+    got = group.gathered_numpy(n_launch - 1, nl[3])
+    # the same chain on this GPU alone, whole matrices
+    x = x0.clone()
+    for l in range(c["layers"]):
+        for j, (N, K) in enumerate(shapes):
+            y = torch.empty(N, device=dev)
+            be.gemv("q4_K", N, K, x[:K].contiguous(), rolled(l, j), y)
+            x = y
+    want = x.cpu().numpy()
+    ok = torch.tensor([0.0 if np.array_equal(got.view(np.uint32), want.view(np.uint32)) else 1.0], device=dev)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MAX)
+    wbytes = c["layers"] * sum(int(N * K * 144 / 256) for N, K in shapes)
+    out = {"shape": "Qwen3-4B decode, the four projections of every layer sharded by rows over the ranks (no lm_head)",
+           "ranks": world, "gathered_buffers": ring, "launches_per_token": n_launch, "weight_bytes_per_token": wbytes,
+           "plain_chain_ms_per_token": round(plain_ms, 4) if plain_ms is not None else None,
+           "ms_per_token": round(ms, 4), "tok/s": round(1e3 / ms, 1), "GB/s": round(wbytes / (ms * 1e-3) / 1e9, 1),
+           "frac_of_aggregate_hbm_peak": round(wbytes / (ms * 1e-3) / 1e9 / (peak * world), 4),
+           "equals_single_gpu_chain": float(ok.item()) == 0.0, "finite": bool(np.isfinite(want).all()),
+           "rms_of_last_vector": float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))}
+    group.close()
+    del shards, bases
+    torch.cuda.empty_cache()
+    return out
+
+
 # --------------------------------------------------------------------------
 # whole-model greedy decoding of a Qwen3-4B-shaped decoder: every operator of the graph, weights from a .bin file
 # --------------------------------------------------------------------------
@@ -797,6 +909,19 @@ def run_ours(args):
             moe = {"error": f"{type(exc).__name__}: {exc}"[:300]}
             failures.append("moe_decode_step: " + moe["error"])
 
+    # every projection of the 4B shape sharded over the ranks (strong scaling), on every rank
+    sharded = None
+    if not args.no_extra:
+        try:
+            sharded = decode_step_sharded(be, torch, dev, dist, world, rank, measured_peak()[0])
+            if "error" in sharded:
+                failures.append("decode_step_sharded: " + sharded["error"])
+            elif not sharded["equals_single_gpu_chain"]:
+                failures.append("decode_step_sharded: the gathered result differs from the single-GPU chain")
+        except Exception as exc:  # noqa: BLE001
+            sharded = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            failures.append("decode_step_sharded: " + sharded["error"])
+
     if rank == 0:
         peak, which = measured_peak()
         total_bytes = world * args.steps * RING * ALG_BYTES
@@ -828,6 +953,9 @@ def run_ours(args):
                           {k: moe[k] for k in ("ranks", "ms_per_token", "us_per_layer", "checksum") if k in moe},
                           "moe_prefill_256": None if not moe or "error" in moe else moe.get("prefill_256_tokens"),
                           "dense_projections_tok_s": decode["tok/s"] if decode else None,
+                          "dense_projections_sharded": None if not sharded or "error" in sharded else
+                          {k: sharded[k] for k in ("ranks", "gathered_buffers", "ms_per_token", "plain_chain_ms_per_token", "tok/s",
+                                                   "frac_of_aggregate_hbm_peak", "equals_single_gpu_chain")},
                           "model_decode_tok_s": model["tok/s"] if model else None,
                           "model_decode_tokens_equal_cpu": model["first_tokens_equal_cpu"] if model else None,
                           "failures": failures},
@@ -838,7 +966,7 @@ def run_ours(args):
                             "kernel": "gemv_q4_K_resident_kernel", "algorithmic_bytes_per_launch": ALG_BYTES},
                "cpu_baseline": cpu_desc, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk,
                "other_decode_gemv_shapes": others, "prefill_gemm_sweep": prefill,
-               "decode_step": decode, "model_decode": model, "moe_decode_step": moe}
+               "decode_step": decode, "decode_step_sharded": sharded, "model_decode": model, "moe_decode_step": moe}
         print(json.dumps(out), flush=True)
     if group is not None:
         group.close()

@@ -200,17 +200,21 @@ class NSplitGroup:
         check(lib().nntr_cuda_epoch_bump_dev(self.epoch, stream))
 
     def gemv(self, qtype: str, K: int, x_ptr: int, w_ptr: int, layer: int, stream: int, pdl: bool = False,
-             x_tagged: bool = True) -> None:
-        """Launch ``layer`` of the sequence. ``x_ptr`` is this rank's slice of the previous gathered vector
-        (``input_ptr``, tagged pairs) or, with ``x_tagged=False``, a plain fp32 vector."""
+             x_tagged: bool = True, n_local: int | None = None) -> None:
+        """Launch ``layer`` of the sequence. ``x_ptr`` is (a slice of) the previous gathered vector (``gathered_ptr`` /
+        ``input_ptr``, tagged pairs) or, with ``x_tagged=False``, a plain fp32 vector. ``n_local``: this launch's rows
+        per rank when the launches of the sequence differ in size (at most the group's ``n_local``)."""
+        n = self.n_local if n_local is None else n_local
+        if n > self.n_local:
+            raise ValueError("a launch's rows per rank exceed the gathered buffers of the group")
         ex = self.exchange(layer, x_tagged)
-        check(lib().nntr_cuda_gemv_nsplit_dev(QTYPE[qtype], self.n_local, K, x_ptr, w_ptr, C.byref(ex),
+        check(lib().nntr_cuda_gemv_nsplit_dev(QTYPE[qtype], n, K, x_ptr, w_ptr, C.byref(ex),
                                               capi.GEMV_PDL if pdl else 0, stream))
 
-    def gathered_numpy(self, layer: int):
+    def gathered_numpy(self, layer: int, n_local: int | None = None):
         """Host copy of the gathered vector launch ``layer`` produced (synchronising; for checks)."""
         import numpy as np
-        raw = np.empty(2 * self.world * self.n_local, dtype=np.float32)
+        raw = np.empty(2 * self.world * (self.n_local if n_local is None else n_local), dtype=np.float32)
         check(lib().nntr_cuda_memcpy(raw.ctypes.data, self.gathered_ptr(layer), raw.nbytes, 2))
         return np.ascontiguousarray(raw[0::2])  # drop the launch numbers
 
