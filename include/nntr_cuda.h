@@ -370,8 +370,13 @@ typedef struct {
                                        the next launch's x) over that many buffers, launch by launch; with four or more
                                        the "done reading" round trip is three launches old when it is needed, i.e. off
                                        the critical path. More than two needs a per-CTA share of at most 64 super-blocks
-                                       (N_local * K / 2048 / SMs), else NNTR_CUDA_ERR_UNSUPPORTED. layers_per_epoch
-                                       must be a multiple of the ring. */
+                                       (N_local * K / 2048 / SMs), else NNTR_CUDA_ERR_UNSUPPORTED, and EVERY launch
+                                       of the sequence must have the same N_local: each CTA keeps its own "done
+                                       reading" slot and a launch checks the slots of as many CTAs as it runs itself,
+                                       so a launch with more CTAs than the one three back would wait (bounded, then
+                                       NNTR_CUDA_ERR_TIMEOUT) for slots nobody writes. Two buffers count the CTAs of
+                                       each launch separately and take any sequence of sizes. layers_per_epoch must
+                                       be a multiple of the ring. */
 } nntr_exchange;
 int nntr_cuda_gemv_nsplit_dev(int qtype, unsigned N_local, unsigned K, const float *x, const void *B,
                               const nntr_exchange *ex, unsigned flags, void *stream);

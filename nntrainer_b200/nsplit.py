@@ -114,6 +114,17 @@ class PeerBuffers:
         self._own = []
 
 
+def check_ring_rows(ring: int, first_n: int | None, n: int) -> int:
+    """With a ring of more than two gathered buffers every CTA keeps its own "done reading" slot and a launch checks the
+    slots of as many CTAs as it runs itself, so every launch of the sequence must run the same number of CTAs: the group
+    then takes launches of ONE size only (rows per rank). Two buffers count the CTAs of each launch separately and take
+    any sizes. Returns the size to remember."""
+    if ring > 2 and first_n is not None and n != first_n:
+        raise ValueError(f"a ring of {ring} gathered buffers takes launches of one size only ({first_n} rows per rank, "
+                         f"now {n}): use ring=2 for sequences of differently sized projections")
+    return n if first_n is None else first_n
+
+
 class NSplitGroup:
     """Per-process state of an N-split group: ``ring`` gathered vectors in rotation, a flag array and an epoch
     word in this rank's memory, and the peers' copies mapped through CUDA IPC."""
@@ -207,6 +218,7 @@ class NSplitGroup:
         n = self.n_local if n_local is None else n_local
         if n > self.n_local:
             raise ValueError("a launch's rows per rank exceed the gathered buffers of the group")
+        self._first_n = check_ring_rows(self.ring, getattr(self, "_first_n", None), n)
         ex = self.exchange(layer, x_tagged)
         check(lib().nntr_cuda_gemv_nsplit_dev(QTYPE[qtype], n, K, x_ptr, w_ptr, C.byref(ex),
                                               capi.GEMV_PDL if pdl else 0, stream))

@@ -86,3 +86,14 @@ def test_odd_launch_count_per_pass_is_rejected():
         seq = [nsplit.sequence_number(e, L, l) for e in (1, 2, 3) for l in range(L)]
         assert all((a + 1) == b for a, b in zip(seq, seq[1:]))
         assert all((nsplit.sequence_number(e, L, l) % 2) == ((l + 1) % 2) for e in (1, 2, 3) for l in range(L))
+
+
+def test_ring_of_four_takes_launches_of_one_size_only():
+    """The per-CTA "done reading" slots of the ring-of-four exchange assume every launch runs the same CTAs; two
+    buffers take any sequence of sizes."""
+    from nntrainer_b200.nsplit import check_ring_rows
+    assert check_ring_rows(4, None, 4096) == 4096
+    assert check_ring_rows(4, 4096, 4096) == 4096
+    with pytest.raises(ValueError):
+        check_ring_rows(4, 4096, 320)
+    assert check_ring_rows(2, 4096, 320) == 4096
