@@ -357,7 +357,7 @@ gemv_q4_K_kernel(const float *__restrict__ x, const BlockQ4Kx8 *__restrict__ W, 
       }
       if (PAIR) {
         // second matrix: y = swiglu(first, second), the SwiGLU layer behind a gated FFN's two projections (its sigmoid
-        // branch takes the first). The partner was stored in this round or an earlier one.
+        // branch takes the first). The partner was stored in this pass of the loop or an earlier one.
         __syncwarp();
         if (have && gl >= ng_rows) {
           const float first = reinterpret_cast<const float *>(smem + L.stash)[(gl - ng_rows) * 8 + r];
