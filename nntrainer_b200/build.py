@@ -36,8 +36,19 @@ def stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile and link if any source is newer than the library. Several processes may call this at once (one rank per
+    GPU, test workers): an exclusive file lock lets one of them build while the others wait and then find it done."""
     if not force and not stale():
         return LIB
+    import fcntl
+    with open(LIB + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not stale():
+            return LIB
+        return _build_locked(verbose)
+
+
+def _build_locked(verbose: bool) -> str:
     objs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
     ccbin = ["-ccbin", HOST_CXX] if os.path.exists(HOST_CXX) else []
