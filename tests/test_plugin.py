@@ -55,6 +55,58 @@ def test_context_plugin_loads_like_an_external_context(built):
     assert "ml_train_context_pluggable" in defined
 
 
+def test_dotqnk_hook_compiles_in_the_reference_and_links_to_the_backend(built):
+    """plugin/hook_dotqnk.py writes the compile-time branch into a temporary copy of the reference's float_tensor.cpp;
+    the copy must compile against the reference's headers with and without -DENABLE_CUDA, the CUDA build must call the
+    three *_cuda functions (so the reference's argument lists type-check against cuda_backend.h) with exactly the symbols
+    libcuda_backend.so defines, and the build without the macro must reference none of them."""
+    import sys
+    from oracle import oracle as O
+    ref = O.reference_root()
+    src = os.path.join(ref or "", "nntrainer", "tensor", "float_tensor.cpp")
+    if not ref or not os.path.exists(src):
+        pytest.skip("needs a checkout of the reference")
+    sys.path.insert(0, os.path.join(ROOT, "plugin"))
+    try:
+        import hook_dotqnk
+    finally:
+        sys.path.pop(0)
+    with open(src, encoding="utf-8") as f:
+        original = f.read()
+    hooked, wrapped = hook_dotqnk.hook(original)
+    assert wrapped == 4  # Q4_K, Q6_K, and the two Q4_0 calls either side of the OpenCL branch
+    # without the macro the preprocessor sees the original text: every added line sits under ENABLE_CUDA
+    kept = [ln for ln in hooked.splitlines() if ln not in ("#ifdef ENABLE_CUDA", "#else", "#endif", "#include <cuda_backend.h>")
+            and "_cuda(" not in ln]
+    stripped = [ln for ln in original.splitlines() if ln not in ("#else", "#endif")]
+    assert kept == stripped
+    with pytest.raises(ValueError):
+        hook_dotqnk.hook(hooked)  # applying it twice is refused
+    n = os.path.join(ref, "nntrainer")
+    inc = [f"-I{d}" for d in (n, f"{n}/layers", f"{n}/tensor", f"{n}/utils", f"{n}/graph", f"{n}/optimizers", f"{n}/models",
+                              f"{n}/compiler", f"{n}/dataset", f"{ref}/api", f"{ref}/api/ccapi/include",
+                              f"{n}/tensor/cpu_backend", f"{n}/tensor/cpu_backend/x86", f"{n}/tensor/cpu_backend/fallback",
+                              f"{n}/tensor/cpu_backend/ggml_interface", os.path.join(ROOT, "plugin"))]
+    with tempfile.TemporaryDirectory() as tmp:
+        cpp = os.path.join(tmp, "float_tensor.cpp")
+        with open(cpp, "w", encoding="utf-8") as f:
+            f.write(hooked)
+        wanted = {}
+        for tag, extra in (("cuda", ["-DENABLE_CUDA"]), ("plain", [])):
+            obj = os.path.join(tmp, f"ft_{tag}.o")
+            r = subprocess.run(["/usr/bin/g++", "-std=c++17", "-O0", "-fPIC", "-c", *inc, *extra, cpp, "-o", obj],
+                               capture_output=True, text=True, timeout=600)
+            assert r.returncode == 0, r.stderr[-2000:]
+            und = subprocess.run(["nm", "--undefined-only", obj], capture_output=True, text=True, check=True).stdout
+            wanted[tag] = {ln.split()[-1] for ln in und.splitlines() if "_cuda" in ln}
+    assert wanted["plain"] == set()
+    assert len(wanted["cuda"]) == 3
+    defined = subprocess.run(["nm", "-D", "--defined-only", os.path.join(built, "libcuda_backend.so")],
+                             capture_output=True, text=True, check=True).stdout
+    have = {ln.split()[-1] for ln in defined.splitlines()}
+    assert wanted["cuda"] <= have, wanted["cuda"] - have
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("q,M,N,K", [("q4_K", 1, 512, 1024), ("q4_K", 6, 136, 512), ("q4_0", 5, 64, 160), ("q6_K", 3, 50, 512)])
 def test_backend_functions_match_the_checker_through_the_gpu(built, port, q, M, N, K):
