@@ -107,6 +107,77 @@ def test_dotqnk_hook_compiles_in_the_reference_and_links_to_the_backend(built):
     assert wanted["cuda"] <= have, wanted["cuda"] - have
 
 
+REFOUT = os.path.join(ROOT, "oracle", "_ref")
+# the quantized tensor classes want N % 8 == 0 for the interleaved Q4_K form and N % 256 == 0 for Q6_K
+TENSOR_DOT_CASES = [("q4_K", 1, 512, 1024), ("q4_K", 6, 136, 512), ("q4_K", 9, 64, 768), ("q4_0", 1, 64, 2880),
+                    ("q4_0", 5, 64, 160), ("q6_K", 1, 256, 256), ("q6_K", 3, 256, 512)]
+
+
+def _tensor_dot(exe, q, M, N, K):
+    """Runs one of the drivers built from the reference's tensor sources (plugin/tensor_dot_driver.cpp) on a seeded
+    case; returns (exit code, output matrix or None, the checker's result, stderr)."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(1000 * M + N + K)
+    gen = {"q4_K": O.random_q4_Kx8, "q4_0": O.random_q4_0x8, "q6_K": O.random_q6_K}[q]
+    B = gen(rng, N, K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    with tempfile.TemporaryDirectory() as td:
+        case, res = os.path.join(td, "case.bin"), os.path.join(td, "res.bin")
+        with open(case, "wb") as f:
+            f.write(struct.pack("<iIII", {"q4_0": 2, "q4_K": 12, "q6_K": 14}[q], M, N, K))
+            f.write(A.tobytes())
+            f.write(B.tobytes())
+        r = subprocess.run([exe, case, res], capture_output=True, text=True, timeout=300)
+        C = np.fromfile(res, dtype=np.float32).reshape(M, N) if r.returncode == 0 else None
+    return r.returncode, C, O.port().gemm(q, A, B, N), r.stderr
+
+
+@pytest.mark.parametrize("q,M,N,K", TENSOR_DOT_CASES)
+def test_the_references_own_tensor_dot_equals_the_checker(built, q, M, N, K):
+    """nntrainer::Tensor::dot on a quantized weight tensor, linked from the reference's unmodified tensor sources (the
+    call FullyConnectedLayer makes), gives the checker's bits: the port is pinned to the reference's public tensor API,
+    not only to its backend functions."""
+    exe = os.path.join(REFOUT, "tensor_dot_cpu")
+    if not os.path.exists(exe):
+        pytest.skip("driver not built (needs a checkout of the reference at build time)")
+    rc, C, want, err = _tensor_dot(exe, q, M, N, K)
+    assert rc == 0, err
+    assert np.array_equal(C.view(np.uint32), want.view(np.uint32))
+
+
+def test_hooked_tensor_dot_without_a_device_throws_what_the_cpu_path_would(built):
+    """The same driver with the ENABLE_CUDA branch in FloatTensor::dotQnK: without a CUDA device the call chain ends in
+    std::runtime_error (exit code 5) raised by the backend's error mapping, never in a CPU fallback; a weight tensor the
+    reference's own classes reject is still std::invalid_argument from the reference (exit code 4)."""
+    torch = pytest.importorskip("torch")
+    exe = os.path.join(REFOUT, "tensor_dot_cuda")
+    if not os.path.exists(exe):
+        pytest.skip("driver not built (needs a checkout of the reference at build time)")
+    rc, _, _, err = _tensor_dot(exe, "q6_K", 3, 56, 512)  # Q6_K_Tensor wants N % 256 == 0
+    assert rc == 4 and "invalid_argument" in err
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present: the no-device behaviour cannot be shown here")
+    rc, C, _, err = _tensor_dot(exe, "q4_K", 1, 512, 1024)
+    assert rc == 5 and C is None and "runtime_error" in err, (rc, err)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("q,M,N,K", TENSOR_DOT_CASES)
+def test_hooked_tensor_dot_runs_on_the_gpu_and_equals_the_checker(built, q, M, N, K):
+    """The reference's Tensor::dot, compiled from its own sources with the hook plugin/hook_dotqnk.py writes and
+    -DENABLE_CUDA, linked to libcuda_backend.so: the product comes from libnntr_cuda.so and equals the CPU result bit
+    for bit (decode GEMV, and GEMM rows below the tensor-core threshold)."""
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    exe = os.path.join(REFOUT, "tensor_dot_cuda")
+    if not os.path.exists(exe):
+        pytest.skip("driver not built (needs a checkout of the reference at build time)")
+    rc, C, want, err = _tensor_dot(exe, q, M, N, K)
+    assert rc == 0, err
+    assert np.array_equal(C.view(np.uint32), want.view(np.uint32))
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("q,M,N,K", [("q4_K", 1, 512, 1024), ("q4_K", 6, 136, 512), ("q4_0", 5, 64, 160), ("q6_K", 3, 50, 512)])
 def test_backend_functions_match_the_checker_through_the_gpu(built, port, q, M, N, K):
