@@ -10,15 +10,13 @@
  *   nntrainer/layers/acti_func.h:166-213 (softmax), :286-288 and :400-405 (sigmoid in double, swish)
  *   nntrainer/tensor/float_tensor.cpp:1108-1180 (topK = std::partial_sort with comparator '>', reproduced with the same call)
  *
- * Parity status: PARTLY PINNED. Pinned to reference code: the expert GEMVs (port.c, bit-equal to oracle/_ref), the
- * GPT-OSS activation (nntrainer::swiglu with a slope, restated in glue_port.c and bit-equal to the reference's
- * x86/avx2_impl.cpp:950-996), the top-k order (the same std::partial_sort call with the same comparator, ties
- * included). NOT pinned, because they need the Tensor class and BLAS, which do not build here: the router product and
- * the sums over experts / over the top-k values (BLAS: OpenBLAS, absent; ascending index is used here), and the
- * softmax / swish exponentials, which are the C library's DOUBLE exp rounded to float (exp_util<float>,
- * nntrainer/utils/util_func.h:118 -- checked: the instantiation links against exp, not expf) and restated as such.
- * Outputs are therefore compared within the path's tolerance (max-rel 2e-3); expert selection exactly whenever the
- * top-k margin exceeds what the unpinned sums can move.
+ * Parity status: PINNED to the reference built without a BLAS library. oracle/_ref/moe_tensor_ref (moe_tensor_ref.cpp)
+ * issues the same layer statements on the reference's own Tensor / ActiFunc / swiglu code, linked from its sources, and
+ * tests/test_moe.py requires this file's indices, routing weights and outputs to equal it bit for bit: both layer forms,
+ * one token (the router product is an sgemv: a float chain in ascending index) and several (an sgemm: float products,
+ * a double accumulator rounded once), exact ties in the top-k included. The softmax / swish exponentials are the C
+ * library's DOUBLE exp rounded to float (exp_util<float>, nntrainer/utils/util_func.h:118). What stays undefined is a
+ * reference built against OpenBLAS, whose summation order in the router product and the row sums is the library's.
  */
 #include <algorithm>
 #include <cmath>
@@ -61,10 +59,24 @@ void port_moe_route(unsigned T, unsigned H, unsigned E, unsigned topk, const flo
   std::vector<float> p(E);
   for (unsigned t = 0; t < T; ++t) {
     for (unsigned e = 0; e < E; ++e) { // qwen_moe_layer.cpp:439 input.dot(gate_weights) -- [T,H] x [H,E]
-      float acc = 0.f;
-      for (unsigned h = 0; h < H; ++h)
-        acc += x[(size_t)t * H + h] * router_w[(size_t)h * E + e];
-      p[e] = acc + (router_bias ? router_bias[e] : 0.f); // gpt_oss_moe_layer.cpp:503-504
+      // The reference built without a BLAS library (fallback_internal.cpp:26-38, 197-219): one token is an sgemv, a
+      // float chain in ascending index; several tokens are an sgemm, whose products are float but whose accumulator
+      // is a double rounded once at the end.
+      float logit;
+      if (T == 1) {
+        float acc = 0.f;
+        for (unsigned h = 0; h < H; ++h)
+          acc += x[(size_t)t * H + h] * router_w[(size_t)h * E + e];
+        logit = acc;
+      } else {
+        double acc = 0.0;
+        for (unsigned h = 0; h < H; ++h) {
+          const float prod = x[(size_t)t * H + h] * router_w[(size_t)h * E + e];
+          acc += prod;
+        }
+        logit = static_cast<float>(1.0f * acc);
+      }
+      p[e] = logit + (router_bias ? router_bias[e] : 0.f); // gpt_oss_moe_layer.cpp:503-504
     }
     const float mx = *std::max_element(p.begin(), p.end()); // acti_func.h:195-199
     for (unsigned e = 0; e < E; ++e)

@@ -49,6 +49,44 @@ def build(ref: bool = True) -> None:
                    check=True, stdout=subprocess.DEVNULL)
 
 
+def moe_tensor_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=0, router_bias=None, gate_b=None,
+                   up_b=None, down_b=None, alpha=1.0):
+    """The MoE forward issued on the reference's own Tensor class (oracle/_ref/moe_tensor_ref, built from
+    moe_tensor_ref.cpp and the reference's tensor sources). Returns (indices [T][k], routing weights [T][k],
+    output [T][H]), or None when the program was not built (no checkout at build time)."""
+    import struct
+    import tempfile
+    exe = os.path.join(HERE, "_ref", "moe_tensor_ref")
+    if not os.path.exists(exe):
+        return None
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    T, H = x.shape
+    E = router_w.shape[1]
+    per = {"q4_K": (256, 144), "q4_0": (32, 18)}[qtype]
+    inter = gate_w[0].size * per[0] // per[1] // H
+    with tempfile.TemporaryDirectory() as td:
+        case, res = os.path.join(td, "case.bin"), os.path.join(td, "res.bin")
+        with open(case, "wb") as f:
+            f.write(struct.pack("<iiIIIIIf", kind, {"q4_K": 12, "q4_0": 2}[qtype], T, H, inter, E, top_k, alpha))
+            f.write(x.tobytes())
+            f.write(np.ascontiguousarray(router_w, dtype=np.float32).tobytes())
+            if kind == 1:
+                f.write(np.ascontiguousarray(router_bias, dtype=np.float32).tobytes())
+            for e in range(E):
+                for a in (gate_w[e], up_w[e], down_w[e]):
+                    f.write(a.tobytes())
+                if kind == 1:
+                    for a in (gate_b[e], up_b[e], down_b[e]):
+                        f.write(np.ascontiguousarray(a, dtype=np.float32).tobytes())
+        r = subprocess.run([exe, case, res], capture_output=True, text=True, timeout=600)
+        if r.returncode != 0:
+            raise RuntimeError(f"moe_tensor_ref failed ({r.returncode}): {r.stderr.strip()[:500]}")
+        raw = np.fromfile(res, dtype=np.uint8)
+    n = T * top_k * 4
+    return (raw[:n].view(np.uint32).reshape(T, top_k), raw[n:2 * n].view(np.float32).reshape(T, top_k),
+            raw[2 * n:].view(np.float32).reshape(T, H))
+
+
 def _cpu_flags() -> set:
     try:
         with open("/proc/cpuinfo") as f:
