@@ -77,6 +77,41 @@ def test_rms_norm_bit_exact(port, ref, width):
     assert np.array_equal(bits(port.rms_norm(x, gamma, 1e-6)), bits(b * gamma[None, :]))
 
 
+@pytest.mark.parametrize("width", [128, 2560, 2880, 4096])
+def test_whole_row_rms_norm_layer_on_the_references_tensor_class_is_a_few_ulps_from_the_helper_order(port, width):
+    """RMSNormLayer (rms_norm.cpp:69-73) is four Tensor statements whose row sum has no explicit order (a float chain in
+    a build without BLAS, the library's order with one); the per-head layer calls an explicit AVX2 helper. The checker
+    and the kernels use the helper's order for both. This runs the layer's statements on the reference's own Tensor
+    class (oracle/_ref/rms_tensor_ref) and bounds the distance: same value to 32 units in the last place, i.e. the two
+    differ by summation order only."""
+    import os
+    import struct
+    import subprocess
+    import tempfile
+    from oracle import oracle as O
+    exe = os.path.join(os.path.dirname(O.__file__), "_ref", "rms_tensor_ref")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/rms_tensor_ref not built (needs a checkout of the reference at build time)")
+    rng = np.random.default_rng(width)
+    rows, eps = 4, 1e-6
+    x = (rng.standard_normal((rows, width)) * 3).astype(np.float32)
+    gamma = rng.uniform(0.5, 1.5, width).astype(np.float32)
+    with tempfile.TemporaryDirectory() as td:
+        case, res = os.path.join(td, "case.bin"), os.path.join(td, "res.bin")
+        with open(case, "wb") as f:
+            f.write(struct.pack("<IIf", rows, width, eps))
+            f.write(x.tobytes())
+            f.write(gamma.tobytes())
+        r = subprocess.run([exe, case, res], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr
+        layer = np.fromfile(res, dtype=np.float32).reshape(rows, width)
+    helper = port.rms_norm(x, gamma, eps)
+    ulps = np.abs(bits(layer).astype(np.int64) - bits(helper).astype(np.int64))
+    print(f"width {width}: {int((ulps > 0).sum())} of {ulps.size} elements differ, at most {int(ulps.max())} ulp")
+    assert ulps.max() <= 32
+    np.testing.assert_allclose(layer, helper, rtol=4e-6)
+
+
 def test_topk_is_the_library_partial_sort(port):
     rng = np.random.default_rng(5)
     p = rng.random(128).astype(np.float32)
