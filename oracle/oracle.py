@@ -87,6 +87,39 @@ def moe_tensor_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=
             raw[2 * n:].view(np.float32).reshape(T, H))
 
 
+def mha_layer_ref(q, k, v, n_heads, n_kv_heads, head_dim, max_timestep, rope_theta, sliding_window=None, sink=None):
+    """Drives the reference's own attention layer (oracle/_ref/mha_layer_ref: mha_core.cpp compiled unmodified) one token
+    at a time: q [steps][n_heads*head_dim], k and v [steps][n_kv_heads*head_dim] are the layer's inputs per step.
+    Returns (outputs [steps][n_heads*head_dim], key cache, value cache as uint16 [max_timestep][n_kv_heads][head_dim]),
+    or None when the program was not built (no checkout at build time)."""
+    import struct
+    import tempfile
+    exe = os.path.join(HERE, "_ref", "mha_layer_ref")
+    if not os.path.exists(exe):
+        return None
+    steps = q.shape[0]
+    with tempfile.TemporaryDirectory() as td:
+        case, res = os.path.join(td, "case.bin"), os.path.join(td, "res.bin")
+        with open(case, "wb") as f:
+            f.write(struct.pack("<8I", n_heads, n_kv_heads, head_dim, steps, max_timestep,
+                                0xffffffff if sliding_window is None else sliding_window, int(rope_theta),
+                                0 if sink is None else 1))
+            if sink is not None:
+                f.write(np.ascontiguousarray(sink, dtype=np.float32).tobytes())
+            for t in range(steps):
+                for a in (q, k, v):
+                    f.write(np.ascontiguousarray(a[t], dtype=np.float32).tobytes())
+        r = subprocess.run([exe, case, res], capture_output=True, text=True, timeout=600)
+        if r.returncode != 0:
+            raise RuntimeError(f"mha_layer_ref failed ({r.returncode}): {r.stderr.strip()[:500]}")
+        raw = np.fromfile(res, dtype=np.uint8)
+    n = steps * n_heads * head_dim * 4
+    caches = raw[n:].view(np.uint16)
+    c = max_timestep * n_kv_heads * head_dim
+    return (raw[:n].view(np.float32).reshape(steps, n_heads * head_dim),
+            caches[:c].reshape(max_timestep, n_kv_heads, head_dim), caches[c:2 * c].reshape(max_timestep, n_kv_heads, head_dim))
+
+
 def _cpu_flags() -> set:
     try:
         with open("/proc/cpuinfo") as f:

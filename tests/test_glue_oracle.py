@@ -112,6 +112,46 @@ def test_whole_row_rms_norm_layer_on_the_references_tensor_class_is_a_few_ulps_f
     np.testing.assert_allclose(layer, helper, rtol=4e-6)
 
 
+@pytest.mark.parametrize("n_heads,n_kv,hd,steps,max_t,window,theta,with_sink", [
+    (8, 2, 128, 20, 32, None, 1000000, False),    # Qwen3-style heads
+    (32, 8, 128, 40, 64, None, 1000000, False),   # the 4B shape's head counts
+    (8, 2, 128, 24, 32, 8, 1000000, False),       # a sliding window shorter than the sequence
+    (16, 2, 64, 20, 24, 6, 150000, True),         # GPT-OSS style: 64-wide heads, window and sinks
+    (8, 8, 64, 12, 16, None, 10000, True),        # no grouping, sinks
+])
+def test_single_token_attention_equals_the_references_attention_layer(port, n_heads, n_kv, hd, steps, max_t, window, theta,
+                                                                       with_sink):
+    """The reference's own attention layer (causallm::MHACoreLayer, mha_core.cpp compiled unmodified and driven through
+    its run context one token at a time, oracle/_ref/mha_layer_ref) against the sequence of helper calls the checker's
+    decoder and the GPU tests use for a decode step -- rotary embedding of q and k from the library's table, fp16 cache
+    append, scores over the window, softmax (with sinks), values: every step's output and both caches bit for bit.
+    This also pins the library's rotary table (nntr_cuda_rope_table, host code) to the layer's precompute_freqs."""
+    from nntrainer_b200 import backend as be
+    from oracle import oracle as O
+    rng = np.random.default_rng(n_heads * 1000 + steps)
+    q = rng.standard_normal((steps, n_heads * hd)).astype(np.float32)
+    k = rng.standard_normal((steps, n_kv * hd)).astype(np.float32)
+    v = rng.standard_normal((steps, n_kv * hd)).astype(np.float32)
+    sink = rng.standard_normal(n_heads).astype(np.float32) if with_sink else None
+    ref = O.mha_layer_ref(q, k, v, n_heads, n_kv, hd, max_t, theta, window, sink)
+    if ref is None:
+        pytest.skip("oracle/_ref/mha_layer_ref not built (needs a checkout of the reference at build time)")
+    out_ref, kc_ref, vc_ref = ref
+    cos, sin = be.rope_table(hd, max_t, float(theta))
+    kc = np.zeros((max_t, n_kv, hd), dtype=np.uint16)
+    vc = np.zeros((max_t, n_kv, hd), dtype=np.uint16)
+    gqa, w = n_heads // n_kv, (2 ** 31 - 1 if window is None else window)
+    for pos in range(steps):  # the statements of oracle/cpu_decoder.py's attention step
+        qr = port.rotary(q[pos], hd, cos[pos], sin[pos])
+        kc[pos] = port.rotary(k[pos], hd, cos[pos], sin[pos], to_fp16=True).reshape(n_kv, -1)
+        vc[pos] = port.rotary(v[pos], hd, cos[pos], sin[pos], to_fp16=True, only_convert=True).reshape(n_kv, -1)
+        sc = port.compute_kcaches(qr, kc, pos + 1, n_kv, hd, gqa, w)
+        pr = port.softmax_rows(sc, 0, sc.shape[0], sink, True)
+        a = port.compute_vcache(pos, pr, vc, n_kv, gqa, hd, w).reshape(-1)
+        assert np.array_equal(bits(a), bits(out_ref[pos])), f"step {pos}"
+    assert np.array_equal(kc[:steps], kc_ref[:steps]) and np.array_equal(vc[:steps], vc_ref[:steps])
+
+
 def test_topk_is_the_library_partial_sort(port):
     rng = np.random.default_rng(5)
     p = rng.random(128).astype(np.float32)
