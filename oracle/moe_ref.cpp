@@ -10,9 +10,11 @@
  *   nntrainer/layers/acti_func.h:166-213 (softmax), :286-288 and :400-405 (sigmoid in double, swish)
  *   nntrainer/tensor/float_tensor.cpp:1108-1180 (topK = std::partial_sort with comparator '>', reproduced with the same call)
  *
- * Parity status: PINNED to the reference built without a BLAS library. oracle/_ref/moe_tensor_ref (moe_tensor_ref.cpp)
- * issues the same layer statements on the reference's own Tensor / ActiFunc / swiglu code, linked from its sources, and
- * tests/test_moe.py requires this file's indices, routing weights and outputs to equal it bit for bit: both layer forms,
+ * Parity status: PINNED to the reference built without a BLAS library. oracle/_ref/moe_layer_ref (moe_layer_ref.cpp)
+ * runs the reference's two layer classes themselves, compiled unmodified, and oracle/_ref/moe_tensor_ref
+ * (moe_tensor_ref.cpp) issues the same statements on the reference's own Tensor / ActiFunc / swiglu code so that the
+ * routing indices and weights are visible too; tests/test_moe.py requires this file's outputs to equal the layers' and
+ * its indices, routing weights and outputs to equal the second program's, bit for bit: both layer forms,
  * one token (the router product is an sgemv: a float chain in ascending index) and several (an sgemm: float products,
  * a double accumulator rounded once), exact ties in the top-k included. The softmax / swish exponentials are the C
  * library's DOUBLE exp rounded to float (exp_util<float>, nntrainer/utils/util_func.h:118). What stays undefined is a

@@ -87,6 +87,46 @@ def moe_tensor_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=
             raw[2 * n:].view(np.float32).reshape(T, H))
 
 
+def moe_layer_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=0, router_bias=None, gate_b=None,
+                  up_b=None, down_b=None):
+    """Runs the reference's own MoE layer (oracle/_ref/moe_layer_ref: qwen_moe_layer.cpp / gpt_oss_moe_layer.cpp compiled
+    unmodified, driven through a run context) on the tokens x [T][H]; returns the layer's output [T][H], or None when the
+    program was not built (no checkout at build time). The GPT-OSS layer's slope is its own constant, 1.702."""
+    import struct
+    import tempfile
+    exe = os.path.join(HERE, "_ref", "moe_layer_ref")
+    if not os.path.exists(exe):
+        return None
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    T, H = x.shape
+    E = router_w.shape[1]
+    per = {"q4_K": (256, 144), "q4_0": (32, 18)}[qtype]
+    inter = gate_w[0].size * per[0] // per[1] // H
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32).tobytes()
+    with tempfile.TemporaryDirectory() as td:
+        case, res = os.path.join(td, "case.bin"), os.path.join(td, "res.bin")
+        with open(case, "wb") as f:  # the layer's weights in the order it requests them, then the activation
+            f.write(struct.pack("<iiIIIII", kind, {"q4_K": 12, "q4_0": 2}[qtype], T, H, inter, E, top_k))
+            f.write(f32(router_w))
+            if kind == 1:
+                f.write(f32(router_bias))
+            for e in range(E):
+                f.write(up_w[e].tobytes())
+                if kind == 1:
+                    f.write(f32(up_b[e]))
+                f.write(gate_w[e].tobytes())
+                if kind == 1:
+                    f.write(f32(gate_b[e]))
+                f.write(down_w[e].tobytes())
+                if kind == 1:
+                    f.write(f32(down_b[e]))
+            f.write(x.tobytes())
+        r = subprocess.run([exe, case, res], capture_output=True, text=True, timeout=600)
+        if r.returncode != 0:
+            raise RuntimeError(f"moe_layer_ref failed ({r.returncode}): {r.stderr.strip()[:500]}")
+        return np.fromfile(res, dtype=np.float32).reshape(T, H)
+
+
 def mha_layer_ref(q, k, v, n_heads, n_kv_heads, head_dim, max_timestep, rope_theta, sliding_window=None, sink=None):
     """Drives the reference's own attention layer (oracle/_ref/mha_layer_ref: mha_core.cpp compiled unmodified) one token
     at a time: q [steps][n_heads*head_dim], k and v [steps][n_kv_heads*head_dim] are the layer's inputs per step.

@@ -101,6 +101,44 @@ def test_restatement_equals_the_layer_issued_on_the_references_tensor_class_gpt_
     assert np.array_equal(ref[2].view(np.uint32), out.view(np.uint32))
 
 
+@pytest.mark.parametrize("T", [1, 5, 33])
+def test_restatement_equals_the_references_own_layer_qwen_form(port, T):
+    """causallm::MoELayer itself (qwen_moe_layer.cpp compiled unmodified, finalized with the application's properties,
+    run through its run context: oracle/_ref/moe_layer_ref) against the restatement: the same output bits."""
+    rng = np.random.default_rng(700 + T)
+    H, I, E, k = 512, 256, 16, 4
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    router, gate, up, down = make_layer(rng, H, I, E)
+    ref = O.moe_layer_ref(x, router, gate, up, down, k)
+    if ref is None:
+        pytest.skip("oracle/_ref/moe_layer_ref not built (needs a checkout of the reference at build time)")
+    out = port.moe_forward(x, router, gate, up, down, k)
+    assert np.array_equal(ref.view(np.uint32), out.view(np.uint32))
+
+
+@pytest.mark.parametrize("T", [1, 6])
+def test_restatement_equals_the_references_own_layer_gpt_oss_form(port, T):
+    """causallm::GptOssMoELayer itself (gpt_oss_moe_layer.cpp, unmodified; its slope is the layer's constant 1.702) with
+    Q4_0 experts, router and expert biases: the same output bits as the restatement."""
+    rng = np.random.default_rng(800 + T)
+    H, I, E, k = 352, 352, 8, 4
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    router = (rng.standard_normal((H, E)) * 0.02).astype(np.float32)
+    rbias = (rng.standard_normal(E) * 0.01).astype(np.float32)
+    gate = [O.random_q4_0x8(rng, I, H) for _ in range(E)]
+    up = [O.random_q4_0x8(rng, I, H) for _ in range(E)]
+    down = [O.random_q4_0x8(rng, H, I) for _ in range(E)]
+    gb = [(rng.standard_normal(I) * 0.1).astype(np.float32) for _ in range(E)]
+    ub = [(rng.standard_normal(I) * 0.1).astype(np.float32) for _ in range(E)]
+    db = [(rng.standard_normal(H) * 0.1).astype(np.float32) for _ in range(E)]
+    ref = O.moe_layer_ref(x, router, gate, up, down, k, qtype="q4_0", kind=1, router_bias=rbias, gate_b=gb, up_b=ub, down_b=db)
+    if ref is None:
+        pytest.skip("oracle/_ref/moe_layer_ref not built (needs a checkout of the reference at build time)")
+    out = port.moe_forward(x, router, gate, up, down, k, qtype="q4_0", kind=1, router_bias=rbias, gate_b=gb, up_b=ub,
+                           down_b=db, alpha=1.702)
+    assert np.array_equal(ref.view(np.uint32), out.view(np.uint32))
+
+
 def test_restatement_orders_exact_ties_like_the_references_topk(port):
     """Duplicated router columns give bit-equal probabilities inside the top-k and across its boundary: the order
     Tensor::topK returns (std::partial_sort's heap moves) is the restatement's."""
