@@ -10,9 +10,12 @@ BIG = 2 ** 31 - 1
 
 
 class CpuDecoder:
-    def __init__(self, cfg: DecoderConfig, weights: dict, cos, sin, matmul=None):
+    def __init__(self, cfg: DecoderConfig, weights: dict, cos, sin, matmul=None, whole_row_norm="helper"):
+        """whole_row_norm: "helper" sums a row's squares in the order of the per-head helper (what the kernels do);
+        "layer" in the order RMSNormLayer's own Tensor statements have in a build of the reference without BLAS."""
         self.c, self.w, self.cos, self.sin = cfg, weights, cos, sin
         self.P = O.port()
+        self.row_norm = self.P.rms_norm if whole_row_norm == "helper" else self.P.rms_norm_layer
         self.mm = matmul or self.P
         self.kc = [np.zeros((cfg.max_seq, cfg.n_kv_heads, cfg.head_dim), dtype=np.uint16) for _ in range(cfg.n_layers)]
         self.vc = [np.zeros((cfg.max_seq, cfg.n_kv_heads, cfg.head_dim), dtype=np.uint16) for _ in range(cfg.n_layers)]
@@ -31,7 +34,7 @@ class CpuDecoder:
         gqa = c.n_heads // c.n_kv_heads
         for i in range(c.n_layers):
             p = f"layer{i}_"
-            n = P.rms_norm(x, self.w[p + "attention_norm"], c.norm_eps)
+            n = self.row_norm(x, self.w[p + "attention_norm"], c.norm_eps)
             v = self.gemv(p + "wv", n)
             k = P.rms_norm(self.gemv(p + "wk", n), self.w[p + "k_norm"], c.norm_eps)
             q = P.rms_norm(self.gemv(p + "wq", n), self.w[p + "q_norm"], c.norm_eps)
@@ -43,10 +46,10 @@ class CpuDecoder:
             pr = P.softmax_rows(sc, 0, sc.shape[0], None, True)
             a = P.compute_vcache(pos, pr, self.vc[i], c.n_kv_heads, gqa, c.head_dim, window).reshape(-1)
             h = x + self.gemv(p + "attention_out", a)
-            n = P.rms_norm(h, self.w[p + "ffn_norm"], c.norm_eps)
+            n = self.row_norm(h, self.w[p + "ffn_norm"], c.norm_eps)
             act = P.swiglu(self.gemv(p + "ffn_up", n), self.gemv(p + "ffn_gate", n))
             x = h + self.gemv(p + "ffn_down", act)
-        n = P.rms_norm(x, self.w["output_norm"], c.norm_eps)
+        n = self.row_norm(x, self.w["output_norm"], c.norm_eps)
         self.last_logits = self.gemv("output_of_causallm", n)
         return int(np.argmax(self.last_logits))  # first maximum, as std::max_element
 

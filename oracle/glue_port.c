@@ -263,3 +263,32 @@ int port_rms_norm(const float *X, const float *gamma, float *Y, size_t rows, siz
       Y[r * width + i] = Y[r * width + i] * gamma[i];
   return 0;
 }
+
+/* The whole-row layer exactly as a build of the reference WITHOUT a BLAS library computes it (rms_norm.cpp:69-73 on the
+ * Tensor class): t = in.multiply(in).average(3).add(eps); t.inv_sqrt_i(); in.multiply(t, out); out.multiply_i(gamma).
+ * average(3) is sum(3) with alpha = float(1.0 / float(width)) (tensor.cpp:787-799), and that sum is an sgemv against a
+ * vector filled with alpha (float_tensor.cpp, case 3 of sum; fallback_internal.cpp:26-38): a float chain in ascending
+ * index of the rounded products sq[i] * alpha. inv_sqrt_i is 1 / std::sqrt(v) in float. Pinned bit for bit against
+ * oracle/_ref/rms_tensor_ref; the kernels and port_rms_norm use the per-head helper's order instead. */
+int port_rms_norm_layer(const float *X, const float *gamma, float *Y, size_t rows, size_t width, float eps) {
+  if (width < 2)
+    return -1; /* average() copies instead of summing when the axis has one element */
+  const float alpha = (float)(1.0 / (double)(float)width);
+  for (size_t r = 0; r < rows; ++r) {
+    const float *x = X + r * width;
+    float *y = Y + r * width;
+    float m = 0.0f;
+    for (size_t i = 0; i < width; ++i) {
+      const float sq = x[i] * x[i];
+      const float term = sq * alpha;
+      m += term;
+    }
+    float t = m + eps;
+    t = 1.0f / sqrtf(t);
+    for (size_t i = 0; i < width; ++i) {
+      const float v = x[i] * t;
+      y[i] = v * gamma[i];
+    }
+  }
+  return 0;
+}

@@ -87,6 +87,26 @@ def moe_tensor_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=
             raw[2 * n:].view(np.float32).reshape(T, H))
 
 
+def decoder_layers_ref(cfg, bin_path, prompt, n_new):
+    """Greedy decoding with a decoder assembled from the reference's own layer classes (oracle/_ref/decoder_layers_ref),
+    weights read from ``bin_path`` by the reference's reader. ``cfg`` has the fields of nntrainer_b200.decoder's
+    DecoderConfig. Returns (tokens [n_new], logits [vocab] after the last step), or None when not built."""
+    import tempfile
+    exe = os.path.join(HERE, "_ref", "decoder_layers_ref")
+    if not os.path.exists(exe):
+        return None
+    with tempfile.TemporaryDirectory() as td:
+        res = os.path.join(td, "res.bin")
+        args = [exe, bin_path, res] + [str(v) for v in (
+            cfg.n_layers, cfg.hidden, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.inter, cfg.vocab, cfg.max_seq,
+            int(cfg.rope_theta), "%.6f" % cfg.norm_eps, cfg.sliding_window or 0, n_new)] + [str(t) for t in prompt]
+        r = subprocess.run(args, capture_output=True, text=True, timeout=3600)
+        if r.returncode != 0:
+            raise RuntimeError(f"decoder_layers_ref failed ({r.returncode}): {r.stderr.strip()[:500]}")
+        raw = np.fromfile(res, dtype=np.uint8)
+    return [int(t) for t in raw[:4 * n_new].view(np.uint32)], raw[4 * n_new:].view(np.float32).copy()
+
+
 def moe_layer_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=0, router_bias=None, gate_b=None,
                   up_b=None, down_b=None):
     """Runs the reference's own MoE layer (oracle/_ref/moe_layer_ref: qwen_moe_layer.cpp / gpt_oss_moe_layer.cpp compiled
@@ -386,6 +406,17 @@ class Port(_Lib):
         g = np.ascontiguousarray(gamma, dtype=np.float32)
         y = np.empty_like(x)
         f = self.lib.port_rms_norm
+        f.argtypes, f.restype = [_vp, _vp, _vp, C.c_size_t, C.c_size_t, C.c_float], C.c_int
+        assert f(_ptr(x), _ptr(g), _ptr(y), x.size // g.size, g.size, eps) == 0
+        return y
+
+    def rms_norm_layer(self, x, gamma, eps):
+        """RMSNormLayer's own statements as a build of the reference without BLAS computes them (a float chain for the
+        row sum); see port_rms_norm_layer. The kernels use rms_norm's order."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        g = np.ascontiguousarray(gamma, dtype=np.float32)
+        y = np.empty_like(x)
+        f = self.lib.port_rms_norm_layer
         f.argtypes, f.restype = [_vp, _vp, _vp, C.c_size_t, C.c_size_t, C.c_float], C.c_int
         assert f(_ptr(x), _ptr(g), _ptr(y), x.size // g.size, g.size, eps) == 0
         return y

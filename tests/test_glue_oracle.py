@@ -105,6 +105,9 @@ def test_whole_row_rms_norm_layer_on_the_references_tensor_class_is_a_few_ulps_f
         r = subprocess.run([exe, case, res], capture_output=True, text=True, timeout=120)
         assert r.returncode == 0, r.stderr
         layer = np.fromfile(res, dtype=np.float32).reshape(rows, width)
+    # the restatement of those statements (a float chain for the row sum) is exact ...
+    assert np.array_equal(bits(port.rms_norm_layer(x, gamma, eps)), bits(layer))
+    # ... and the helper's order, which the kernels use for this layer too, is a few units in the last place away
     helper = port.rms_norm(x, gamma, eps)
     ulps = np.abs(bits(layer).astype(np.int64) - bits(helper).astype(np.int64))
     print(f"width {width}: {int((ulps > 0).sum())} of {ulps.size} elements differ, at most {int(ulps.max())} ulp")
