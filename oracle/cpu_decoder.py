@@ -50,7 +50,8 @@ class CpuDecoder:
             act = P.swiglu(self.gemv(p + "ffn_up", n), self.gemv(p + "ffn_gate", n))
             x = h + self.gemv(p + "ffn_down", act)
         n = self.row_norm(x, self.w["output_norm"], c.norm_eps)
-        self.last_logits = self.gemv("output_of_causallm", n)
+        # tied embeddings: the lm_head is the embedding tensor itself (TieWordEmbedding's second mode)
+        self.last_logits = self.gemv("embedding0" if c.tie_word_embeddings else "output_of_causallm", n)
         return int(np.argmax(self.last_logits))  # first maximum, as std::max_element
 
 

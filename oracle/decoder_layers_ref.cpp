@@ -18,7 +18,10 @@
  * and -- with its whole-row norm set to this build's summation order -- the same logits bit for bit.
  *
  * usage: decoder_layers_ref <model.bin> <result file> n_layers hidden n_heads n_kv_heads head_dim inter vocab max_seq
- *                           rope_theta norm_eps sliding_window(0: none) n_new prompt_token...
+ *                           rope_theta norm_eps sliding_window(0: none) tie(0|1) n_new prompt_token...
+ * tie = 1: embedding and lm_head are the two modes of TieWordEmbedding (tie_word_embedding.cpp) on ONE Q6_K tensor
+ * [vocab][hidden], as causal_lm.cpp:187-229 builds them for models with tied embeddings; the file then holds no lm_head
+ * tensor and the head's product is Tensor::dot with a transposed-dimension weight.
  * Result file: uint32 tokens [n_new], then the logits [vocab] fp32 behind the last generated token's successor.
  */
 #include <algorithm>
@@ -41,6 +44,7 @@
 #include <rms_norm.h>
 #include <swiglu.h>
 #include <tensor.h>
+#include <tie_word_embedding.h>
 #include <var_grad.h>
 #include <weight.h>
 
@@ -59,7 +63,8 @@ struct Node {
 
 /* finalize the layer on the dimensions of its inputs, create what it asked for, read its weights from the file */
 static std::unique_ptr<Node> make(nntrainer::Layer *layer, const std::vector<std::string> &props, const std::vector<Var_Grad *> &ins,
-                                  const std::string &weight_dtype, std::ifstream &bin, const std::string &name) {
+                                  const std::string &weight_dtype, std::ifstream &bin, const std::string &name,
+                                  const nntrainer::Tensor *shared_from = nullptr) {
   std::unique_ptr<Node> n(new Node);
   n->layer.reset(layer);
   layer->setProperty(props);
@@ -73,7 +78,14 @@ static std::unique_ptr<Node> make(nntrainer::Layer *layer, const std::vector<std
   for (auto const &spec : init.getWeightsSpec()) {
     n->weights.emplace_back(new Weight(std::get<0>(spec), nntrainer::Initializer::ZEROS, nntrainer::WeightRegularizer::NONE, 0.0f, 0.0f,
                                        0.0f, false, true, std::get<8>(spec)));
-    n->weights.back()->getVariableRef().read(bin); // the reference's reader: scheme word, block bytes
+    if (shared_from) { // a weight another layer has read already (shared_from=embedding0): same bytes, nothing in the file
+      if (shared_from->getMemoryBytes() != n->weights.back()->getVariableRef().getMemoryBytes())
+        throw std::runtime_error("shared weight: sizes differ");
+      std::copy(shared_from->getData<uint8_t>(), shared_from->getData<uint8_t>() + shared_from->getMemoryBytes(),
+                n->weights.back()->getVariableRef().getData<uint8_t>());
+    } else {
+      n->weights.back()->getVariableRef().read(bin); // the reference's reader: scheme word, block bytes
+    }
     wptr.push_back(n->weights.back().get());
   }
   auto own = [&n](const TensorDim &d, const std::string &nm) {
@@ -90,18 +102,18 @@ static std::unique_ptr<Node> make(nntrainer::Layer *layer, const std::vector<std
 }
 
 int main(int argc, char **argv) {
-  if (argc < 16) {
+  if (argc < 17) {
     fprintf(stderr, "usage: %s model.bin result n_layers hidden n_heads n_kv_heads head_dim inter vocab max_seq rope_theta norm_eps "
-                    "sliding_window n_new prompt...\n", argv[0]);
+                    "sliding_window tie n_new prompt...\n", argv[0]);
     return 2;
   }
   try {
     const unsigned L = atoi(argv[3]), H = atoi(argv[4]), NH = atoi(argv[5]), NKV = atoi(argv[6]), HD = atoi(argv[7]), I = atoi(argv[8]),
                    V = atoi(argv[9]), S = atoi(argv[10]);
     const std::string theta = argv[11], eps = argv[12];
-    const unsigned window = atoi(argv[13]), n_new = atoi(argv[14]);
+    const unsigned window = atoi(argv[13]), tie = atoi(argv[14]), n_new = atoi(argv[15]);
     std::vector<unsigned> prompt;
-    for (int i = 15; i < argc; ++i)
+    for (int i = 16; i < argc; ++i)
       prompt.push_back((unsigned)atoi(argv[i]));
     std::ifstream bin(argv[1], std::ios::binary);
     if (!bin)
@@ -123,8 +135,11 @@ int main(int argc, char **argv) {
       return add(new causallm::RMSNormLayer(), {"epsilon=" + eps}, {in}, "FP32", name);
     };
 
-    Var_Grad *x = add(new causallm::EmbeddingLayer(), {"in_dim=" + std::to_string(V), "out_dim=" + std::to_string(H)}, {&token}, "Q6_K",
-                      "embedding0");
+    Var_Grad *x = tie ? add(new causallm::TieWordEmbedding(), {"in_dim=" + std::to_string(V), "out_dim=" + std::to_string(H)}, {&token},
+                            "Q6_K", "embedding0")
+                      : add(new causallm::EmbeddingLayer(), {"in_dim=" + std::to_string(V), "out_dim=" + std::to_string(H)}, {&token},
+                            "Q6_K", "embedding0");
+    const nntrainer::Tensor *embedding_weight = &nodes[0]->weights[0]->getVariableRef();
     for (unsigned l = 0; l < L; ++l) {
       const std::string p = "layer" + std::to_string(l) + "_";
       Var_Grad *an = norm(x, p + "attention_norm");
@@ -150,7 +165,14 @@ int main(int argc, char **argv) {
       x = add(new nntrainer::AdditionLayer(), {}, {h, down}, "FP32", p + "decoder_output");
     }
     Var_Grad *on = norm(x, "output_norm");
-    Var_Grad *logits = fc(on, V, "Q6_K", "output_of_causallm");
+    Var_Grad *logits;
+    if (tie) {
+      nodes.push_back(make(new causallm::TieWordEmbedding(), {"unit=" + std::to_string(V), "disable_bias=true"}, {on}, "Q6_K", bin,
+                           "output_of_causallm", embedding_weight));
+      logits = nodes.back()->out();
+    } else {
+      logits = fc(on, V, "Q6_K", "output_of_causallm");
+    }
     if (bin.peek() != std::ifstream::traits_type::eof())
       throw std::runtime_error("the model file holds more bytes than the layers read");
 

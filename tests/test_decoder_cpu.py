@@ -23,6 +23,10 @@ from oracle.cpu_decoder import CpuDecoder, synthetic_weights, write_bin
 CONFIGS = {
     "two_layers_qwen3_heads": (DecoderConfig(n_layers=2, hidden=1024, n_heads=16, n_kv_heads=4, head_dim=128, inter=3072,
                                              vocab=2048, max_seq=80), [11, 409, 2047, 5], 64, 0),
+    # embedding and lm_head as the two modes of the reference's TieWordEmbedding on one tensor; a vocabulary that is not
+    # a multiple of the 256-row tile (the tied tensor is [vocab][hidden], so only the hidden size has to be whole blocks)
+    "tied_embeddings_vocab_1000": (DecoderConfig(n_layers=1, hidden=512, n_heads=8, n_kv_heads=2, head_dim=64, inter=768,
+                                                 vocab=1000, max_seq=40, tie_word_embeddings=True), [7, 999, 0], 32, 2),
     "sliding_window_16": (DecoderConfig(n_layers=1, hidden=512, n_heads=8, n_kv_heads=2, head_dim=64, inter=768, vocab=1024,
                                         max_seq=48, sliding_window=16), [1, 2, 3], 40, 1),
 }
