@@ -17,6 +17,10 @@
  * The checker's pipeline (oracle/cpu_decoder.py), which the GPU decoder is compared with, must produce the same tokens
  * and -- with its whole-row norm set to this build's summation order -- the same logits bit for bit.
  *
+ * plugin/Makefile builds this file a second time (decoder_layers_cuda) with -DENABLE_CUDA against the copy of
+ * float_tensor.cpp that plugin/hook_dotqnk.py writes: the same layer classes, but every projection's Tensor::dot ends in
+ * libnntr_cuda.so. That program must print the same tokens and logits as this one (tests/test_plugin.py, -m gpu).
+ *
  * usage: decoder_layers_ref <model.bin> <result file> n_layers hidden n_heads n_kv_heads head_dim inter vocab max_seq
  *                           rope_theta norm_eps sliding_window(0: none) tie(0|1) n_new prompt_token...
  * tie = 1: embedding and lm_head are the two modes of TieWordEmbedding (tie_word_embedding.cpp) on ONE Q6_K tensor
@@ -47,6 +51,10 @@
 #include <tie_word_embedding.h>
 #include <var_grad.h>
 #include <weight.h>
+
+#ifdef ENABLE_CUDA
+#include <cuda_backend.h> /* plugin/: the build with the hooked float_tensor.cpp sends every Tensor::dot to the GPU */
+#endif
 
 using nntrainer::TensorDim;
 using nntrainer::Var_Grad;
@@ -119,6 +127,9 @@ int main(int argc, char **argv) {
     if (!bin)
       return 2;
     nntrainer::init_backend();
+#ifdef ENABLE_CUDA
+    nntrainer::init_backend_cuda(0); // what the context plug-in's init() does once per process
+#endif
 
     const TensorDim::TensorType fp32 = {nntrainer::Tformat::NCHW, nntrainer::Tdatatype::FP32};
     Var_Grad token(TensorDim({1, 1, 1, 1}, fp32), nntrainer::Initializer::ZEROS, false, true, "input0");
@@ -197,7 +208,11 @@ int main(int argc, char **argv) {
     fwrite(out.data(), 4, out.size(), o);
     fwrite(logits->getVariableRef().getData<float>(), 4, V, o);
     fclose(o);
-    printf("ok %zu layers\n", nodes.size());
+#ifdef ENABLE_CUDA
+    printf("ok %zu layers cuda\n", nodes.size());
+#else
+    printf("ok %zu layers cpu\n", nodes.size());
+#endif
     return 0;
   } catch (const std::exception &e) {
     fprintf(stderr, "exception: %s\n", e.what());

@@ -87,12 +87,14 @@ def moe_tensor_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=
             raw[2 * n:].view(np.float32).reshape(T, H))
 
 
-def decoder_layers_ref(cfg, bin_path, prompt, n_new):
+def decoder_layers_ref(cfg, bin_path, prompt, n_new, cuda=False):
     """Greedy decoding with a decoder assembled from the reference's own layer classes (oracle/_ref/decoder_layers_ref),
     weights read from ``bin_path`` by the reference's reader. ``cfg`` has the fields of nntrainer_b200.decoder's
-    DecoderConfig. Returns (tokens [n_new], logits [vocab] after the last step), or None when not built."""
+    DecoderConfig. Returns (tokens [n_new], logits [vocab] after the last step), or None when not built.
+    ``cuda``: the same program built with the ENABLE_CUDA hook in FloatTensor::dotQnK (decoder_layers_cuda): the layer
+    classes are the reference's, every projection runs in libnntr_cuda.so."""
     import tempfile
-    exe = os.path.join(HERE, "_ref", "decoder_layers_ref")
+    exe = os.path.join(HERE, "_ref", "decoder_layers_cuda" if cuda else "decoder_layers_ref")
     if not os.path.exists(exe):
         return None
     with tempfile.TemporaryDirectory() as td:

@@ -161,6 +161,53 @@ def test_hooked_tensor_dot_without_a_device_throws_what_the_cpu_path_would(built
     assert rc == 5 and C is None and "runtime_error" in err, (rc, err)
 
 
+def _small_model(td, tie=False):
+    from nntrainer_b200.decoder import DecoderConfig
+    from oracle.cpu_decoder import synthetic_weights, write_bin
+    cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=8, n_kv_heads=2, head_dim=64, inter=768, vocab=1024, max_seq=48,
+                        tie_word_embeddings=tie)
+    path = os.path.join(td, "model.bin")
+    write_bin(path, cfg, synthetic_weights(cfg, 3))
+    return cfg, path
+
+
+def test_layer_class_decoder_with_the_hook_needs_a_device(built):
+    """The decoder assembled from the reference's layer classes, built with the hook: without a CUDA device its first
+    projection raises (the backend's std::runtime_error), it does not quietly compute on the CPU."""
+    torch = pytest.importorskip("torch")
+    from oracle import oracle as O
+    if not os.path.exists(os.path.join(REFOUT, "decoder_layers_cuda")):
+        pytest.skip("driver not built (needs a checkout of the reference at build time)")
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present: the no-device behaviour cannot be shown here")
+    with tempfile.TemporaryDirectory() as td:
+        cfg, path = _small_model(td)
+        with pytest.raises(RuntimeError, match="cuda|CUDA"):
+            O.decoder_layers_ref(cfg, path, [1, 2, 3], 4, cuda=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tie", [False, True], ids=["own_lm_head", "tied_embeddings"])
+def test_layer_class_decoder_with_the_hook_generates_the_cpu_builds_tokens(built, tie):
+    """The drop-in at model level: the reference's own layer classes (embedding, norms, fully connected, attention,
+    SwiGLU, additions), unmodified, with only the ENABLE_CUDA branch in FloatTensor::dotQnK -- every projection and the
+    lm_head run in libnntr_cuda.so through the host-pointer entry points, everything else in the reference's CPU code.
+    32 greedy tokens and the final logits must equal the same program built without the hook, bit for bit."""
+    torch = pytest.importorskip("torch")
+    from oracle import oracle as O
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    if not (os.path.exists(os.path.join(REFOUT, "decoder_layers_cuda")) and os.path.exists(os.path.join(REFOUT, "decoder_layers_ref"))):
+        pytest.skip("drivers not built (need a checkout of the reference at build time)")
+    with tempfile.TemporaryDirectory() as td:
+        cfg, path = _small_model(td, tie)
+        cpu_tokens, cpu_logits = O.decoder_layers_ref(cfg, path, [5, 900, 17], 32)
+        gpu_tokens, gpu_logits = O.decoder_layers_ref(cfg, path, [5, 900, 17], 32, cuda=True)
+    assert gpu_tokens == cpu_tokens
+    assert len(set(cpu_tokens)) > 4
+    assert np.array_equal(gpu_logits.view(np.uint32), cpu_logits.view(np.uint32))
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("q,M,N,K", TENSOR_DOT_CASES)
 def test_hooked_tensor_dot_runs_on_the_gpu_and_equals_the_checker(built, q, M, N, K):
