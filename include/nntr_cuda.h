@@ -263,6 +263,12 @@ typedef struct {
 /** cos / sin tables of MHACoreLayer::precompute_freqs with the default rope parameters (mha_core.cpp:617-688):
  *  HOST arrays [seq_len][head_dim], filled on the host with the C library's cos/sin as the reference does. */
 int nntr_cuda_rope_table(unsigned head_dim, unsigned seq_len, float theta, float *cos_out, float *sin_out);
+/** The same tables for rope_scaling_type "yarn" (MHACoreLayer::_compute_yarn_parameters, mha_core.cpp:689-781; the
+ *  properties rope_scaling_factor and rope_scaling_max_position_embeddings): interpolated / extrapolated inverse
+ *  frequencies blended over a linear ramp between the correction dimensions of 32 and 1 rotations, and cos / sin scaled by
+ *  0.1 * log(factor) + 1. The attention kernels take the tables as they are, so nothing else changes for such a model. */
+int nntr_cuda_rope_table_yarn(unsigned head_dim, unsigned seq_len, float theta, float factor,
+                              unsigned original_max_position_embeddings, float *cos_out, float *sin_out);
 /** First half of MHACoreLayer::one_batch_incremental_forwarding for one token at position pos (mha_core.cpp:489-506):
  *  rotary embedding of q in place (fp32), of k into row pos of the fp16 key cache, and v converted into row pos of the
  *  fp16 value cache (compute_rotary_emb_value, x86/avx2_impl.cpp:1652-1738). Caches: [row][kv head][head_dim] fp16.

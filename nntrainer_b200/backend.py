@@ -468,11 +468,17 @@ def embedding(qtype: str | None, table, ids_f, in_dim: int, out_dim: int, out=No
 
 
 # ------------------------------------------------------- attention (one token)
-def rope_table(head_dim: int, seq_len: int, theta: float):
-    """MHACoreLayer::precompute_freqs, default rope (mha_core.cpp:617-688): host numpy [seq_len, head_dim] cos, sin."""
+def rope_table(head_dim: int, seq_len: int, theta: float, yarn_factor: float | None = None,
+               yarn_original_max_position_embeddings: int = 4096):
+    """MHACoreLayer::precompute_freqs (mha_core.cpp:617-688): host numpy [seq_len, head_dim] cos, sin. Default rope
+    parameters, or with ``yarn_factor`` the layer's rope_scaling_type "yarn" (mha_core.cpp:689-781)."""
     cos = np.empty((seq_len, head_dim), dtype=np.float32)
     sin = np.empty((seq_len, head_dim), dtype=np.float32)
-    check(lib().nntr_cuda_rope_table(head_dim, seq_len, theta, _np_ptr(cos), _np_ptr(sin)))
+    if yarn_factor is None:
+        check(lib().nntr_cuda_rope_table(head_dim, seq_len, theta, _np_ptr(cos), _np_ptr(sin)))
+    else:
+        check(lib().nntr_cuda_rope_table_yarn(head_dim, seq_len, theta, yarn_factor, yarn_original_max_position_embeddings,
+                                              _np_ptr(cos), _np_ptr(sin)))
     return cos, sin
 
 

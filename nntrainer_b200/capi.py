@@ -47,6 +47,7 @@ SIGNATURES = {
     "nntr_cuda_argmax_dev": (_i, [_vp, _i64, _i64, _i64, _vp, _vp, _u, _vp]),
     "nntr_cuda_embedding_dev": (_i, [_i, _vp, _vp, _vp, _u, _u, _u, _u, _vp]),
     "nntr_cuda_rope_table": (_i, [_u, _u, C.c_float, _vp, _vp]),
+    "nntr_cuda_rope_table_yarn": (_i, [_u, _u, C.c_float, C.c_float, _u, _vp, _vp]),
     "nntr_cuda_rope_cache_append_dev": (_i, [_vp, _u, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u, _vp]),
     "nntr_cuda_qk_norm_rope_cache_append_dev": (_i, [_vp, _u, _vp, _vp, _vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp,
                                                      _u, _vp]),

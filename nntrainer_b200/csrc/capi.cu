@@ -612,6 +612,10 @@ int nntr_cuda_embedding_dev(int qtype, const void *table, const float *ids, floa
 int nntr_cuda_rope_table(unsigned head_dim, unsigned seq_len, float theta, float *cos_out, float *sin_out) {
   return rope_table(head_dim, seq_len, theta, cos_out, sin_out);
 }
+int nntr_cuda_rope_table_yarn(unsigned head_dim, unsigned seq_len, float theta, float factor,
+                              unsigned original_max_position_embeddings, float *cos_out, float *sin_out) {
+  return rope_table_yarn(head_dim, seq_len, theta, factor, original_max_position_embeddings, cos_out, sin_out);
+}
 int nntr_cuda_rope_cache_append_dev(const nntr_attn_desc *a, unsigned pos, const unsigned *pos_dev, float *q,
                                     const float *k, const float *v, void *kcache, void *vcache, const float *cos_tab,
                                     const float *sin_tab, unsigned flags, void *stream) {

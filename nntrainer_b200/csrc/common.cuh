@@ -376,6 +376,8 @@ int launch_attention_step(const nntr_attn_desc *a, unsigned pos, const unsigned 
 int bin_layout(const nntr_bin_tensor *t, size_t n, size_t *data_offset, size_t *bytes, size_t *total);
 int bin_load(const char *path, const nntr_bin_tensor *t, size_t n, int rank, int n_ranks, void **dev_ptrs, void **arena);
 int rope_table(unsigned head_dim, unsigned seq_len, float theta, float *cos_out, float *sin_out);
+int rope_table_yarn(unsigned head_dim, unsigned seq_len, float theta, float factor, unsigned original_max_position_embeddings,
+                    float *cos_out, float *sin_out);
 /* status words: clear = zero the word after reading it */
 int clear_device_status_words();
 int clear_umma_status();

@@ -208,4 +208,48 @@ int rope_table(unsigned head_dim, unsigned seq_len, float theta, float *cos_out,
   return NNTR_CUDA_OK;
 }
 
+/* MHACoreLayer::_compute_yarn_parameters (mha_core.cpp:689-781) followed by the table loop of precompute_freqs: the
+ * same float / double mix statement by statement -- the correction dimensions come out of a double expression and are
+ * rounded to float, the two inverse-frequency sets are 1.0 / (float) rounded to float, the ramp and the blend are float,
+ * and cos / sin are scaled by 0.1 * log(factor) + 1 (1 when the factor is at most 1). beta_fast = 32, beta_slow = 1, no
+ * truncation, partial rotary factor 1: the reference fixes them. */
+int rope_table_yarn(unsigned head_dim, unsigned seq_len, float theta, float factor, unsigned original_max_position_embeddings,
+                    float *cos_out, float *sin_out) {
+  if (!cos_out || !sin_out || head_dim == 0 || head_dim % 2)
+    return set_error(NNTR_CUDA_ERR_INVALID, "rope_table_yarn: head_dim must be even and the outputs non-null");
+  if (!(factor > 0.f) || original_max_position_embeddings == 0)
+    return set_error(NNTR_CUDA_ERR_INVALID, "rope_table_yarn: factor and original_max_position_embeddings must be positive");
+  const int dim = static_cast<int>(head_dim * 1.0f);
+  const float base = theta, scale = factor;
+  const float attention_scaling = (scale <= 1.0f) ? 1.0f : (0.1f * 1.0f * std::log(scale) + 1.0f);
+  const float beta_fast = 32.0f, beta_slow = 1.0f;
+  auto find_correction_dim = [&](float num_rotations) {
+    return (dim * std::log(original_max_position_embeddings / (num_rotations * 2 * M_PI))) / (2 * std::log(base));
+  };
+  float low = find_correction_dim(beta_fast), high = find_correction_dim(beta_slow);
+  const size_t half = dim / 2;
+  std::vector<float> thetas(half), extrapolation, interpolation;
+  for (size_t i = 0; i < half; ++i) {
+    extrapolation.push_back(1.0 / (std::pow(theta, (2 * i) / static_cast<float>(head_dim))));
+    interpolation.push_back(1.0 / (scale * std::pow(theta, (2 * i) / static_cast<float>(head_dim))));
+  }
+  if (low == high)
+    high += 0.001f; // the reference's guard against a zero-width ramp
+  std::vector<float> keep(half);
+  for (int i = 0; i < (int)half; ++i) {
+    const float val = (i - low) / (high - low);
+    keep[i] = 1.0f - std::min(std::max(val, 0.0f), 1.0f);
+  }
+  for (size_t i = 0; i < half; ++i)
+    thetas[i] = extrapolation[i] * keep[i] + interpolation[i] * (1.0f - keep[i]);
+  for (unsigned i = 0; i < seq_len; ++i)
+    for (unsigned j = 0; j < half; ++j) {
+      const float angle = i * thetas[j];
+      float *c = cos_out + (size_t)i * head_dim, *s = sin_out + (size_t)i * head_dim;
+      c[j] = c[j + half] = std::cos(angle) * attention_scaling;
+      s[j] = s[j + half] = std::sin(angle) * attention_scaling;
+    }
+  return NNTR_CUDA_OK;
+}
+
 } // namespace nntr

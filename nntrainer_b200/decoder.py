@@ -36,6 +36,8 @@ class DecoderConfig:
     lmhead_dtype: str = "q6_K"
     tie_word_embeddings: bool = False
     sliding_window: int | None = None
+    rope_scaling_factor: float | None = None  # rope_scaling_type "yarn" with this factor (None: default rope)
+    rope_scaling_max_position_embeddings: int = 4096
 
 
 def tensor_list(c: DecoderConfig):
@@ -73,7 +75,8 @@ class Qwen3Decoder:
         self.ptr = {name: self.w.ptr[i] for i, (name, *_r) in enumerate(self.tensors)}
         self._shape = {name: (d, n, k) for name, d, n, k in self.tensors}
         self.pdl = pdl
-        cos, sin = be.rope_table(cfg.head_dim, cfg.max_seq, cfg.rope_theta)
+        cos, sin = be.rope_table(cfg.head_dim, cfg.max_seq, cfg.rope_theta, yarn_factor=cfg.rope_scaling_factor,
+                                 yarn_original_max_position_embeddings=cfg.rope_scaling_max_position_embeddings)
         tabs = (torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device))
         self.attn = [be.Attention(cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.max_seq, window=cfg.sliding_window,
                                   device=device, tables=tabs) for _ in range(cfg.n_layers)]

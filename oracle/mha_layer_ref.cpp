@@ -12,8 +12,8 @@
  * step (tests/test_glue_oracle.py).
  *
  * Input file: uint32 n_heads, n_kv_heads, head_dim, steps, max_timestep, sliding_window (0xffffffff: none),
- *   rope_theta, use_sink; then (use_sink: sink [n_heads] fp32); then per step: q [n_heads*head_dim], k [n_kv*head_dim],
- *   v [n_kv*head_dim] fp32.
+ *   rope_theta, use_sink, yarn_original_max_position_embeddings (0: default rope), float yarn_factor; then (use_sink:
+ *   sink [n_heads] fp32); then per step: q [n_heads*head_dim], k [n_kv*head_dim], v [n_kv*head_dim] fp32.
  * Output file: per step the layer's output row [n_heads*head_dim] fp32; then the key cache and the value cache
  *   ([max_timestep][n_kv*head_dim] uint16 each) as the layer left them.
  */
@@ -50,16 +50,24 @@ int main(int argc, char **argv) {
     FILE *f = fopen(argv[1], "rb");
     if (!f)
       return 2;
-    uint32_t nh, nkv, hd, steps, max_t, window, theta, use_sink;
+    uint32_t nh, nkv, hd, steps, max_t, window, theta, use_sink, yarn_max;
+    float yarn_factor;
     rd(f, &nh, 4), rd(f, &nkv, 4), rd(f, &hd, 4), rd(f, &steps, 4), rd(f, &max_t, 4), rd(f, &window, 4), rd(f, &theta, 4),
-      rd(f, &use_sink, 4);
+      rd(f, &use_sink, 4), rd(f, &yarn_max, 4), rd(f, &yarn_factor, 4);
     nntrainer::init_backend();
 
     causallm::MHACoreLayer layer;
-    layer.setProperty({"num_heads=" + std::to_string(nh), "num_heads_kv=" + std::to_string(nkv),
-                       "max_timestep=" + std::to_string(max_t), "sliding_window=" + std::to_string(window),
-                       "rope_theta=" + std::to_string(theta), "max_new_tokens=" + std::to_string(max_t),
-                       "max_position_embeddings=" + std::to_string(max_t), std::string("use_sink=") + (use_sink ? "true" : "false")});
+    std::vector<std::string> props = {"num_heads=" + std::to_string(nh), "num_heads_kv=" + std::to_string(nkv),
+                                      "max_timestep=" + std::to_string(max_t), "sliding_window=" + std::to_string(window),
+                                      "rope_theta=" + std::to_string(theta), "max_new_tokens=" + std::to_string(max_t),
+                                      "max_position_embeddings=" + std::to_string(max_t),
+                                      std::string("use_sink=") + (use_sink ? "true" : "false")};
+    if (yarn_max) {
+      props.push_back("rope_scaling_type=yarn");
+      props.push_back("rope_scaling_factor=" + std::to_string(yarn_factor));
+      props.push_back("rope_scaling_max_position_embeddings=" + std::to_string(yarn_max));
+    }
+    layer.setProperty(props);
 
     const TensorDim::TensorType fp32 = {nntrainer::Tformat::NCHW, nntrainer::Tdatatype::FP32};
     // the graph gives the layer inputs of the full sequence length; a step uses the first (to - from) rows

@@ -150,7 +150,8 @@ def moe_layer_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=0
         return np.fromfile(res, dtype=np.float32).reshape(T, H)
 
 
-def mha_layer_ref(q, k, v, n_heads, n_kv_heads, head_dim, max_timestep, rope_theta, sliding_window=None, sink=None):
+def mha_layer_ref(q, k, v, n_heads, n_kv_heads, head_dim, max_timestep, rope_theta, sliding_window=None, sink=None,
+                  yarn_factor=None, yarn_original_max=4096):
     """Drives the reference's own attention layer (oracle/_ref/mha_layer_ref: mha_core.cpp compiled unmodified) one token
     at a time: q [steps][n_heads*head_dim], k and v [steps][n_kv_heads*head_dim] are the layer's inputs per step.
     Returns (outputs [steps][n_heads*head_dim], key cache, value cache as uint16 [max_timestep][n_kv_heads][head_dim]),
@@ -164,9 +165,10 @@ def mha_layer_ref(q, k, v, n_heads, n_kv_heads, head_dim, max_timestep, rope_the
     with tempfile.TemporaryDirectory() as td:
         case, res = os.path.join(td, "case.bin"), os.path.join(td, "res.bin")
         with open(case, "wb") as f:
-            f.write(struct.pack("<8I", n_heads, n_kv_heads, head_dim, steps, max_timestep,
+            f.write(struct.pack("<9If", n_heads, n_kv_heads, head_dim, steps, max_timestep,
                                 0xffffffff if sliding_window is None else sliding_window, int(rope_theta),
-                                0 if sink is None else 1))
+                                0 if sink is None else 1, 0 if yarn_factor is None else yarn_original_max,
+                                0.0 if yarn_factor is None else yarn_factor))
             if sink is not None:
                 f.write(np.ascontiguousarray(sink, dtype=np.float32).tobytes())
             for t in range(steps):

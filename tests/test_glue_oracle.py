@@ -115,20 +115,24 @@ def test_whole_row_rms_norm_layer_on_the_references_tensor_class_is_a_few_ulps_f
     np.testing.assert_allclose(layer, helper, rtol=4e-6)
 
 
-@pytest.mark.parametrize("n_heads,n_kv,hd,steps,max_t,window,theta,with_sink", [
-    (8, 2, 128, 20, 32, None, 1000000, False),    # Qwen3-style heads
-    (32, 8, 128, 40, 64, None, 1000000, False),   # the 4B shape's head counts
-    (8, 2, 128, 24, 32, 8, 1000000, False),       # a sliding window shorter than the sequence
-    (16, 2, 64, 20, 24, 6, 150000, True),         # GPT-OSS style: 64-wide heads, window and sinks
-    (8, 8, 64, 12, 16, None, 10000, True),        # no grouping, sinks
+@pytest.mark.parametrize("n_heads,n_kv,hd,steps,max_t,window,theta,with_sink,yarn", [
+    (8, 2, 128, 20, 32, None, 1000000, False, None),    # Qwen3-style heads
+    (32, 8, 128, 40, 64, None, 1000000, False, None),   # the 4B shape's head counts
+    (8, 2, 128, 24, 32, 8, 1000000, False, None),       # a sliding window shorter than the sequence
+    (16, 2, 64, 20, 24, 6, 150000, True, None),         # GPT-OSS style: 64-wide heads, window and sinks
+    (8, 8, 64, 12, 16, None, 10000, True, None),        # no grouping, sinks
+    (16, 2, 64, 40, 64, 6, 150000, True, (32.0, 4096)), # GPT-OSS's rope scaling: yarn, factor 32 over 4096 positions
+    (8, 2, 128, 40, 64, None, 10000, False, (4.0, 16)), # yarn with the ramp inside the table: 40 steps over 16 original
+    (8, 2, 64, 16, 16, None, 10000, False, (0.5, 16)),  # a factor below one: no amplitude scaling
 ])
 def test_single_token_attention_equals_the_references_attention_layer(port, n_heads, n_kv, hd, steps, max_t, window, theta,
-                                                                       with_sink):
+                                                                       with_sink, yarn):
     """The reference's own attention layer (causallm::MHACoreLayer, mha_core.cpp compiled unmodified and driven through
     its run context one token at a time, oracle/_ref/mha_layer_ref) against the sequence of helper calls the checker's
     decoder and the GPU tests use for a decode step -- rotary embedding of q and k from the library's table, fp16 cache
     append, scores over the window, softmax (with sinks), values: every step's output and both caches bit for bit.
-    This also pins the library's rotary table (nntr_cuda_rope_table, host code) to the layer's precompute_freqs."""
+    This also pins the library's rotary tables (nntr_cuda_rope_table and nntr_cuda_rope_table_yarn, host code) to the
+    layer's precompute_freqs, for the default parameters and for rope_scaling_type "yarn"."""
     from nntrainer_b200 import backend as be
     from oracle import oracle as O
     rng = np.random.default_rng(n_heads * 1000 + steps)
@@ -136,11 +140,15 @@ def test_single_token_attention_equals_the_references_attention_layer(port, n_he
     k = rng.standard_normal((steps, n_kv * hd)).astype(np.float32)
     v = rng.standard_normal((steps, n_kv * hd)).astype(np.float32)
     sink = rng.standard_normal(n_heads).astype(np.float32) if with_sink else None
-    ref = O.mha_layer_ref(q, k, v, n_heads, n_kv, hd, max_t, theta, window, sink)
+    yf, ymax = yarn if yarn else (None, 4096)
+    ref = O.mha_layer_ref(q, k, v, n_heads, n_kv, hd, max_t, theta, window, sink, yarn_factor=yf, yarn_original_max=ymax)
     if ref is None:
         pytest.skip("oracle/_ref/mha_layer_ref not built (needs a checkout of the reference at build time)")
     out_ref, kc_ref, vc_ref = ref
-    cos, sin = be.rope_table(hd, max_t, float(theta))
+    cos, sin = be.rope_table(hd, max_t, float(theta), yarn_factor=yf, yarn_original_max_position_embeddings=ymax)
+    if yarn:  # the scaled table really is a different table
+        c0, _ = be.rope_table(hd, max_t, float(theta))
+        assert not np.array_equal(c0, cos)
     kc = np.zeros((max_t, n_kv, hd), dtype=np.uint16)
     vc = np.zeros((max_t, n_kv, hd), dtype=np.uint16)
     gqa, w = n_heads // n_kv, (2 ** 31 - 1 if window is None else window)
