@@ -190,6 +190,12 @@ def run_reference(args):
             "sample": f"{steps} passes over a ring of {len(ring)} matrices ({steps * len(ring)} GEMV calls, M=1 N=K=4096) "
                       f"in {dt:.1f} s; {os.path.basename(lib.path)}; host has {os.cpu_count()} logical cores, the reference's "
                       f"GEMV driver uses 4 OpenMP threads (ggml_interface_omp.cpp:406)"}
+    model = None
+    if not args.no_model:
+        try:
+            model = reference_model_decode()
+        except Exception as exc:  # noqa: BLE001  (a side figure: recorded, never fatal for the arm)
+            model = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     out = {"impl": "reference", "metric": "Q4_K GEMV HBM GB/s", "value": round(value, 3), "unit": "GB/s",
            "n_gpus": args.gpus, "steps": steps, "warmup": max(args.warmup, 1), "ms_per_step": round(dt / steps * 1e3, 3),
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u4xs8->s32, f32 scales",
@@ -199,8 +205,38 @@ def run_reference(args):
                       "note": "the same GEMV calls on the same ring of matrices; the CPU arm feeds every call the same "
                               "activation (chaining outputs changes nothing for its timing)"},
            "cpu_baseline": desc,
-           "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+           "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "model_decode_reference": model}
     print(json.dumps(out))
+
+
+def reference_model_decode(new_tokens=24):
+    """Whole-model greedy decoding on the host cores by the reference's OWN layer classes (the decoder of
+    oracle/decoder_layers_ref.cpp, built where a checkout of the reference was present): the Qwen3-4B shape of our arm's
+    model_decode leg -- 36 layers, hidden 2560, 32 / 8 heads of 128, SwiGLU 9728, vocabulary 151936, Q4_K projections --
+    with tied Q6_K embeddings, because the reference's Q6_K tensor class wants a width that is a multiple of 256 and
+    151936 is not, so its own model ties the lm_head to the embedding tensor [vocab][hidden]. Synthetic weights, a short
+    context (the CPU time per token is the 2.4 GB of weights, not the cache)."""
+    import tempfile
+    from nntrainer_b200.decoder import DecoderConfig
+    from oracle import oracle as O
+    from oracle.cpu_decoder import synthetic_weights, write_bin
+    exe = os.path.join(os.path.dirname(os.path.abspath(O.__file__)), "_ref", "decoder_layers_ref")
+    if not os.path.exists(exe):
+        return {"unavailable": "oracle/_ref/decoder_layers_ref was not built (needs a checkout of the reference at build time)"}
+    cfg = DecoderConfig(n_layers=36, hidden=2560, n_heads=32, n_kv_heads=8, head_dim=128, inter=9728, vocab=151936,
+                        max_seq=new_tokens + 8, tie_word_embeddings=True)
+    w = synthetic_weights(cfg, seed=5)
+    wbytes = sum(int(a.nbytes) for a in w.values() if a.dtype == np.uint8)
+    with tempfile.TemporaryDirectory() as td:
+        path = os.path.join(td, "qwen3_4b_shape_tied.bin")
+        write_bin(path, cfg, w)
+        del w
+        tokens, _, ms = O.decoder_layers_ref(cfg, path, [11, 7, 5], new_tokens, timing=True)
+    return {"shape": "Qwen3-4B decode, tied Q6_K embeddings, every layer the reference's own class", "tokens": new_tokens,
+            "ms_per_token": round(ms, 3), "tok/s": round(1e3 / ms, 2), "weight_bytes_per_token": wbytes,
+            "GB/s": round(wbytes / (ms * 1e-3) / 1e9, 2), "host_logical_cores": os.cpu_count(),
+            "distinct_tokens": len(set(tokens))}
 
 
 # --------------------------------------------------------------------------

@@ -29,6 +29,7 @@
  * Result file: uint32 tokens [n_new], then the logits [vocab] fp32 behind the last generated token's successor.
  */
 #include <algorithm>
+#include <chrono>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -198,10 +199,12 @@ int main(int argc, char **argv) {
     for (unsigned t : prompt)
       next = step(t, pos++);
     std::vector<uint32_t> out;
+    const auto t0 = std::chrono::steady_clock::now();
     for (unsigned i = 0; i < n_new; ++i) {
       out.push_back(next);
       next = step(next, pos++);
     }
+    const double gen_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     FILE *o = fopen(argv[2], "wb");
     if (!o)
       return 2;
@@ -209,9 +212,9 @@ int main(int argc, char **argv) {
     fwrite(logits->getVariableRef().getData<float>(), 4, V, o);
     fclose(o);
 #ifdef ENABLE_CUDA
-    printf("ok %zu layers cuda\n", nodes.size());
+    printf("ok %zu layers cuda ms_per_token=%.4f\n", nodes.size(), n_new ? gen_ms / n_new : 0.0);
 #else
-    printf("ok %zu layers cpu\n", nodes.size());
+    printf("ok %zu layers cpu ms_per_token=%.4f\n", nodes.size(), n_new ? gen_ms / n_new : 0.0);
 #endif
     return 0;
   } catch (const std::exception &e) {

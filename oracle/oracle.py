@@ -87,12 +87,13 @@ def moe_tensor_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=
             raw[2 * n:].view(np.float32).reshape(T, H))
 
 
-def decoder_layers_ref(cfg, bin_path, prompt, n_new, cuda=False):
+def decoder_layers_ref(cfg, bin_path, prompt, n_new, cuda=False, timing=False):
     """Greedy decoding with a decoder assembled from the reference's own layer classes (oracle/_ref/decoder_layers_ref),
     weights read from ``bin_path`` by the reference's reader. ``cfg`` has the fields of nntrainer_b200.decoder's
     DecoderConfig. Returns (tokens [n_new], logits [vocab] after the last step), or None when not built.
     ``cuda``: the same program built with the ENABLE_CUDA hook in FloatTensor::dotQnK (decoder_layers_cuda): the layer
-    classes are the reference's, every projection runs in libnntr_cuda.so."""
+    classes are the reference's, every projection runs in libnntr_cuda.so. ``timing``: also return the milliseconds per
+    generated token the program measured around its generation loop."""
     import tempfile
     exe = os.path.join(HERE, "_ref", "decoder_layers_cuda" if cuda else "decoder_layers_ref")
     if not os.path.exists(exe):
@@ -107,7 +108,11 @@ def decoder_layers_ref(cfg, bin_path, prompt, n_new, cuda=False):
         if r.returncode != 0:
             raise RuntimeError(f"decoder_layers_ref failed ({r.returncode}): {r.stderr.strip()[:500]}")
         raw = np.fromfile(res, dtype=np.uint8)
-    return [int(t) for t in raw[:4 * n_new].view(np.uint32)], raw[4 * n_new:].view(np.float32).copy()
+    tokens, logits = [int(t) for t in raw[:4 * n_new].view(np.uint32)], raw[4 * n_new:].view(np.float32).copy()
+    if timing:  # wall time of the generation loop as the program measured it, per token
+        ms = float(r.stdout.split("ms_per_token=")[1].split()[0])
+        return tokens, logits, ms
+    return tokens, logits
 
 
 def moe_layer_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=0, router_bias=None, gate_b=None,
