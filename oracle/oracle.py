@@ -104,7 +104,7 @@ def decoder_layers_ref(cfg, bin_path, prompt, n_new, cuda=False, timing=False):
             cfg.n_layers, cfg.hidden, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.inter, cfg.vocab, cfg.max_seq,
             int(cfg.rope_theta), "%.6f" % cfg.norm_eps, cfg.sliding_window or 0, 1 if cfg.tie_word_embeddings else 0,
             n_new)] + [str(t) for t in prompt]
-        r = subprocess.run(args, capture_output=True, text=True, timeout=3600)
+        r = subprocess.run(args, capture_output=True, text=True, timeout=300 if cuda else 3600)
         if r.returncode != 0:
             raise RuntimeError(f"decoder_layers_ref failed ({r.returncode}): {r.stderr.strip()[:500]}")
         raw = np.fromfile(res, dtype=np.uint8)
