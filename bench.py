@@ -196,6 +196,12 @@ def run_reference(args):
             model = reference_model_decode()
         except Exception as exc:  # noqa: BLE001  (a side figure: recorded, never fatal for the arm)
             model = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    moe = None
+    if not args.no_moe:
+        try:
+            moe = reference_moe_layer_decode()
+        except Exception as exc:  # noqa: BLE001
+            moe = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     out = {"impl": "reference", "metric": "Q4_K GEMV HBM GB/s", "value": round(value, 3), "unit": "GB/s",
            "n_gpus": args.gpus, "steps": steps, "warmup": max(args.warmup, 1), "ms_per_step": round(dt / steps * 1e3, 3),
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u4xs8->s32, f32 scales",
@@ -206,8 +212,30 @@ def run_reference(args):
                               "activation (chaining outputs changes nothing for its timing)"},
            "cpu_baseline": desc,
            "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-           "model_decode_reference": model}
+           "model_decode_reference": model, "moe_decode_reference": moe}
     print(json.dumps(out))
+
+
+def reference_moe_layer_decode(reps=20):
+    """One decode token through the reference's OWN mixture-of-experts layer class (causallm::MoELayer, run by
+    oracle/moe_layer_ref.cpp) with the Qwen3-30B-A3B layer shape of our arm's moe_decode_step: hidden 2048, 128 experts of
+    768, top-8, Q4_K experts (16 distinct expert weight sets cycled over the 128 to keep the case file small; the eight
+    selected experts are what a call touches). Wall time per call on the host cores."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(30)
+    H, I, E, k, distinct = 2048, 768, 128, 8, 16
+    x = rng.standard_normal((1, H)).astype(np.float32)
+    router = (rng.standard_normal((H, E)) * 0.02).astype(np.float32)
+    pool = [(O.random_q4_Kx8(rng, I, H), O.random_q4_Kx8(rng, I, H), O.random_q4_Kx8(rng, H, I)) for _ in range(distinct)]
+    gate, up, down = ([pool[e % distinct][j] for e in range(E)] for j in range(3))
+    r = O.moe_layer_ref(x, router, gate, up, down, k, timed_reps=reps)
+    if r is None:
+        return {"unavailable": "oracle/_ref/moe_layer_ref was not built (needs a checkout of the reference at build time)"}
+    out, ms = r
+    touched = k * 3 * I * H * 144 // 256 + H * E * 4
+    return {"shape": "Qwen3-30B-A3B MoE layer, one token, the reference's own layer class", "us_per_layer": round(ms * 1e3, 1),
+            "ms_per_token_48_layers": round(ms * 48, 3), "bytes_touched_per_layer": touched,
+            "GB/s": round(touched / (ms * 1e-3) / 1e9, 2), "finite": bool(np.isfinite(out).all())}
 
 
 def reference_model_decode(new_tokens=24):

@@ -16,8 +16,10 @@
  *   down bias [H]); then x [T][H].
  * Output file: the layer's output [T][H] fp32.
  */
+#include <chrono>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <memory>
 #include <stdexcept>
 #include <string>
@@ -40,8 +42,8 @@ static void rd(FILE *f, void *p, size_t bytes) {
 }
 
 int main(int argc, char **argv) {
-  if (argc != 3) {
-    fprintf(stderr, "usage: %s <case file> <result file>\n", argv[0]);
+  if (argc != 3 && argc != 4) {
+    fprintf(stderr, "usage: %s <case file> <result file> [timed repetitions]\n", argv[0]);
     return 2;
   }
   try {
@@ -94,13 +96,22 @@ int main(int argc, char **argv) {
 
     nntrainer::RunLayerContext run("moe", false, 0.0f, false, 1.0f, nullptr, false, weight_ptrs, ins, outs, tensors);
     layer->incremental_forwarding(run, 0, T, false);
+    // optional timing (third argument: repetitions): the same call again, wall time per call
+    double ms = 0.0;
+    if (argc > 3 && atoi(argv[3]) > 0) {
+      const int reps = atoi(argv[3]);
+      const auto t0 = std::chrono::steady_clock::now();
+      for (int r = 0; r < reps; ++r)
+        layer->incremental_forwarding(run, 0, T, false);
+      ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() / reps;
+    }
 
     FILE *o = fopen(argv[2], "wb");
     if (!o)
       return 2;
     fwrite(outs[0]->getVariableRef().getData<float>(), 4, (size_t)T * H, o);
     fclose(o);
-    printf("ok %zu weights\n", weight_ptrs.size());
+    printf("ok %zu weights ms_per_call=%.4f\n", weight_ptrs.size(), ms);
     return 0;
   } catch (const std::exception &e) {
     fprintf(stderr, "exception: %s\n", e.what());

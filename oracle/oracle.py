@@ -116,10 +116,11 @@ def decoder_layers_ref(cfg, bin_path, prompt, n_new, cuda=False, timing=False):
 
 
 def moe_layer_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=0, router_bias=None, gate_b=None,
-                  up_b=None, down_b=None):
+                  up_b=None, down_b=None, timed_reps=0):
     """Runs the reference's own MoE layer (oracle/_ref/moe_layer_ref: qwen_moe_layer.cpp / gpt_oss_moe_layer.cpp compiled
     unmodified, driven through a run context) on the tokens x [T][H]; returns the layer's output [T][H], or None when the
-    program was not built (no checkout at build time). The GPT-OSS layer's slope is its own constant, 1.702."""
+    program was not built (no checkout at build time). The GPT-OSS layer's slope is its own constant, 1.702.
+    ``timed_reps`` > 0: also return the milliseconds per call over that many repetitions."""
     import struct
     import tempfile
     exe = os.path.join(HERE, "_ref", "moe_layer_ref")
@@ -149,10 +150,14 @@ def moe_layer_ref(x, router_w, gate_w, up_w, down_w, top_k, qtype="q4_K", kind=0
                 if kind == 1:
                     f.write(f32(down_b[e]))
             f.write(x.tobytes())
-        r = subprocess.run([exe, case, res], capture_output=True, text=True, timeout=600)
+        r = subprocess.run([exe, case, res] + ([str(timed_reps)] if timed_reps else []), capture_output=True, text=True,
+                           timeout=600)
         if r.returncode != 0:
             raise RuntimeError(f"moe_layer_ref failed ({r.returncode}): {r.stderr.strip()[:500]}")
-        return np.fromfile(res, dtype=np.float32).reshape(T, H)
+        out = np.fromfile(res, dtype=np.float32).reshape(T, H)
+        if timed_reps:  # wall time of one incremental_forwarding call as the program measured it
+            return out, float(r.stdout.split("ms_per_call=")[1].split()[0])
+        return out
 
 
 def mha_layer_ref(q, k, v, n_heads, n_kv_heads, head_dim, max_timestep, rope_theta, sliding_window=None, sink=None,
