@@ -167,7 +167,7 @@ def _small_model(td, tie=False):
     cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=8, n_kv_heads=2, head_dim=64, inter=768, vocab=1024, max_seq=48,
                         tie_word_embeddings=tie)
     path = os.path.join(td, "model.bin")
-    write_bin(path, cfg, synthetic_weights(cfg, 3))
+    write_bin(path, cfg, synthetic_weights(cfg, 8))  # a seed whose greedy streams visit about twenty different tokens
     return cfg, path
 
 
@@ -204,7 +204,7 @@ def test_layer_class_decoder_with_the_hook_generates_the_cpu_builds_tokens(built
         cpu_tokens, cpu_logits = O.decoder_layers_ref(cfg, path, [5, 900, 17], 32)
         gpu_tokens, gpu_logits = O.decoder_layers_ref(cfg, path, [5, 900, 17], 32, cuda=True)
     assert gpu_tokens == cpu_tokens
-    assert len(set(cpu_tokens)) > 4
+    assert len(set(cpu_tokens)) > 10, "degenerate stream: the test would not notice a wrong projection"
     assert np.array_equal(gpu_logits.view(np.uint32), cpu_logits.view(np.uint32))
 
 
