@@ -55,6 +55,35 @@ def test_context_plugin_loads_like_an_external_context(built):
     assert "ml_train_context_pluggable" in defined
 
 
+def test_dotqnk_hook_tool_on_synthetic_text():
+    """The tool finds the function by name and its body by brace matching, wraps only calls inside it, and refuses text
+    it does not understand (no such function, no call inside it, no cpu_backend include, already hooked)."""
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "plugin"))
+    try:
+        import hook_dotqnk as H
+    finally:
+        sys.path.pop(0)
+    text = ("#include <cpu_backend.h>\n#include <other.h>\nnamespace n {\n"
+            "void before() {\n  gemm_q4_K(1, 2, 3, a, 3, b, 2, c, 2);\n}\n"
+            "Tensor &FloatTensor::dotQnK(Tensor const &input, Tensor &output) const {\n  switch (t) {\n  case A:\n"
+            "    gemm_q4_K(M, N, K, data, K, (void *)mdata, N, rdata, N);\n    break;\n  default: {\n"
+            "    gemm_q6_K(M, N, K, data, K, (void *)mdata, N, rdata, N);\n  }\n  }\n  return output;\n}\n"
+            "void after() {\n  gemm_q4_0(1, 2, 3, a, 3, b, 2, c, 2);\n}\n}\n")
+    hooked, n = H.hook(text)
+    assert n == 2
+    assert hooked.count("gemm_q4_K_cuda(M, N, K, data, K, (void *)mdata, N, rdata, N);") == 1
+    assert hooked.count("gemm_q6_K_cuda(") == 1 and "gemm_q4_0_cuda(" not in hooked
+    assert hooked.index("#include <cuda_backend.h>") < hooked.index("#include <other.h>")
+    assert "  gemm_q4_K(1, 2, 3, a, 3, b, 2, c, 2);\n}" in hooked  # the call outside the function is untouched
+    for bad in (text.replace("FloatTensor::dotQnK(", "FloatTensor::dotOther("),      # no such function
+                text.replace("    gemm_q4_K(M", "    other(M").replace("    gemm_q6_K(M", "    other(M"),  # nothing to wrap
+                text.replace("#include <cpu_backend.h>\n", ""),                      # nowhere to put the include
+                hooked):                                                              # already hooked
+        with pytest.raises(ValueError):
+            H.hook(bad)
+
+
 def test_dotqnk_hook_compiles_in_the_reference_and_links_to_the_backend(built):
     """plugin/hook_dotqnk.py writes the compile-time branch into a temporary copy of the reference's float_tensor.cpp;
     the copy must compile against the reference's headers with and without -DENABLE_CUDA, the CUDA build must call the
