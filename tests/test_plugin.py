@@ -230,8 +230,13 @@ def test_layer_class_decoder_with_the_hook_generates_the_cpu_builds_tokens(built
         pytest.skip("drivers not built (need a checkout of the reference at build time)")
     with tempfile.TemporaryDirectory() as td:
         cfg, path = _small_model(td, tie)
-        cpu_tokens, cpu_logits = O.decoder_layers_ref(cfg, path, [5, 900, 17], 32)
-        gpu_tokens, gpu_logits = O.decoder_layers_ref(cfg, path, [5, 900, 17], 32, cuda=True)
+        try:
+            cpu_tokens, cpu_logits = O.decoder_layers_ref(cfg, path, [5, 900, 17], 32)
+            gpu_tokens, gpu_logits = O.decoder_layers_ref(cfg, path, [5, 900, 17], 32, cuda=True)
+        except RuntimeError as exc:
+            if "(127)" in str(exc) or "error while loading shared libraries" in str(exc):
+                pytest.skip("the prebuilt drivers do not start on this machine: " + str(exc)[:200])
+            raise
     assert gpu_tokens == cpu_tokens
     assert len(set(cpu_tokens)) > 10, "degenerate stream: the test would not notice a wrong projection"
     assert np.array_equal(gpu_logits.view(np.uint32), cpu_logits.view(np.uint32))
@@ -250,6 +255,8 @@ def test_hooked_tensor_dot_runs_on_the_gpu_and_equals_the_checker(built, q, M, N
     if not os.path.exists(exe):
         pytest.skip("driver not built (needs a checkout of the reference at build time)")
     rc, C, want, err = _tensor_dot(exe, q, M, N, K)
+    if rc == 127 or "error while loading shared libraries" in err:
+        pytest.skip("the prebuilt driver does not start on this machine: " + err.strip()[:200])
     assert rc == 0, err
     assert np.array_equal(C.view(np.uint32), want.view(np.uint32))
 
